@@ -1,0 +1,61 @@
+"""Replay through bin/trace_run against the plain implementation: the same
+requests whole, with the last 32 tokens decoded one by one, in portions of
+changing size, and mixed with other requests on so few pages that they are
+used again, in float32 and in bfloat16."""
+import pytest
+
+import replay_util as ru
+from tiny import TINY, make_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+
+SHARPEN = {r"\.(q|k)_proj\.weight": 8.0, r"embed_tokens|lm_head": 5.0}
+LENGTHS = {"a": [1, 7, 33, 100, 128, 65], "b": [5, 19, 64, 100, 200, 131], "c": [3, 40, 97, 150, 260, 64]}
+
+
+@pytest.fixture(scope="module", params=sorted(TINY))
+def model(request, tmp_path_factory):
+    folder, config, page = make_folder(tmp_path_factory, request.param, scale=SHARPEN)
+    requests = {f"r{i}": random_ids(n, config.vocab_size, 100 + i)
+                for i, n in enumerate(LENGTHS[request.param])}
+    return folder, config, page, requests, ru.reference_logits(folder, requests)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole(model, dtype, tmp_path):
+    folder, config, page, requests, want = model
+    steps = ru.steps_whole(requests)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), budget, page))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    ru.compare(got, want, dtype, "whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_tokens_one_by_one(model, dtype, tmp_path):
+    folder, config, page, requests, want = model
+    steps = ru.steps_decode_tail(requests, 32)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), budget, page))
+    ru.compare(got, want, dtype, "decode tail")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_of_changing_size(model, dtype, tmp_path):
+    folder, config, page, requests, want = model
+    steps = ru.steps_portions(requests)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), budget, page))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    ru.compare(got, want, dtype, "portions")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_with_page_reuse(model, dtype, tmp_path):
+    folder, config, page, requests, want = model
+    steps, peak = ru.steps_mixed(requests, max_live=4)
+    total = sum(ru.rounded64(len(v)) for v in requests.values())
+    assert peak < total, "the trace must force pages to be used again"
+    got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), peak, page))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    ru.compare(got, want, dtype, "mixed")

@@ -1,0 +1,78 @@
+// Shared helpers of the sm_100a kernels: the export macro, status codes,
+// element conversions and block reductions.  Launchers are `extern "C"`, take
+// raw device pointers and a stream, allocate nothing and return a status:
+// 0, a cudaError_t (> 0), or one of the negative codes below.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TOKB200_API extern "C" __attribute__((visibility("default")))
+
+enum : int {
+  TOKB200_OK = 0,
+  TOKB200_BAD_SIZE = -1,      // a size this kernel refuses (message in Python)
+  TOKB200_BAD_DTYPE = -2,
+  TOKB200_BAD_ALIGNMENT = -3,
+  TOKB200_TIMEOUT = -4,       // a bounded device wait gave up
+};
+
+// dtype tags shared with Python
+enum : int { TOKB200_F32 = 0, TOKB200_BF16 = 1 };
+
+static inline int tokb200_launch_status() {
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide reductions for blocks of up to 1024 threads (a multiple of 32).
+// `scratch` holds 33 floats.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : 0.f;
+    w = warp_sum(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : -INFINITY;
+    w = warp_max(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}

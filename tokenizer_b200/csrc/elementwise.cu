@@ -1,0 +1,243 @@
+// Memory-bound parts of the step: embedding gather, RMSNorm with the residual
+// add folded in, rotary encoding fused with the bias add and the write of K and
+// V into cache pages, the gated activation, row gathers.  The residual stream is
+// 32-bit in both precisions; `T` is the type of the matrix-product operands
+// (float for the 32-bit path, bfloat16 for serving).  Statistics, angles and
+// sums are 32-bit throughout.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------
+// embedding gather: x[t, :] = table[ids[t], :], widened to 32-bit
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ x, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read outside
+  const T* row = table + (size_t)id * hidden;
+  float* out = x + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype, float* x,
+                              int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (n_tokens <= 0) return TOKB200_OK;
+  if (table_dtype == TOKB200_F32)
+    embed_kernel<float><<<n_tokens, 256, 0, stream>>>(ids, (const float*)table, x, hidden, vocab);
+  else if (table_dtype == TOKB200_BF16)
+    embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x,
+                                                             hidden, vocab);
+  else
+    return TOKB200_BAD_DTYPE;
+  return tokb200_launch_status();
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm, optionally after x += delta (the pending residual):
+//   x <- x + delta (stored back, 32-bit);  y = x / sqrt(mean(x^2) + eps) * gain
+// One block per row.  `rows` optionally names the rows to read (a gather of the
+// wanted rows before the final norm); y is then dense [n_rows, hidden].
+// ----------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                const float* __restrict__ gain, TO* __restrict__ y,
+                                const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * hidden;
+  const TD* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) {
+      v += to_float(dr[i]);
+      xr[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* yr = y + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    yr[i] = from_float<TO>(xr[i] * inv * gain[i]);
+}
+
+TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, const float* gain,
+                                 void* y, int y_dtype, const int* rows, int n_rows, int hidden,
+                                 float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (hidden <= 0) return TOKB200_BAD_SIZE;
+  const int threads = hidden >= 1024 ? 256 : 128;
+#define LAUNCH(TD, TO) \
+  rms_norm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(x, (const TD*)delta, gain, (TO*)y, rows, hidden, eps)
+  if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_F32) LAUNCH(float, float);
+  else if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+  else if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return TOKB200_BAD_DTYPE;
+#undef LAUNCH
+  return tokb200_launch_status();
+}
+
+// x += delta, elementwise (a pending residual that no norm follows)
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) x[i] += to_float(delta[i]);
+}
+
+TOKB200_API int tokb200_residual_add(float* x, const void* delta, int delta_dtype, long long n,
+                                     cudaStream_t stream) {
+  if (n <= 0) return TOKB200_OK;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  if (delta_dtype == TOKB200_F32)
+    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+  else if (delta_dtype == TOKB200_BF16)
+    residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+  else
+    return TOKB200_BAD_DTYPE;
+  return tokb200_launch_status();
+}
+
+// ----------------------------------------------------------------------------
+// rotary tables: cos/sin of float(position) * inv_freq[i], 32-bit
+// ----------------------------------------------------------------------------
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ cos_t,
+                                  float* __restrict__ sin_t, int n_positions, int half) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_positions * half) return;
+  const int p = (int)(i / half), f = (int)(i % half);
+  const float angle = (float)p * inv_freq[f];
+  cos_t[i] = cosf(angle);
+  sin_t[i] = sinf(angle);
+}
+
+TOKB200_API int tokb200_rope_table(const float* inv_freq, float* cos_t, float* sin_t,
+                                   int n_positions, int half, cudaStream_t stream) {
+  const size_t n = (size_t)n_positions * half;
+  if (n == 0) return TOKB200_OK;
+  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(inv_freq, cos_t, sin_t,
+                                                                    n_positions, half);
+  return tokb200_launch_status();
+}
+
+// ----------------------------------------------------------------------------
+// bias + rotary encoding + cache write.
+// qkv is [T, (nh + 2 nkv) d]: query heads, then key heads, then value heads.
+// Per token: q and k get their bias and are rotated by the half-split rule over
+// the first `rotary` lanes of each head (pairs (i, i + rotary/2)); v gets its
+// bias.  q goes to q_out [T, nh d]; k and v go to the cache at slot[t]
+// (page * page_size + offset), pool layout [slots, nkv, d].  A negative slot, or
+// no pool, skips the write (a layer that reads another layer's cache).
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_store_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+                                  const int* __restrict__ pos, const int* __restrict__ slot,
+                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                  T* __restrict__ q_out, T* __restrict__ k_pool,
+                                  T* __restrict__ v_pool, int nh, int nkv, int d, int rotary,
+                                  int table_half) {
+  const int t = blockIdx.x;
+  const int p = pos[t];
+  const int s = slot ? slot[t] : -1;
+  const int width = (nh + 2 * nkv) * d;
+  const T* row = qkv + (size_t)t * width;
+  const int half_d = d / 2;            // work items per head: pairs (j, j + d/2)
+  const int rot_half = rotary / 2;
+  const int items = (nh + 2 * nkv) * half_d;
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    const int head = it / half_d, j = it % half_d;
+    // the two lanes this item owns.  Inside the rotary width lanes pair up as
+    // (j, j + rot_half); outside it they are copied.  Items cover lanes j and
+    // j + half_d, so remap: item j < rot_half rotates (j, j + rot_half); the
+    // remaining lanes are passed through in pairs.
+    int a, b;
+    bool rotate;
+    if (j < rot_half) { a = j; b = j + rot_half; rotate = true; }
+    else { a = rotary + (j - rot_half) * 2; b = a + 1; rotate = false; }
+    float va = to_float(row[head * d + a]);
+    float vb = to_float(row[head * d + b]);
+    if (bias) { va += bias[head * d + a]; vb += bias[head * d + b]; }
+    T* dst;
+    if (head < nh) {
+      dst = q_out + (size_t)t * nh * d + head * d;
+    } else if (head < nh + nkv) {
+      if (s < 0 || !k_pool) continue;
+      dst = k_pool + ((size_t)s * nkv + (head - nh)) * d;
+    } else {
+      if (s < 0 || !v_pool) continue;
+      dst = v_pool + ((size_t)s * nkv + (head - nh - nkv)) * d;
+      rotate = false;
+    }
+    if (rotate) {
+      const float c = cos_t[(size_t)p * table_half + j], sn = sin_t[(size_t)p * table_half + j];
+      const float ra = va * c - vb * sn;
+      const float rb = vb * c + va * sn;
+      va = ra; vb = rb;
+    }
+    dst[a] = from_float<T>(va);
+    dst[b] = from_float<T>(vb);
+  }
+}
+
+TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int* pos,
+                                   const int* slot, const float* cos_t, const float* sin_t,
+                                   void* q_out, void* k_pool, void* v_pool, int dtype,
+                                   int n_tokens, int nh, int nkv, int d, int rotary,
+                                   cudaStream_t stream) {
+  if (n_tokens <= 0) return TOKB200_OK;
+  if (d <= 0 || (d & 1) || rotary < 0 || rotary > d || (rotary & 1) || ((d - rotary) & 1))
+    return TOKB200_BAD_SIZE;
+  const int items = (nh + 2 * nkv) * (d / 2);
+  int threads = items < 256 ? ((items + 31) / 32) * 32 : 256;
+  if (dtype == TOKB200_F32)
+    rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (const float*)qkv, bias, pos, slot, cos_t, sin_t, (float*)q_out, (float*)k_pool,
+        (float*)v_pool, nh, nkv, d, rotary, rotary / 2);
+  else if (dtype == TOKB200_BF16)
+    rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, bias, pos, slot, cos_t, sin_t, (__nv_bfloat16*)q_out,
+        (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d, rotary, rotary / 2);
+  else
+    return TOKB200_BAD_DTYPE;
+  return tokb200_launch_status();
+}
+
+// ----------------------------------------------------------------------------
+// gated activation: out[t, i] = silu(gu[t, i]) * gu[t, inner + i]
+// silu(z) = z * sigmoid(z) = z / (1 + exp(-z)), in 32-bit
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner) {
+  const int t = blockIdx.y;
+  const T* row = gu + (size_t)t * 2 * inner;
+  T* orow = out + (size_t)t * inner;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inner; i += gridDim.x * blockDim.x) {
+    const float g = to_float(row[i]), u = to_float(row[inner + i]);
+    orow[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_tokens, int inner,
+                                  cudaStream_t stream) {
+  if (n_tokens <= 0) return TOKB200_OK;
+  if (inner <= 0 || n_tokens > 65535 * 1024) return TOKB200_BAD_SIZE;
+  // grid.y is limited to 65535 rows; tile rows over several launches beyond it
+  for (int row0 = 0; row0 < n_tokens; row0 += 65535) {
+    const int rows = n_tokens - row0 < 65535 ? n_tokens - row0 : 65535;
+    dim3 grid((inner + 255) / 256 < 64 ? (inner + 255) / 256 : 64, rows);
+    if (dtype == TOKB200_F32)
+      silu_gate_kernel<float><<<grid, 256, 0, stream>>>(
+          (const float*)gu + (size_t)row0 * 2 * inner, (float*)out + (size_t)row0 * inner, inner);
+    else if (dtype == TOKB200_BF16)
+      silu_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+          (const __nv_bfloat16*)gu + (size_t)row0 * 2 * inner,
+          (__nv_bfloat16*)out + (size_t)row0 * inner, inner);
+    else
+      return TOKB200_BAD_DTYPE;
+  }
+  return tokb200_launch_status();
+}

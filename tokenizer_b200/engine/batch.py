@@ -1,0 +1,185 @@
+"""Turning a step's entries into the device-side description of the batch.
+
+All integer metadata of a step (ids, positions, the request of each row, cache
+slots, block tables, wanted rows) is packed into ONE int32 buffer on the host
+and copied to the device with one transfer; the parts receive views into it.
+The layout is a function of the capacities alone, so a step replayed from a
+captured graph finds every array at the same address.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import RequestCache
+from ..parts.base import GroupView, StepContext
+
+
+@dataclass
+class StepEntry:
+    """A request's share of one step: its next tokens and the places among
+    them (0-based) whose logits are wanted."""
+
+    cache: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _round4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+@dataclass
+class BatchLayout:
+    """Offsets (in int32 elements) of every array in the packed buffer."""
+
+    T: int
+    R: int
+    W: int
+    table_widths: List[int]
+    ids: int = 0
+    pos: int = 0
+    row_req: int = 0
+    q_start: int = 0
+    kv_len: int = 0
+    state_slot: int = 0
+    want: int = 0
+    slots: Optional[List[int]] = None
+    tables: Optional[List[int]] = None
+    total: int = 0
+
+    @classmethod
+    def compute(cls, T: int, R: int, W: int, table_widths: List[int]) -> "BatchLayout":
+        lay = cls(T, R, W, list(table_widths))
+        at = 0
+
+        def take(n):
+            nonlocal at
+            start = at
+            at += _round4(max(n, 1))
+            return start
+
+        lay.ids, lay.pos, lay.row_req = take(T), take(T), take(T)
+        lay.q_start, lay.kv_len, lay.state_slot = take(R + 1), take(R), take(R)
+        lay.want = take(W)
+        lay.slots = [take(T) for _ in table_widths]
+        lay.tables = [take(R * w) for w in table_widths]
+        lay.total = at
+        return lay
+
+
+class BatchBuilder:
+    def __init__(self, plan, vocab_size: int, max_positions: int, device):
+        self.plan = plan
+        self.vocab_size = vocab_size
+        self.max_positions = max_positions
+        self.device = device
+        self._host: Optional[torch.Tensor] = None
+        self._dev: Optional[torch.Tensor] = None
+        self._copied: Optional[torch.cuda.Event] = None
+
+    def _buffers(self, total: int):
+        if self._host is None or self._host.numel() < total:
+            capacity = max(total * 2, 4096)
+            pin = self.device.type == "cuda"
+            self._host = torch.empty(capacity, dtype=torch.int32, pin_memory=pin)
+            self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        return self._host, self._dev
+
+    def validate(self, entries: List[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.cache.request_id!r} brings no tokens to this step")
+            if e.cache.closed:
+                raise ValueError(f"request {e.cache.request_id!r} is closed")
+            if id(e.cache) in seen:
+                raise ValueError(f"request {e.cache.request_id!r} appears twice in one step")
+            seen.add(id(e.cache))
+            if e.cache.length + n > self.max_positions:
+                raise ValueError(
+                    f"positions {e.cache.length}..{e.cache.length + n} exceed "
+                    f"max_position_embeddings {self.max_positions}")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"wanted place {w} is not among the {n} tokens brought")
+            if self.plan.pages_missing(e.cache, n) != [0] * len(self.plan.groups):
+                raise ValueError(
+                    f"request {e.cache.request_id!r} has no pages reserved for {n} more tokens")
+
+    def build(self, entries: List[StepEntry], pad_requests: int = 0, pad_tokens: int = 0,
+              pad_want: int = 0, table_widths: Optional[List[int]] = None):
+        """Pack the step.  The `pad_*` capacities (graph replay) extend the
+        batch with idle rows: request index -1, which every kernel skips."""
+        plan = self.plan
+        page = plan.page_size
+        T = sum(len(e.tokens) for e in entries)
+        R = len(entries)
+        W = sum(len(e.want) for e in entries)
+        widths = []
+        for g in range(len(plan.groups)):
+            need = max([len(e.cache.tables[g]) for e in entries] + [1])
+            widths.append(need if table_widths is None else table_widths[g])
+            if widths[-1] < need:
+                raise ValueError("the captured block-table width is too small for this step")
+        Tc, Rc, Wc = max(T, pad_tokens), max(R, pad_requests), max(W, pad_want)
+        lay = BatchLayout.compute(Tc, Rc, Wc, widths)
+        if self._copied is not None:
+            self._copied.synchronize()  # the last step's copy still reads the host buffer
+        host, dev = self._buffers(lay.total)
+        buf = host.numpy()
+        buf[:lay.total] = 0
+        buf[lay.row_req:lay.row_req + Tc] = -1
+        for g in range(len(widths)):
+            buf[lay.slots[g]:lay.slots[g] + Tc] = -1
+            buf[lay.tables[g]:lay.tables[g] + Rc * widths[g]] = -1
+        q_lens, kv_lens, state_slots = [], [], []
+        row = 0
+        want_at = 0
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            start = e.cache.length
+            buf[lay.ids + row:lay.ids + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            positions = np.arange(start, start + n, dtype=np.int32)
+            buf[lay.pos + row:lay.pos + row + n] = positions
+            buf[lay.row_req + row:lay.row_req + row + n] = r
+            buf[lay.q_start + r] = row
+            buf[lay.kv_len + r] = start + n
+            buf[lay.state_slot + r] = e.cache.state_slot
+            for w in e.want:
+                buf[lay.want + want_at] = row + int(w)
+                want_at += 1
+            for g in range(len(widths)):
+                table = np.asarray(e.cache.tables[g], dtype=np.int32)
+                buf[lay.tables[g] + r * widths[g]:lay.tables[g] + r * widths[g] + len(table)] = table
+                buf[lay.slots[g] + row:lay.slots[g] + row + n] = \
+                    table[positions // page] * page + positions % page
+            q_lens.append(n)
+            kv_lens.append(start + n)
+            state_slots.append(e.cache.state_slot)
+            row += n
+        buf[lay.q_start + R:lay.q_start + Rc + 1] = row
+        dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
+        if dev.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+
+        def view(offset, n):
+            return dev[offset:offset + n]
+
+        groups = [GroupView(page, view(lay.slots[g], Tc),
+                            view(lay.tables[g], Rc * widths[g]).view(Rc, widths[g]))
+                  for g in range(len(widths))]
+        ctx = StepContext(
+            n_tokens=Tc, n_requests=Rc, ids=view(lay.ids, Tc), pos=view(lay.pos, Tc),
+            row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
+            kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
+            q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots)
+        return ctx, view(lay.want, Wc), W

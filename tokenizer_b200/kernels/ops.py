@@ -1,0 +1,164 @@
+"""Python faces of the CUDA launchers.  Every function takes CUDA tensors,
+launches on the current stream and raises instead of returning a wrong result:
+`KernelError` for a launch that failed, `ValueError` for a size a kernel
+refuses.  There is no CPU path: a tensor that is not on a GPU is an error."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_DTYPE_TAG = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_STATUS_TEXT = {
+    -1: "a size this kernel does not take",
+    -2: "a dtype this kernel does not take",
+    -3: "a pointer or stride that is not aligned as the kernel needs",
+    -4: "a bounded wait on the device ran out",
+}
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise ValueError(f"{what}: {_STATUS_TEXT.get(status, f'status {status}')}")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _tag(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_TAG[t.dtype]
+    except KeyError:
+        raise ValueError(f"kernels take float32 or bfloat16, found {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("tokenizer_b200 kernels run on a GPU only; got a CPU tensor")
+    if not t.is_contiguous():
+        raise ValueError("kernels take contiguous tensors")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_i, _f, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def _lib(name):
+    return load_library(name + ".cu")
+
+
+# --------------------------------------------------------------------------- #
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    n, hidden = out.shape
+    _check(_lib("elementwise").tokb200_embed(
+        _ptr(ids), _ptr(table), _i(_tag(table)), _ptr(out), _i(n), _i(hidden),
+        _i(table.shape[0]), _stream()), "embed")
+
+
+def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """out = norm(x [+ delta]) * gain; with `delta`, x is updated in place.  With
+    `rows` (int32), only those rows are read and `out` is dense [len(rows), H]."""
+    hidden = x.shape[-1]
+    n_rows = out.shape[0]
+    if x.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise ValueError("rms_norm: the residual stream and the gain are float32")
+    if gain.numel() != hidden or out.shape[-1] != hidden:
+        raise ValueError("rms_norm: sizes of x, gain and out disagree")
+    if delta is not None and rows is not None:
+        raise ValueError("rms_norm: a pending residual and a row gather do not combine")
+    _check(_lib("elementwise").tokb200_rms_norm(
+        _ptr(x), _ptr(delta), _i(_tag(delta) if delta is not None else F32), _ptr(gain),
+        _ptr(out), _i(_tag(out)), _ptr(rows), _i(n_rows), _i(hidden), _f(eps), _stream()),
+        "rms_norm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    if x.dtype != torch.float32 or x.numel() != delta.numel():
+        raise ValueError("residual_add: x is float32 and delta has its size")
+    _check(_lib("elementwise").tokb200_residual_add(
+        _ptr(x), _ptr(delta), _i(_tag(delta)), _ll(x.numel()), _stream()), "residual_add")
+
+
+def rope_table(inv_freq: torch.Tensor, n_positions: int):
+    half = inv_freq.numel()
+    cos = torch.empty((n_positions, half), dtype=torch.float32, device=inv_freq.device)
+    sin = torch.empty_like(cos)
+    _check(_lib("elementwise").tokb200_rope_table(
+        _ptr(inv_freq), _ptr(cos), _ptr(sin), _i(n_positions), _i(half), _stream()), "rope_table")
+    return cos, sin
+
+
+def rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, rotary) -> None:
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise ValueError("rope_store: qkv width is not (heads + 2 kv heads) * head_dim")
+    if rotary % 2 or (d - rotary) % 2 or rotary > d or cos.shape[1] != rotary // 2:
+        raise ValueError(f"rope_store: rotary width {rotary} does not fit head size {d}")
+    _check(_lib("elementwise").tokb200_rope_store(
+        _ptr(qkv), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), _ptr(q_out),
+        _ptr(k_pool), _ptr(v_pool), _i(_tag(qkv)), _i(n), _i(nh), _i(nkv), _i(d), _i(rotary),
+        _stream()), "rope_store")
+
+
+def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:
+    n, inner = out.shape
+    if gu.shape[1] != 2 * inner or gu.dtype != out.dtype:
+        raise ValueError("silu_gate: input is [T, 2 I], output [T, I], same dtype")
+    _check(_lib("elementwise").tokb200_silu_gate(
+        _ptr(gu), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _stream()), "silu_gate")
+
+
+def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page,
+                            window, scale) -> None:
+    if d > 512:
+        raise ValueError(f"attention: head size {d} is beyond 512")
+    if nh % nkv:
+        raise ValueError(f"attention: {nh} heads do not divide into {nkv} groups")
+    _check(_lib("attention_generic").tokb200_paged_attention_generic(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _i(_tag(q)), _ptr(block_table),
+        _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(q.shape[0]), _i(nh), _i(nkv),
+        _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
+        "paged_attention")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+             out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] w[N,K]^T (+ bias), true 32-bit."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise ValueError("gemm_f32: shapes do not chain")
+    for t in (a, w, out):
+        if t.dtype != torch.float32:
+            raise ValueError("gemm_f32 takes float32")
+    _check(_lib("gemm_f32").tokb200_gemm_f32(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(M), _i(N), _i(K), _i(K), _i(N), _stream()),
+        "gemm_f32")
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
+           out: torch.Tensor) -> None:
+    """One token per row of float32 logits; all-None parameters mean greedy."""
+    if logits.dtype != torch.float32 or out.dtype != torch.int32:
+        raise ValueError("sample: logits are float32, ids int32")
+    _check(_lib("sampling").tokb200_sample(
+        _ptr(logits), _i(logits.shape[0]), _i(logits.shape[1]), _ptr(temperature), _ptr(top_p),
+        _ptr(uniform), _ptr(out), _stream()), "sample")

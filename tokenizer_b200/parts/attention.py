@@ -1,0 +1,98 @@
+"""Grouped-query attention over the paged cache.
+
+q = h Wq^T + bq, k = h Wk^T + bk, v = h Wv^T + bv (one fused product over the
+stacked weights); q and k are rotated at their absolute positions; k (after the
+rotation) and v are written into the cache pages of their request; every row
+then attends to the keys of its request up to its own position (inside the
+window, where the layer has one: a key is hidden when key + window < query),
+scores q.k / sqrt(head_dim) with the scale applied after the product, softmax
+in float32; kv head g serves query heads g*n .. (g+1)*n - 1; the merged heads go
+through Wo (reference: qwen-infer/src/model.rs:262-328, 397-414, 119-129).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..config.spec import ConfigError
+from ..kernels import ops
+from ..weights.store import TensorSpec
+from .base import CacheNeed, KVNeed, build_part, register_part
+from .linear import Linear
+
+_position_tables = {}
+
+
+class GQAttention:
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        q_out, kv_out = p["num_heads"] * p["head_dim"], p["num_kv_heads"] * p["head_dim"]
+        out = [
+            TensorSpec(x + ".q_proj.weight", (q_out, p["hidden_size"])),
+            TensorSpec(x + ".k_proj.weight", (kv_out, p["hidden_size"])),
+            TensorSpec(x + ".v_proj.weight", (kv_out, p["hidden_size"])),
+            TensorSpec(x + ".o_proj.weight", (p["hidden_size"], q_out)),
+        ]
+        if p.get("qkv_bias"):
+            out += [TensorSpec(x + ".q_proj.bias", (q_out,)),
+                    TensorSpec(x + ".k_proj.bias", (kv_out,)),
+                    TensorSpec(x + ".v_proj.bias", (kv_out,))]
+        if p.get("out_bias"):
+            out.append(TensorSpec(x + ".o_proj.bias", (p["hidden_size"],)))
+        return out
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.window = p.get("window")
+        if self.nh % self.nkv:
+            raise ConfigError(f"{self.nh} query heads is not a multiple of {self.nkv} kv heads")
+        if self.d % 2:
+            raise ConfigError(f"head size {self.d} must be even")
+        self.scale = 1.0 / math.sqrt(float(self.d))
+        # one stacked product for q, k and v
+        w_qkv = torch.cat([store.get(x + f".{n}_proj.weight") for n in "qkv"], dim=0)
+        self.qkv = Linear(runtime.matrix(w_qkv))
+        self.qkv_bias = None
+        if p.get("qkv_bias"):
+            self.qkv_bias = runtime.vector(
+                torch.cat([store.get(x + f".{n}_proj.bias").to(torch.float32) for n in "qkv"]))
+        self.out = Linear(
+            runtime.matrix(store.get(x + ".o_proj.weight")),
+            runtime.vector(store.get(x + ".o_proj.bias")) if p.get("out_bias") else None)
+        # layers with the same position constants share one table
+        pos_spec = p["position"]
+        key = (pos_spec.kind, tuple(sorted(pos_spec.params.items())), str(runtime.device))
+        if key not in _position_tables:
+            _position_tables[key] = build_part("position", pos_spec, store, runtime)
+        self.position = _position_tables[key]
+        if self.position.rotary_dim > self.d:
+            raise ConfigError("the rotary width exceeds the head size")
+
+    def cache_need(self):
+        return CacheNeed(kv=KVNeed(self.nkv, self.d, self.window))
+
+    def forward(self, h, ctx, cache):
+        qkv = self.qkv.forward(h)
+        q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+        group = ctx.groups[cache.group]
+        ops.rope_store(
+            qkv, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
+            self.position.cos, self.position.sin, q,
+            cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None,
+            self.nh, self.nkv, self.d, self.position.rotary_dim)
+        mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+        self.attend(q, mixed, ctx, group, cache)
+        return self.out.forward(mixed)
+
+    def attend(self, q, out, ctx, group, cache):
+        ops.paged_attention_generic(
+            q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

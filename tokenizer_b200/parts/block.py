@@ -1,0 +1,19 @@
+"""Arrangement of a layer's parts.  Pre-norm residual: x += mixer(norm(x));
+x += feed_forward(norm(x)) (reference: qwen-infer/src/model.rs:603-623).  The
+adds are left pending on the stream so the next norm performs them."""
+from __future__ import annotations
+
+from .base import register_part
+
+
+class PreNormResidual:
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, stream, ctx, cache):
+        stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache))
+        stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm)))
+
+
+register_part("block", "pre_norm_residual", PreNormResidual)

@@ -1,0 +1,42 @@
+"""Gated feed-forward: down(act(gate(x)) * up(x)), no biases; the gate and up
+products are one stacked product (reference: qwen-infer/src/model.rs:226-250,
+silu(z) = z * sigmoid(z))."""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import ConfigError
+from ..kernels import ops
+from ..weights.store import TensorSpec
+from .base import register_part
+from .linear import Linear
+
+
+class GatedMLP:
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        return [
+            TensorSpec(x + ".gate_proj.weight", (p["intermediate_size"], p["hidden_size"])),
+            TensorSpec(x + ".up_proj.weight", (p["intermediate_size"], p["hidden_size"])),
+            TensorSpec(x + ".down_proj.weight", (p["hidden_size"], p["intermediate_size"])),
+        ]
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        if p["activation"] != "silu":
+            raise ConfigError(f"gated feed-forward knows the silu activation, found {p['activation']}")
+        self.runtime = runtime
+        self.inner = int(p["intermediate_size"])
+        self.gate_up = Linear(runtime.matrix(torch.cat(
+            [store.get(x + ".gate_proj.weight"), store.get(x + ".up_proj.weight")], dim=0)))
+        self.down = Linear(runtime.matrix(store.get(x + ".down_proj.weight")))
+
+    def forward(self, h):
+        gu = self.gate_up.forward(h)
+        act = self.runtime.empty(h.shape[0], self.inner)
+        ops.silu_gate(gu, act)
+        return self.down.forward(act)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

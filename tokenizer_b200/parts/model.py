@@ -1,0 +1,70 @@
+"""The generic decoder: parts assembled from a `ModelSpec`, run in the order
+the spec lists.  Nothing here names an architecture."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..weights.store import TensorSpec, WeightStore
+from .base import CacheBinding, ResidualStream, Runtime, StepContext, build_part, part_class
+
+
+def declared_tensors(spec: ModelSpec) -> List[TensorSpec]:
+    """Every tensor the model's parts declare, from the spec alone."""
+    out = list(part_class("embedding", spec.embedding.kind).tensors(spec.embedding))
+    for layer in spec.layers:
+        out += part_class("mixer", layer.mixer.kind).tensors(layer.mixer)
+        out += part_class("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
+        out += part_class("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
+        out += part_class("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
+    out += part_class("norm", spec.final_norm.kind).tensors(spec.final_norm)
+    out += part_class("head", spec.head.kind).tensors(spec.head)
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, store: WeightStore, runtime: Runtime):
+        spec.validate()
+        ignorable = ["lm_head.weight"] if spec.head.params.get("tied_to") else []
+        store.check(declared_tensors(spec), ignorable=ignorable)
+        self.spec, self.runtime = spec, runtime
+        self.vocab_size, self.hidden_size = spec.vocab_size, spec.hidden_size
+        self.max_positions = spec.max_positions
+        self.embedding = build_part("embedding", spec.embedding, store, runtime)
+        self.blocks = []
+        for layer in spec.layers:
+            self.blocks.append(part_class("block", layer.block)(
+                build_part("mixer", layer.mixer, store, runtime),
+                build_part("feed_forward", layer.feed_forward, store, runtime),
+                build_part("norm", layer.mixer_norm, store, runtime),
+                build_part("norm", layer.feed_forward_norm, store, runtime)))
+        self.final_norm = build_part("norm", spec.final_norm, store, runtime)
+        head_cls = part_class("head", spec.head.kind)
+        tied = self.embedding.table if spec.head.params.get("tied_to") else None
+        self.head = head_cls(spec.head, store, runtime, tied_table=tied)
+        self.order = spec.order
+
+    def cache_needs(self):
+        """One entry per call of the order: the need of the mixer that runs
+        there, or None where the call reads an earlier call's cache."""
+        needs = []
+        for call in self.order:
+            needs.append(None if call.cache is not None
+                         else self.blocks[call.layer].mixer.cache_need())
+        return needs
+
+    def forward(self, ctx: StepContext, bindings: List[CacheBinding],
+                want_rows: torch.Tensor) -> torch.Tensor:
+        """Run the rows of `ctx` through every call of the order and return the
+        float32 logits of `want_rows` (int32 row indices), [len(want_rows), vocab]."""
+        stream = ResidualStream(self.embedding.forward(ctx.ids))
+        for call, binding in zip(self.order, bindings):
+            self.blocks[call.layer].forward(stream, ctx, binding)
+        if want_rows.shape[0] == 0:
+            stream.pending = None
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.runtime.device)
+        stream.flush()
+        h = self.final_norm.forward(stream.x, rows=want_rows)
+        return self.head.forward(h)
