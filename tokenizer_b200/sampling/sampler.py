@@ -1,0 +1,52 @@
+"""Greedy, temperature and nucleus sampling on the device, one row of float32
+logits per request (reference: qwen-infer/src/sample.rs:43-137).  temperature 0
+is argmax with ties to the lower id and ignores top_p; otherwise weights
+exp((l - max)/T), candidates by logit descending, the shortest prefix whose
+share reaches top_p, and one draw u scaled by the kept weight."""
+from __future__ import annotations
+
+import math
+from typing import List, Sequence
+
+import torch
+
+from ..kernels import ops
+
+
+def validate_sampling(temperature: float, top_p: float) -> None:
+    """sample.rs:77-88 and generate.rs:409-424."""
+    if not math.isfinite(temperature):
+        raise ValueError(f"temperature {temperature} is not finite")
+    if temperature < 0:
+        raise ValueError(f"temperature {temperature} is negative")
+    if not math.isfinite(top_p):
+        raise ValueError(f"top_p {top_p} is not finite")
+    if top_p < 0:
+        raise ValueError(f"top_p {top_p} is negative")
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_p: Sequence[float],
+               uniform: Sequence[float]) -> List[int]:
+        """One id per row.  All-greedy batches skip the parameter upload."""
+        n = logits.shape[0]
+        if n == 0:
+            return []
+        if logits.shape[1] == 0:
+            raise ValueError("no logits to sample")
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if all(t == 0 for t in temperature):
+            ops.sample(logits, None, None, None, out)
+        else:
+            params = torch.tensor([list(temperature), list(top_p), list(uniform)],
+                                  dtype=torch.float32).to(self.device, non_blocking=True)
+            ops.sample(logits, params[0], params[1], params[2], out)
+        return out.tolist()
+
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        ops.sample(logits, None, None, None, out)
+        return out
