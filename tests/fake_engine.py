@@ -1,0 +1,64 @@
+"""A stand-in for the engine in scheduler tests: the real host-side cache plan,
+and logits that are a fixed function of the request's whole history, so any
+fault in cutting, preemption or recompute changes the sampled ids."""
+import hashlib
+
+import numpy as np
+
+import plain_qwen2 as plain
+from tokenizer_b200.cache import CachePlan
+from tokenizer_b200.parts.base import CacheNeed, KVNeed
+
+
+def logits_of(history, vocab):
+    digest = hashlib.sha256(np.asarray(history, dtype=np.int64).tobytes()).digest()
+    rng = np.random.RandomState(int.from_bytes(digest[:4], "little"))
+    return rng.standard_normal(vocab).astype(np.float32) * 3.0
+
+
+class FakeEngine:
+    def __init__(self, num_pages, page_size=4, max_requests=8, vocab=50, max_positions=512,
+                 share_prefixes=False, needs=None):
+        needs = needs or [CacheNeed(kv=KVNeed(1, 8, None))]
+        self.cache = CachePlan(needs, num_pages, page_size, max_requests, share_prefixes)
+        self.vocab = vocab
+        self.max_positions = max_positions
+        self.page_contents = {}      # (page, offset) -> (token, position, digest of the prefix)
+        self.history = {}            # id(cache) -> tokens the cache holds
+        self.steps = []              # [(request id, n tokens)] per step
+
+    def step(self, entries):
+        rows = []
+        self.steps.append([(e.cache.request_id, len(e.tokens)) for e in entries])
+        for e in entries:
+            assert len(e.tokens) > 0
+            assert self.cache.pages_missing(e.cache, len(e.tokens)) == [0] * len(self.cache.groups)
+            held = self.history.get(id(e.cache), [])
+            if len(held) != e.cache.length:
+                # pages adopted from a shared prefix: rebuild what they hold
+                held = self._read_back(e.cache)
+            assert len(held) == e.cache.length
+            for i, token in enumerate(e.tokens):
+                position = e.cache.length + i
+                page = e.cache.tables[0][position // self.cache.page_size]
+                assert page >= 0
+                self.page_contents[(page, position % self.cache.page_size)] = (token, position)
+                held = held + [token]
+                if i in e.want:
+                    rows.append(logits_of(held, self.vocab))
+            self.history[id(e.cache)] = held
+            self.cache.commit(e.cache, len(e.tokens))
+        return np.stack(rows) if rows else np.zeros((0, self.vocab), dtype=np.float32)
+
+    def _read_back(self, cache):
+        out = []
+        for position in range(cache.length):
+            page = cache.tables[0][position // self.cache.page_size]
+            token, at = self.page_contents[(page, position % self.cache.page_size)]
+            assert at == position
+            out.append(token)
+        return out
+
+    def sample(self, logits, temperature, top_p, uniform):
+        return [plain.sample_token(row, t, p, u)
+                for row, t, p, u in zip(np.asarray(logits), temperature, top_p, uniform)]

@@ -1,0 +1,172 @@
+"""The scheduler's decisions, against a fake engine (no GPU): batching equals
+running alone, joining, the token budget, what happens when pages run out,
+failures, shared beginnings, and that every page comes back.  The cases mirror
+the reference's engine tests (qwen-server/src/engine.rs:1328-1407, 1830-1963,
+1965-2084, 2470-2529)."""
+import pytest
+
+from fake_engine import FakeEngine
+from tokenizer_b200.engine.generate import GenerateParams, StopReason
+from tokenizer_b200.engine.scheduler import Scheduler
+from tiny import random_ids
+
+
+def solo(prompt, params, **engine_kw):
+    engine = FakeEngine(num_pages=256, **engine_kw)
+    s = Scheduler(engine, max_batch_size=1, token_budget=1 << 20)
+    rid = s.add_request(prompt, params)
+    return s.run()[rid]
+
+
+def run_checked(s):
+    while s.has_work():
+        s.step()
+        s.cache.check()
+    for a in s.cache.allocators:
+        assert a.all_released() and a.available == a.capacity
+    assert not s.cache.requests
+    return s.finished
+
+
+def test_batched_equals_solo_for_eight_requests():
+    prompts = [random_ids(n, 50, 10 + n) for n in (1, 2, 3, 4, 5, 6, 9, 17)]
+    params = [GenerateParams(max_tokens=3 + i, temperature=0.0) for i in range(8)]
+    s = Scheduler(FakeEngine(num_pages=256), max_batch_size=8, token_budget=64)
+    ids = [s.add_request(p, q) for p, q in zip(prompts, params)]
+    out = run_checked(s)
+    for rid, p, q in zip(ids, prompts, params):
+        assert out[rid].tokens == solo(p, q).tokens
+        assert out[rid].reason == StopReason.MAX_TOKENS and len(out[rid].tokens) == q.max_tokens
+    assert s.stats.max_running == 8 and s.stats.preemptions == 0
+    assert s.stats.requests_finished == 8
+
+
+def test_sampled_requests_do_not_depend_on_the_batch():
+    prompts = [random_ids(n, 50, 30 + n) for n in (5, 19, 64, 100)]
+    params = [GenerateParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=7 + i) for i in range(4)]
+    s = Scheduler(FakeEngine(num_pages=256), max_batch_size=4, token_budget=24)
+    ids = [s.add_request(p, q) for p, q in zip(prompts, params)]
+    out = run_checked(s)
+    for rid, p, q in zip(ids, prompts, params):
+        assert out[rid].tokens == solo(p, q).tokens
+    again = solo(prompts[0], params[0])
+    other_seed = solo(prompts[0], GenerateParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=99))
+    assert again.tokens == out[ids[0]].tokens and other_seed.tokens != again.tokens
+
+
+def test_token_budget_cuts_prompts_and_decodes_go_first():
+    engine = FakeEngine(num_pages=256)
+    s = Scheduler(engine, max_batch_size=4, token_budget=10)
+    a = s.add_request(random_ids(3, 50, 1), GenerateParams(max_tokens=8))
+    s.step()                                   # a's prompt runs whole
+    b = s.add_request(random_ids(25, 50, 2), GenerateParams(max_tokens=2))
+    run_checked(s)
+    assert engine.steps[0] == [(a, 3)]
+    assert engine.steps[1] == [(a, 1), (b, 9)]           # one decode, the rest of the budget
+    assert engine.steps[2] == [(a, 1), (b, 9)]
+    assert engine.steps[3] == [(a, 1), (b, 7)]
+    assert all(sum(n for _, n in step) <= 10 for step in engine.steps)
+    assert s.finished[b].tokens == solo(random_ids(25, 50, 2), GenerateParams(max_tokens=2)).tokens
+
+
+def test_short_request_joins_a_running_long_one():
+    engine = FakeEngine(num_pages=256)
+    s = Scheduler(engine, max_batch_size=4, token_budget=64)
+    long = s.add_request(random_ids(6, 50, 3), GenerateParams(max_tokens=12))
+    for _ in range(4):
+        s.step()
+    short = s.add_request(random_ids(2, 50, 4), GenerateParams(max_tokens=3))
+    finished_order = []
+    while s.has_work():
+        finished_order += s.step()
+    assert finished_order == [short, long]
+    assert s.finished[long].tokens == solo(random_ids(6, 50, 3), GenerateParams(max_tokens=12)).tokens
+    assert s.stats.max_running == 2
+
+
+def test_out_of_pages_preempts_the_newest_and_recomputes():
+    # three pages of four tokens: two requests of prompt 3 + 6 new need 3 pages each at the end
+    engine = FakeEngine(num_pages=3, page_size=4)
+    s = Scheduler(engine, max_batch_size=4, token_budget=64)
+    prompts = [random_ids(3, 50, 40), random_ids(3, 50, 41), random_ids(2, 50, 42)]
+    ids = [s.add_request(p, GenerateParams(max_tokens=6)) for p in prompts]
+    out = run_checked(s)
+    for rid, p in zip(ids, prompts):
+        assert out[rid].reason == StopReason.MAX_TOKENS
+        assert out[rid].tokens == solo(p, GenerateParams(max_tokens=6), page_size=4).tokens
+    assert s.stats.preemptions >= 1
+    assert s.stats.last_preempted_id in ids[1:]          # never the oldest
+    assert s.stats.peak_pages <= 3
+
+
+def test_request_larger_than_the_pool_fails_and_the_next_runs():
+    s = Scheduler(FakeEngine(num_pages=3, page_size=4), max_batch_size=4, token_budget=64)
+    big = s.add_request(random_ids(13, 50, 5), GenerateParams(max_tokens=2))
+    ok = s.add_request(random_ids(4, 50, 6), GenerateParams(max_tokens=2))
+    out = run_checked(s)
+    assert out[big].reason == StopReason.FAILED and "3 pages" in out[big].error
+    assert out[ok].reason == StopReason.MAX_TOKENS and len(out[ok].tokens) == 2
+    assert s.stats.requests_failed == 1
+
+
+def test_lone_request_that_outgrows_the_pool_fails():
+    s = Scheduler(FakeEngine(num_pages=2, page_size=4), max_batch_size=2, token_budget=64)
+    rid = s.add_request(random_ids(6, 50, 7), GenerateParams(max_tokens=10))
+    out = run_checked(s)
+    assert out[rid].reason == StopReason.FAILED and len(out[rid].tokens) == 3  # 6 + 2 fill both pages
+
+
+def test_shared_beginnings_use_the_same_pages_and_match_solo():
+    engine = FakeEngine(num_pages=64, page_size=4, share_prefixes=True)
+    s = Scheduler(engine, max_batch_size=4, token_budget=64)
+    prompt = random_ids(14, 50, 8)
+    first = s.add_request(prompt, GenerateParams(max_tokens=4))
+    s.step()
+    second = s.add_request(prompt, GenerateParams(max_tokens=4))
+    third = s.add_request(prompt[:9] + [1, 2, 3], GenerateParams(max_tokens=4))
+    out = run_checked(s)
+    want = solo(prompt, GenerateParams(max_tokens=4), page_size=4).tokens
+    assert out[first].tokens == want and out[second].tokens == want
+    assert out[third].tokens == solo(prompt[:9] + [1, 2, 3], GenerateParams(max_tokens=4), page_size=4).tokens
+    assert s.stats.shared_prefix_tokens == 12 + 8        # 3 full pages, then 2
+    # the second copy ran only what was not shared
+    assert (second, 2) in engine.steps[1]
+
+
+def test_context_limit_and_empty_prompt():
+    s = Scheduler(FakeEngine(num_pages=8, max_positions=16), max_batch_size=2)
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        s.add_request(list(range(10)), GenerateParams(max_tokens=7))
+    with pytest.raises(ValueError, match="no tokens"):
+        s.add_request([], GenerateParams(max_tokens=1))
+    with pytest.raises(ValueError, match="temperature"):
+        s.add_request([1], GenerateParams(max_tokens=1, temperature=-1.0))
+
+
+def test_max_tokens_zero_runs_the_prompt_and_draws_nothing():
+    engine = FakeEngine(num_pages=8)
+    s = Scheduler(engine, max_batch_size=2)
+    rid = s.add_request([1, 2, 3], GenerateParams(max_tokens=0))
+    out = run_checked(s)
+    assert out[rid].tokens == [] and out[rid].reason == StopReason.MAX_TOKENS
+    assert engine.steps == [[(rid, 3)]] and s.stats.tokens_sampled == 0
+
+
+def test_forward_count_is_one_prefill_plus_n_minus_one_decodes():
+    engine = FakeEngine(num_pages=64)
+    s = Scheduler(engine, max_batch_size=1, token_budget=1 << 20)
+    s.add_request([4, 5, 6, 7, 8], GenerateParams(max_tokens=5))
+    run_checked(s)
+    assert len(engine.steps) == 5            # generate.rs:686-704
+
+
+def test_windowed_groups_through_the_scheduler():
+    from tokenizer_b200.parts.base import CacheNeed, KVNeed
+    needs = [CacheNeed(kv=KVNeed(1, 8, None)), CacheNeed(kv=KVNeed(1, 8, 5))]
+    engine = FakeEngine(num_pages=12, page_size=4, needs=needs)
+    s = Scheduler(engine, max_batch_size=3, token_budget=16)
+    prompts = [random_ids(n, 50, 60 + n) for n in (9, 14, 3)]
+    ids = [s.add_request(p, GenerateParams(max_tokens=7)) for p in prompts]
+    out = run_checked(s)
+    for rid, p in zip(ids, prompts):
+        assert out[rid].tokens == solo(p, GenerateParams(max_tokens=7), page_size=4).tokens

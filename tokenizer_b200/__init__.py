@@ -4,6 +4,11 @@ token.  See `generate` for the entry point."""
 from .config import ConfigError, Qwen2Config, load_config, register_architecture
 from .weights import WeightError, write_random_model
 
-__all__ = ["ConfigError", "Qwen2Config", "WeightError", "load_config", "register_architecture",
+from .api import (Control, Engine, Generated, GenerateParams, StopReason, engine_for, generate,
+                  generate_batch, generate_with, greedy_tokens, load_eos_token_ids, load_model)
+
+__all__ = ["Control", "Engine", "Generated", "GenerateParams", "StopReason", "engine_for",
+           "generate", "generate_batch", "generate_with", "greedy_tokens", "load_eos_token_ids",
+           "load_model", "ConfigError", "Qwen2Config", "WeightError", "load_config", "register_architecture",
            "write_random_model"]
 __version__ = "0.1.0"

@@ -1,0 +1,232 @@
+"""Continuous batching above the step function.
+
+Every request is a *context* (its prompt and the ids sampled so far) and a
+count of how much of that context the cache already holds.  One iteration:
+
+ 1. admit waiting requests in arrival order while a batch slot is free and the
+    pool could hold the head's whole context now; a blocked head blocks those
+    behind it, and a context that no empty pool could hold fails;
+ 2. give every running request its share of this step: requests one token short
+    of their context (decoding) first, one token each, then the others get
+    portions of their context, oldest first, under what is left of the token
+    budget;
+ 3. reserve pages for those tokens, oldest request first.  When pages run out,
+    the newest running request loses all its pages and goes back to the front
+    of the waiting line; its context is run again later (nothing is sampled
+    twice: a draw happens only when the whole context is in the cache).  A
+    request that is alone and still does not fit fails;
+ 4. run the step, draw one id for each request whose context is now whole, let
+    its cursor decide between going on and finishing, free what finished.
+
+The reference's scheduler (qwen-server/src/engine.rs:229-402, 455-704) admits
+and preempts in the same way but runs a whole prompt per iteration; the token
+budget and the portions are this engine's.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence
+
+from ..cache.manager import OutOfPages
+from .batch import StepEntry
+from .generate import Control, Generated, GenerateParams, SampleCursor, StopReason
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    max_running: int = 0
+    preemptions: int = 0
+    last_preempted_id: int = -1
+    requests_finished: int = 0
+    requests_failed: int = 0
+    peak_pages: int = 0
+    tokens_run: int = 0
+    tokens_sampled: int = 0
+    shared_prefix_tokens: int = 0
+
+
+@dataclass
+class _Request:
+    id: int
+    prompt: List[int]
+    cursor: SampleCursor
+    context: List[int]
+    cache: object = None
+    published: bool = False
+    arrived: float = 0.0
+    prompt_done: Optional[float] = None
+
+
+class Scheduler:
+    def __init__(self, engine, max_batch_size: int = 8, token_budget: int = 512):
+        """`engine` offers `cache` (a CachePlan), `step(entries) -> logits`,
+        `sample(logits, temperature, top_p, uniform) -> ids` and
+        `max_positions`."""
+        if max_batch_size < 1 or token_budget < 1:
+            raise ValueError("the batch holds at least one request and one token")
+        self.engine = engine
+        self.cache = engine.cache
+        self.max_batch_size = max_batch_size
+        self.token_budget = token_budget
+        self.waiting: Deque[_Request] = deque()
+        self.running: List[_Request] = []
+        self.finished: Dict[int, Generated] = {}
+        self.stats = SchedulerStats()
+        self._next_id = 0
+
+    # ---- requests -------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: GenerateParams,
+                    token_bytes: Optional[Callable[[int], bytes]] = None,
+                    on_chunk: Optional[Callable[[str], Control]] = None) -> int:
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("the prompt has no tokens")
+        if len(prompt) + params.max_tokens > self.engine.max_positions:
+            raise ValueError(
+                f"prompt of {len(prompt)} plus max_tokens {params.max_tokens} exceeds "
+                f"max_position_embeddings {self.engine.max_positions}")
+        request = _Request(self._next_id, prompt, SampleCursor(params, token_bytes, on_chunk),
+                           list(prompt), arrived=time.perf_counter())
+        self._next_id += 1
+        self.waiting.append(request)
+        return request.id
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def run(self) -> Dict[int, Generated]:
+        while self.has_work():
+            self.step()
+        return self.finished
+
+    # ---- one iteration -----------------------------------------------------------
+    def step(self) -> List[int]:
+        """Run one iteration; returns the ids of the requests that finished."""
+        done_before = set(self.finished)
+        self._admit()
+        plan = self._plan_and_reserve()
+        if plan:
+            entries = [StepEntry(r.cache, r.context[r.cache.length:r.cache.length + n],
+                                 [n - 1] if r.cache.length + n == len(r.context) else [])
+                       for r, n in plan]
+            logits = self.engine.step(entries)
+            self.stats.steps += 1
+            self.stats.tokens_run += sum(n for _, n in plan)
+            self.stats.max_running = max(self.stats.max_running, len(self.running))
+            self.stats.peak_pages = max(
+                self.stats.peak_pages, max((a.live for a in self.cache.allocators), default=0))
+            self._sample([r for r, n in plan if r.cache.length == len(r.context)], logits)
+        return [i for i in self.finished if i not in done_before]
+
+    def _context_pages(self, request: _Request) -> int:
+        return self.cache.pages_for_tokens(len(request.context))
+
+    def _admit(self) -> None:
+        while self.waiting and len(self.running) < self.max_batch_size:
+            head = self.waiting[0]
+            if self._context_pages(head) > self.cache.num_pages:
+                self.waiting.popleft()
+                self._fail(head, f"the cache has {self.cache.num_pages} pages of "
+                                 f"{self.cache.page_size}; this request needs {self._context_pages(head)}")
+                continue
+            cache = self.cache.open(head.id)
+            adopted = self.cache.adopt_prefix(cache, head.context[:-1])
+            if not self.cache.can_reserve(cache, len(head.context) - cache.length):
+                self.cache.close(cache)
+                break
+            self.stats.shared_prefix_tokens += adopted
+            head.cache = cache
+            self.running.append(self.waiting.popleft())
+
+    def _shares(self) -> List:
+        """(request, tokens this step): decoding requests first, then portions
+        of contexts, oldest first, under the token budget."""
+        by_age = sorted(self.running, key=lambda r: r.id)
+        left = self.token_budget
+        shares = []
+        for r in by_age:
+            if len(r.context) - r.cache.length == 1:
+                shares.append((r, 1))
+                left -= 1
+        for r in by_age:
+            remaining = len(r.context) - r.cache.length
+            if remaining > 1 and left > 0:
+                shares.append((r, min(remaining, left)))
+                left -= shares[-1][1]
+        return shares
+
+    def _plan_and_reserve(self) -> List:
+        while True:
+            shares = self._shares()
+            short = None
+            for r, n in sorted(shares, key=lambda s: s[0].id):
+                try:
+                    self.cache.reserve(r.cache, n)
+                except OutOfPages:
+                    short = r
+                    break
+            if short is None:
+                return shares
+            victim = max(self.running, key=lambda r: r.id)
+            if victim is short and len(self.running) == 1:
+                self.running.remove(short)
+                self.cache.close(short.cache)
+                self._fail(short, f"the cache has {self.cache.num_pages} pages of "
+                                  f"{self.cache.page_size}; this request cannot go on alone")
+                continue
+            self._preempt(victim)
+
+    def _preempt(self, victim: _Request) -> None:
+        self.running.remove(victim)
+        self.cache.close(victim.cache)
+        victim.cache = None
+        self.stats.preemptions += 1
+        self.stats.last_preempted_id = victim.id
+        # To the front of the line.  Victims are taken newest first and every
+        # waiting request is newer than any running one, so the line stays in
+        # arrival order.
+        self.waiting.appendleft(victim)
+
+    def _sample(self, ready: List[_Request], logits) -> None:
+        now = time.perf_counter()
+        rows, drawing = [], []
+        for row, r in enumerate(ready):
+            if r.prompt_done is None:
+                r.prompt_done = now
+            if not r.published and r.cache.length >= len(r.prompt):
+                self.cache.publish_prompt(r.cache, r.prompt)
+                r.published = True
+            if r.cursor.wants_sample():
+                rows.append(row)
+                drawing.append(r)
+        if drawing:
+            picked = logits if len(rows) == len(ready) else logits[rows]
+            ids = self.engine.sample(
+                picked, [r.cursor.params.temperature for r in drawing],
+                [r.cursor.params.top_p for r in drawing],
+                [r.cursor.next_uniform() for r in drawing])
+            self.stats.tokens_sampled += len(ids)
+            for r, token in zip(drawing, ids):
+                if r.cursor.accept(int(token)):
+                    r.context.append(int(token))
+        for r in ready:
+            if r.cursor.done is not None:
+                self._retire(r, now)
+
+    def _retire(self, r: _Request, now: float) -> None:
+        self.running.remove(r)
+        self.cache.close(r.cache)
+        r.cache = None
+        result = r.cursor.done
+        result.prefill = (r.prompt_done or now) - r.arrived
+        result.decode = time.perf_counter() - (r.prompt_done or now)
+        self.finished[r.id] = result
+        self.stats.requests_finished += 1
+
+    def _fail(self, r: _Request, message: str) -> None:
+        self.finished[r.id] = Generated(list(r.cursor.tokens), r.cursor.text, list(r.cursor.chunks),
+                                        StopReason.FAILED, r.cursor.produced, error=message)
+        self.stats.requests_failed += 1

@@ -20,6 +20,7 @@ from ..kernels.ops import KernelError
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
 from ..weights.store import WeightStore
+from ..sampling.sampler import Sampler
 from .batch import BatchBuilder, StepEntry
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -60,6 +61,8 @@ class Engine:
         self.bindings = self.cache.bindings(model.order)
         self.builder = BatchBuilder(self.cache, model.vocab_size, model.max_positions,
                                     model.runtime.device)
+        self.sampler = Sampler(model.runtime.device)
+        self.max_positions = model.max_positions
         self.steps_run = 0
 
     @classmethod
@@ -80,3 +83,8 @@ class Engine:
             self.cache.commit(e.cache, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def sample(self, logits: torch.Tensor, temperature, top_p, uniform) -> List[int]:
+        """Draw one id per row of `logits` on the device."""
+        with torch.cuda.device(self.runtime.device):
+            return self.sampler.sample(logits, temperature, top_p, uniform)
