@@ -241,3 +241,60 @@ TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_to
   }
   return tokb200_launch_status();
 }
+
+// ----------------------------------------------------------------------------
+// Decoding several steps without the host: after a step's ids were drawn, make
+// the next step's metadata in place.  For each live row r: the drawn id becomes
+// the next input, its position and stored length grow by one, its cache slot is
+// looked up in its block table (pages were reserved ahead), and the id is
+// appended to `history[step, r]`; `step_counter` counts the steps.
+// ----------------------------------------------------------------------------
+struct AdvanceGroups {
+  int* slots[4];
+  const int* tables[4];
+  int widths[4];
+  int count;
+};
+
+__global__ void advance_decode_kernel(int* __restrict__ ids, const int* __restrict__ drawn,
+                                      int* __restrict__ pos, int* __restrict__ kv_len,
+                                      const int* __restrict__ row_req, AdvanceGroups groups,
+                                      int page, int n_rows, int* __restrict__ history,
+                                      int* __restrict__ step_counter) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = *step_counter;
+  if (r < n_rows && row_req[r] >= 0) {
+    const int id = drawn[r];
+    ids[r] = id;
+    history[(size_t)step * n_rows + r] = id;
+    const int p = pos[r] + 1;
+    pos[r] = p;
+    kv_len[r] += 1;
+    for (int g = 0; g < groups.count; ++g) {
+      const int pg = groups.tables[g][(size_t)r * groups.widths[g] + p / page];
+      groups.slots[g][r] = pg < 0 ? -1 : pg * page + p % page;
+    }
+  }
+}
+
+__global__ void bump_counter_kernel(int* counter) { *counter += 1; }
+
+TOKB200_API int tokb200_advance_decode(int* ids, const int* drawn, int* pos, int* kv_len,
+                                       const int* row_req, int n_groups, int** slots,
+                                       const int** tables, const int* widths, int page,
+                                       int n_rows, int* history, int* step_counter,
+                                       cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (n_groups < 0 || n_groups > 4) return TOKB200_BAD_SIZE;
+  AdvanceGroups groups;
+  groups.count = n_groups;
+  for (int g = 0; g < n_groups; ++g) {
+    groups.slots[g] = slots[g];
+    groups.tables[g] = tables[g];
+    groups.widths[g] = widths[g];
+  }
+  advance_decode_kernel<<<(n_rows + 127) / 128, 128, 0, stream>>>(
+      ids, drawn, pos, kv_len, row_req, groups, page, n_rows, history, step_counter);
+  bump_counter_kernel<<<1, 1, 0, stream>>>(step_counter);
+  return tokb200_launch_status();
+}

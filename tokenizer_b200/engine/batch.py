@@ -80,6 +80,7 @@ class BatchBuilder:
         self._host: Optional[torch.Tensor] = None
         self._dev: Optional[torch.Tensor] = None
         self._copied: Optional[torch.cuda.Event] = None
+        self.last_bytes = 0
 
     def _buffers(self, total: int):
         if self._host is None or self._host.numel() < total:
@@ -88,6 +89,14 @@ class BatchBuilder:
             self._host = torch.empty(capacity, dtype=torch.int32, pin_memory=pin)
             self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
         return self._host, self._dev
+
+    def device_buffer_ptr(self) -> int:
+        return 0 if self._dev is None else self._dev.data_ptr()
+
+    def reserve_capacity(self, total: int) -> None:
+        """Size the buffers once, so that later steps never move them (captured
+        graphs hold their addresses)."""
+        self._buffers(total)
 
     def validate(self, entries: List[StepEntry]) -> None:
         seen = set()
@@ -167,6 +176,7 @@ class BatchBuilder:
             row += n
         buf[lay.q_start + R:lay.q_start + Rc + 1] = row
         dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
+        self.last_bytes = lay.total * 4
         if dev.is_cuda:
             self._copied = torch.cuda.Event()
             self._copied.record()

@@ -53,7 +53,7 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
 
 class Engine:
     def __init__(self, model: DecoderModel, num_pages: int, page_size: int = 16,
-                 max_requests: int = 64, share_prefixes: bool = False):
+                 max_requests: int = 64, share_prefixes: bool = False, use_graphs: bool = True):
         self.model = model
         self.runtime = model.runtime
         self.cache = DeviceCache(model.cache_needs(), num_pages, page_size, max_requests,
@@ -64,6 +64,11 @@ class Engine:
         self.sampler = Sampler(model.runtime.device)
         self.max_positions = model.max_positions
         self.steps_run = 0
+        self.use_graphs = bool(use_graphs)
+        self._graphs = {}
+        self._graph_buffer = 0
+        tables = sum(max_requests * (model.max_positions // page_size + 8) for _ in self.cache.groups)
+        self.builder.reserve_capacity(16 * 8192 + tables)
 
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
@@ -77,12 +82,130 @@ class Engine:
                                device=self.runtime.device)
         self.builder.validate(entries)
         with torch.cuda.device(self.runtime.device):
-            ctx, want_rows, n_want = self.builder.build(entries)
-            logits = self.model.forward(ctx, self.bindings, want_rows[:n_want])
+            if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+                logits = self._step_captured(entries)
+            else:
+                ctx, want_rows, n_want = self.builder.build(entries)
+                logits = self.model.forward(ctx, self.bindings, want_rows[:n_want])
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ---- decoding steps replayed from CUDA graphs ---------------------------------
+    @staticmethod
+    def _bucket(n: int, least: int = 1) -> int:
+        b = least
+        while b < n:
+            b *= 2
+        return b
+
+    def _step_captured(self, entries: List[StepEntry]) -> torch.Tensor:
+        """A step of single tokens only.  Its launches are captured once per
+        (padded batch size, padded block-table widths) and replayed afterwards;
+        only the packed metadata changes between replays, at fixed addresses.
+        Idle rows of the padded batch carry request -1, which kernels skip."""
+        from ..kernels.ops import counter
+        rows = self._bucket(len(entries))
+        widths = [self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
+                  for g in range(len(self.cache.groups))]
+        key = (rows, tuple(widths))
+        ctx, want_rows, n_want = self.builder.build(
+            entries, pad_requests=rows, pad_tokens=rows, pad_want=rows, table_widths=widths)
+        if self._graph_buffer != self.builder.device_buffer_ptr():
+            self._graphs.clear()           # the metadata moved: captured addresses are stale
+            self._graph_buffer = self.builder.device_buffer_ptr()
+        slot = self._graphs.get(key)
+        if slot is None:
+            # first use: run it once plainly (this also compiles what is missing)
+            self._graphs[key] = {}
+            return self.model.forward(ctx, self.bindings, want_rows)[:n_want]
+        if "graph" not in slot:
+            graph = torch.cuda.CUDAGraph()
+            before = counter.launches
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, self.bindings, want_rows)
+            slot.update(graph=graph, out=out, launches=counter.launches - before)
+            counter.launches = before
+        slot["graph"].replay()
+        counter.launches += slot["launches"]
+        return slot["out"][:n_want]
+
+    def decode_steps(self, entries: List[StepEntry], n_steps: int) -> List[List[int]]:
+        """Greedy decoding of `n_steps` tokens for every entry without going
+        back to the host between steps: each entry brings the one token to run
+        next; the drawn id becomes the next input on the device.  Returns the
+        drawn ids, [n_steps][len(entries)].  Pages for all the steps are
+        reserved here; OutOfPages leaves everything as it was."""
+        from ..kernels import ops
+        from ..kernels.ops import counter
+        if n_steps <= 0 or not entries:
+            return []
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise ValueError("decode_steps takes one token per request")
+            if e.cache.length + n_steps > self.max_positions:
+                raise ValueError("the steps would pass max_position_embeddings")
+        for e in entries:
+            if not self.cache.can_reserve(e.cache, n_steps):
+                from ..cache.manager import OutOfPages
+                raise OutOfPages(f"no pages for {n_steps} more tokens of {e.cache.request_id!r}")
+        for e in entries:
+            self.cache.reserve(e.cache, n_steps)
+        for e in entries:
+            e.want = [0]
+        self.builder.validate(entries)
+        device = self.runtime.device
+        with torch.cuda.device(device):
+            rows = self._bucket(len(entries))
+            widths = [self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
+                      for g in range(len(self.cache.groups))]
+            ctx, want_rows, n_want = self.builder.build(
+                entries, pad_requests=rows, pad_tokens=rows, pad_want=rows, table_widths=widths)
+            if self._graph_buffer != self.builder.device_buffer_ptr():
+                self._graphs.clear()
+                self._graph_buffer = self.builder.device_buffer_ptr()
+            key = ("steps", rows, tuple(widths))
+            slot = self._graphs.get(key)
+            if slot is None:
+                slot = self._graphs[key] = {
+                    "history": torch.zeros(4096 * rows, dtype=torch.int32, device=device),
+                    "counter": torch.zeros(1, dtype=torch.int32, device=device),
+                    "drawn": torch.zeros(rows, dtype=torch.int32, device=device)}
+            if n_steps > 4096:
+                raise ValueError("decode_steps runs at most 4096 steps a call")
+            slot["counter"].zero_()
+
+            def iteration():
+                logits = self.model.forward(ctx, self.bindings, want_rows)
+                ops.sample(logits, None, None, None, slot["drawn"])
+                ops.advance_decode(ctx.ids, slot["drawn"], ctx.pos, ctx.kv_len, ctx.row_req,
+                                   [g.slots for g in ctx.groups],
+                                   [g.block_table for g in ctx.groups], self.cache.page_size,
+                                   slot["history"], slot["counter"])
+
+            done = 0
+            if "graph" not in slot:
+                iteration()              # plainly once: compiles and warms
+                done = 1
+                if n_steps > 1:
+                    graph = torch.cuda.CUDAGraph()
+                    before = counter.launches
+                    torch.cuda.synchronize()
+                    # capture replays the step on the live metadata; it does not run
+                    with torch.cuda.graph(graph):
+                        iteration()
+                    slot.update(graph=graph, launches=counter.launches - before)
+                    counter.launches = before
+            for _ in range(done, n_steps):
+                slot["graph"].replay()
+                counter.launches += slot["launches"]
+            history = slot["history"][:n_steps * rows].view(n_steps, rows)[:, :len(entries)].tolist()
+        for e in entries:
+            self.cache.commit(e.cache, n_steps)
+        self.steps_run += n_steps
+        return history
 
     def sample(self, logits: torch.Tensor, temperature, top_p, uniform) -> List[int]:
         """Draw one id per row of `logits` on the device."""

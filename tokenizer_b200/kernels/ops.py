@@ -27,8 +27,17 @@ _STATUS_TEXT = {
 }
 
 
+class _Counter:
+    """How many of the framework's own kernels were launched (the bench reports it)."""
+    launches = 0
+
+
+counter = _Counter()
+
+
 def _check(status: int, what: str) -> None:
     if status == 0:
+        counter.launches += 1
         return
     if status < 0:
         raise ValueError(f"{what}: {_STATUS_TEXT.get(status, f'status {status}')}")
@@ -162,3 +171,19 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor],
     _check(_lib("sampling").tokb200_sample(
         _ptr(logits), _i(logits.shape[0]), _i(logits.shape[1]), _ptr(temperature), _ptr(top_p),
         _ptr(uniform), _ptr(out), _stream()), "sample")
+
+
+def advance_decode(ids, drawn, pos, kv_len, row_req, slots, tables, page, history,
+                   step_counter) -> None:
+    """After a decoding step: the drawn ids become the next inputs and every
+    row's position, stored length and cache slot move on by one (on the device)."""
+    n = len(slots)
+    if n > 4:
+        raise ValueError("advance_decode handles up to four cache groups")
+    slot_ptrs = (ctypes.c_void_p * max(n, 1))(*[t.data_ptr() for t in slots])
+    table_ptrs = (ctypes.c_void_p * max(n, 1))(*[t.data_ptr() for t in tables])
+    widths = (ctypes.c_int * max(n, 1))(*[t.shape[1] for t in tables])
+    _check(_lib("elementwise").tokb200_advance_decode(
+        _ptr(ids), _ptr(drawn), _ptr(pos), _ptr(kv_len), _ptr(row_req), _i(n), slot_ptrs,
+        table_ptrs, widths, _i(page), _i(ids.shape[0]), _ptr(history), _ptr(step_counter),
+        _stream()), "advance_decode")

@@ -1,0 +1,15 @@
+"""Every library the package can load, with the variants (compile-time sizes)
+that are built ahead of time.  A library outside this list is still compiled
+at its first use."""
+from __future__ import annotations
+
+
+def all_variants():
+    """[(source, defines, extra flags)] for `compile_many`."""
+    jobs = [
+        ("elementwise.cu", (), ()),
+        ("attention_generic.cu", (), ()),
+        ("gemm_f32.cu", (), ()),
+        ("sampling.cu", (), ()),
+    ]
+    return jobs
