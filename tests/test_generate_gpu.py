@@ -1,0 +1,164 @@
+"""Generation through the Python entry point on the GPU: greedy ids against the
+plain implementation, long decoding, the first tokens of a sequence, decoding
+steps that stay on the device, and sampled requests under batching."""
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from tiny import TINY, make_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+
+SHARPEN = {r"\.(q|k)_proj\.weight": 8.0, r"embed_tokens|lm_head": 5.0}
+
+
+@pytest.fixture(scope="module", params=["a", "b", "c"])
+def folder(request, tmp_path_factory):
+    return make_folder(tmp_path_factory, request.param, scale=SHARPEN)
+
+
+def margins_ok(cfg, w, ids, n_prompt, least):
+    """Greedy ids of two implementations can only be compared where the best
+    logit leads the second by more than their rounding."""
+    logits = plain.all_logits(cfg, w, ids)[n_prompt - 1:-1]
+    top2 = torch.topk(logits, 2, dim=-1).values
+    return bool(((top2[:, 0] - top2[:, 1]) > least).all())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_equals_the_plain_implementation(folder, dtype):
+    import tokenizer_b200 as tb
+    path, config, page = folder
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype=dtype)
+    checked = 0
+    for n in (1, 7, 33):
+        prompt = random_ids(n, config.vocab_size, 200 + n)
+        want = plain.greedy_generate(cfg, w, prompt, 16)
+        out = tb.generate(model, prompt, tb.GenerateParams.greedy(16))
+        assert out.reason == tb.StopReason.MAX_TOKENS and out.completion_tokens == 16
+        if dtype == "float32":
+            assert out.tokens == want
+            checked += 1
+        elif margins_ok(cfg, w, prompt + want, n, 0.05 * float(plain.all_logits(cfg, w, prompt + want).abs().max())):
+            assert out.tokens == want
+            checked += 1
+        assert tb.greedy_tokens(model, prompt, 16) == out.tokens     # the same call twice
+    assert dtype == "bfloat16" or checked == 3
+
+
+def test_eos_stops_generation(folder):
+    import tokenizer_b200 as tb
+    path, config, page = folder
+    model = tb.load_model(path, dtype="float32")
+    prompt = random_ids(9, config.vocab_size, 3)
+    free = tb.generate(model, prompt, tb.GenerateParams.greedy(8)).tokens
+    out = tb.generate(model, prompt, tb.GenerateParams(max_tokens=8, eos=[free[3]]))
+    first = free.index(free[3])
+    assert out.tokens == free[:first] and out.reason == tb.StopReason.EOS
+    assert out.completion_tokens == first + 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_device_side_steps(folder, dtype):
+    """Decode far past the prompt (many pages, the window passing pages by), one
+    step at a time through the scheduler and in steps that stay on the device;
+    both must give the ids of a whole-sequence recompute."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    path, config, page = folder
+    cfg, w = plain.load_folder(path)
+    n_new = min(100, config.max_position_embeddings - 12)
+    prompt = random_ids(11, config.vocab_size, 77)
+    model = tb.load_model(path, dtype=dtype)
+    out = tb.generate(model, prompt, tb.GenerateParams.greedy(n_new)).tokens
+    assert len(out) == n_new
+    # every id is the argmax of the plain logits given the ids before it, up to rounding
+    logits = plain.all_logits(cfg, w, prompt + out)
+    lead = logits[len(prompt) - 1:-1]
+    chosen = lead.gather(1, torch.tensor(out)[:, None])[:, 0]
+    slack = 1e-4 if dtype == "float32" else 0.04 * float(logits.abs().max())
+    worst = float((lead.max(dim=1).values - chosen).max())
+    assert worst <= slack, f"token {int((lead.max(dim=1).values - chosen).argmax())} is {worst} below the best"
+    # the same through decode_steps, two requests side by side
+    engine = tb.engine_for(model, 2 * (len(prompt) + n_new + 64), page, max_requests=2)
+    caches = [engine.cache.open(i) for i in range(2)]
+    for c in caches:
+        engine.cache.reserve(c, len(prompt))
+    first = engine.sampler.greedy(engine.step([StepEntry(c, prompt, [len(prompt) - 1]) for c in caches])).tolist()
+    assert first == [out[0], out[0]]
+    ids = engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, first)], 40)
+    ids += engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, ids[-1])], n_new - 41)
+    assert [row[0] for row in ids] == [row[1] for row in ids]
+    got = [out[0]] + [row[0] for row in ids]
+    if dtype == "float32":
+        assert got == out
+    assert caches[0].length == len(prompt) + n_new - 1
+    for c in caches:
+        engine.cache.close(c)
+    assert all(a.all_released() for a in engine.cache.allocators)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folder, dtype):
+    """Positions 0, 1, 2 alone: one key, no page filled, the rotation at angle 0."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    path, config, page = folder
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype=dtype)
+    engine = tb.engine_for(model, 64, page, max_requests=4)
+    ids = random_ids(3, config.vocab_size, 9)
+    want = plain.all_logits(cfg, w, ids)
+    cache = engine.cache.open("x")
+    rows = []
+    for t in ids:
+        engine.cache.reserve(cache, 1)
+        rows.append(engine.step([StepEntry(cache, [t], [0])]).cpu()[0])
+    bound = 1e-4 if dtype == "float32" else 2e-2 * float(want.abs().max())
+    assert float((torch.stack(rows) - want).abs().max()) <= bound
+
+
+def test_sampled_requests_in_a_batch_follow_their_own_draws(tmp_path_factory):
+    """Config B's run: four requests of 5/19/64/100 tokens, temperature 0.8 from a
+    fixed seed, portions of 24 tokens mixed with decoded tokens.  Each request's
+    ids must be what its own draws select from the plain logits of its own history."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.sampling import uniform
+    path, config, page = make_folder(tmp_path_factory, "b", scale=SHARPEN)
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype="float32")
+    prompts = [random_ids(n, config.vocab_size, 300 + n) for n in (5, 19, 64, 100)]
+    params = [tb.GenerateParams(max_tokens=12, temperature=0.8, top_p=0.95, seed=40 + i) for i in range(4)]
+    outs = tb.generate_batch(model, prompts, params, max_batch_size=4, token_budget=24, page_size=page)
+    solo = [tb.generate(model, p, q) for p, q in zip(prompts, params)]
+    for prompt, q, out, alone in zip(prompts, params, outs, solo):
+        assert len(out.tokens) == 12 and out.tokens == alone.tokens
+        logits = plain.all_logits(cfg, w, prompt + out.tokens)
+        for k, token in enumerate(out.tokens):
+            kept, mass = plain.sample_intervals(logits[len(prompt) - 1 + k], 0.8, 0.95)
+            assert token in kept
+            at, total = kept.index(token), sum(mass)
+            u = uniform(q.seed, k)
+            assert sum(mass[:at]) - 1e-4 * total <= u * total < sum(mass[:at + 1]) + 1e-4 * total
+
+
+def test_the_engine_refuses_what_it_cannot_run(folder):
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    path, config, page = folder
+    model = tb.load_model(path, dtype="float32")
+    engine = tb.engine_for(model, 64, page, max_requests=2)
+    cache = engine.cache.open("x")
+    with pytest.raises(ValueError, match="no pages reserved"):
+        engine.step([StepEntry(cache, [1, 2], [0])])
+    engine.cache.reserve(cache, 2)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        engine.step([StepEntry(cache, [1, config.vocab_size], [0])])
+    with pytest.raises(ValueError, match="wanted place"):
+        engine.step([StepEntry(cache, [1, 2], [2])])
+    with pytest.raises(ValueError, match="twice"):
+        engine.step([StepEntry(cache, [1], [0]), StepEntry(cache, [2], [0])])
+    with pytest.raises(Exception, match="GPU"):
+        tb.load_model(path, dtype="float32", device="cpu")
+    assert engine.step([StepEntry(cache, [1, 2], [1])]).shape == (1, config.vocab_size)

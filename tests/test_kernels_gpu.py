@@ -1,0 +1,311 @@
+"""Each kernel alone against a plain float32 restatement of the same operation,
+at sizes other than the engine's (widths that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from tokenizer_b200.kernels import ops as o
+    return o
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, dtype):
+    got, want = got.float().cpu(), want.float().cpu()
+    if dtype == torch.float32:
+        assert torch.allclose(got, want, atol=2e-5, rtol=2e-5), float((got - want).abs().max())
+    else:  # one rounding to bfloat16 of a value computed in float32
+        assert torch.allclose(got, want, atol=1e-3, rtol=2 ** -7), float((got - want).abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = rnd(301, 70, dtype=dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 70, device=DEV)
+    ops().embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [48, 200, 1030, 3000])
+def test_rms_norm_with_pending_add_and_rows(dtype, hidden):
+    x = rnd(7, hidden, seed=1, scale=3.0)
+    delta = rnd(7, hidden, seed=2, dtype=dtype)
+    gain = 1 + rnd(hidden, seed=3, scale=0.1)
+    eps = 1e-5
+    want_x = x + delta.float()
+    want = want_x / torch.sqrt((want_x * want_x).mean(-1, keepdim=True) + eps) * gain
+    out = torch.empty(7, hidden, dtype=dtype, device=DEV)
+    x_run = x.clone()
+    ops().rms_norm(x_run, gain, eps, out, delta=delta)
+    assert torch.allclose(x_run, want_x, atol=1e-6)          # the sum is stored back in float32
+    close(out, want, dtype)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out_rows = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    ops().rms_norm(x_run, gain, eps, out_rows, rows=rows)
+    close(out_rows, want[rows.long()], dtype)
+    y = x.clone()
+    ops().residual_add(y, delta)
+    assert torch.allclose(y, want_x, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,rotary", [(5, 5, 48, 48), (6, 2, 16, 16), (3, 1, 80, 32), (14, 2, 64, 64)])
+def test_rope_bias_and_cache_write(dtype, nh, nkv, d, rotary):
+    o = ops()
+    T, page, pages = 9, 4, 6
+    theta = 1e4
+    inv_freq = torch.tensor([1.0 / theta ** (i / rotary) for i in range(0, rotary, 2)],
+                            dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 700)
+    positions = torch.arange(700, dtype=torch.float32, device=DEV)[:, None] * inv_freq[None]
+    assert torch.allclose(cos, torch.cos(positions), atol=2e-6)
+    assert torch.allclose(sin, torch.sin(positions), atol=2e-6)
+    qkv = rnd(T, (nh + 2 * nkv) * d, seed=4, dtype=dtype)
+    bias = rnd((nh + 2 * nkv) * d, seed=5, scale=0.3)
+    pos = torch.tensor([0, 1, 2, 3, 650, 651, 17, 5, 6], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([4, 5, 6, 7, 20, 21, 0, -1, 13], dtype=torch.int32, device=DEV)
+    k_pool = torch.full((pages * page, nkv, d), 7.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((pages * page, nkv, d), 7.0, dtype=dtype, device=DEV)
+    q_out = torch.empty(T, nh * d, dtype=dtype, device=DEV)
+    o.rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, rotary)
+
+    full = (qkv.float() + bias).view(T, nh + 2 * nkv, d)
+
+    def rotate(x):  # x [T, heads, d]
+        half = rotary // 2
+        c, s = cos[pos.long()][:, None, :], sin[pos.long()][:, None, :]
+        x1, x2, rest = x[..., :half], x[..., half:rotary], x[..., rotary:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
+
+    close(q_out.view(T, nh, d), rotate(full[:, :nh]), dtype)
+    k_want, v_want = rotate(full[:, nh:nh + nkv]), full[:, nh + nkv:]
+    for t in range(T):
+        if int(slot[t]) < 0:
+            continue
+        close(k_pool[int(slot[t])], k_want[t], dtype)
+        close(v_pool[int(slot[t])], v_want[t], dtype)
+    untouched = [s for s in range(pages * page) if s not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
+    # a call that reads another layer's cache rotates q and writes no keys
+    k2 = k_pool.clone()
+    o.rope_store(qkv, bias, pos, None, cos, sin, q_out, None, None, nh, nkv, d, rotary)
+    assert torch.equal(k2, k_pool)
+    with pytest.raises(ValueError):
+        o.rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, rotary + 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_gate(dtype):
+    gu = rnd(5, 2 * 177, seed=6, dtype=dtype, scale=3.0)
+    out = torch.empty(5, 177, dtype=dtype, device=DEV)
+    ops().silu_gate(gu, out)
+    g, u = gu.float()[:, :177], gu.float()[:, 177:]
+    close(out, g * torch.sigmoid(g) * u, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 70), (65, 64, 17), (200, 301, 96), (2, 1000, 896)])
+def test_gemm_f32_is_true_32_bit(M, N, K):
+    a, w, bias = rnd(M, K, seed=7), rnd(N, K, seed=8), rnd(N, seed=9)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a, w, bias, out)
+    want = (a.double().cpu() @ w.double().cpu().t() + bias.double().cpu()).float()
+    assert torch.allclose(out.cpu(), want, atol=1e-4 * math.sqrt(K) / 8, rtol=1e-5)
+    # a row's result does not depend on the rows around it
+    alone = torch.empty(1, N, device=DEV)
+    ops().gemm_f32(a[M - 1:].contiguous(), w, bias, alone)
+    assert torch.equal(alone[0], out[M - 1])
+
+
+def paged_setup(lengths, nh, nkv, d, page, dtype, seed=10, shuffle=True):
+    """Random keys and values for requests of the given lengths, scattered over
+    pages in a shuffled order; returns pools, tables and the dense copies."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum((n + page - 1) // page for n in lengths) + 3
+    order = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    k_pool = torch.full((n_pages * page, nkv, d), float("nan"), dtype=dtype)
+    v_pool = torch.full((n_pages * page, nkv, d), float("nan"), dtype=dtype)
+    width = max((n + page - 1) // page for n in lengths) + 1
+    tables = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    dense = []
+    for r, n in enumerate(lengths):
+        k = torch.randn(n, nkv, d, generator=g).to(dtype)
+        v = torch.randn(n, nkv, d, generator=g).to(dtype)
+        for b in range((n + page - 1) // page):
+            pg = order.pop()
+            tables[r, b] = pg
+            rows = slice(b * page, min(n, (b + 1) * page))
+            k_pool[pg * page:pg * page + rows.stop - rows.start] = k[rows]
+            v_pool[pg * page:pg * page + rows.stop - rows.start] = v[rows]
+        dense.append((k.float(), v.float()))
+    return k_pool.to(DEV), v_pool.to(DEV), tables.to(DEV), dense
+
+
+def attention_reference(q, dense, row_req, pos, nh, nkv, window, scale):
+    out = torch.zeros_like(q)
+    for t in range(q.shape[0]):
+        k, v = dense[row_req[t]]
+        p = pos[t]
+        lo = 0 if window is None else max(0, p - window)
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (k[lo:p + 1, g] @ q[t, h]) * scale
+            out[t, h] = torch.softmax(s, 0) @ v[lo:p + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 32, 24), (14, 2, 64, 16, None),
+    (6, 3, 112, 4, 7), (2, 1, 256, 16, None)])
+def test_paged_attention(dtype, nh, nkv, d, page, window):
+    lengths = [1, 37, 130, 300]
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype)
+    # rows: the last 3 positions of every request (a portion) and a few inner ones
+    row_req, pos = [], []
+    for r, n in enumerate(lengths):
+        for p in sorted(set([max(0, n - 3), max(0, n - 2), n - 1, n // 2, min(n - 1, page - 1),
+                             min(n - 1, page)])):
+            row_req.append(r)
+            pos.append(p)
+    q = rnd(len(pos), nh, d, seed=11, dtype=dtype)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    ops().paged_attention_generic(
+        q.view(len(pos), nh * d), k_pool, v_pool, out.view(len(pos), nh * d), tables,
+        torch.tensor(row_req, dtype=torch.int32, device=DEV),
+        torch.tensor(pos, dtype=torch.int32, device=DEV), nh, nkv, d, page, window, scale)
+    want = attention_reference(q.float().cpu(), dense, row_req, pos, nh, nkv, window, scale)
+    assert torch.isfinite(out.float()).all()       # unused slots (NaN) are never read
+    close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
+    """One key among hundreds is made to stand out; the output must be its
+    value.  With a window, a key exactly `window` back is seen, one further is not."""
+    nh, nkv, d, page, n = 2, 1, 32, 16, 400
+    k_pool, v_pool, tables, dense = paged_setup([n], nh, nkv, d, page, dtype, seed=12)
+    scale = 1.0 / math.sqrt(d)
+    q = rnd(1, nh, d, seed=13, dtype=dtype)
+    for far in (0, 15, 16, 17, 255, 256, 399 - 25, 399 - 24, 399):
+        k, v = dense[0]
+        k, v = k.clone(), v.clone()
+        k[far, 0] = q[0, 0].float().cpu() * 40.0            # score stands out for head 0
+        pg, off = int(tables[0, far // page]), far % page
+        k_pool2 = k_pool.clone()
+        k_pool2[pg * page + off, 0] = k[far, 0].to(dtype).to(DEV)
+        for window in (None, 24):
+            out = torch.empty(1, nh * d, dtype=dtype, device=DEV)
+            ops().paged_attention_generic(
+                q.view(1, nh * d), k_pool2, v_pool, out, tables,
+                torch.zeros(1, dtype=torch.int32, device=DEV),
+                torch.tensor([n - 1], dtype=torch.int32, device=DEV), nh, nkv, d, page, window, scale)
+            visible = window is None or far + window >= n - 1
+            got = out.view(nh, d)[0].float().cpu()
+            if visible:
+                close(got, v[far, 0], dtype)
+            else:
+                assert float((got - v[far, 0]).abs().max()) > 0.1
+            want = attention_reference(q.float().cpu(), [(k, v)], [0], [n - 1], nh, nkv, window, scale)
+            close(out.view(1, nh, d), want, dtype)
+
+
+def test_attention_refuses_sizes_it_cannot_take():
+    q = torch.zeros(1, 6 * 16, device=DEV)
+    pool = torch.zeros(16, 4, 16, device=DEV)
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ValueError, match="do not divide"):
+        ops().paged_attention_generic(q, pool, pool, q.clone(), table, z, z, 6, 4, 16, 16, None, 1.0)
+    with pytest.raises(ValueError, match="beyond 512"):
+        ops().paged_attention_generic(q, pool, pool, q.clone(), table, z, z, 1, 1, 1024, 16, None, 1.0)
+
+
+def test_argmax_ties_and_sampling_against_the_plain_rule():
+    import plain_qwen2 as plain
+    o = ops()
+    V = 3001
+    logits = rnd(6, V, seed=14, scale=2.0)
+    logits[0, 17] = logits[0, 2900] = 50.0          # ties keep the lower id
+    logits[1] = 0.0                                  # all equal: id 0
+    logits[2, 3000] = 60.0                           # the last id
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    o.sample(logits, None, None, None, out)
+    got = out.tolist()
+    assert got[:3] == [17, 0, 3000]
+    assert got == [plain.greedy_token(row) for row in logits.cpu()]
+
+    rows = []
+    for i, (temp, top_p) in enumerate([(0.8, 1.0), (0.8, 0.9), (1.5, 0.5), (0.3, 0.95), (1.0, 0.0),
+                                       (0.0, 0.5), (2.0, 0.999)]):
+        for u in (0.0, 0.013, 0.37, 0.5, 0.77, 0.999999):
+            rows.append((i % 6, temp, top_p, u))
+    batch = torch.stack([logits[r] for r, _, _, _ in rows])
+    temps = torch.tensor([t for _, t, _, _ in rows], device=DEV)
+    tops = torch.tensor([p for _, _, p, _ in rows], device=DEV)
+    us = torch.tensor([u for _, _, _, u in rows], device=DEV)
+    out = torch.empty(len(rows), dtype=torch.int32, device=DEV)
+    o.sample(batch, temps, tops, us, out)
+    for (r, temp, top_p, u), token in zip(rows, out.tolist()):
+        row = logits[r].cpu()
+        if temp == 0.0:
+            assert token == plain.greedy_token(row)
+            continue
+        kept, mass = plain.sample_intervals(row, temp, top_p)
+        assert token in kept, (temp, top_p, u, token)
+        # the drawn id's interval in the walking order holds u * kept weight (float32 sums
+        # differ in order, so allow the width of a few roundings of the total)
+        at = kept.index(token)
+        total = sum(mass)
+        before = sum(mass[:at])
+        slack = 1e-5 * total
+        assert before - slack <= u * total < before + mass[at] + slack, (temp, top_p, u, token)
+    # top_p 0 keeps only the best id whatever the draw
+    assert all(t == plain.greedy_token(logits[r].cpu()) for (r, temp, p, u), t in zip(rows, out.tolist())
+               if p == 0.0 and temp > 0)
+
+
+def test_sampling_follows_the_distribution():
+    o = ops()
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 3.0]], device=DEV).repeat(4000, 1).contiguous()
+    temps = torch.full((4000,), 0.7, device=DEV)
+    tops = torch.ones(4000, device=DEV)
+    us = torch.rand(4000, generator=torch.Generator().manual_seed(3)).to(DEV)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    o.sample(logits, temps, tops, us, out)
+    freq = torch.bincount(out.long().cpu(), minlength=5).float() / 4000
+    want = torch.softmax(logits[0].cpu() / 0.7, 0)
+    assert float((freq - want).abs().max()) < 0.03
+
+
+def test_advance_decode():
+    o = ops()
+    page = 4
+    ids = torch.tensor([5, 6, 0, 0], dtype=torch.int32, device=DEV)
+    drawn = torch.tensor([9, 8, 7, 7], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([2, 7, 0, 0], dtype=torch.int32, device=DEV)
+    kv = torch.tensor([3, 8, 0, 0], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([0, 1, -1, -1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([4 * 3 + 2, 4 * 1 + 3, -1, -1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, -1, -1], [5, 1, 6], [-1, -1, -1], [-1, -1, -1]], dtype=torch.int32, device=DEV)
+    history = torch.zeros(3 * 4, dtype=torch.int32, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.advance_decode(ids, drawn, pos, kv, row_req, [slots], [table], page, history, counter)
+    assert ids.tolist() == [9, 8, 0, 0] and pos.tolist() == [3, 8, 0, 0] and kv.tolist() == [4, 9, 0, 0]
+    assert slots.tolist() == [4 * 3 + 3, 4 * 6 + 0, -1, -1]
+    assert int(counter) == 1 and history.tolist()[:4] == [9, 8, 0, 0]
+    o.advance_decode(ids, drawn, pos, kv, row_req, [slots], [table], page, history, counter)
+    assert slots.tolist()[0] == -1 and history.tolist()[4:6] == [9, 8] and int(counter) == 2

@@ -64,7 +64,9 @@ class Engine:
         self.sampler = Sampler(model.runtime.device)
         self.max_positions = model.max_positions
         self.steps_run = 0
-        self.use_graphs = bool(use_graphs)
+        # a captured step bakes its launches: only mixers that say so may be replayed
+        self.use_graphs = bool(use_graphs) and all(
+            getattr(block.mixer, "graph_safe", False) for block in model.blocks)
         self._graphs = {}
         self._graph_buffer = 0
         tables = sum(max_requests * (model.max_positions // page_size + 8) for _ in self.cache.groups)

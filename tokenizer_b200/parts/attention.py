@@ -25,6 +25,8 @@ _position_tables = {}
 
 
 class GQAttention:
+    graph_safe = True   # launches depend on device-side metadata only
+
     @staticmethod
     def tensors(spec):
         p, x = spec.params, spec.prefix
