@@ -309,3 +309,60 @@ def test_advance_decode():
     assert int(counter) == 1 and history.tolist()[:4] == [9, 8, 0, 0]
     o.advance_decode(ids, drawn, pos, kv, row_req, [slots], [table], page, history, counter)
     assert slots.tolist()[0] == -1 and history.tolist()[4:6] == [9, 8] and int(counter) == 2
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 32, 24), (14, 2, 64, 16, None),
+    (6, 3, 112, 4, 7), (8, 1, 256, 16, None), (7, 1, 64, 16, 100), (12, 2, 128, 64, None)])
+def test_decode_attention_splits_and_merges(nh, nkv, d, page, window):
+    """The split-key kernel: one row per request at the request's last position
+    (one split, several splits, pieces longer than a tile), idle rows skipped."""
+    dtype = torch.bfloat16
+    lengths = [1, 2, 63, 64, 65, 130, 700, 2500]
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=21)
+    row_req = list(range(len(lengths))) + [-1, 3]
+    pos = [n - 1 for n in lengths] + [0, 40]
+    q = rnd(len(pos), nh, d, seed=22, dtype=dtype)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(d)
+    for _ in range(2):          # twice: the merge counters must be left ready
+        ops().decode_attention(
+            q.view(len(pos), nh * d), k_pool, v_pool, out.view(len(pos), nh * d), tables,
+            torch.tensor(row_req, dtype=torch.int32, device=DEV),
+            torch.tensor(pos, dtype=torch.int32, device=DEV), nh, nkv, d, page, window, scale)
+        live = [i for i, r in enumerate(row_req) if r >= 0]
+        want = attention_reference(q.float().cpu()[live], dense, [row_req[i] for i in live],
+                                   [pos[i] for i in live], nh, nkv, window, scale)
+        assert torch.isfinite(out.float()).all()
+        close(out[live], want, dtype)
+        assert bool((out[len(lengths)] == 9.0).all())     # the idle row is not written
+        out.fill_(9.0)
+
+
+def test_decode_attention_far_key_across_splits():
+    nh, nkv, d, page, n = 7, 1, 64, 16, 1500
+    dtype = torch.bfloat16
+    k_pool, v_pool, tables, dense = paged_setup([n], nh, nkv, d, page, dtype, seed=23)
+    q = rnd(1, nh, d, seed=24, dtype=dtype)
+    scale = 1.0 / math.sqrt(d)
+    for far in (0, 63, 64, 640, 1499 - 200, 1499 - 201, 1499):
+        k, v = dense[0][0].clone(), dense[0][1]
+        k[far, 0] = q[0, 3].float().cpu() * 30.0
+        k_pool2 = k_pool.clone()
+        k_pool2[int(tables[0, far // page]) * page + far % page, 0] = k[far, 0].to(dtype).to(DEV)
+        for window in (None, 200):
+            out = torch.empty(1, nh * d, dtype=dtype, device=DEV)
+            ops().decode_attention(q.view(1, nh * d), k_pool2, v_pool, out, tables,
+                                   torch.zeros(1, dtype=torch.int32, device=DEV),
+                                   torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                   nh, nkv, d, page, window, scale)
+            want = attention_reference(q.float().cpu(), [(k, v)], [0], [n - 1], nh, nkv, window, scale)
+            close(out.view(1, nh, d), want, dtype)
+            if window is None or far + window >= n - 1:
+                close(out.view(nh, d)[3], v[far, 0], dtype)
+
+
+def test_decode_attention_refuses_groups_it_cannot_hold():
+    assert not ops().decode_attention_supported(18, 2, 64)
+    assert not ops().decode_attention_supported(4, 2, 24)
+    assert ops().decode_attention_supported(14, 2, 64)

@@ -187,3 +187,37 @@ def advance_decode(ids, drawn, pos, kv_len, row_req, slots, tables, page, histor
         _ptr(ids), _ptr(drawn), _ptr(pos), _ptr(kv_len), _ptr(row_req), _i(n), slot_ptrs,
         table_ptrs, widths, _i(page), _i(ids.shape[0]), _ptr(history), _ptr(step_counter),
         _stream()), "advance_decode")
+
+
+DECODE_MAX_GROUP = 8
+_decode_scratch = {}
+
+
+def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
+    """Sizes the split-key decoding kernel takes; others go to the general kernel."""
+    return d % 16 == 0 and 16 <= d <= 256 and nh % nkv == 0 and nh // nkv <= DECODE_MAX_GROUP
+
+
+def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page, window,
+                     scale) -> None:
+    """Attention for rows of one token each (bfloat16): keys are split over
+    blocks and merged; the scratch for the pieces is kept per (device, rows,
+    heads, head size) and reused by every layer, which run one after another."""
+    if q.dtype != torch.bfloat16:
+        raise ValueError("decode_attention is the bfloat16 kernel")
+    if not decode_attention_supported(nh, nkv, d):
+        raise ValueError(f"decode_attention: {nh} heads over {nkv} groups of size {d} is not taken")
+    lib = load_library("attention_decode.cu", defines=(f"HEAD_DIM={d}",))
+    n_rows = q.shape[0]
+    key = (q.device.index, n_rows, nh, nkv, d)
+    if key not in _decode_scratch:
+        lib.tokb200_decode_attention_scratch_floats.restype = ctypes.c_longlong
+        floats = lib.tokb200_decode_attention_scratch_floats(_i(n_rows), _i(nh))
+        _decode_scratch[key] = (torch.empty(floats, dtype=torch.float32, device=q.device),
+                                torch.zeros(n_rows * nkv, dtype=torch.int32, device=q.device))
+    scratch, counters = _decode_scratch[key]
+    _check(lib.tokb200_decode_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
+        _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
+        _i(page), _i(-1 if window is None else int(window)), _f(scale), _ptr(scratch),
+        _ptr(counters), _stream()), "decode_attention")

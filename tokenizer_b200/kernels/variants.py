@@ -12,4 +12,6 @@ def all_variants():
         ("gemm_f32.cu", (), ()),
         ("sampling.cu", (), ()),
     ]
+    for head_dim in (16, 32, 48, 64, 128):
+        jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))
     return jobs

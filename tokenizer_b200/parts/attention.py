@@ -92,6 +92,13 @@ class GQAttention:
         return self.out.forward(mixed)
 
     def attend(self, q, out, ctx, group, cache):
+        """Choose the kernel by precision and by the shape of the batch."""
+        if q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and \
+                ops.decode_attention_supported(self.nh, self.nkv, self.d):
+            ops.decode_attention(
+                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
+            return
         ops.paged_attention_generic(
             q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
             self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
