@@ -114,6 +114,8 @@ def main():
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    parser.add_argument("--only-decode", action="store_true",
+                        help="time the decode steps only and print a short line (for profiling)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -154,7 +156,7 @@ def main():
 
     # ---- prefill of 2,048 tokens in one step ------------------------------------
     prefill_ms = []
-    for rep in range(3 + 5):
+    for rep in range(0 if args.only_decode else 3 + 5):
         cache = engine.cache.open(("prefill", rep))
         engine.cache.reserve(cache, PREFILL_TOKENS)
         entry = StepEntry(cache, random_prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])
@@ -167,7 +169,7 @@ def main():
         if rep >= 3:
             prefill_ms.append(start.elapsed_time(stop))
         engine.cache.close(cache)
-    prefill_best = sorted(prefill_ms)[len(prefill_ms) // 2]
+    prefill_best = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
     prefill = {"value": PREFILL_TOKENS / (prefill_best / 1e3), "tokens": PREFILL_TOKENS,
                "ms": prefill_best,
                "frac": prefill_flops(cfg, args.layers, PREFILL_TOKENS) / (prefill_best / 1e3)
@@ -206,7 +208,11 @@ def main():
         return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3),
                 "launches": launches, "clocks": clock_record, "context_end": context}
 
-    main_run = decode_run(args.batch, args.steps, args.warmup, True)
+    main_run = decode_run(args.batch, args.steps, args.warmup, not args.only_decode)
+    if args.only_decode:
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": main_run["ms_per_step"],
+                          "tok_s": main_run["tok_s"], "gpu_launches": main_run["launches"]}))
+        return 0
     points = {}
     if not args.no_points:
         for b in (1, 64):

@@ -203,7 +203,7 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
     for far in (0, 15, 16, 17, 255, 256, 399 - 25, 399 - 24, 399):
         k, v = dense[0]
         k, v = k.clone(), v.clone()
-        k[far, 0] = q[0, 0].float().cpu() * 40.0            # score stands out for head 0
+        k[far, 0] = (q[0, 0].float().cpu() * 40.0).to(dtype).float()   # score stands out for head 0
         pg, off = int(tables[0, far // page]), far % page
         k_pool2 = k_pool.clone()
         k_pool2[pg * page + off, 0] = k[far, 0].to(dtype).to(DEV)
@@ -347,7 +347,7 @@ def test_decode_attention_far_key_across_splits():
     scale = 1.0 / math.sqrt(d)
     for far in (0, 63, 64, 640, 1499 - 200, 1499 - 201, 1499):
         k, v = dense[0][0].clone(), dense[0][1]
-        k[far, 0] = q[0, 3].float().cpu() * 30.0
+        k[far, 0] = (q[0, 3].float().cpu() * 30.0).to(dtype).float()
         k_pool2 = k_pool.clone()
         k_pool2[int(tables[0, far // page]) * page + far % page, 0] = k[far, 0].to(dtype).to(DEV)
         for window in (None, 200):
@@ -366,3 +366,48 @@ def test_decode_attention_refuses_groups_it_cannot_hold():
     assert not ops().decode_attention_supported(18, 2, 64)
     assert not ops().decode_attention_supported(4, 2, 24)
     assert ops().decode_attention_supported(14, 2, 64)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 32), (3, 130, 72), (8, 1152, 896), (8, 896, 4864), (5, 301, 96),
+                                   (16, 64, 64), (17, 200, 176), (33, 1000, 256), (64, 896, 896),
+                                   (8, 20000, 96), (2, 896, 1000)])
+def test_linear_small_m(M, N, K):
+    """The streaming product for few rows against float64, bfloat16 and float32
+    results, with a bias, and cut along k into partial sums."""
+    o = ops()
+    x = rnd(M, K, seed=31, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=32, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=33)
+    want = x.double().cpu() @ w.double().cpu().t()
+    out32 = torch.empty(M, N, device=DEV)
+    o.linear_small_m(x, w, None, out32)
+    tol = 2e-5 * float(want.abs().max()) + 1e-6 * K
+    assert float((out32.double().cpu() - want).abs().max()) <= tol
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    o.linear_small_m(x, w, bias, out16)
+    close(out16, (want + bias.double().cpu()).float(), torch.bfloat16)
+    for splits in (2, 5):
+        parts = torch.full((splits, M, N), 7.0, device=DEV)
+        o.linear_small_m(x, w, None, parts, k_splits=splits)
+        assert float((parts.sum(0).double().cpu() - want).abs().max()) <= tol
+    again = torch.empty(M, N, device=DEV)
+    o.linear_small_m(x, w, None, again)
+    assert torch.equal(again, out32)            # fixed order of sums: reproducible
+    with pytest.raises(ValueError):
+        o.linear_small_m(rnd(65, K, dtype=torch.bfloat16), w, None, torch.empty(65, N, device=DEV))
+
+
+def test_norm_adds_partial_sums():
+    x = rnd(5, 200, seed=41)
+    parts = rnd(3, 5, 200, seed=42)
+    gain = 1 + rnd(200, seed=43, scale=0.1)
+    want_x = x + parts.sum(0)
+    out = torch.empty(5, 200, device=DEV)
+    x1 = x.clone()
+    ops().rms_norm(x1, gain, 1e-6, out, delta=parts)
+    assert torch.allclose(x1, want_x, atol=1e-6)
+    want = want_x / torch.sqrt((want_x * want_x).mean(-1, keepdim=True) + 1e-6) * gain
+    assert torch.allclose(out, want, atol=2e-5)
+    x2 = x.clone()
+    ops().residual_add(x2, parts)
+    assert torch.allclose(x2, want_x, atol=1e-6)

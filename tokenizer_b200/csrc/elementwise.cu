@@ -42,7 +42,8 @@ TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype
 template <typename TD, typename TO>
 __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                 const float* __restrict__ gain, TO* __restrict__ y,
-                                const int* __restrict__ rows, int hidden, float eps) {
+                                const int* __restrict__ rows, int hidden, float eps,
+                                int n_partials, size_t partial_stride) {
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -52,7 +53,8 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ de
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = xr[i];
     if (dr) {
-      v += to_float(dr[i]);
+      // the pending residual may come as partial sums of a product cut along k
+      for (int s = 0; s < n_partials; ++s) v += to_float(dr[(size_t)s * partial_stride + i]);
       xr[i] = v;
     }
     ss += v * v;
@@ -64,14 +66,15 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ de
     yr[i] = from_float<TO>(xr[i] * inv * gain[i]);
 }
 
-TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, const float* gain,
-                                 void* y, int y_dtype, const int* rows, int n_rows, int hidden,
-                                 float eps, cudaStream_t stream) {
+TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, int n_partials,
+                                 long long partial_stride, const float* gain, void* y,
+                                 int y_dtype, const int* rows, int n_rows, int hidden, float eps,
+                                 cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
-  if (hidden <= 0) return TOKB200_BAD_SIZE;
+  if (hidden <= 0 || n_partials < 1) return TOKB200_BAD_SIZE;
   const int threads = hidden >= 1024 ? 256 : 128;
 #define LAUNCH(TD, TO) \
-  rms_norm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(x, (const TD*)delta, gain, (TO*)y, rows, hidden, eps)
+  rms_norm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(x, (const TD*)delta, gain, (TO*)y, rows, hidden, eps, n_partials, (size_t)partial_stride)
   if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_F32) LAUNCH(float, float);
   else if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
   else if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
@@ -83,20 +86,26 @@ TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, c
 
 // x += delta, elementwise (a pending residual that no norm follows)
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n,
+                                    int n_partials) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < n; i += stride) x[i] += to_float(delta[i]);
+  for (; i < n; i += stride) {
+    float v = x[i];
+    for (int s = 0; s < n_partials; ++s) v += to_float(delta[(size_t)s * n + i]);
+    x[i] = v;
+  }
 }
 
-TOKB200_API int tokb200_residual_add(float* x, const void* delta, int delta_dtype, long long n,
-                                     cudaStream_t stream) {
+TOKB200_API int tokb200_residual_add(float* x, const void* delta, int delta_dtype, int n_partials,
+                                     long long n, cudaStream_t stream) {
   if (n <= 0) return TOKB200_OK;
+  if (n_partials < 1) return TOKB200_BAD_SIZE;
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   if (delta_dtype == TOKB200_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n, n_partials);
   else if (delta_dtype == TOKB200_BF16)
-    residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n, n_partials);
   else
     return TOKB200_BAD_DTYPE;
   return tokb200_launch_status();

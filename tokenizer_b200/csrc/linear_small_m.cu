@@ -1,0 +1,139 @@
+// y[M,N] = x[M,K] W[N,K]^T (+ bias) for few rows (decoding: M <= 64), bfloat16
+// operands, 32-bit accumulation.  The product is bound by reading W once, so the
+// kernel is built around that stream: the weight rows play the M side of the
+// tensor-core instruction (mma.sync m16n8k16, 16 weight rows per warp) and the
+// batch plays its N side (8 rows of x per instruction), and every thread feeds
+// its fragments straight from 16-byte global loads, with no staging of W in
+// shared memory.  That works because a dot product does not care about the
+// order of k: within a step of 32 k, thread t of a quad loads k = 8t .. 8t+7 of
+// its weight row, and the same 8 of its x row, and both are handed to the two
+// instructions of the step under the same (permuted) k slots.
+//
+// Work is cut three ways: row tiles of 16 over the grid's x, the warps of a block
+// share a row tile by interleaved k steps and add up in shared memory in warp
+// order, and (for matrices with few rows) K is also cut over the grid's y into
+// `k_splits` pieces whose 32-bit partial results [k_splits, M, N] the consumer
+// adds in index order.  Every sum has a fixed order: results are reproducible.
+#include "common.cuh"
+
+#define LSM_WARPS 8
+#define LSM_THREADS (LSM_WARPS * 32)
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
+                                               unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool ok) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (ok) v = __ldg(reinterpret_cast<const uint4*>(p));
+  return v;
+}
+
+// MT: tiles of 8 rows of x (M <= 8 MT).  TPB: row tiles of W per block; the
+// block's warps split into TPB teams of LSM_WARPS / TPB warps, a team per row tile.
+template <int MT, int TPB>
+__global__ void __launch_bounds__(LSM_THREADS)
+linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                      const float* __restrict__ bias, void* __restrict__ out, int out_is_f32,
+                      int M, int N, int K, int k_per_split) {
+  constexpr int TEAM = LSM_WARPS / TPB;
+  __shared__ float part[LSM_WARPS][16][8 * MT + 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int team = warp / TEAM, member = warp % TEAM;
+  const int row0 = (blockIdx.x * TPB + team) * 16;
+  const int k_begin = blockIdx.y * k_per_split;
+  const int k_end = min(K, k_begin + k_per_split);
+
+  float acc[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+  const bool row_a_ok = row0 + g < N, row_b_ok = row0 + g + 8 < N;
+  const __nv_bfloat16* wa = w + (size_t)(row0 + g) * K + 8 * t;
+  const __nv_bfloat16* wb = w + (size_t)(row0 + g + 8) * K + 8 * t;
+
+#pragma unroll 4
+  for (int k = k_begin + member * 32; k < k_end; k += TEAM * 32) {
+    const bool k_ok = k + 8 * t + 8 <= k_end;
+    const uint4 a = load16(wa + k, row_a_ok && k_ok);
+    const uint4 b = load16(wb + k, row_b_ok && k_ok);
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int m = 8 * j + g;
+      const uint4 xv = load16(x + (size_t)m * K + k + 8 * t, m < M && k_ok);
+      mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
+      mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+    }
+  }
+
+  // accumulator layout: c0,c1 -> (row g, columns 2t, 2t+1); c2,c3 -> (row g + 8, same)
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    part[warp][g][8 * j + 2 * t] = acc[j][0];
+    part[warp][g][8 * j + 2 * t + 1] = acc[j][1];
+    part[warp][g + 8][8 * j + 2 * t] = acc[j][2];
+    part[warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+
+  // each team's 16 x M results: consecutive threads take consecutive weight rows (n)
+  const bool partial = gridDim.y > 1;
+  for (int i = threadIdx.x; i < TPB * 16 * M; i += LSM_THREADS) {
+    const int tm = i / (16 * M);
+    const int m = (i / 16) % M, rr = i % 16;
+    const int n = (blockIdx.x * TPB + tm) * 16 + rr;
+    if (n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < TEAM; ++s) v += part[tm * TEAM + s][rr][m];
+    if (partial) {
+      reinterpret_cast<float*>(out)[((size_t)blockIdx.y * M + m) * N + n] = v;
+    } else {
+      if (bias) v += bias[n];
+      if (out_is_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
+      else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+template <int MT>
+static int launch_small_m(const void* x, const void* w, const float* bias, void* out,
+                          int out_is_f32, int M, int N, int K, int k_splits,
+                          cudaStream_t stream) {
+  const int tiles = (N + 15) / 16;
+  int k_per_split = (K + k_splits - 1) / k_splits;
+  k_per_split = (k_per_split + 31) / 32 * 32;
+  // many row tiles: two per block (teams of 4 warps); few: one per block (8 warps on its k)
+  if (tiles >= 1024) {
+    dim3 grid((tiles + 1) / 2, k_splits);
+    linear_small_m_kernel<MT, 2><<<grid, LSM_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32, M, N, K, k_per_split);
+  } else {
+    dim3 grid(tiles, k_splits);
+    linear_small_m_kernel<MT, 1><<<grid, LSM_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32, M, N, K, k_per_split);
+  }
+  return tokb200_launch_status();
+}
+
+// out: [M, N] bfloat16 or float32 when k_splits == 1 (bias added); float32
+// partial sums [k_splits, M, N] otherwise (no bias: the consumer adds them up).
+TOKB200_API int tokb200_linear_small_m(const void* x, const void* w, const float* bias, void* out,
+                                       int out_is_f32, int M, int N, int K, int k_splits,
+                                       cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (M > 64 || K <= 0 || K % 8 || k_splits < 1 || k_splits > 64) return TOKB200_BAD_SIZE;
+  if (k_splits > 1 && (bias || !out_is_f32)) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M <= 8) return launch_small_m<1>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
+  if (M <= 16) return launch_small_m<2>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
+  if (M <= 32) return launch_small_m<4>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
+  return launch_small_m<8>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
+}

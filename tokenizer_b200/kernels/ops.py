@@ -92,17 +92,33 @@ def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
         raise ValueError("rms_norm: sizes of x, gain and out disagree")
     if delta is not None and rows is not None:
         raise ValueError("rms_norm: a pending residual and a row gather do not combine")
+    n_partials, stride = _partials(delta, x)
     _check(_lib("elementwise").tokb200_rms_norm(
-        _ptr(x), _ptr(delta), _i(_tag(delta) if delta is not None else F32), _ptr(gain),
+        _ptr(x), _ptr(delta), _i(_tag(delta) if delta is not None else F32), _i(n_partials),
+        _ll(stride), _ptr(gain),
         _ptr(out), _i(_tag(out)), _ptr(rows), _i(n_rows), _i(hidden), _f(eps), _stream()),
         "rms_norm")
 
 
+def _partials(delta, x):
+    """A pending residual is [T, H], or float32 partial sums [S, T, H] of a
+    product that was cut along k; returns (S, elements between partials)."""
+    if delta is None or delta.dim() == x.dim():
+        if delta is not None and delta.shape != x.shape:
+            raise ValueError("the pending residual has another shape than the stream")
+        return 1, 0
+    if delta.dim() != x.dim() + 1 or delta.shape[1:] != x.shape or delta.dtype != torch.float32:
+        raise ValueError("partial sums are float32 [S, T, H]")
+    return delta.shape[0], x.numel()
+
+
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
-    if x.dtype != torch.float32 or x.numel() != delta.numel():
-        raise ValueError("residual_add: x is float32 and delta has its size")
+    if x.dtype != torch.float32:
+        raise ValueError("residual_add: x is float32")
+    n_partials, _ = _partials(delta, x)
     _check(_lib("elementwise").tokb200_residual_add(
-        _ptr(x), _ptr(delta), _i(_tag(delta)), _ll(x.numel()), _stream()), "residual_add")
+        _ptr(x), _ptr(delta), _i(_tag(delta)), _i(n_partials), _ll(x.numel()), _stream()),
+        "residual_add")
 
 
 def rope_table(inv_freq: torch.Tensor, n_positions: int):
@@ -221,3 +237,24 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
         _i(page), _i(-1 if window is None else int(window)), _f(scale), _ptr(scratch),
         _ptr(counters), _stream()), "decode_attention")
+
+
+def linear_small_m_supported(M: int, K: int) -> bool:
+    return 0 < M <= 64 and K % 8 == 0
+
+
+def linear_small_m(x, w, bias, out, k_splits: int = 1) -> None:
+    """out = x w^T (+ bias) for at most 64 rows of bfloat16 x.  With k_splits > 1
+    `out` is float32 [k_splits, M, N]: partial sums that the consumer adds."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not linear_small_m_supported(M, K):
+        raise ValueError(f"linear_small_m takes up to 64 rows and K a multiple of 8; got {M} x {K}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("linear_small_m: bfloat16 x [M,K] and w [N,K]")
+    want = (M, N) if k_splits == 1 else (k_splits, M, N)
+    if tuple(out.shape) != want or (k_splits > 1 and out.dtype != torch.float32):
+        raise ValueError(f"linear_small_m: out must be {want}")
+    _check(_lib("linear_small_m").tokb200_linear_small_m(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
+        _i(M), _i(N), _i(K), _i(k_splits), _stream()), "linear_small_m")

@@ -11,6 +11,7 @@ def all_variants():
         ("attention_generic.cu", (), ()),
         ("gemm_f32.cu", (), ()),
         ("sampling.cu", (), ()),
+        ("linear_small_m.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

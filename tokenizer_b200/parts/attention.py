@@ -89,7 +89,7 @@ class GQAttention:
             self.nh, self.nkv, self.d, self.position.rotary_dim)
         mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
         self.attend(q, mixed, ctx, group, cache)
-        return self.out.forward(mixed)
+        return self.out.forward(mixed, partials_ok=True)
 
     def attend(self, q, out, ctx, group, cache):
         """Choose the kernel by precision and by the shape of the batch."""

@@ -9,8 +9,10 @@ with `tensors(spec)` and works on the rows it is handed.
 Interfaces (duck-typed; the classes below marked "interface" document them):
 
   mixer         tensors(spec); __init__(spec, store, runtime); cache_need();
-                forward(h [T,H], ctx: StepContext, cache: CacheBinding) -> delta [T,H]
-  feed_forward  tensors(spec); __init__(spec, store, runtime); forward(h [T,H]) -> delta [T,H]
+                forward(h [T,H], ctx: StepContext, cache: CacheBinding) -> delta
+  feed_forward  tensors(spec); __init__(spec, store, runtime); forward(h [T,H]) -> delta
+                (delta is [T,H] in the compute dtype, or float32 partial sums [S,T,H]
+                that the residual stream adds up in index order)
   norm          tensors(spec); __init__(spec, store, runtime);
                 forward(x f32 [T,H], delta=None, rows=None) -> h (compute dtype)
   position      tensors(spec); __init__(spec, store, runtime); tables used by the mixer

@@ -36,7 +36,7 @@ class GatedMLP:
         gu = self.gate_up.forward(h)
         act = self.runtime.empty(h.shape[0], self.inner)
         ops.silu_gate(gu, act)
-        return self.down.forward(act)
+        return self.down.forward(act, partials_ok=True)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

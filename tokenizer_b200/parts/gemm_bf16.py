@@ -9,13 +9,37 @@ import torch
 
 from ..kernels import ops
 
+# blocks wanted in flight before a product with few weight rows is also cut along k
+_TARGET_BLOCKS = 296
+
+
+def choose_k_splits(M: int, N: int, K: int) -> int:
+    """How many pieces along k a small-M product is cut into (1: none)."""
+    tiles = (N + 15) // 16
+    blocks = (tiles + 1) // 2 if tiles >= 1024 else tiles
+    if blocks >= _TARGET_BLOCKS // 2:
+        return 1
+    return max(1, min(-(-_TARGET_BLOCKS // blocks), K // 256, 16))
+
 
 def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
-    """out[M,N] = a[M,K] weight[N,K]^T (+ bias float32); out is bfloat16 or float32."""
-    if out.dtype == torch.bfloat16:
-        torch.mm(a, weight.t(), out=out)
+                out_dtype: torch.dtype, partials_ok: bool = False) -> torch.Tensor:
+    """a[M,K] weight[N,K]^T (+ bias float32) as bfloat16 or float32 [M,N]; with
+    `partials_ok` the result may be float32 partial sums [S,M,N] instead."""
+    M, K = a.shape
+    N = weight.shape[0]
+    if ops.linear_small_m_supported(M, K):
+        splits = choose_k_splits(M, N, K) if (partials_ok and bias is None) else 1
+        if splits > 1:
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+        else:
+            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        ops.linear_small_m(a, weight, bias, out, splits)
+        return out
+    if out_dtype == torch.bfloat16:
+        out = torch.mm(a, weight.t())
     else:
-        out.copy_(torch.mm(a, weight.t(), out_dtype=torch.float32))
+        out = torch.mm(a, weight.t(), out_dtype=torch.float32)
     if bias is not None:
         out.add_(bias.to(out.dtype) if out.dtype != torch.float32 else bias)
+    return out
