@@ -1,0 +1,272 @@
+// Attention for portions of prompts: many rows of one request at once, over the
+// paged cache (bfloat16, tensor cores, 32-bit softmax).
+//
+// The rows of a step are cut on the host into tiles of up to 64 consecutive rows
+// of one request.  A block takes one (tile, query head): its four warps hold 16
+// rows each, walk the request's keys in blocks of 64 from the first key any row of
+// the tile can see to the tile's last position, and keep a running maximum, sum
+// and weighted value per row (the flash-attention recurrence).  Keys and values
+// are gathered from their pages into shared memory with 16-byte asynchronous
+// copies (two stages: the next block loads while this one is multiplied), so any
+// page size works.  q k^T and p v run on mma.sync m16n8k16 with fragments read by
+// ldmatrix from rows padded by 16 bytes (conflict-free for every head size that
+// is a multiple of 16).  A row's arithmetic depends on its position, its window
+// and its place in its 64-row tile only.
+//
+// HEAD_DIM is a compile-time size (multiple of 16, at most 128), -DHEAD_DIM=...
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head size");
+
+#define PF_ROWS 64          // rows of a tile (4 warps x 16)
+#define PF_KEYS 64          // keys of a block
+#define PF_THREADS 128
+constexpr int kStride = HEAD_DIM + 8;          // elements between rows in shared memory
+constexpr int kChunks = HEAD_DIM / 8;          // 16-byte pieces of a row
+constexpr int kTile = PF_KEYS * kStride;       // elements of one staged tile
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool ok) {
+  const int bytes = ok ? 16 : 0;   // 0: the 16 bytes are filled with zeros, src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src),
+               "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Stage the keys (or values) key0 .. key0 + 63 of one kv head; keys outside
+// [first_ok, last_ok] are zero-filled and their pages are not touched.
+__device__ __forceinline__ void stage_tile(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pool,
+                                           const int* __restrict__ table, int page, int nkv, int kvh,
+                                           int key0, int first_ok, int last_ok) {
+  for (int i = threadIdx.x; i < PF_KEYS * kChunks; i += PF_THREADS) {
+    const int j = i / kChunks, c = i % kChunks;
+    const int key = key0 + j;
+    const bool ok = key >= first_ok && key <= last_ok;
+    const __nv_bfloat16* src = pool;
+    if (ok) {
+      const int slot = table[key / page] * page + key % page;
+      src = pool + ((size_t)slot * nkv + kvh) * HEAD_DIM + c * 8;
+    }
+    cp_async16(dst + j * kStride + c * 8, src, ok);
+  }
+}
+
+__global__ void __launch_bounds__(PF_THREADS)
+prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
+                         const int* __restrict__ block_table, int table_stride,
+                         const int* __restrict__ row_req, const int* __restrict__ pos,
+                         const int* __restrict__ tiles, int nh, int nkv, int page, int window,
+                         float scale_log2) {
+  extern __shared__ __align__(16) __nv_bfloat16 smem[];
+  __nv_bfloat16* q_s = smem;                       // [64][kStride]
+  __nv_bfloat16* k_s = q_s + kTile;                // 2 stages
+  __nv_bfloat16* v_s = k_s + 2 * kTile;            // 2 stages
+
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int row0 = tiles[2 * tile], n_rows = tiles[2 * tile + 1];
+  const int r = row_req[row0];
+  if (r < 0 || n_rows <= 0) return;
+  const int kvh = h / (nh / nkv);
+  const int pos0 = pos[row0];
+  const int pos_last = pos0 + n_rows - 1;
+  const int lo_first = (window >= 0 && pos0 - window > 0) ? pos0 - window : 0;  // first key any row sees
+  const int* table = block_table + (size_t)r * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- stage q and the first key/value block ----
+  for (int i = threadIdx.x; i < PF_ROWS * kChunks; i += PF_THREADS) {
+    const int j = i / kChunks, c = i % kChunks;
+    const bool ok = j < n_rows;
+    const __nv_bfloat16* src = ok ? q + ((size_t)(row0 + j) * nh + h) * HEAD_DIM + c * 8 : q;
+    cp_async16(q_s + j * kStride + c * 8, src, ok);
+  }
+  const int kb_first = lo_first / PF_KEYS * PF_KEYS;
+  const int n_blocks = (pos_last - kb_first) / PF_KEYS + 1;
+  stage_tile(k_s, k_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
+  stage_tile(v_s, v_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
+  cp_async_commit();
+
+  // per thread: rows g and g + 8 of the warp's 16
+  const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
+  int p_row[2], lo_row[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    p_row[i] = pos0 + min(my_row[i], n_rows - 1);       // rows past the tile repeat its last row
+    lo_row[i] = (window >= 0 && p_row[i] - window > 0) ? p_row[i] - window : 0;
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HEAD_DIM / 8][4];
+#pragma unroll
+  for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  unsigned q_frag[HEAD_DIM / 16][4];
+
+  for (int b = 0; b < n_blocks; ++b) {
+    const int kb = kb_first + b * PF_KEYS;
+    const int stage = b & 1;
+    if (b + 1 < n_blocks) {
+      stage_tile(k_s + (stage ^ 1) * kTile, k_pool, table, page, nkv, kvh, kb + PF_KEYS, lo_first, pos_last);
+      stage_tile(v_s + (stage ^ 1) * kTile, v_pool, table, page, nkv, kvh, kb + PF_KEYS, lo_first, pos_last);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (b == 0) {
+#pragma unroll
+      for (int ks = 0; ks < HEAD_DIM / 16; ++ks)
+        ldmatrix_x4(q_frag[ks], q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kStride +
+                                    ks * 16 + (lane >> 4) * 8);
+    }
+    const __nv_bfloat16* kt = k_s + stage * kTile;
+    const __nv_bfloat16* vt = v_s + stage * kTile;
+
+    // ---- scores s[16 x 64] = q k^T ----
+    float s[PF_KEYS / 8][4];
+#pragma unroll
+    for (int i = 0; i < PF_KEYS / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+#pragma unroll
+      for (int np = 0; np < PF_KEYS / 16; ++np) {
+        unsigned kf[4];
+        ldmatrix_x4(kf, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * kStride + ks * 16 +
+                            ((lane >> 3) & 1) * 8);
+        mma16816(s[2 * np], q_frag[ks], kf[0], kf[1]);
+        mma16816(s[2 * np + 1], q_frag[ks], kf[2], kf[3]);
+      }
+    }
+    // ---- scale, mask, running softmax (rows g and g + 8) ----
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int key = kb + nt * 8 + 2 * t + (e & 1);
+        const bool seen = key <= p_row[i] && key >= lo_row[i];
+        s[nt][e] = seen ? s[nt][e] * scale_log2 : -INFINITY;
+        m_new[i] = fmaxf(m_new[i], s[nt][e]);
+      }
+    }
+    float corr[2], m_use[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+      m_use[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing seen yet: keep exp() finite
+      corr[i] = exp2f(m_run[i] - m_use[i]);                   // exp2(-inf) = 0
+      m_run[i] = m_new[i];
+    }
+#pragma unroll
+    for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pe = exp2f(s[nt][e] - m_use[e >> 1]);
+        s[nt][e] = pe;
+        sum[e >> 1] += pe;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      l_run[i] = l_run[i] * corr[i] + sum[i];
+    }
+#pragma unroll
+    for (int i = 0; i < HEAD_DIM / 8; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // ---- o += p v ----
+#pragma unroll
+    for (int ks = 0; ks < PF_KEYS / 16; ++ks) {
+      unsigned pf[4];
+      pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+      pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+      pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HEAD_DIM / 16; ++dp) {
+        unsigned vf[4];
+        ldmatrix_x4_trans(vf, vt + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kStride +
+                                  dp * 16 + (lane >> 4) * 8);
+        mma16816(o[2 * dp], pf, vf[0], vf[1]);
+        mma16816(o[2 * dp + 1], pf, vf[2], vf[3]);
+      }
+    }
+    __syncthreads();   // this stage is overwritten by the load issued in the next iteration
+  }
+
+  // ---- write the rows that exist ----
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (my_row[i] >= n_rows) continue;
+    const float inv = 1.0f / l_run[i];
+    __nv_bfloat16* dst = out + ((size_t)(row0 + my_row[i]) * nh + h) * HEAD_DIM;
+#pragma unroll
+    for (int nt = 0; nt < HEAD_DIM / 8; ++nt) {
+      *reinterpret_cast<unsigned*>(dst + nt * 8 + 2 * t) =
+          pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+    }
+  }
+}
+
+TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
+
+// tiles: [n_tiles][2] = (first row, rows) of consecutive rows of one request, rows <= 64
+TOKB200_API int tokb200_prefill_attention(
+    const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
+    int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
+    int nkv, int d, int page, int window, float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return TOKB200_OK;
+  if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || nh > 65535)
+    return TOKB200_BAD_SIZE;
+  if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
+    return TOKB200_BAD_ALIGNMENT;
+  const size_t smem = (size_t)5 * kTile * sizeof(__nv_bfloat16);
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+  if (!configured[device]) {   // the larger shared memory is granted per device
+    cudaError_t err = cudaFuncSetAttribute(prefill_attention_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    configured[device] = true;
+  }
+  dim3 grid(n_tiles, nh);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+      (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, nh, nkv, page, window,
+      scale_log2);
+  return tokb200_launch_status();
+}

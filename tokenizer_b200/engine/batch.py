@@ -28,6 +28,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+Q_TILE_ROWS = 64   # rows of one request that the prompt-attention kernel takes per block
+
+
 def _round4(n: int) -> int:
     return (n + 3) // 4 * 4
 
@@ -47,6 +50,8 @@ class BatchLayout:
     kv_len: int = 0
     state_slot: int = 0
     want: int = 0
+    tiles: int = 0
+    max_tiles: int = 0
     slots: Optional[List[int]] = None
     tables: Optional[List[int]] = None
     total: int = 0
@@ -65,6 +70,8 @@ class BatchLayout:
         lay.ids, lay.pos, lay.row_req = take(T), take(T), take(T)
         lay.q_start, lay.kv_len, lay.state_slot = take(R + 1), take(R), take(R)
         lay.want = take(W)
+        lay.max_tiles = T // Q_TILE_ROWS + R
+        lay.tiles = take(2 * lay.max_tiles)
         lay.slots = [take(T) for _ in table_widths]
         lay.tables = [take(R * w) for w in table_widths]
         lay.total = at
@@ -152,6 +159,7 @@ class BatchBuilder:
         q_lens, kv_lens, state_slots = [], [], []
         row = 0
         want_at = 0
+        n_tiles = 0
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = e.cache.length
@@ -165,6 +173,10 @@ class BatchBuilder:
             for w in e.want:
                 buf[lay.want + want_at] = row + int(w)
                 want_at += 1
+            for first in range(0, n, Q_TILE_ROWS):
+                buf[lay.tiles + 2 * n_tiles] = row + first
+                buf[lay.tiles + 2 * n_tiles + 1] = min(Q_TILE_ROWS, n - first)
+                n_tiles += 1
             for g in range(len(widths)):
                 table = np.asarray(e.cache.tables[g], dtype=np.int32)
                 buf[lay.tables[g] + r * widths[g]:lay.tables[g] + r * widths[g] + len(table)] = table
@@ -191,5 +203,6 @@ class BatchBuilder:
             n_tokens=Tc, n_requests=Rc, ids=view(lay.ids, Tc), pos=view(lay.pos, Tc),
             row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
             kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
-            q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots)
+            q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots,
+            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=n_tiles)
         return ctx, view(lay.want, Wc), W

@@ -258,3 +258,26 @@ def linear_small_m(x, w, bias, out, k_splits: int = 1) -> None:
     _check(_lib("linear_small_m").tokb200_linear_small_m(
         _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
         _i(M), _i(N), _i(K), _i(k_splits), _stream()), "linear_small_m")
+
+
+PREFILL_TILE_ROWS = 64
+
+
+def prefill_attention_supported(nh: int, nkv: int, d: int) -> bool:
+    return d % 16 == 0 and 16 <= d <= 128 and nh % nkv == 0
+
+
+def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv,
+                      d, page, window, scale) -> None:
+    """Attention for portions of prompts (bfloat16).  `tiles` is int32 [n, 2]:
+    (first row, rows <= 64) of consecutive rows of one request."""
+    if q.dtype != torch.bfloat16:
+        raise ValueError("prefill_attention is the bfloat16 kernel")
+    if not prefill_attention_supported(nh, nkv, d):
+        raise ValueError(f"prefill_attention: {nh} heads over {nkv} groups of size {d} is not taken")
+    lib = load_library("attention_prefill.cu", defines=(f"HEAD_DIM={d}",))
+    _check(lib.tokb200_prefill_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
+        _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
+        "prefill_attention")

@@ -99,6 +99,13 @@ class GQAttention:
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
             return
+        if q.dtype == torch.bfloat16 and ctx.q_tiles is not None and \
+                ops.prefill_attention_supported(self.nh, self.nkv, self.d):
+            ops.prefill_attention(
+                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                ctx.q_tiles, ctx.n_q_tiles, self.nh, self.nkv, self.d, group.page_size,
+                self.window, self.scale)
+            return
         ops.paged_attention_generic(
             q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
             self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)

@@ -129,6 +129,10 @@ class StepContext:
     kv_len: torch.Tensor         # [R] int32, tokens held after this step
     state_slot: torch.Tensor     # [R] int32
     groups: List[GroupView]
+    # the rows cut into tiles of up to 64 consecutive rows of one request:
+    # int32 [n_q_tiles, 2] = (first row, rows); None when the builder made none
+    q_tiles: Optional[torch.Tensor] = None
+    n_q_tiles: int = 0
     # host copies, for choosing kernels and for mixers that loop over requests
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)
