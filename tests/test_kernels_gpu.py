@@ -411,3 +411,70 @@ def test_norm_adds_partial_sums():
     x2 = x.clone()
     ops().residual_add(x2, parts)
     assert torch.allclose(x2, want_x, atol=1e-6)
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 32, 24), (14, 2, 64, 16, None),
+    (6, 3, 112, 4, 7), (4, 1, 128, 16, None), (2, 2, 64, 16, 100)])
+def test_prefill_attention_tiles(nh, nkv, d, page, window):
+    """The tensor-core kernel for portions of prompts: portions that start at 0 and
+    in the middle of a page, of 1, 2, 63, 64, 65 and 200 rows, beside single rows."""
+    dtype = torch.bfloat16
+    lengths = [1, 2, 70, 64, 129, 333, 520]
+    starts = [0, 0, 7, 0, 64, 133, 519]          # the portion is start .. length - 1
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=51)
+    row_req, pos, tiles = [], [], []
+    for r, (n, s0) in enumerate(zip(lengths, starts)):
+        first = len(pos)
+        for p in range(s0, n):
+            row_req.append(r)
+            pos.append(p)
+        for off in range(0, n - s0, 64):
+            tiles.append([first + off, min(64, n - s0 - off)])
+    q = rnd(len(pos), nh, d, seed=52, dtype=dtype)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(d)
+    tiles_t = torch.tensor(tiles + [[0, 0]], dtype=torch.int32, device=DEV)
+    ops().prefill_attention(
+        q.view(len(pos), nh * d), k_pool, v_pool, out.view(len(pos), nh * d), tables,
+        torch.tensor(row_req, dtype=torch.int32, device=DEV),
+        torch.tensor(pos, dtype=torch.int32, device=DEV), tiles_t, len(tiles), nh, nkv, d, page,
+        window, scale)
+    want = attention_reference(q.float().cpu(), dense, row_req, pos, nh, nkv, window, scale)
+    assert torch.isfinite(out.float()).all()
+    got = out.float().cpu()
+    # probabilities are rounded to bfloat16 before they meet the values (2^-9 relative
+    # per term), on top of the output's own rounding
+    err = (got - want).abs()
+    bound = 6e-3 + 2 ** -7 * want.abs()
+    bad = (err > bound).nonzero()
+    assert bad.numel() == 0, (
+        f"first wrong row {int(bad[0][0])} (request {row_req[int(bad[0][0])]}, "
+        f"position {pos[int(bad[0][0])]}): {float(err.max())}")
+
+
+def test_prefill_attention_far_key_and_window_edge():
+    nh, nkv, d, page, n = 2, 1, 64, 16, 400
+    dtype = torch.bfloat16
+    k_pool, v_pool, tables, dense = paged_setup([n], nh, nkv, d, page, dtype, seed=53)
+    rows = 70                                   # positions 330 .. 399 in one portion
+    q = rnd(rows, nh, d, seed=54, dtype=dtype)
+    scale = 1.0 / math.sqrt(d)
+    tiles = torch.tensor([[0, 64], [64, 6]], dtype=torch.int32, device=DEV)
+    pos = list(range(n - rows, n))
+    for far in (0, 63, 64, 200, 399 - 30, 399 - 31, 335):
+        k, v = dense[0][0].clone(), dense[0][1]
+        k[far, 0] = (q[rows - 1, 0].float().cpu() * 40.0).to(dtype).float()   # for the last row, head 0
+        k_pool2 = k_pool.clone()
+        k_pool2[int(tables[0, far // page]) * page + far % page, 0] = k[far, 0].to(dtype).to(DEV)
+        for window in (None, 30):
+            out = torch.empty(rows, nh * d, dtype=dtype, device=DEV)
+            ops().prefill_attention(q.view(rows, nh * d), k_pool2, v_pool, out, tables,
+                                    torch.zeros(rows, dtype=torch.int32, device=DEV),
+                                    torch.tensor(pos, dtype=torch.int32, device=DEV), tiles, 2,
+                                    nh, nkv, d, page, window, scale)
+            got = out.view(rows, nh, d)[rows - 1, 0].float().cpu()
+            if window is None or far + window >= n - 1:
+                assert float((got - v[far, 0]).abs().max()) < 0.03
+            else:
+                assert float((got - v[far, 0]).abs().max()) > 0.1

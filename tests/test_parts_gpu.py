@@ -178,4 +178,4 @@ def test_order_is_data_a_layer_twice_and_a_shared_cache(dtype, tmp_path):
     bound = 1e-4 if dtype == torch.float32 else 2e-2 * scale
     assert float((got - want).abs().max()) <= bound
     # and it is not the plain order: the result differs from running the layers once
-    assert float((plain.all_logits(cfg, w, ids) - want).abs().max()) > 0.1 * scale
+    assert float((plain.all_logits(cfg, w, ids) - want).abs().max()) > 0.02 * scale

@@ -25,6 +25,35 @@ static inline int tokb200_launch_status() {
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// The step's kernels are launched with the attribute below: a kernel may start
+// while its predecessor in the stream still runs, so that its launch and its
+// reads of weights (which no kernel of the step writes) overlap the
+// predecessor's tail.  `pdl_wait()` returns once the predecessor has completed
+// and its writes are visible; every kernel calls it before it touches anything
+// a predecessor wrote and before it writes anything a predecessor may read, and
+// every block calls it before it exits, so completion stays transitive along the
+// stream.  `pdl_launch()` lets the successor start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+static inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_float(float v);

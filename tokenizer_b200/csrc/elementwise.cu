@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ x, int hidden, int vocab) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read outside
@@ -24,13 +26,12 @@ TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype
                               int n_tokens, int hidden, int vocab, cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;
   if (table_dtype == TOKB200_F32)
-    embed_kernel<float><<<n_tokens, 256, 0, stream>>>(ids, (const float*)table, x, hidden, vocab);
-  else if (table_dtype == TOKB200_BF16)
-    embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x,
-                                                             hidden, vocab);
-  else
-    return TOKB200_BAD_DTYPE;
-  return tokb200_launch_status();
+    return launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, ids,
+                            (const float*)table, x, hidden, vocab);
+  if (table_dtype == TOKB200_BF16)
+    return launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, ids,
+                            (const __nv_bfloat16*)table, x, hidden, vocab);
+  return TOKB200_BAD_DTYPE;
 }
 
 // ----------------------------------------------------------------------------
@@ -39,31 +40,76 @@ TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype
 // One block per row.  `rows` optionally names the rows to read (a gather of the
 // wanted rows before the final norm); y is then dense [n_rows, hidden].
 // ----------------------------------------------------------------------------
+// Each thread keeps its elements in registers between the two passes (up to
+// RMS_MAX_PER_THREAD of them; wider rows fall back to re-reading), and all loads
+// of a pass are issued before the first use, so a row costs one round trip to
+// memory, not one per element.
+#define RMS_MAX_PER_THREAD 8
+
 template <typename TD, typename TO>
 __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                 const float* __restrict__ gain, TO* __restrict__ y,
                                 const int* __restrict__ rows, int hidden, float eps,
                                 int n_partials, size_t partial_stride) {
   __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* xr = x + (size_t)src * hidden;
   const TD* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  TO* yr = y + (size_t)r * hidden;
+  const bool in_registers = hidden <= RMS_MAX_PER_THREAD * (int)blockDim.x;
+  float v[RMS_MAX_PER_THREAD];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
+  if (in_registers) {
+#pragma unroll
+    for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
+      const int i = threadIdx.x + e * blockDim.x;
+      v[e] = i < hidden ? xr[i] : 0.f;
+    }
     if (dr) {
       // the pending residual may come as partial sums of a product cut along k
-      for (int s = 0; s < n_partials; ++s) v += to_float(dr[(size_t)s * partial_stride + i]);
-      xr[i] = v;
+      for (int s = 0; s < n_partials; ++s) {
+        float d[RMS_MAX_PER_THREAD];
+#pragma unroll
+        for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
+          const int i = threadIdx.x + e * blockDim.x;
+          d[e] = i < hidden ? to_float(dr[(size_t)s * partial_stride + i]) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) v[e] += d[e];
+      }
+#pragma unroll
+      for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
+        const int i = threadIdx.x + e * blockDim.x;
+        if (i < hidden) xr[i] = v[e];
+      }
     }
-    ss += v * v;
+#pragma unroll
+    for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) ss += v[e] * v[e];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float a = xr[i];
+      if (dr) {
+        for (int s = 0; s < n_partials; ++s) a += to_float(dr[(size_t)s * partial_stride + i]);
+        xr[i] = a;
+      }
+      ss += a * a;
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
-  TO* yr = y + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    yr[i] = from_float<TO>(xr[i] * inv * gain[i]);
+  if (in_registers) {
+#pragma unroll
+    for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
+      const int i = threadIdx.x + e * blockDim.x;
+      if (i < hidden) yr[i] = from_float<TO>(v[e] * inv * gain[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      yr[i] = from_float<TO>(xr[i] * inv * gain[i]);
+  }
 }
 
 TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, int n_partials,
@@ -72,22 +118,26 @@ TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, i
                                  cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (hidden <= 0 || n_partials < 1) return TOKB200_BAD_SIZE;
-  const int threads = hidden >= 1024 ? 256 : 128;
-#define LAUNCH(TD, TO) \
-  rms_norm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(x, (const TD*)delta, gain, (TO*)y, rows, hidden, eps, n_partials, (size_t)partial_stride)
+  int threads = 128;   // rows of up to 8 elements a thread stay in registers
+  while (threads < 1024 && hidden > threads * 4) threads *= 2;
+#define LAUNCH(TD, TO)                                                                        \
+  return launch_dependent(rms_norm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, x, \
+                          (const TD*)delta, gain, (TO*)y, rows, hidden, eps, n_partials,     \
+                          (size_t)partial_stride)
   if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_F32) LAUNCH(float, float);
-  else if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
-  else if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
-  else if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-  else return TOKB200_BAD_DTYPE;
+  if (delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+  if (delta_dtype == TOKB200_BF16 && y_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
-  return tokb200_launch_status();
+  return TOKB200_BAD_DTYPE;
 }
 
 // x += delta, elementwise (a pending residual that no norm follows)
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n,
                                     int n_partials) {
+  pdl_wait();
+  pdl_launch();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
@@ -149,6 +199,8 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, const float* __rest
                                   T* __restrict__ q_out, T* __restrict__ k_pool,
                                   T* __restrict__ v_pool, int nh, int nkv, int d, int rotary,
                                   int table_half) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int p = pos[t];
   const int s = slot ? slot[t] : -1;
@@ -203,16 +255,15 @@ TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int
   const int items = (nh + 2 * nkv) * (d / 2);
   int threads = items < 256 ? ((items + 31) / 32) * 32 : 256;
   if (dtype == TOKB200_F32)
-    rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
-        (const float*)qkv, bias, pos, slot, cos_t, sin_t, (float*)q_out, (float*)k_pool,
-        (float*)v_pool, nh, nkv, d, rotary, rotary / 2);
-  else if (dtype == TOKB200_BF16)
-    rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, bias, pos, slot, cos_t, sin_t, (__nv_bfloat16*)q_out,
-        (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d, rotary, rotary / 2);
-  else
-    return TOKB200_BAD_DTYPE;
-  return tokb200_launch_status();
+    return launch_dependent(rope_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream,
+                            (const float*)qkv, bias, pos, slot, cos_t, sin_t, (float*)q_out,
+                            (float*)k_pool, (float*)v_pool, nh, nkv, d, rotary, rotary / 2);
+  if (dtype == TOKB200_BF16)
+    return launch_dependent(rope_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0,
+                            stream, (const __nv_bfloat16*)qkv, bias, pos, slot, cos_t, sin_t,
+                            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                            nh, nkv, d, rotary, rotary / 2);
+  return TOKB200_BAD_DTYPE;
 }
 
 // ----------------------------------------------------------------------------
@@ -221,6 +272,8 @@ TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int
 // ----------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.y;
   const T* row = gu + (size_t)t * 2 * inner;
   T* orow = out + (size_t)t * inner;
@@ -238,17 +291,20 @@ TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_to
   for (int row0 = 0; row0 < n_tokens; row0 += 65535) {
     const int rows = n_tokens - row0 < 65535 ? n_tokens - row0 : 65535;
     dim3 grid((inner + 255) / 256 < 64 ? (inner + 255) / 256 : 64, rows);
+    int status;
     if (dtype == TOKB200_F32)
-      silu_gate_kernel<float><<<grid, 256, 0, stream>>>(
-          (const float*)gu + (size_t)row0 * 2 * inner, (float*)out + (size_t)row0 * inner, inner);
+      status = launch_dependent(silu_gate_kernel<float>, grid, dim3(256), 0, stream,
+                                (const float*)gu + (size_t)row0 * 2 * inner,
+                                (float*)out + (size_t)row0 * inner, inner);
     else if (dtype == TOKB200_BF16)
-      silu_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-          (const __nv_bfloat16*)gu + (size_t)row0 * 2 * inner,
-          (__nv_bfloat16*)out + (size_t)row0 * inner, inner);
+      status = launch_dependent(silu_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream,
+                                (const __nv_bfloat16*)gu + (size_t)row0 * 2 * inner,
+                                (__nv_bfloat16*)out + (size_t)row0 * inner, inner);
     else
       return TOKB200_BAD_DTYPE;
+    if (status != TOKB200_OK) return status;
   }
-  return tokb200_launch_status();
+  return TOKB200_OK;
 }
 
 // ----------------------------------------------------------------------------
@@ -270,6 +326,8 @@ __global__ void advance_decode_kernel(int* __restrict__ ids, const int* __restri
                                       const int* __restrict__ row_req, AdvanceGroups groups,
                                       int page, int n_rows, int* __restrict__ history,
                                       int* __restrict__ step_counter) {
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;
   if (r < n_rows && row_req[r] >= 0) {
@@ -286,7 +344,11 @@ __global__ void advance_decode_kernel(int* __restrict__ ids, const int* __restri
   }
 }
 
-__global__ void bump_counter_kernel(int* counter) { *counter += 1; }
+__global__ void bump_counter_kernel(int* counter) {
+  pdl_wait();
+  pdl_launch();
+  *counter += 1;
+}
 
 TOKB200_API int tokb200_advance_decode(int* ids, const int* drawn, int* pos, int* kv_len,
                                        const int* row_req, int n_groups, int** slots,
@@ -302,8 +364,9 @@ TOKB200_API int tokb200_advance_decode(int* ids, const int* drawn, int* pos, int
     groups.tables[g] = tables[g];
     groups.widths[g] = widths[g];
   }
-  advance_decode_kernel<<<(n_rows + 127) / 128, 128, 0, stream>>>(
-      ids, drawn, pos, kv_len, row_req, groups, page, n_rows, history, step_counter);
-  bump_counter_kernel<<<1, 1, 0, stream>>>(step_counter);
-  return tokb200_launch_status();
+  int status = launch_dependent(advance_decode_kernel, dim3((n_rows + 127) / 128), dim3(128), 0,
+                                stream, ids, drawn, pos, kv_len, row_req, groups, page, n_rows,
+                                history, step_counter);
+  if (status != TOKB200_OK) return status;
+  return launch_dependent(bump_counter_kernel, dim3(1), dim3(1), 0, stream, step_counter);
 }

@@ -18,6 +18,7 @@
 
 #define LSM_WARPS 8
 #define LSM_THREADS (LSM_WARPS * 32)
+#define LSM_PRE 4            // steps of weights in flight per thread
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
                                                unsigned a3, unsigned b0, unsigned b1) {
@@ -59,17 +60,40 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   const __nv_bfloat16* wa = w + (size_t)(row0 + g) * K + 8 * t;
   const __nv_bfloat16* wb = w + (size_t)(row0 + g + 8) * K + 8 * t;
 
-#pragma unroll 4
-  for (int k = k_begin + member * 32; k < k_end; k += TEAM * 32) {
-    const bool k_ok = k + 8 * t + 8 <= k_end;
-    const uint4 a = load16(wa + k, row_a_ok && k_ok);
-    const uint4 b = load16(wb + k, row_b_ok && k_ok);
+  // A ring of LSM_PRE steps of weights is requested before the wait on the
+  // predecessor (weights are written by no kernel of the step); x, which the
+  // predecessor produced, is read after it.
+  constexpr int step = TEAM * 32;
+  const int k_first = k_begin + member * 32;
+  uint4 a_ring[LSM_PRE], b_ring[LSM_PRE];
 #pragma unroll
-    for (int j = 0; j < MT; ++j) {
-      const int m = 8 * j + g;
-      const uint4 xv = load16(x + (size_t)m * K + k + 8 * t, m < M && k_ok);
-      mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
-      mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+  for (int i = 0; i < LSM_PRE; ++i) {
+    const int kk = k_first + i * step;
+    const bool k_ok = kk + 8 * t + 8 <= k_end;
+    a_ring[i] = load16(wa + kk, row_a_ok && k_ok);
+    b_ring[i] = load16(wb + kk, row_b_ok && k_ok);
+  }
+  pdl_wait();
+  pdl_launch();
+  for (int k = k_first; k < k_end; k += LSM_PRE * step) {
+#pragma unroll
+    for (int i = 0; i < LSM_PRE; ++i) {
+      const int kk = k + i * step;
+      const uint4 a = a_ring[i], b = b_ring[i];
+      const int kn = kk + LSM_PRE * step;
+      const bool next_ok = kn + 8 * t + 8 <= k_end;
+      a_ring[i] = load16(wa + kn, row_a_ok && next_ok);
+      b_ring[i] = load16(wb + kn, row_b_ok && next_ok);
+      const bool k_ok = kk + 8 * t + 8 <= k_end;
+      if (kk < k_end) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          const int m = 8 * j + g;
+          const uint4 xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
+          mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
+          mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+        }
+      }
     }
   }
 
@@ -113,14 +137,14 @@ static int launch_small_m(const void* x, const void* w, const float* bias, void*
   // many row tiles: two per block (teams of 4 warps); few: one per block (8 warps on its k)
   if (tiles >= 1024) {
     dim3 grid((tiles + 1) / 2, k_splits);
-    linear_small_m_kernel<MT, 2><<<grid, LSM_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32, M, N, K, k_per_split);
-  } else {
-    dim3 grid(tiles, k_splits);
-    linear_small_m_kernel<MT, 1><<<grid, LSM_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32, M, N, K, k_per_split);
+    return launch_dependent(linear_small_m_kernel<MT, 2>, grid, dim3(LSM_THREADS), 0, stream,
+                            (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
+                            M, N, K, k_per_split);
   }
-  return tokb200_launch_status();
+  dim3 grid(tiles, k_splits);
+  return launch_dependent(linear_small_m_kernel<MT, 1>, grid, dim3(LSM_THREADS), 0, stream,
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
+                          M, N, K, k_per_split);
 }
 
 // out: [M, N] bfloat16 or float32 when k_splits == 1 (bias added); float32

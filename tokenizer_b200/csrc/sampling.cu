@@ -78,6 +78,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   __shared__ float scratch[33];
   __shared__ BestPair pair_scratch[33];
   __shared__ int count_scratch[SAMPLE_THREADS];
+  pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -175,7 +177,6 @@ TOKB200_API int tokb200_sample(const float* logits, int n_rows, int vocab,
                                const float* uniform, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (vocab <= 0) return TOKB200_BAD_SIZE;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_p, uniform,
-                                                      out);
-  return tokb200_launch_status();
+  return launch_dependent(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits,
+                          vocab, temperature, top_p, uniform, out);
 }
