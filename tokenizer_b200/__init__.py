@@ -1,6 +1,7 @@
 """tokenizer_b200: a small, whole inference engine for one GPU (NVIDIA B200,
 sm_100a): from a model folder (config.json, model.safetensors) to the next
 token.  See `generate` for the entry point."""
+from . import config
 from .config import ConfigError, Qwen2Config, load_config, register_architecture
 from .weights import WeightError, write_random_model
 

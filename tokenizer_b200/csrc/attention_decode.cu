@@ -29,9 +29,16 @@
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 
-// value lanes owned by one lane of a warp in the weighted sum
-constexpr int kOwn = HEAD_DIM >= 64 ? HEAD_DIM / 32 : 2;
+// value lanes owned by one lane of a warp in the weighted sum: the smallest even
+// count that divides the head size and leaves at most 32 owners
+constexpr int own_lanes(int d) {
+  for (int n = 2; n <= 8; n += 2)
+    if (d % n == 0 && d / n <= 32) return n;
+  return 8;
+}
+constexpr int kOwn = own_lanes(HEAD_DIM);
 constexpr int kOwners = HEAD_DIM / kOwn;             // lanes that own value lanes (<= 32)
+static_assert(kOwn % 2 == 0 && HEAD_DIM % kOwn == 0 && kOwners <= 32, "value lanes per lane");
 
 struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
 

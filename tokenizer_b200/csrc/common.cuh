@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TOKB200_API extern "C" __attribute__((visibility("default")))
 
@@ -45,9 +46,14 @@ static inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 blo
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
+  // TOKB200_PDL=0 in the environment launches every kernel strictly after its predecessor
+  static const int overlap = [] {
+    const char* v = getenv("TOKB200_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
   cudaLaunchAttribute attribute[1];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  attribute[0].val.programmaticStreamSerializationAllowed = overlap;
   config.attrs = attribute;
   config.numAttrs = 1;
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
