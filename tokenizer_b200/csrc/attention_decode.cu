@@ -1,18 +1,21 @@
 // Attention for rows that read far more keys than they bring: decoding.
 //
-// One block works on (a row, one kv head, one split of that row's keys) and
-// serves all query heads of the kv head at once, so keys and values are read
-// once per group.  A row's visible keys lo..pos are cut into n_splits pieces of
-// `chunk` keys; chunk is 128 * 2^k, the smallest that needs at most MAX_SPLITS
-// pieces, so the cut is a function of the row's own position and window and does
-// not change with the batch around it.  Inside a block every warp walks its own
-// keys, 32 at a time (a lane per key for the scores, a lane per pair of value
-// lanes for the weighted sum), with its own running maximum and sum and without
-// block-wide barriers; the warps are merged once at the end.  A step is bound by
-// latency, not by arithmetic, so loads are issued in batches before their first
-// use.  Pieces of several blocks meet in scratch memory; the block that finishes
-// last for a (row, kv head) merges them in index order and writes the output.
-// Scores, maxima, sums and the weighted values are 32-bit.
+// A decoding step is bound by latency, not by arithmetic or bytes: few rows, a few
+// hundred keys each.  So the work is spread over as many short, independent warps
+// as possible.  One block works on (a row, one kv head, one split of that row's
+// keys); each of its warps takes ONE query head of the kv head's group, so the
+// keys and values of the split are fetched from L2 once and met again in L1 by the
+// other warps.  A warp walks its keys 32 at a time: a lane per key for the scores
+// (q is read from shared memory, broadcast), a lane per few value lanes for the
+// weighted sum, its own running maximum and sum, no block-wide barrier.
+//
+// A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk
+// is 32 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
+// function of the row's own position and window and does not change with the
+// batch around it.  Pieces meet in scratch memory (max, sum, weighted values per
+// (row, head, split)); the block that finishes last for a (row, kv head) merges
+// them in index order and writes the output.  Everything but q, k, v and the
+// output is 32-bit.
 //
 // HEAD_DIM is a compile-time size (a multiple of 16, at most 256), given with
 // -DHEAD_DIM=...; the library is built per head size at first use.
@@ -21,11 +24,9 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
 #endif
-#define DEC_WARPS 4
-#define DEC_THREADS (DEC_WARPS * 32)
-#define DEC_MAX_GROUP 8        // query heads per kv head served by one pass
+#define DEC_MAX_GROUP 8        // query heads per kv head: one warp each
 #define DEC_MAX_SPLITS 32
-#define DEC_BLOCK_KEYS (DEC_WARPS * 32)
+#define DEC_TILE 32            // keys a warp takes per pass
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 
@@ -43,12 +44,12 @@ static_assert(kOwn % 2 == 0 && HEAD_DIM % kOwn == 0 && kOwners <= 32, "value lan
 struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
 
 __device__ __forceinline__ int split_chunk(int n_keys) {
-  int chunk = DEC_BLOCK_KEYS;
+  int chunk = DEC_TILE;
   while ((n_keys + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
   return chunk;
 }
 
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_MAX_GROUP * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ block_table, int table_stride,
@@ -66,33 +67,27 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int chunk = split_chunk(n_keys);
   const int n_splits = (n_keys + chunk - 1) / chunk;
   if (split >= n_splits) return;
-  const int group = nh / nkv;                       // <= DEC_MAX_GROUP, checked by the launcher
+  const int group = nh / nkv;                       // == warps of the block
   const int first = lo + split * chunk;
   const int last = min(p, first + chunk - 1);
   const int* table = block_table + (size_t)r * table_stride;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, h = tid >> 5, lane = tid & 31;   // h: this warp's head in the group
+  const int head = kvh * group + h;
 
   __shared__ float q_s[DEC_MAX_GROUP][HEAD_DIM];
-  __shared__ float acc_s[DEC_WARPS][DEC_MAX_GROUP][HEAD_DIM];
-  __shared__ float m_s[DEC_WARPS][DEC_MAX_GROUP], l_s[DEC_WARPS][DEC_MAX_GROUP];
   __shared__ int is_last;
 
-  for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
-    const int h = i / HEAD_DIM, c = i % HEAD_DIM;
-    q_s[h][c] = __bfloat162float(q[((size_t)t * nh + kvh * group + h) * HEAD_DIM + c]);
-  }
-  __syncthreads();
+  // each warp stages its own head's q: no block-wide barrier is needed
+  for (int c = lane; c < HEAD_DIM; c += 32)
+    q_s[h][c] = __bfloat162float(q[((size_t)t * nh + head) * HEAD_DIM + c]);
+  __syncwarp();
 
-  float m_run[DEC_MAX_GROUP], l_run[DEC_MAX_GROUP], acc[DEC_MAX_GROUP][kOwn];
+  float m_run = -INFINITY, l_run = 0.f, acc[kOwn];
 #pragma unroll
-  for (int h = 0; h < DEC_MAX_GROUP; ++h) {
-    m_run[h] = -INFINITY;
-    l_run[h] = 0.f;
-#pragma unroll
-    for (int e = 0; e < kOwn; ++e) acc[h][e] = 0.f;
-  }
+  for (int e = 0; e < kOwn; ++e) acc[e] = 0.f;
+  const int own = (lane < kOwners ? lane : 0) * kOwn;
 
-  for (int k0 = first + warp * 32; k0 <= last; k0 += DEC_BLOCK_KEYS) {
+  for (int k0 = first; k0 <= last; k0 += DEC_TILE) {
     // ---- scores: a lane per key ----
     const int key = k0 + lane;
     const bool live = key <= last;
@@ -102,103 +97,70 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     Bf16x8 kreg[HEAD_DIM / 8];
 #pragma unroll
     for (int c = 0; c < HEAD_DIM / 8; ++c) kreg[c] = row[c];
-    float s[DEC_MAX_GROUP];
-#pragma unroll
-    for (int h = 0; h < DEC_MAX_GROUP; ++h) s[h] = 0.f;
+    float dot[4] = {0.f, 0.f, 0.f, 0.f};                // four chains instead of one
 #pragma unroll
     for (int c = 0; c < HEAD_DIM / 8; ++c) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 kf = __bfloat1622float2(kreg[c].v[e]);
-#pragma unroll
-        for (int h = 0; h < DEC_MAX_GROUP; ++h)
-          if (h < group) s[h] += q_s[h][c * 8 + e * 2] * kf.x + q_s[h][c * 8 + e * 2 + 1] * kf.y;
+        const float2 qf = *reinterpret_cast<const float2*>(&q_s[h][c * 8 + e * 2]);
+        dot[e] += qf.x * kf.x + qf.y * kf.y;
       }
     }
+    const float s = live ? ((dot[0] + dot[1]) + (dot[2] + dot[3])) * scale : -INFINITY;
     // ---- running softmax of this warp ----
-    float corr[DEC_MAX_GROUP];
+    const float m_new = fmaxf(m_run, warp_max(s));      // finite: lane 0's key is live
+    const float w = expf(s - m_new);                     // exp(-inf) = 0 for idle lanes
+    const float corr = expf(m_run - m_new);              // 0 on the first pass
+    l_run = l_run * corr + warp_sum(w);
+    m_run = m_new;
 #pragma unroll
-    for (int h = 0; h < DEC_MAX_GROUP; ++h) {
-      if (h < group) {
-        const float sh = live ? s[h] * scale : -INFINITY;
-        const float m_new = fmaxf(m_run[h], warp_max(sh));      // finite: lane 0's key is live
-        const float e = expf(sh - m_new);                        // exp(-inf) = 0 for idle lanes
-        corr[h] = expf(m_run[h] - m_new);                        // 0 on the first pass
-        l_run[h] = l_run[h] * corr[h] + warp_sum(e);
-        m_run[h] = m_new;
-        s[h] = e;
-      }
-    }
-    // ---- weighted values: a lane per kOwn value lanes, keys one after another ----
+    for (int e = 0; e < kOwn; ++e) acc[e] *= corr;
+    // ---- weighted values: a lane per kOwn value lanes; loads in batches of 8 keys ----
+    const int n = min(DEC_TILE, last - k0 + 1);
 #pragma unroll
-    for (int h = 0; h < DEC_MAX_GROUP; ++h) {
-      if (h < group) {
+    for (int j0 = 0; j0 < DEC_TILE; j0 += 8) {
+      if (j0 < n) {                                       // idle keys of a batch carry weight 0
+        float vals[8][kOwn];
 #pragma unroll
-        for (int e = 0; e < kOwn; ++e) acc[h][e] *= corr[h];
-      }
-    }
-    const int n = min(32, last - k0 + 1);
-    const int own = (lane < kOwners ? lane : 0) * kOwn;
-#pragma unroll 8
-    for (int j = 0; j < 32; ++j) {
-      const int slot_j = __shfl_sync(0xffffffffu, slot, j);      // idle keys carry weight 0
-      float vals[kOwn];
-      const __nv_bfloat16* vrow = v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own;
+        for (int j = 0; j < 8; ++j) {
+          const int slot_j = __shfl_sync(0xffffffffu, slot, j0 + j);
+          const __nv_bfloat16* vrow = v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own;
 #pragma unroll
-      for (int e = 0; e < kOwn; e += 2) {
-        const float2 vf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + e));
-        vals[e] = vf.x;
-        vals[e + 1] = vf.y;
-      }
+          for (int e = 0; e < kOwn; e += 2) {
+            const float2 vf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + e));
+            vals[j][e] = vf.x;
+            vals[j][e + 1] = vf.y;
+          }
+        }
 #pragma unroll
-      for (int h = 0; h < DEC_MAX_GROUP; ++h) {
-        if (h < group) {
-          const float w = __shfl_sync(0xffffffffu, s[h], j);
+        for (int j = 0; j < 8; ++j) {
+          const float wj = __shfl_sync(0xffffffffu, w, j0 + j);
 #pragma unroll
-          for (int e = 0; e < kOwn; ++e) acc[h][e] += w * vals[e];
+          for (int e = 0; e < kOwn; ++e) acc[e] += wj * vals[j][e];
         }
       }
-      if (j + 1 >= n && ((j + 1) & 7) == 0) break;                // whole batches of 8 keys only
     }
   }
-
-  // ---- merge the warps of the block ----
-#pragma unroll
-  for (int h = 0; h < DEC_MAX_GROUP; ++h) {
-    if (h < group) {
-      if (lane < kOwners) {
-#pragma unroll
-        for (int e = 0; e < kOwn; ++e) acc_s[warp][h][lane * kOwn + e] = acc[h][e];
-      }
-      if (lane == 0) { m_s[warp][h] = m_run[h]; l_s[warp][h] = l_run[h]; }
-    }
-  }
-  __syncthreads();
 
   // scratch layout per (row, head): [split][HEAD_DIM + 2] = weighted values, max, sum
   const size_t per_head = (size_t)DEC_MAX_SPLITS * (HEAD_DIM + 2);
-  float* base = scratch + ((size_t)t * nh + kvh * group) * per_head;
-  for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
-    const int h = i / HEAD_DIM, c = i % HEAD_DIM;
-    float m = -INFINITY;
+  if (n_splits == 1) {
+    if (lane < kOwners) {
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* dst = out + ((size_t)t * nh + head) * HEAD_DIM + own;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, m_s[w][h]);   // a warp without keys has -inf
-    float num = 0.f, den = 0.f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
-      const float f = expf(m_s[w][h] - m);
-      num += f * acc_s[w][h][c];
-      den += f * l_s[w][h];
+      for (int e = 0; e < kOwn; e += 2)
+        *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
     }
-    if (n_splits == 1) {
-      out[((size_t)t * nh + kvh * group + h) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
-    } else {
-      float* piece = base + h * per_head + (size_t)split * (HEAD_DIM + 2);
-      piece[c] = num;
-      if (c == 0) { piece[HEAD_DIM] = m; piece[HEAD_DIM + 1] = den; }
-    }
+    return;
   }
-  if (n_splits == 1) return;
+  float* piece = scratch + ((size_t)t * nh + head) * per_head + (size_t)split * (HEAD_DIM + 2);
+  if (lane < kOwners) {
+#pragma unroll
+    for (int e = 0; e < kOwn; ++e) piece[own + e] = acc[e];
+  }
+  if (lane == 0) { piece[HEAD_DIM] = m_run; piece[HEAD_DIM + 1] = l_run; }
   // ---- the last block to finish merges the pieces, in index order ----
   __threadfence();
   __syncthreads();
@@ -210,28 +172,29 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
-    const int h = i / HEAD_DIM, c = i % HEAD_DIM;
-    const float* piece = base + h * per_head;
-    float ms[DEC_MAX_SPLITS], ls[DEC_MAX_SPLITS], vs[DEC_MAX_SPLITS];
+  // warp h merges head h: lane s holds split s's maximum and sum
+  const float* pieces = scratch + ((size_t)t * nh + head) * per_head;
+  const bool on = lane < n_splits;
+  const float m_s = on ? __ldcg(&pieces[(size_t)lane * (HEAD_DIM + 2) + HEAD_DIM]) : -INFINITY;
+  const float l_s = on ? __ldcg(&pieces[(size_t)lane * (HEAD_DIM + 2) + HEAD_DIM + 1]) : 0.f;
+  const float m_all = warp_max(m_s);
+  const float f = expf(m_s - m_all);                    // 0 for lanes without a split
+  const float den = warp_sum(f * l_s);
+  for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+    const int c = c0 + lane;
+    float num = 0.f;
+    if (c < HEAD_DIM) {
+      float v[DEC_MAX_SPLITS];
 #pragma unroll
-    for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) {
-      const bool on = sp < n_splits;
-      ms[sp] = on ? __ldcg(&piece[(size_t)sp * (HEAD_DIM + 2) + HEAD_DIM]) : -INFINITY;
-      ls[sp] = on ? __ldcg(&piece[(size_t)sp * (HEAD_DIM + 2) + HEAD_DIM + 1]) : 0.f;
-      vs[sp] = on ? __ldcg(&piece[(size_t)sp * (HEAD_DIM + 2) + c]) : 0.f;
+      for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp)
+        v[sp] = sp < n_splits ? __ldcg(&pieces[(size_t)sp * (HEAD_DIM + 2) + c]) : 0.f;
+#pragma unroll
+      for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) num += __shfl_sync(0xffffffffu, f, sp) * v[sp];
+    } else {
+#pragma unroll
+      for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) (void)__shfl_sync(0xffffffffu, f, sp);
     }
-    float m = -INFINITY;
-#pragma unroll
-    for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) m = fmaxf(m, ms[sp]);
-    float num = 0.f, den = 0.f;
-#pragma unroll
-    for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) {
-      const float f = expf(ms[sp] - m);
-      num += f * vs[sp];
-      den += f * ls[sp];
-    }
-    out[((size_t)t * nh + kvh * group + h) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
+    if (c < HEAD_DIM) out[((size_t)t * nh + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
   }
 }
 
@@ -255,7 +218,7 @@ TOKB200_API int tokb200_decode_attention(
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
     return TOKB200_BAD_ALIGNMENT;
   dim3 grid(DEC_MAX_SPLITS, nkv, n_rows);
-  return launch_dependent(decode_attention_kernel, grid, dim3(DEC_THREADS), 0, stream,
+  return launch_dependent(decode_attention_kernel, grid, dim3(32 * (nh / nkv)), 0, stream,
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                           table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
