@@ -40,6 +40,7 @@ constexpr int own_lanes(int d) {
 constexpr int kOwn = own_lanes(HEAD_DIM);
 constexpr int kOwners = HEAD_DIM / kOwn;             // lanes that own value lanes (<= 32)
 static_assert(kOwn % 2 == 0 && HEAD_DIM % kOwn == 0 && kOwners <= 32, "value lanes per lane");
+constexpr int kBatch = 64 / kOwn;                   // keys whose values a lane holds at once (32, 16, 8)
 
 struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
 
@@ -97,6 +98,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     Bf16x8 kreg[HEAD_DIM / 8];
 #pragma unroll
     for (int c = 0; c < HEAD_DIM / 8; ++c) kreg[c] = row[c];
+    // the values do not wait for the scores: the first batch is requested together
+    // with the keys, so one trip to memory serves both
+    const int n = min(DEC_TILE, last - k0 + 1);
+    __nv_bfloat162 vreg[kBatch][kOwn / 2];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int slot_j = __shfl_sync(0xffffffffu, slot, j);
+      const __nv_bfloat162* vrow = reinterpret_cast<const __nv_bfloat162*>(
+          v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own);
+#pragma unroll
+      for (int e = 0; e < kOwn / 2; ++e) vreg[j][e] = vrow[e];
+    }
     float dot[4] = {0.f, 0.f, 0.f, 0.f};                // four chains instead of one
 #pragma unroll
     for (int c = 0; c < HEAD_DIM / 8; ++c) {
@@ -116,28 +129,29 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     m_run = m_new;
 #pragma unroll
     for (int e = 0; e < kOwn; ++e) acc[e] *= corr;
-    // ---- weighted values: a lane per kOwn value lanes; loads in batches of 8 keys ----
-    const int n = min(DEC_TILE, last - k0 + 1);
+    // ---- weighted values: a lane per kOwn value lanes; idle keys carry weight 0 ----
 #pragma unroll
-    for (int j0 = 0; j0 < DEC_TILE; j0 += 8) {
-      if (j0 < n) {                                       // idle keys of a batch carry weight 0
-        float vals[8][kOwn];
+    for (int j0 = 0; j0 < DEC_TILE; j0 += kBatch) {
+      if (j0 > 0 && j0 < n) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kBatch; ++j) {
           const int slot_j = __shfl_sync(0xffffffffu, slot, j0 + j);
-          const __nv_bfloat16* vrow = v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own;
+          const __nv_bfloat162* vrow = reinterpret_cast<const __nv_bfloat162*>(
+              v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own);
 #pragma unroll
-          for (int e = 0; e < kOwn; e += 2) {
-            const float2 vf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + e));
-            vals[j][e] = vf.x;
-            vals[j][e + 1] = vf.y;
-          }
+          for (int e = 0; e < kOwn / 2; ++e) vreg[j][e] = vrow[e];
         }
+      }
+      if (j0 < n) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kBatch; ++j) {
           const float wj = __shfl_sync(0xffffffffu, w, j0 + j);
 #pragma unroll
-          for (int e = 0; e < kOwn; ++e) acc[e] += wj * vals[j][e];
+          for (int e = 0; e < kOwn / 2; ++e) {
+            const float2 vf = __bfloat1622float2(vreg[j][e]);
+            acc[2 * e] += wj * vf.x;
+            acc[2 * e + 1] += wj * vf.y;
+          }
         }
       }
     }

@@ -172,6 +172,91 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   }
 }
 
+// ----------------------------------------------------------------------------
+// Greedy only: the vocabulary of a row is cut over ARGMAX_SPLITS blocks; each
+// leaves its best (value, id) in scratch and the block that finishes last for the
+// row picks among them, in index order (higher value, then lower id).
+// scratch: [n_rows][ARGMAX_SPLITS] pairs; counters: [n_rows] ints, zero between
+// launches.
+// ----------------------------------------------------------------------------
+#define ARGMAX_SPLITS 32
+#define ARGMAX_THREADS 256
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out,
+              BestPair* __restrict__ scratch, int* __restrict__ counters) {
+  __shared__ BestPair pair_scratch[33];
+  __shared__ int is_last;
+  pdl_wait();
+  pdl_launch();
+  const int split = blockIdx.x, r = blockIdx.y;
+  const float* row = logits + (size_t)r * vocab;
+  const int per = (vocab + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS;
+  const int begin = min(vocab, split * per), end = min(vocab, begin + per);
+  BestPair best{-INFINITY, -1};
+  // four loads in flight per thread
+  for (int i0 = begin + threadIdx.x; i0 < end; i0 += 4 * ARGMAX_THREADS) {
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i0 + e * ARGMAX_THREADS;
+      v[e] = i < end ? row[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (v[e] > best.value) { best.value = v[e]; best.index = i0 + e * ARGMAX_THREADS; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    BestPair other{__shfl_xor_sync(0xffffffffu, best.value, o),
+                   __shfl_xor_sync(0xffffffffu, best.index, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) pair_scratch[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    BestPair w = lane < ARGMAX_THREADS / 32 ? pair_scratch[lane] : BestPair{-INFINITY, -1};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      BestPair other{__shfl_xor_sync(0xffffffffu, w.value, o),
+                     __shfl_xor_sync(0xffffffffu, w.index, o)};
+      w = better(w, other);
+    }
+    if (lane == 0) {
+      scratch[(size_t)r * ARGMAX_SPLITS + split] = w;
+      __threadfence();
+      const int done = atomicAdd(&counters[r], 1);
+      is_last = done == ARGMAX_SPLITS - 1;
+      if (is_last) counters[r] = 0;
+    }
+  }
+  __syncthreads();
+  if (!is_last || warp != 0) return;
+  __threadfence();
+  const BestPair* mine = scratch + (size_t)r * ARGMAX_SPLITS;
+  BestPair w{__ldcg(&mine[lane].value), __ldcg(&mine[lane].index)};   // ARGMAX_SPLITS == 32 lanes
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    BestPair other{__shfl_xor_sync(0xffffffffu, w.value, o),
+                   __shfl_xor_sync(0xffffffffu, w.index, o)};
+    w = better(w, other);
+  }
+  if (lane == 0) out[r] = w.index < 0 ? 0 : w.index;
+}
+
+TOKB200_API long long tokb200_argmax_scratch_bytes(int n_rows) {
+  return (long long)n_rows * ARGMAX_SPLITS * sizeof(BestPair);
+}
+
+TOKB200_API int tokb200_argmax(const float* logits, int n_rows, int vocab, int* out, void* scratch,
+                               int* counters, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (vocab <= 0 || n_rows > 65535) return TOKB200_BAD_SIZE;
+  return launch_dependent(argmax_kernel, dim3(ARGMAX_SPLITS, n_rows), dim3(ARGMAX_THREADS), 0,
+                          stream, logits, vocab, out, (BestPair*)scratch, counters);
+}
+
 TOKB200_API int tokb200_sample(const float* logits, int n_rows, int vocab,
                                const float* temperature, const float* top_p,
                                const float* uniform, int* out, cudaStream_t stream) {

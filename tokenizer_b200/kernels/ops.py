@@ -184,6 +184,8 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor],
     """One token per row of float32 logits; all-None parameters mean greedy."""
     if logits.dtype != torch.float32 or out.dtype != torch.int32:
         raise ValueError("sample: logits are float32, ids int32")
+    if temperature is None:
+        return argmax(logits, out)
     _check(_lib("sampling").tokb200_sample(
         _ptr(logits), _i(logits.shape[0]), _i(logits.shape[1]), _ptr(temperature), _ptr(top_p),
         _ptr(uniform), _ptr(out), _stream()), "sample")
@@ -281,3 +283,22 @@ def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
         _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
         "prefill_attention")
+
+
+_argmax_scratch = {}
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """Greedy ids (ties keep the lower id): the vocabulary is cut over blocks
+    that meet in scratch kept per (device, rows)."""
+    n_rows, vocab = logits.shape
+    lib = _lib("sampling")
+    key = (logits.device.index, n_rows)
+    if key not in _argmax_scratch:
+        lib.tokb200_argmax_scratch_bytes.restype = ctypes.c_longlong
+        size = lib.tokb200_argmax_scratch_bytes(_i(n_rows))
+        _argmax_scratch[key] = (torch.empty(size, dtype=torch.uint8, device=logits.device),
+                                torch.zeros(n_rows, dtype=torch.int32, device=logits.device))
+    scratch, counters = _argmax_scratch[key]
+    _check(lib.tokb200_argmax(_ptr(logits), _i(n_rows), _i(vocab), _ptr(out), _ptr(scratch),
+                              _ptr(counters), _stream()), "argmax")
