@@ -1,21 +1,24 @@
-// Attention for rows that read far more keys than they bring: decoding.
+// Attention for rows that read far more keys than they bring: decoding
+// (bfloat16, tensor cores, 32-bit softmax).
 //
-// A decoding step is bound by latency, not by arithmetic or bytes: few rows, a few
-// hundred keys each.  So the work is spread over as many short, independent warps
-// as possible.  One block works on (a row, one kv head, one split of that row's
-// keys); each of its warps takes ONE query head of the kv head's group, so the
-// keys and values of the split are fetched from L2 once and met again in L1 by the
-// other warps.  A warp walks its keys 32 at a time: a lane per key for the scores
-// (q is read from shared memory, broadcast), a lane per few value lanes for the
-// weighted sum, its own running maximum and sum, no block-wide barrier.
+// One block works on (a row, one kv head, one split of that row's keys) and
+// serves all query heads of the kv head's group at once: the group is the M side
+// of mma.sync m16n8k16 (up to 16 heads), the keys are its N side, so keys and
+// values are read once per group and a 32-key tile costs a warp a few dozen
+// instructions.  q k^T takes its fragments straight from 16-byte global loads (a
+// dot product does not care about the order of the head's lanes, so a thread's 8
+// consecutive lanes are handed to two instructions under permuted k slots, the
+// same permutation for q and k); p v needs v transposed, so each warp stages its
+// tile's values in shared memory and reads them with ldmatrix.trans.
 //
 // A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk
-// is 32 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
+// is 128 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
 // function of the row's own position and window and does not change with the
-// batch around it.  Pieces meet in scratch memory (max, sum, weighted values per
-// (row, head, split)); the block that finishes last for a (row, kv head) merges
-// them in index order and writes the output.  Everything but q, k, v and the
-// output is 32-bit.
+// batch around it.  The four warps of a block take tiles of 32 keys in turn, each
+// with its own running maximum, sum and weighted values; they are merged once at
+// the end.  Pieces of several blocks meet in scratch memory (max, sum, weighted
+// values per (row, head, split)); the block that finishes last for a (row, kv
+// head) merges them in index order and writes the output.
 //
 // HEAD_DIM is a compile-time size (a multiple of 16, at most 256), given with
 // -DHEAD_DIM=...; the library is built per head size at first use.
@@ -24,191 +27,276 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
 #endif
-#define DEC_MAX_GROUP 8        // query heads per kv head: one warp each
+#define DEC_WARPS 4
+#define DEC_THREADS (DEC_WARPS * 32)
+#define DEC_MAX_GROUP 16       // query heads per kv head: the rows of one mma
 #define DEC_MAX_SPLITS 32
 #define DEC_TILE 32            // keys a warp takes per pass
+#define DEC_BLOCK_KEYS (DEC_WARPS * DEC_TILE)
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
-
-// value lanes owned by one lane of a warp in the weighted sum: the smallest even
-// count that divides the head size and leaves at most 32 owners
-constexpr int own_lanes(int d) {
-  for (int n = 2; n <= 8; n += 2)
-    if (d % n == 0 && d / n <= 32) return n;
-  return 8;
-}
-constexpr int kOwn = own_lanes(HEAD_DIM);
-constexpr int kOwners = HEAD_DIM / kOwn;             // lanes that own value lanes (<= 32)
-static_assert(kOwn % 2 == 0 && HEAD_DIM % kOwn == 0 && kOwners <= 32, "value lanes per lane");
-constexpr int kBatch = 64 / kOwn;                   // keys whose values a lane holds at once (32, 16, 8)
-
-struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
+constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma
+constexpr bool kTail16 = HEAD_DIM % 32 != 0;         // one more step of 16 lanes: an 8-byte load
+constexpr int kVStride = HEAD_DIM + 8;               // elements between staged value rows
 
 __device__ __forceinline__ int split_chunk(int n_keys) {
-  int chunk = DEC_TILE;
+  int chunk = DEC_BLOCK_KEYS;
   while ((n_keys + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
   return chunk;
 }
+__device__ __forceinline__ void dec_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void dec_ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ unsigned dec_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ uint4 dec_load16(const __nv_bfloat16* p, bool ok) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (ok) v = *reinterpret_cast<const uint4*>(p);
+  return v;
+}
+__device__ __forceinline__ uint2 dec_load8(const __nv_bfloat16* p, bool ok) {
+  uint2 v = make_uint2(0u, 0u);
+  if (ok) v = *reinterpret_cast<const uint2*>(p);
+  return v;
+}
 
-__global__ void __launch_bounds__(DEC_MAX_GROUP * 32)
+__global__ void __launch_bounds__(DEC_THREADS)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
                         int nkv, int page, int window, float scale,
                         float* __restrict__ scratch, int* __restrict__ counters) {
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  __shared__ int is_last;
   pdl_wait();
   pdl_launch();
-  const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
-  const int r = row_req[t];
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int r = row_req[row];
   if (r < 0) return;
-  const int p = pos[t];
+  const int p = pos[row];
   const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
   const int n_keys = p - lo + 1;
   const int chunk = split_chunk(n_keys);
   const int n_splits = (n_keys + chunk - 1) / chunk;
   if (split >= n_splits) return;
-  const int group = nh / nkv;                       // == warps of the block
+  const int group = nh / nkv;                       // <= DEC_MAX_GROUP, checked by the launcher
   const int first = lo + split * chunk;
   const int last = min(p, first + chunk - 1);
   const int* table = block_table + (size_t)r * table_stride;
-  const int tid = threadIdx.x, h = tid >> 5, lane = tid & 31;   // h: this warp's head in the group
-  const int head = kvh * group + h;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
 
-  __shared__ float q_s[DEC_MAX_GROUP][HEAD_DIM];
-  __shared__ int is_last;
-
-  // each warp stages its own head's q: no block-wide barrier is needed
-  for (int c = lane; c < HEAD_DIM; c += 32)
-    q_s[h][c] = __bfloat162float(q[((size_t)t * nh + head) * HEAD_DIM + c]);
-  __syncwarp();
-
-  float m_run = -INFINITY, l_run = 0.f, acc[kOwn];
+  // ---- q fragments: heads g and g + 8 of the group, lanes in the permuted order ----
+  unsigned qa[kSteps32 > 0 ? kSteps32 : 1][2][4];
+  unsigned qt[4];
+  {
+    const bool ok_a = g < group, ok_b = g + 8 < group;
+    const __nv_bfloat16* qa_row = q + ((size_t)row * nh + kvh * group + g) * HEAD_DIM;
+    const __nv_bfloat16* qb_row = qa_row + (size_t)8 * HEAD_DIM;
 #pragma unroll
-  for (int e = 0; e < kOwn; ++e) acc[e] = 0.f;
-  const int own = (lane < kOwners ? lane : 0) * kOwn;
-
-  for (int k0 = first; k0 <= last; k0 += DEC_TILE) {
-    // ---- scores: a lane per key ----
-    const int key = k0 + lane;
-    const bool live = key <= last;
-    const int key_ok = live ? key : k0;                 // idle lanes read the first key again
-    const int slot = table[key_ok / page] * page + key_ok % page;
-    const Bf16x8* row = reinterpret_cast<const Bf16x8*>(k_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM);
-    Bf16x8 kreg[HEAD_DIM / 8];
-#pragma unroll
-    for (int c = 0; c < HEAD_DIM / 8; ++c) kreg[c] = row[c];
-    // the values do not wait for the scores: the first batch is requested together
-    // with the keys, so one trip to memory serves both
-    const int n = min(DEC_TILE, last - k0 + 1);
-    __nv_bfloat162 vreg[kBatch][kOwn / 2];
-#pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-      const int slot_j = __shfl_sync(0xffffffffu, slot, j);
-      const __nv_bfloat162* vrow = reinterpret_cast<const __nv_bfloat162*>(
-          v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own);
-#pragma unroll
-      for (int e = 0; e < kOwn / 2; ++e) vreg[j][e] = vrow[e];
+    for (int st = 0; st < kSteps32; ++st) {
+      const uint4 a = dec_load16(qa_row + st * 32 + 8 * t, ok_a);
+      const uint4 b = dec_load16(qb_row + st * 32 + 8 * t, ok_b);
+      qa[st][0][0] = a.x; qa[st][0][1] = b.x; qa[st][0][2] = a.y; qa[st][0][3] = b.y;
+      qa[st][1][0] = a.z; qa[st][1][1] = b.z; qa[st][1][2] = a.w; qa[st][1][3] = b.w;
     }
-    float dot[4] = {0.f, 0.f, 0.f, 0.f};                // four chains instead of one
+    if (kTail16) {
+      const uint2 a = dec_load8(qa_row + kSteps32 * 32 + 4 * t, ok_a);
+      const uint2 b = dec_load8(qb_row + kSteps32 * 32 + 4 * t, ok_b);
+      qt[0] = a.x; qt[1] = b.x; qt[2] = a.y; qt[3] = b.y;
+    }
+  }
+
+  __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(dec_smem) + (size_t)warp * DEC_TILE * kVStride;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HEAD_DIM / 8][4];
 #pragma unroll
-    for (int c = 0; c < HEAD_DIM / 8; ++c) {
+  for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float scale_log2 = scale * 1.4426950408889634f;
+
+  for (int k0 = first + warp * DEC_TILE; k0 <= last; k0 += DEC_BLOCK_KEYS) {
+    // ---- request the values of this tile (a lane per key) and the keys (mma layout) ----
+    uint4 vreg[HEAD_DIM / 8];
+    {
+      const int key = k0 + lane;
+      const bool ok = key <= last;
+      const int key_ok = ok ? key : k0;
+      const int slot = table[key_ok / page] * page + key_ok % page;
+      const __nv_bfloat16* vrow = v_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM;
+#pragma unroll
+      for (int c = 0; c < HEAD_DIM / 8; ++c) vreg[c] = dec_load16(vrow + c * 8, ok);   // idle keys: zeros
+    }
+    float s[DEC_TILE / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      const int key = k0 + nt * 8 + g;
+      const bool ok = key <= last;
+      const int key_ok = ok ? key : k0;
+      const int slot = table[key_ok / page] * page + key_ok % page;
+      const __nv_bfloat16* krow = k_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM;
+#pragma unroll
+      for (int st = 0; st < kSteps32; ++st) {
+        const uint4 kv = dec_load16(krow + st * 32 + 8 * t, ok);
+        dec_mma(s[nt], qa[st][0], kv.x, kv.y);
+        dec_mma(s[nt], qa[st][1], kv.z, kv.w);
+      }
+      if (kTail16) {
+        const uint2 kv = dec_load8(krow + kSteps32 * 32 + 4 * t, ok);
+        dec_mma(s[nt], qt, kv.x, kv.y);
+      }
+    }
+    // ---- stage the values for the transposed read ----
+#pragma unroll
+    for (int c = 0; c < HEAD_DIM / 8; ++c)
+      *reinterpret_cast<uint4*>(v_s + lane * kVStride + c * 8) = vreg[c];
+    // ---- scale, mask, running softmax: rows g (heads 0..7) and g + 8 (heads 8..15) ----
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 kf = __bfloat1622float2(kreg[c].v[e]);
-        const float2 qf = *reinterpret_cast<const float2*>(&q_s[h][c * 8 + e * 2]);
-        dot[e] += qf.x * kf.x + qf.y * kf.y;
+        const int key = k0 + nt * 8 + 2 * t + (e & 1);
+        s[nt][e] = key <= last ? s[nt][e] * scale_log2 : -INFINITY;
+        m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
       }
     }
-    const float s = live ? ((dot[0] + dot[1]) + (dot[2] + dot[3])) * scale : -INFINITY;
-    // ---- running softmax of this warp ----
-    const float m_new = fmaxf(m_run, warp_max(s));      // finite: lane 0's key is live
-    const float w = expf(s - m_new);                     // exp(-inf) = 0 for idle lanes
-    const float corr = expf(m_run - m_new);              // 0 on the first pass
-    l_run = l_run * corr + warp_sum(w);
-    m_run = m_new;
+    float corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int e = 0; e < kOwn; ++e) acc[e] *= corr;
-    // ---- weighted values: a lane per kOwn value lanes; idle keys carry weight 0 ----
+    for (int i = 0; i < 2; ++i) {
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));   // finite: key k0 is live
+      corr[i] = exp2f(m_run[i] - m_new[i]);                                      // 0 on the first pass
+      m_run[i] = m_new[i];
+    }
 #pragma unroll
-    for (int j0 = 0; j0 < DEC_TILE; j0 += kBatch) {
-      if (j0 > 0 && j0 < n) {
+    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          const int slot_j = __shfl_sync(0xffffffffu, slot, j0 + j);
-          const __nv_bfloat162* vrow = reinterpret_cast<const __nv_bfloat162*>(
-              v_pool + ((size_t)slot_j * nkv + kvh) * HEAD_DIM + own);
-#pragma unroll
-          for (int e = 0; e < kOwn / 2; ++e) vreg[j][e] = vrow[e];
-        }
-      }
-      if (j0 < n) {
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          const float wj = __shfl_sync(0xffffffffu, w, j0 + j);
-#pragma unroll
-          for (int e = 0; e < kOwn / 2; ++e) {
-            const float2 vf = __bfloat1622float2(vreg[j][e]);
-            acc[2 * e] += wj * vf.x;
-            acc[2 * e + 1] += wj * vf.y;
-          }
-        }
+      for (int e = 0; e < 4; ++e) {
+        const float pe = exp2f(s[nt][e] - m_new[e >> 1]);
+        s[nt][e] = pe;
+        sum[e >> 1] += pe;
       }
     }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      l_run[i] = l_run[i] * corr[i] + sum[i];
+    }
+#pragma unroll
+    for (int i = 0; i < HEAD_DIM / 8; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    __syncwarp();
+    // ---- o += p v ----
+#pragma unroll
+    for (int ks = 0; ks < DEC_TILE / 16; ++ks) {
+      unsigned pf[4];
+      pf[0] = dec_pack(s[2 * ks][0], s[2 * ks][1]);
+      pf[1] = dec_pack(s[2 * ks][2], s[2 * ks][3]);
+      pf[2] = dec_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      pf[3] = dec_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HEAD_DIM / 16; ++dp) {
+        unsigned vf[4];
+        dec_ldmatrix_x4_trans(vf, v_s + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kVStride +
+                                      dp * 16 + (lane >> 4) * 8);
+        dec_mma(o[2 * dp], pf, vf[0], vf[1]);
+        dec_mma(o[2 * dp + 1], pf, vf[2], vf[3]);
+      }
+    }
+    __syncwarp();   // the staged values are overwritten by the next tile
   }
 
-  // scratch layout per (row, head): [split][HEAD_DIM + 2] = weighted values, max, sum
-  const size_t per_head = (size_t)DEC_MAX_SPLITS * (HEAD_DIM + 2);
-  if (n_splits == 1) {
-    if (lane < kOwners) {
-      const float inv = 1.0f / l_run;
-      __nv_bfloat16* dst = out + ((size_t)t * nh + head) * HEAD_DIM + own;
+  // ---- merge the warps of the block (the merge buffer takes the place of the staging area) ----
+  __syncthreads();
+  float* acc_s = reinterpret_cast<float*>(dec_smem);           // [warp][head][HEAD_DIM + 2]
+  constexpr int kRow = HEAD_DIM + 2;
 #pragma unroll
-      for (int e = 0; e < kOwn; e += 2)
-        *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
+  for (int i = 0; i < 2; ++i) {
+    const int head = g + 8 * i;
+    if (head < group) {
+      float* dst = acc_s + ((size_t)warp * group + head) * kRow;
+#pragma unroll
+      for (int nt = 0; nt < HEAD_DIM / 8; ++nt) {
+        dst[nt * 8 + 2 * t] = o[nt][2 * i];
+        dst[nt * 8 + 2 * t + 1] = o[nt][2 * i + 1];
+      }
+      if (t == 0) { dst[HEAD_DIM] = m_run[i]; dst[HEAD_DIM + 1] = l_run[i]; }
     }
-    return;
   }
-  float* piece = scratch + ((size_t)t * nh + head) * per_head + (size_t)split * (HEAD_DIM + 2);
-  if (lane < kOwners) {
+  __syncthreads();
+
+  // scratch layout per (row, head): [split][HEAD_DIM + 2] = weighted values, max (log2 units), sum
+  const size_t per_head = (size_t)DEC_MAX_SPLITS * kRow;
+  float* base = scratch + ((size_t)row * nh + kvh * group) * per_head;
+  for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
+    const int head = i / HEAD_DIM, c = i % HEAD_DIM;
+    float m = -INFINITY;
 #pragma unroll
-    for (int e = 0; e < kOwn; ++e) piece[own + e] = acc[e];
+    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, acc_s[((size_t)w * group + head) * kRow + HEAD_DIM]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float* src = acc_s + ((size_t)w * group + head) * kRow;
+      const float f = exp2f(src[HEAD_DIM] - m);          // a warp without keys has max -inf: weight 0
+      num += f * src[c];
+      den += f * src[HEAD_DIM + 1];
+    }
+    if (n_splits == 1) {
+      out[((size_t)row * nh + kvh * group + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
+    } else {
+      float* piece = base + head * per_head + (size_t)split * kRow;
+      piece[c] = num;
+      if (c == 0) { piece[HEAD_DIM] = m; piece[HEAD_DIM + 1] = den; }
+    }
   }
-  if (lane == 0) { piece[HEAD_DIM] = m_run; piece[HEAD_DIM + 1] = l_run; }
+  if (n_splits == 1) return;
   // ---- the last block to finish merges the pieces, in index order ----
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int done = atomicAdd(&counters[t * nkv + kvh], 1);
+    const int done = atomicAdd(&counters[row * nkv + kvh], 1);
     is_last = done == n_splits - 1;
-    if (is_last) counters[t * nkv + kvh] = 0;   // ready for the next launch
+    if (is_last) counters[row * nkv + kvh] = 0;   // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // warp h merges head h: lane s holds split s's maximum and sum
-  const float* pieces = scratch + ((size_t)t * nh + head) * per_head;
-  const bool on = lane < n_splits;
-  const float m_s = on ? __ldcg(&pieces[(size_t)lane * (HEAD_DIM + 2) + HEAD_DIM]) : -INFINITY;
-  const float l_s = on ? __ldcg(&pieces[(size_t)lane * (HEAD_DIM + 2) + HEAD_DIM + 1]) : 0.f;
-  const float m_all = warp_max(m_s);
-  const float f = expf(m_s - m_all);                    // 0 for lanes without a split
-  const float den = warp_sum(f * l_s);
-  for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-    const int c = c0 + lane;
-    float num = 0.f;
-    if (c < HEAD_DIM) {
+  // a warp per head: lane s holds split s's maximum and sum
+  for (int head = warp; head < group; head += DEC_WARPS) {
+    const float* pieces = base + head * per_head;
+    const bool on = lane < n_splits;
+    const float m_s = on ? __ldcg(&pieces[(size_t)lane * kRow + HEAD_DIM]) : -INFINITY;
+    const float l_s = on ? __ldcg(&pieces[(size_t)lane * kRow + HEAD_DIM + 1]) : 0.f;
+    const float m_all = warp_max(m_s);
+    const float f = exp2f(m_s - m_all);                   // 0 for lanes without a split
+    const float den = warp_sum(f * l_s);
+    for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+      const int c = c0 + lane;
+      const bool have = c < HEAD_DIM;
       float v[DEC_MAX_SPLITS];
 #pragma unroll
       for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp)
-        v[sp] = sp < n_splits ? __ldcg(&pieces[(size_t)sp * (HEAD_DIM + 2) + c]) : 0.f;
+        v[sp] = (have && sp < n_splits) ? __ldcg(&pieces[(size_t)sp * kRow + c]) : 0.f;
+      float num = 0.f;
 #pragma unroll
       for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) num += __shfl_sync(0xffffffffu, f, sp) * v[sp];
-    } else {
-#pragma unroll
-      for (int sp = 0; sp < DEC_MAX_SPLITS; ++sp) (void)__shfl_sync(0xffffffffu, f, sp);
+      if (have) out[((size_t)row * nh + kvh * group + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
     }
-    if (c < HEAD_DIM) out[((size_t)t * nh + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
   }
 }
 
@@ -231,8 +319,23 @@ TOKB200_API int tokb200_decode_attention(
     return TOKB200_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
     return TOKB200_BAD_ALIGNMENT;
+  const int group = nh / nkv;
+  const size_t stage = (size_t)DEC_WARPS * DEC_TILE * kVStride * sizeof(__nv_bfloat16);
+  const size_t merge = (size_t)DEC_WARPS * group * (HEAD_DIM + 2) * sizeof(float);
+  const size_t smem = stage > merge ? stage : merge;
+  if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
+    static bool configured[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+    if (!configured[device]) {
+      cudaError_t err = cudaFuncSetAttribute(decode_attention_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+      if (err != cudaSuccess) return (int)err;
+      configured[device] = true;
+    }
+  }
   dim3 grid(DEC_MAX_SPLITS, nkv, n_rows);
-  return launch_dependent(decode_attention_kernel, grid, dim3(32 * (nh / nkv)), 0, stream,
+  return launch_dependent(decode_attention_kernel, grid, dim3(DEC_THREADS), smem, stream,
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                           table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,

@@ -207,7 +207,7 @@ def advance_decode(ids, drawn, pos, kv_len, row_req, slots, tables, page, histor
         _stream()), "advance_decode")
 
 
-DECODE_MAX_GROUP = 8
+DECODE_MAX_GROUP = 16
 _decode_scratch = {}
 
 
