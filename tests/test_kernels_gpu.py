@@ -21,6 +21,16 @@ def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
 
 
+def close_tensor_core_attention(got, want):
+    """bfloat16 attention on tensor cores rounds the probabilities to bfloat16
+    before they meet the values (2^-9 relative per term, so up to 2^-9 of the
+    largest value in the sum), on top of the output's own rounding (2^-8)."""
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs()
+    bound = 6e-3 + 2 ** -7 * want.abs()
+    assert bool((err <= bound).all()), f"max |diff| {float(err.max()):.4e} at {int(err.argmax())}"
+
+
 def close(got, want, dtype):
     got, want = got.float().cpu(), want.float().cpu()
     if dtype == torch.float32:
@@ -313,7 +323,8 @@ def test_advance_decode():
 
 @pytest.mark.parametrize("nh,nkv,d,page,window", [
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 32, 24), (14, 2, 64, 16, None),
-    (6, 3, 112, 4, 7), (8, 1, 256, 16, None), (7, 1, 64, 16, 100), (12, 2, 128, 64, None)])
+    (6, 3, 112, 4, 7), (8, 1, 256, 16, None), (7, 1, 64, 16, 100), (12, 2, 128, 64, None),
+    (16, 1, 32, 16, None), (24, 2, 64, 16, None), (9, 1, 80, 16, None)])
 def test_decode_attention_splits_and_merges(nh, nkv, d, page, window):
     """The split-key kernel: one row per request at the request's last position
     (one split, several splits, pieces longer than a tile), idle rows skipped."""
@@ -334,7 +345,7 @@ def test_decode_attention_splits_and_merges(nh, nkv, d, page, window):
         want = attention_reference(q.float().cpu()[live], dense, [row_req[i] for i in live],
                                    [pos[i] for i in live], nh, nkv, window, scale)
         assert torch.isfinite(out.float()).all()
-        close(out[live], want, dtype)
+        close_tensor_core_attention(out[live], want)
         assert bool((out[len(lengths)] == 9.0).all())     # the idle row is not written
         out.fill_(9.0)
 
@@ -357,13 +368,13 @@ def test_decode_attention_far_key_across_splits():
                                    torch.tensor([n - 1], dtype=torch.int32, device=DEV),
                                    nh, nkv, d, page, window, scale)
             want = attention_reference(q.float().cpu(), [(k, v)], [0], [n - 1], nh, nkv, window, scale)
-            close(out.view(1, nh, d), want, dtype)
+            close_tensor_core_attention(out.view(1, nh, d), want)
             if window is None or far + window >= n - 1:
-                close(out.view(nh, d)[3], v[far, 0], dtype)
+                close_tensor_core_attention(out.view(nh, d)[3], v[far, 0])
 
 
 def test_decode_attention_refuses_groups_it_cannot_hold():
-    assert not ops().decode_attention_supported(18, 2, 64)
+    assert not ops().decode_attention_supported(34, 2, 64)     # 17 heads to a group
     assert not ops().decode_attention_supported(4, 2, 24)
     assert ops().decode_attention_supported(14, 2, 64)
 
