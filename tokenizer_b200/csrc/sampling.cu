@@ -265,3 +265,59 @@ TOKB200_API int tokb200_sample(const float* logits, int n_rows, int vocab,
   return launch_dependent(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits,
                           vocab, temperature, top_p, uniform, out);
 }
+
+// ----------------------------------------------------------------------------
+// The greedy choice without any allocation: the scratch of argmax_kernel lives
+// in this library (see no_alloc.h for who needs that and for the rules).
+// ----------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#define ARGMAX_NO_ALLOC_MAX_ROWS 256
+
+struct ArgmaxStaticScratch {
+  BestPair pairs[ARGMAX_NO_ALLOC_MAX_ROWS * ARGMAX_SPLITS];
+  int counters[ARGMAX_NO_ALLOC_MAX_ROWS];
+};
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never an
+// address a kernel may be given.
+static __device__ __align__(256) unsigned char argmax_static_scratch[sizeof(ArgmaxStaticScratch)];
+
+TOKB200_API int tokb200_argmax_no_alloc_max_rows(void) { return ARGMAX_NO_ALLOC_MAX_ROWS; }
+
+TOKB200_API const char* tokb200_no_alloc_error(int status) {
+  switch (status) {
+    case TOKB200_OK: return "ok";
+    case TOKB200_BAD_SIZE:
+      return "refused: rows beyond the built-in scratch (256), an empty vocabulary, or a null pointer";
+    case TOKB200_BAD_ALIGNMENT: return "refused: logits and out must be 4-byte aligned";
+    default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+  }
+}
+
+TOKB200_API int tokb200_argmax_no_alloc(const float* logits, int n_rows, int vocab, int* out,
+                                        cudaStream_t stream) {
+  if (n_rows == 0) return TOKB200_OK;
+  if (n_rows < 0 || n_rows > ARGMAX_NO_ALLOC_MAX_ROWS || vocab <= 0 || !logits || !out)
+    return TOKB200_BAD_SIZE;
+  if (((uintptr_t)logits | (uintptr_t)out) & 3) return TOKB200_BAD_ALIGNMENT;
+  // set-up, once per device: the device address of the array, asked for with
+  // that device current
+  static void* scratch_of_device[64] = {};
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+  if (!scratch_of_device[device]) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, argmax_static_scratch);
+    if (err != cudaSuccess) return (int)err;
+    scratch_of_device[device] = address;
+  }
+  ArgmaxStaticScratch* scratch = static_cast<ArgmaxStaticScratch*>(scratch_of_device[device]);
+  // the counters must start at zero whatever the last call left behind
+  err = cudaMemsetAsync(scratch->counters, 0, sizeof(int) * n_rows, stream);
+  if (err != cudaSuccess) return (int)err;
+  return launch_dependent(argmax_kernel, dim3(ARGMAX_SPLITS, n_rows), dim3(ARGMAX_THREADS), 0,
+                          stream, logits, vocab, out, scratch->pairs, scratch->counters);
+}
