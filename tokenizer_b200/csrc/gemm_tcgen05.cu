@@ -1,0 +1,311 @@
+// y[M,N] = x[M,K] W[N,K]^T (+ bias) for many rows (portions of prompts), bfloat16
+// operands, 32-bit accumulation, on the fifth-generation tensor cores of sm_100a:
+//
+//   * TMA (cp.async.bulk.tensor) brings 128 x 64 tiles of x and BLOCK_N x 64 tiles
+//     of W into shared memory in the 128-byte swizzled layout, STAGES deep, each
+//     stage guarded by a "full" mbarrier (armed with the bytes to arrive) and an
+//     "empty" mbarrier;
+//   * one thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BLOCK_N,
+//     K = 16, both operands K-major from shared-memory descriptors); the 128 x
+//     BLOCK_N float accumulator lives in tensor memory (TMEM); tcgen05.commit
+//     releases a stage when the instructions that read it have finished, and
+//     signals the epilogue after the last one;
+//   * four epilogue warps read the accumulator back with tcgen05.ld (each warp its
+//     quarter of the 128 lanes), add the bias, convert and store.
+//
+// Warp roles: warp 0 loads, warp 1 allocates TMEM and issues the products, warps
+// 2..5 are the epilogue.  No operand tile is shared between CTAs (no cluster, no
+// multicast).  Rows and columns past M, N or K are zero-filled by TMA and masked
+// at the store.  Every wait on an mbarrier is bounded: when it runs out the
+// thread records an error flag, and all roles fall through to the common exit,
+// where TMEM is given back.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BLOCK_M 128
+#define TC_BLOCK_K 64          // 64 bfloat16 = 128 bytes = one swizzle row
+#define TC_UMMA_K 16
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT (1u << 24)
+
+__device__ int tc_error_flag = 0;   // set when a bounded wait gave up
+
+__device__ __forceinline__ unsigned tc_smem(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(bar)), "r"(bytes)
+               : "memory");
+}
+// Waits for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  const unsigned addr = tc_smem(bar);
+  for (unsigned spin = 0; spin < TC_WAIT_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&tc_error_flag, 1);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(tc_smem(dst)), "l"(map), "r"(tc_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile with 128-byte swizzle, rows of 128
+// bytes, 8-row groups 1024 bytes apart (sm_100 descriptor version 1).
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+  const unsigned long long addr = (tc_smem(tile) & 0x3FFFFu) >> 4;
+  return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a_desc,
+                                          unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+      "%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BLOCK_N, int STAGES>
+struct TcSmem {
+  static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2;
+  static constexpr int kBBytes = BLOCK_N * TC_BLOCK_K * 2;
+  static constexpr int kStage = kABytes + kBBytes;
+  static constexpr int kTotal = STAGES * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, void* __restrict__ out, int out_is_f32, int M,
+                    int N, int K) {
+  using S = TcSmem<BLOCK_N, STAGES>;
+  extern __shared__ unsigned char tc_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);        // swizzle atoms: 1024-aligned
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(tiles + STAGES * S::kStage);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* accum_ready = empty + STAGES;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum_ready + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * TC_BLOCK_M, n0 = blockIdx.y * BLOCK_N;
+  const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // one warp allocates the accumulator's columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tc_smem(tmem_slot)), "r"((unsigned)BLOCK_N) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  pdl_wait();      // x may be the predecessor's output
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: fill the ring ----
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) break;
+        unsigned char* a_tile = tiles + s * S::kStage;
+        mbar_expect_tx(&full[s], S::kStage);
+        tma_load_2d(a_tile, &map_x, &full[s], kb * TC_BLOCK_K, m0);
+        tma_load_2d(a_tile + S::kABytes, &map_w, &full[s], kb * TC_BLOCK_K, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- products: D[128 x BLOCK_N] (+)= A[128 x 16] B[BLOCK_N x 16]^T, four per stage ----
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BLOCK_N >> 3) << 17) |
+                             ((unsigned)(TC_BLOCK_M >> 4) << 24);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&full[s], (kb / STAGES) & 1)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned char* a_tile = tiles + s * S::kStage;
+        const unsigned long long a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + S::kABytes);
+#pragma unroll
+        for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k) {
+          // 16 bfloat16 = 32 bytes along K inside the swizzled row: +2 in units of 16 bytes
+          umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+        }
+        umma_commit(&empty[s]);            // the stage is free once these products have read it
+      }
+      umma_commit(accum_ready);            // all products done: the accumulator is complete
+    }
+  } else {
+    // ---- epilogue: warp w reads lanes 32 (w % 4) .. + 31 of the accumulator ----
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    if (mbar_wait(accum_ready, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+        unsigned v[32];
+        tmem_load_32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+        const int col0 = n0 + c0;
+        if (row < M && col0 < N) {
+          if (out_is_f32) {
+            float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col0;
+            if (col0 + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o;
+                o.x = __uint_as_float(v[j]) + (bias ? bias[col0 + j] : 0.f);
+                o.y = __uint_as_float(v[j + 1]) + (bias ? bias[col0 + j + 1] : 0.f);
+                o.z = __uint_as_float(v[j + 2]) + (bias ? bias[col0 + j + 2] : 0.f);
+                o.w = __uint_as_float(v[j + 3]) + (bias ? bias[col0 + j + 3] : 0.f);
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                dst[j] = __uint_as_float(v[j]) + (bias ? bias[col0 + j] : 0.f);
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col0;
+            if (col0 + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float lo = __uint_as_float(v[j + 2 * e]) + (bias ? bias[col0 + j + 2 * e] : 0.f);
+                  const float hi = __uint_as_float(v[j + 2 * e + 1]) + (bias ? bias[col0 + j + 2 * e + 1] : 0.f);
+                  __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                  ow[e] = *reinterpret_cast<unsigned*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]) + (bias ? bias[col0 + j] : 0.f));
+            }
+          }
+        }
+      }
+    }
+  }
+  // ---- common exit: everybody arrives, then tensor memory is given back ----
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  pdl_launch();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((unsigned)BLOCK_N) : "memory");
+  }
+}
+
+// ---- host side ----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A map over a row-major [rows, K] bfloat16 matrix, boxes of box_rows x 64, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TOKB200_BAD_SIZE;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {TC_BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
+}
+
+template <int BLOCK_N, int STAGES>
+static int launch_tc(const void* x, const void* w, const float* bias, void* out, int out_is_f32, int M,
+                     int N, int K, cudaStream_t stream) {
+  using S = TcSmem<BLOCK_N, STAGES>;
+  CUtensorMap map_x, map_w;
+  int status = make_map(&map_x, x, M, K, TC_BLOCK_M);
+  if (status != TOKB200_OK) return status;
+  status = make_map(&map_w, w, N, K, BLOCK_N);
+  if (status != TOKB200_OK) return status;
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+  if (!configured[device]) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N, STAGES>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (err != cudaSuccess) return (int)err;
+    configured[device] = true;
+  }
+  dim3 grid((M + TC_BLOCK_M - 1) / TC_BLOCK_M, (N + BLOCK_N - 1) / BLOCK_N);
+  return launch_dependent(gemm_tcgen05_kernel<BLOCK_N, STAGES>, grid, dim3(TC_THREADS),
+                          (size_t)S::kTotal, stream, map_x, map_w, bias, out, out_is_f32, M, N, K);
+}
+
+// 1 when some launch since the last call recorded a wait that ran out; clears the flag.
+TOKB200_API int tokb200_gemm_tcgen05_error(void) {
+  int flag = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&flag, tc_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (flag) cudaMemcpyToSymbol(tc_error_flag, &zero, sizeof(int));
+  return flag;
+}
+
+TOKB200_API int tokb200_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out,
+                                     int out_is_f32, int M, int N, int K, int block_n,
+                                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (K <= 0 || K % 8) return TOKB200_BAD_SIZE;          // TMA: row pitch a multiple of 16 bytes
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (((uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  switch (block_n) {
+    case 64: return launch_tc<64, 4>(x, w, bias, out, out_is_f32, M, N, K, stream);
+    case 128: return launch_tc<128, 3>(x, w, bias, out, out_is_f32, M, N, K, stream);
+    case 256: return launch_tc<256, 4>(x, w, bias, out, out_is_f32, M, N, K, stream);
+    default: return TOKB200_BAD_SIZE;
+  }
+}

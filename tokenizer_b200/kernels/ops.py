@@ -302,3 +302,32 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     scratch, counters = _argmax_scratch[key]
     _check(lib.tokb200_argmax(_ptr(logits), _i(n_rows), _i(vocab), _ptr(out), _ptr(scratch),
                               _ptr(counters), _stream()), "argmax")
+
+
+def gemm_tcgen05_supported(M: int, N: int, K: int) -> bool:
+    return M > 0 and N > 0 and K > 0 and K % 8 == 0
+
+
+def gemm_tcgen05(a, w, bias, out, block_n: int = 0) -> None:
+    """out[M,N] = a[M,K] w[N,K]^T (+ bias) on tcgen05 tensor cores with TMA-fed
+    operands; bfloat16 in, bfloat16 or float32 out.  K must be a multiple of 8."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("gemm_tcgen05: bfloat16 a [M,K] and w [N,K]")
+    if not gemm_tcgen05_supported(M, N, K):
+        raise ValueError(f"gemm_tcgen05: K = {K} must be a multiple of 8")
+    if tuple(out.shape) != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("gemm_tcgen05: out is [M,N] bfloat16 or float32")
+    if not block_n:
+        block_n = 256 if (N >= 2048 and M >= 1024) else (128 if N > 64 else 64)
+    _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
+        _i(M), _i(N), _i(K), _i(block_n), _stream()), "gemm_tcgen05")
+
+
+def gemm_tcgen05_check() -> None:
+    """Raise if a bounded wait inside the tensor-core product ran out since the last check."""
+    flag = _lib("gemm_tcgen05").tokb200_gemm_tcgen05_error()
+    if flag:
+        raise KernelError("gemm_tcgen05: a wait on the device ran out (status %d)" % flag)
