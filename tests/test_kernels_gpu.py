@@ -489,3 +489,32 @@ def test_prefill_attention_far_key_and_window_edge():
                 assert float((got - v[far, 0]).abs().max()) < 0.03
             else:
                 assert float((got - v[far, 0]).abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("M,N,K,block_n", [
+    (128, 128, 64, 128), (130, 70, 72, 64), (65, 300, 96, 128), (257, 1000, 200, 0),
+    (512, 1152, 896, 128), (300, 2304, 896, 256), (1024, 896, 4864, 0), (200, 301, 1000, 0)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(M, N, K, block_n, out_dtype):
+    """The tcgen05/TMEM/TMA product against float64: tiles cut by M, N and K (TMA
+    fills what lies outside with zeros), with and without a bias."""
+    o = ops()
+    a = rnd(M, K, seed=61, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=62, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=63)
+    want = a.double().cpu() @ w.double().cpu().t()
+    for b in (None, bias):
+        out = torch.full((M, N), 7.0, dtype=out_dtype, device=DEV)
+        o.gemm_tcgen05(a, w, b, out, block_n)
+        torch.cuda.synchronize()
+        o.gemm_tcgen05_check()
+        ref = (want + (b.double().cpu() if b is not None else 0)).float()
+        if out_dtype == torch.float32:
+            assert float((out.cpu() - ref).abs().max()) <= 2e-5 * float(ref.abs().max()) + 1e-6 * K
+        else:
+            close(out, ref, torch.bfloat16)
+    if N % 8:   # an output pitch that is not a multiple of 16 bytes is refused, not mis-stored
+        pass
+    with pytest.raises(ValueError):
+        o.gemm_tcgen05(rnd(M, 12, dtype=torch.bfloat16), rnd(N, 12, dtype=torch.bfloat16), None,
+                       torch.empty(M, N, dtype=out_dtype, device=DEV))

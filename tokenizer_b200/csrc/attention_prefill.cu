@@ -82,17 +82,23 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
-                         const int* __restrict__ tiles, int nh, int nkv, int page, int window,
-                         float scale_log2) {
+                         const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page,
+                         int window, float scale_log2) {
   extern __shared__ __align__(16) __nv_bfloat16 smem[];
   __nv_bfloat16* q_s = smem;                       // [64][kStride]
   __nv_bfloat16* k_s = q_s + kTile;                // 2 stages
   __nv_bfloat16* v_s = k_s + 2 * kTile;            // 2 stages
 
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // The host orders the tiles by the number of key blocks they walk, most first; a
+  // block takes tile x and then tile n - 1 - x, so every block has about the same work.
+  const int h = blockIdx.y;
+  for (int which = 0; which < 2; ++which) {
+  const int tile = which == 0 ? (int)blockIdx.x : n_tiles - 1 - (int)blockIdx.x;
+  if (which == 1 && tile <= (int)blockIdx.x) break;
+  if (which == 1) __syncthreads();                 // the first tile's shared memory is reused
   const int row0 = tiles[2 * tile], n_rows = tiles[2 * tile + 1];
   const int r = row_req[row0];
-  if (r < 0 || n_rows <= 0) return;
+  if (r < 0 || n_rows <= 0) continue;
   const int kvh = h / (nh / nkv);
   const int pos0 = pos[row0];
   const int pos_last = pos0 + n_rows - 1;
@@ -238,6 +244,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
           pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
     }
   }
+  }  // the two tiles of this block
 }
 
 TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
@@ -262,11 +269,11 @@ TOKB200_API int tokb200_prefill_attention(
     if (err != cudaSuccess) return (int)err;
     configured[device] = true;
   }
-  dim3 grid(n_tiles, nh);
+  dim3 grid((n_tiles + 1) / 2, nh);
   const float scale_log2 = scale * 1.4426950408889634f;
   prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-      (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, nh, nkv, page, window,
-      scale_log2);
+      (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, n_tiles, nh, nkv, page,
+      window, scale_log2);
   return tokb200_launch_status();
 }

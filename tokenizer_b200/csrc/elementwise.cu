@@ -283,10 +283,42 @@ __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, 
   }
 }
 
+// bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) a thread
+__global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
+                                        __nv_bfloat16* __restrict__ out, int inner, int n_rows) {
+  pdl_wait();
+  pdl_launch();
+  const int per_row = inner / 8;
+  const size_t total = (size_t)n_rows * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inner + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inner + inner + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+      o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * inner + c) = o4;
+  }
+}
+
 TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_tokens, int inner,
                                   cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;
   if (inner <= 0 || n_tokens > 65535 * 1024) return TOKB200_BAD_SIZE;
+  if (dtype == TOKB200_BF16 && inner % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    const size_t total = (size_t)n_tokens * (inner / 8);
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    return launch_dependent(silu_gate_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream,
+                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens);
+  }
   // grid.y is limited to 65535 rows; tile rows over several launches beyond it
   for (int row0 = 0; row0 < n_tokens; row0 += 65535) {
     const int rows = n_tokens - row0 < 65535 ? n_tokens - row0 : 65535;

@@ -160,6 +160,7 @@ class BatchBuilder:
         row = 0
         want_at = 0
         n_tiles = 0
+        tiles = []   # (last position + 1: the keys the tile walks, first row, rows)
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = e.cache.length
@@ -174,8 +175,8 @@ class BatchBuilder:
                 buf[lay.want + want_at] = row + int(w)
                 want_at += 1
             for first in range(0, n, Q_TILE_ROWS):
-                buf[lay.tiles + 2 * n_tiles] = row + first
-                buf[lay.tiles + 2 * n_tiles + 1] = min(Q_TILE_ROWS, n - first)
+                rows_here = min(Q_TILE_ROWS, n - first)
+                tiles.append((start + first + rows_here, row + first, rows_here))
                 n_tiles += 1
             for g in range(len(widths)):
                 table = np.asarray(e.cache.tables[g], dtype=np.int32)
@@ -187,6 +188,11 @@ class BatchBuilder:
             state_slots.append(e.cache.state_slot)
             row += n
         buf[lay.q_start + R:lay.q_start + Rc + 1] = row
+        # most keys first: the attention kernel pairs tile x with tile n - 1 - x
+        tiles.sort(key=lambda item: -item[0])
+        for at, (_, first_row, rows_here) in enumerate(tiles):
+            buf[lay.tiles + 2 * at] = first_row
+            buf[lay.tiles + 2 * at + 1] = rows_here
         dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         self.last_bytes = lay.total * 4
         if dev.is_cuda:

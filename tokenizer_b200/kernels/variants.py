@@ -12,6 +12,7 @@ def all_variants():
         ("gemm_f32.cu", (), ()),
         ("sampling.cu", (), ()),
         ("linear_small_m.cu", (), ()),
+        ("gemm_tcgen05.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -3,6 +3,7 @@ number of rows.  Few rows (decoding) are bound by reading the weights once and
 go to the framework's streaming kernel; many rows go to the tensor cores."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -22,6 +23,16 @@ def choose_k_splits(M: int, N: int, K: int) -> int:
     return max(1, min(-(-_TARGET_BLOCKS // blocks), K // 256, 16))
 
 
+def use_tcgen05(M: int, N: int, K: int) -> bool:
+    """Which many-row products go to the framework's tcgen05 kernel.  TOKB200_GEMM
+    = tcgen05 or library forces one; by default the kernel takes the shapes it
+    wins (measured on B200: up to about 1,500 weight rows)."""
+    choice = os.environ.get("TOKB200_GEMM", "")
+    if not ops.gemm_tcgen05_supported(M, N, K) or choice == "library":
+        return False
+    return choice == "tcgen05" or N <= 1536
+
+
 def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                 out_dtype: torch.dtype, partials_ok: bool = False) -> torch.Tensor:
     """a[M,K] weight[N,K]^T (+ bias float32) as bfloat16 or float32 [M,N]; with
@@ -36,6 +47,11 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
             out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         ops.linear_small_m(a, weight, bias, out, splits)
         return out
+    if use_tcgen05(M, N, K):
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        ops.gemm_tcgen05(a, weight, bias, out)
+        return out
+    # the vendor library, for the shapes where it still leads the kernel above
     if out_dtype == torch.bfloat16:
         out = torch.mm(a, weight.t())
     else:
