@@ -59,21 +59,28 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Stage the keys (or values) key0 .. key0 + 63 of one kv head; keys outside
-// [first_ok, last_ok] are zero-filled and their pages are not touched.
-__device__ __forceinline__ void stage_tile(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pool,
-                                           const int* __restrict__ table, int page, int nkv, int kvh,
-                                           int key0, int first_ok, int last_ok) {
-  for (int i = threadIdx.x; i < PF_KEYS * kChunks; i += PF_THREADS) {
-    const int j = i / kChunks, c = i % kChunks;
-    const int key = key0 + j;
-    const bool ok = key >= first_ok && key <= last_ok;
-    const __nv_bfloat16* src = pool;
-    if (ok) {
-      const int slot = table[key / page] * page + key % page;
-      src = pool + ((size_t)slot * nkv + kvh) * HEAD_DIM + c * 8;
-    }
-    cp_async16(dst + j * kStride + c * 8, src, ok);
+// Stage the keys and the values key0 .. key0 + 63 of one kv head.  Two threads
+// share a key: one look-up in the block table serves the key's and the value's row,
+// and all of a thread's copies are issued behind that single dependent load.  Keys
+// outside [first_ok, last_ok] are zero-filled and their pages are not touched.
+__device__ __forceinline__ void stage_kv(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
+                                         const __nv_bfloat16* __restrict__ k_pool,
+                                         const __nv_bfloat16* __restrict__ v_pool,
+                                         const int* __restrict__ table, int page, int nkv, int kvh,
+                                         int key0, int first_ok, int last_ok) {
+  static_assert(PF_THREADS == 2 * PF_KEYS && kChunks % 2 == 0, "two threads a key");
+  const int j = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * (kChunks / 2);
+  const int key = key0 + j;
+  const bool ok = key >= first_ok && key <= last_ok;
+  size_t offset = 0;
+  if (ok) {
+    const int slot = table[key / page] * page + key % page;
+    offset = ((size_t)slot * nkv + kvh) * HEAD_DIM;
+  }
+#pragma unroll
+  for (int c = 0; c < kChunks / 2; ++c) {
+    cp_async16(k_dst + j * kStride + (c0 + c) * 8, k_pool + offset + (c0 + c) * 8, ok);
+    cp_async16(v_dst + j * kStride + (c0 + c) * 8, v_pool + offset + (c0 + c) * 8, ok);
   }
 }
 
@@ -116,8 +123,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   }
   const int kb_first = lo_first / PF_KEYS * PF_KEYS;
   const int n_blocks = (pos_last - kb_first) / PF_KEYS + 1;
-  stage_tile(k_s, k_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
-  stage_tile(v_s, v_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
+  stage_kv(k_s, v_s, k_pool, v_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
   cp_async_commit();
 
   // per thread: rows g and g + 8 of the warp's 16
@@ -138,8 +144,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int kb = kb_first + b * PF_KEYS;
     const int stage = b & 1;
     if (b + 1 < n_blocks) {
-      stage_tile(k_s + (stage ^ 1) * kTile, k_pool, table, page, nkv, kvh, kb + PF_KEYS, lo_first, pos_last);
-      stage_tile(v_s + (stage ^ 1) * kTile, v_pool, table, page, nkv, kvh, kb + PF_KEYS, lo_first, pos_last);
+      stage_kv(k_s + (stage ^ 1) * kTile, v_s + (stage ^ 1) * kTile, k_pool, v_pool, table, page, nkv,
+               kvh, kb + PF_KEYS, lo_first, pos_last);
       cp_async_commit();
       cp_async_wait<1>();
     } else {

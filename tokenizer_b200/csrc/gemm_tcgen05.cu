@@ -231,6 +231,190 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
+// ----------------------------------------------------------------------------
+// The persistent form, for outputs whose row pitch is a multiple of 16 bytes: one
+// CTA per SM walks output tiles (tile t = blockIdx.x + i * gridDim.x, m fastest so
+// that CTAs running side by side share a tile of W in L2).  The accumulator is
+// double-buffered in tensor memory (2 x BLOCK_N columns), so the epilogue of a
+// tile overlaps the products of the next; the epilogue stages the tile in shared
+// memory (128-byte swizzled slabs) and writes it with TMA stores, which also clip
+// what lies past M and N.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(tc_smem(src)), "r"(x), "r"(y) : "memory");
+}
+
+template <int BLOCK_N, int STAGES, bool OUT_F32>
+struct TcPersistentSmem {
+  static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2;
+  static constexpr int kBBytes = BLOCK_N * TC_BLOCK_K * 2;
+  static constexpr int kStage = kABytes + kBBytes;
+  static constexpr int kSlabCols = OUT_F32 ? 32 : 64;                  // 128 bytes of output
+  static constexpr int kSlabs = BLOCK_N / kSlabCols;
+  static constexpr int kSlabBytes = TC_BLOCK_M * 128;
+  static constexpr int kOutBytes = kSlabs * kSlabBytes;
+  static constexpr int kTotal = STAGES * kStage + kOutBytes + 1024 + 256;
+};
+
+template <int BLOCK_N, int STAGES, bool OUT_F32>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
+                               const __grid_constant__ CUtensorMap map_w,
+                               const __grid_constant__ CUtensorMap map_out,
+                               const float* __restrict__ bias, int M, int N, int K) {
+  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
+  extern __shared__ unsigned char tc_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* staging = tiles + STAGES * S::kStage;                 // 1024-aligned as well
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(staging + S::kOutBytes);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_full = empty + STAGES;
+  unsigned long long* acc_empty = acc_full + 2;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + TC_BLOCK_M - 1) / TC_BLOCK_M;
+  const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tc_smem(tmem_slot)), "r"((unsigned)(2 * BLOCK_N)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;                                   // k blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { ok = false; break; }   // fresh barriers pass
+          unsigned char* a_tile = tiles + s * S::kStage;
+          mbar_expect_tx(&full[s], S::kStage);
+          tma_load_2d(a_tile, &map_x, &full[s], kb * TC_BLOCK_K, m0);
+          tma_load_2d(a_tile + S::kABytes, &map_w, &full[s], kb * TC_BLOCK_K, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BLOCK_N >> 3) << 17) |
+                             ((unsigned)(TC_BLOCK_M >> 4) << 24);
+      int it = 0, round = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++round) {
+        const int buf = round & 1;
+        if (!mbar_wait(&acc_empty[buf], ((round >> 1) & 1) ^ 1)) break;     // the epilogue has drained it
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned tmem_d = tmem_base + (unsigned)(buf * BLOCK_N);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned char* a_tile = tiles + s * S::kStage;
+          const unsigned long long a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k)
+            umma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;              // this thread's row of the tile
+    const bool issuer = warp == 2 && lane == 0;     // the thread that issues the TMA stores
+    int round = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+      const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
+      const int buf = round & 1;
+      if (!mbar_wait(&acc_full[buf], (round >> 1) & 1)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // the stores of the previous tile must have read the staging area
+      if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      epilogue_barrier();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+        unsigned v[32];
+        tmem_load_32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BLOCK_N + c0), v);
+        if (OUT_F32) {
+          // a slab is 32 columns: row r holds 8 pieces of 16 bytes, piece j at (j ^ (r % 8))
+          unsigned char* slab = staging + (c0 / 32) * S::kSlabBytes + r * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * j]) + (bias && n0 + c0 + 4 * j < N ? bias[n0 + c0 + 4 * j] : 0.f);
+            o.y = __uint_as_float(v[4 * j + 1]) + (bias && n0 + c0 + 4 * j + 1 < N ? bias[n0 + c0 + 4 * j + 1] : 0.f);
+            o.z = __uint_as_float(v[4 * j + 2]) + (bias && n0 + c0 + 4 * j + 2 < N ? bias[n0 + c0 + 4 * j + 2] : 0.f);
+            o.w = __uint_as_float(v[4 * j + 3]) + (bias && n0 + c0 + 4 * j + 3 < N ? bias[n0 + c0 + 4 * j + 3] : 0.f);
+            *reinterpret_cast<float4*>(slab + ((j ^ (r & 7)) << 4)) = o;
+          }
+        } else {
+          // a slab is 64 columns: these 32 are pieces 4 * (c0 / 32 % 2) .. + 3 of row r
+          unsigned char* slab = staging + (c0 / 64) * S::kSlabBytes + r * 128;
+          const int piece0 = (c0 / 32 % 2) * 4;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int col = n0 + c0 + 8 * j + 2 * e;
+              const float lo = __uint_as_float(v[8 * j + 2 * e]) + (bias && col < N ? bias[col] : 0.f);
+              const float hi = __uint_as_float(v[8 * j + 2 * e + 1]) + (bias && col + 1 < N ? bias[col + 1] : 0.f);
+              __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+              ow[e] = *reinterpret_cast<unsigned*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(slab + (((piece0 + j) ^ (r & 7)) << 4)) = o;
+          }
+        }
+      }
+      // the accumulator buffer is free for the products of the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> TMA reads
+      epilogue_barrier();
+      if (issuer) {
+#pragma unroll 1
+        for (int sl = 0; sl < S::kSlabs; ++sl)
+          if (n0 + sl * S::kSlabCols < N)
+            tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // before the CTA's memory goes
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  pdl_launch();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((unsigned)(2 * BLOCK_N)) : "memory");
+  }
+}
+
 // ---- host side ----------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -261,6 +445,51 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
+}
+
+// A map over the row-major [M, N] output, boxes of 128 rows x 128 bytes, 128-byte swizzle.
+static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, bool f32) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TOKB200_BAD_SIZE;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * (f32 ? 4 : 2)};
+  const cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : 64), TC_BLOCK_M};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                  dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
+}
+
+template <int BLOCK_N, int STAGES, bool OUT_F32>
+static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
+                                int K, cudaStream_t stream) {
+  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
+  static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
+  CUtensorMap map_x, map_w, map_out;
+  int status = make_map(&map_x, x, M, K, TC_BLOCK_M);
+  if (status != TOKB200_OK) return status;
+  status = make_map(&map_w, w, N, K, BLOCK_N);
+  if (status != TOKB200_OK) return status;
+  status = make_out_map(&map_out, out, M, N, OUT_F32);
+  if (status != TOKB200_OK) return status;
+  static bool configured[64] = {};
+  static int sm_count[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+  if (!configured[device]) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (err != cudaSuccess) return (int)err;
+    err = cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device);
+    if (err != cudaSuccess) return (int)err;
+    configured[device] = true;
+  }
+  const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
+  dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
+  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32>, grid,
+                          dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out, bias, M, N,
+                          K);
 }
 
 template <int BLOCK_N, int STAGES>
@@ -302,6 +531,20 @@ TOKB200_API int tokb200_gemm_tcgen05(const void* x, const void* w, const float* 
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
   if (((uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  // block_n + 1000 asks for the persistent kernel (TMA-stored output): the output's
+  // row pitch must then be a multiple of 16 bytes
+  if (block_n >= 1000) {
+    if ((out_is_f32 ? N % 4 : N % 8) != 0) return TOKB200_BAD_SIZE;
+    switch (block_n - 1000) {
+      case 128:
+        return out_is_f32 ? launch_tc_persistent<128, 4, true>(x, w, bias, out, M, N, K, stream)
+                          : launch_tc_persistent<128, 5, false>(x, w, bias, out, M, N, K, stream);
+      case 256:
+        return out_is_f32 ? TOKB200_BAD_SIZE
+                          : launch_tc_persistent<256, 3, false>(x, w, bias, out, M, N, K, stream);
+      default: return TOKB200_BAD_SIZE;
+    }
+  }
   switch (block_n) {
     case 64: return launch_tc<64, 4>(x, w, bias, out, out_is_f32, M, N, K, stream);
     case 128: return launch_tc<128, 3>(x, w, bias, out, out_is_f32, M, N, K, stream);

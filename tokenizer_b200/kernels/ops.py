@@ -320,7 +320,12 @@ def gemm_tcgen05(a, w, bias, out, block_n: int = 0) -> None:
     if tuple(out.shape) != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("gemm_tcgen05: out is [M,N] bfloat16 or float32")
     if not block_n:
-        block_n = 256 if (N >= 2048 and M >= 1024) else (128 if N > 64 else 64)
+        pitch_ok = N % (4 if out.dtype == torch.float32 else 8) == 0
+        if pitch_ok and M * N >= 128 * 128 * 32:
+            # persistent kernel, TMA-stored output: the wide tile where it divides the work well
+            block_n = 1256 if (out.dtype == torch.bfloat16 and N >= 2048) else 1128
+        else:
+            block_n = 128 if N > 64 else 64
     _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
         _i(M), _i(N), _i(K), _i(block_n), _stream()), "gemm_tcgen05")
