@@ -518,3 +518,27 @@ def test_gemm_tcgen05(M, N, K, block_n, out_dtype):
     with pytest.raises(ValueError):
         o.gemm_tcgen05(rnd(M, 12, dtype=torch.bfloat16), rnd(N, 12, dtype=torch.bfloat16), None,
                        torch.empty(M, N, dtype=out_dtype, device=DEV))
+
+
+@pytest.mark.parametrize("M,inner,K", [(1, 128, 64), (8, 256, 96), (5, 4864, 896), (33, 384, 200),
+                                       (64, 128, 72), (65, 128, 64), (300, 640, 896), (2048, 1280, 128)])
+def test_gated_linear(M, inner, K):
+    """Gate and up products with silu(gate) * up folded into the epilogue, for few
+    rows (streaming kernel) and many (tcgen05), from the interleaved weight."""
+    o = ops()
+    x = rnd(M, K, seed=71, dtype=torch.bfloat16)
+    gate = rnd(inner, K, seed=72, dtype=torch.bfloat16, scale=0.2)
+    up = rnd(inner, K, seed=73, dtype=torch.bfloat16, scale=0.2)
+    w = o.interleave_gate_up(gate, up)
+    assert w.shape == (2 * inner, K)
+    assert torch.equal(w[:128], gate[:128]) and torch.equal(w[128:256], up[:128])
+    out = torch.full((M, inner), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gated_linear(x, w, out)
+    torch.cuda.synchronize()
+    if M > 64:
+        o.gemm_tcgen05_check()
+    g = x.double().cpu() @ gate.double().cpu().t()
+    u = x.double().cpu() @ up.double().cpu().t()
+    close(out, (g * torch.sigmoid(g) * u).float(), torch.bfloat16)
+    with pytest.raises(ValueError):
+        o.gated_linear(x, w[:-8], torch.empty(M, inner - 4, dtype=torch.bfloat16, device=DEV))

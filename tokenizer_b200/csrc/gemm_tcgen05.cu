@@ -261,13 +261,17 @@ struct TcPersistentSmem {
   static constexpr int kTotal = STAGES * kStage + kOutBytes + 1024 + 256;
 };
 
-template <int BLOCK_N, int STAGES, bool OUT_F32>
+// GATED: the weight rows come in blocks of 256 = 128 "gate" rows followed by the 128
+// "up" rows of the same outputs; the epilogue writes silu(gate) * up, 128 columns a
+// tile, and the 2 N wide product never goes to memory.
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_out,
                                const float* __restrict__ bias, int M, int N, int K) {
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
+  static_assert(!GATED || (BLOCK_N == 256 && !OUT_F32), "the gated epilogue pairs two halves of a 256 tile");
   extern __shared__ unsigned char tc_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
@@ -354,6 +358,31 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
       // the stores of the previous tile must have read the staging area
       if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       epilogue_barrier();
+      if (GATED) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          unsigned gate[32], up[32];
+          const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BLOCK_N);
+          tmem_load_32(lane_base + (unsigned)c0, gate);
+          tmem_load_32(lane_base + (unsigned)(128 + c0), up);
+          unsigned char* slab = staging + (c0 / 64) * S::kSlabBytes + r * 128;
+          const int piece0 = (c0 / 32 % 2) * 4;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float g0 = __uint_as_float(gate[8 * j + 2 * e]), g1 = __uint_as_float(gate[8 * j + 2 * e + 1]);
+              const float u0 = __uint_as_float(up[8 * j + 2 * e]), u1 = __uint_as_float(up[8 * j + 2 * e + 1]);
+              __nv_bfloat162 pair = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0,
+                                                          g1 / (1.0f + expf(-g1)) * u1);
+              ow[e] = *reinterpret_cast<unsigned*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(slab + (((piece0 + j) ^ (r & 7)) << 4)) = o;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
         unsigned v[32];
@@ -390,16 +419,24 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
           }
         }
       }
+      }
       // the accumulator buffer is free for the products of the tile after next
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> TMA reads
       epilogue_barrier();
       if (issuer) {
+        if (GATED) {   // the tile's 128 output columns start at n0 / 2
 #pragma unroll 1
-        for (int sl = 0; sl < S::kSlabs; ++sl)
-          if (n0 + sl * S::kSlabCols < N)
-            tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+          for (int sl = 0; sl < 2; ++sl)
+            if (n0 / 2 + sl * 64 < N / 2)
+              tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 / 2 + sl * 64, m0);
+        } else {
+#pragma unroll 1
+          for (int sl = 0; sl < S::kSlabs; ++sl)
+            if (n0 + sl * S::kSlabCols < N)
+              tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
@@ -461,7 +498,7 @@ static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, 
   return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
 }
 
-template <int BLOCK_N, int STAGES, bool OUT_F32>
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false>
 static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
                                 int K, cudaStream_t stream) {
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
@@ -471,14 +508,14 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   if (status != TOKB200_OK) return status;
   status = make_map(&map_w, w, N, K, BLOCK_N);
   if (status != TOKB200_OK) return status;
-  status = make_out_map(&map_out, out, M, N, OUT_F32);
+  status = make_out_map(&map_out, out, M, GATED ? N / 2 : N, OUT_F32);
   if (status != TOKB200_OK) return status;
   static bool configured[64] = {};
   static int sm_count[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
   if (!configured[device]) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32>,
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (err != cudaSuccess) return (int)err;
     err = cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device);
@@ -487,7 +524,7 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   }
   const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
   dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
-  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32>, grid,
+  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED>, grid,
                           dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out, bias, M, N,
                           K);
 }
@@ -551,4 +588,15 @@ TOKB200_API int tokb200_gemm_tcgen05(const void* x, const void* w, const float* 
     case 256: return launch_tc<256, 4>(x, w, bias, out, out_is_f32, M, N, K, stream);
     default: return TOKB200_BAD_SIZE;
   }
+}
+
+// out[M, N/2] = silu(x Wg^T) * (x Wu^T) where w [N, K] holds, for every 128 outputs,
+// their 128 gate rows followed by their 128 up rows (N a multiple of 256).
+TOKB200_API int tokb200_gemm_tcgen05_gated(const void* x, const void* w, void* out, int M, int N, int K,
+                                           cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (K <= 0 || K % 8 || N % 256) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  return launch_tc_persistent<256, 3, false, true>(x, w, nullptr, out, M, N, K, stream);
 }

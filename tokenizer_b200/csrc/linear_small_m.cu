@@ -37,7 +37,10 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool ok) {
 
 // MT: tiles of 8 rows of x (M <= 8 MT).  TPB: row tiles of W per block; the
 // block's warps split into TPB teams of LSM_WARPS / TPB warps, a team per row tile.
-template <int MT, int TPB>
+// GATED: w [N, K] holds, for every 128 outputs, their 128 "gate" rows followed by
+// their 128 "up" rows; a row tile is then 8 gate rows and the 8 up rows of the same
+// outputs, and the result is silu(gate) * up, [M, N / 2].
+template <int MT, int TPB, bool GATED>
 __global__ void __launch_bounds__(LSM_THREADS)
 linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                       const float* __restrict__ bias, void* __restrict__ out, int out_is_f32,
@@ -56,9 +59,16 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 #pragma unroll
   for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
-  const bool row_a_ok = row0 + g < N, row_b_ok = row0 + g + 8 < N;
-  const __nv_bfloat16* wa = w + (size_t)(row0 + g) * K + 8 * t;
-  const __nv_bfloat16* wb = w + (size_t)(row0 + g + 8) * K + 8 * t;
+  // the weight rows behind rows g and g + 8 of the tile
+  int row_a = row0 + g, row_b = row0 + g + 8;
+  if (GATED) {
+    const int out0 = (blockIdx.x * TPB + team) * 8;           // 8 outputs a tile
+    row_a = (out0 / 128) * 256 + out0 % 128 + g;
+    row_b = row_a + 128;
+  }
+  const bool row_a_ok = row_a < N, row_b_ok = row_b < N;
+  const __nv_bfloat16* wa = w + (size_t)row_a * K + 8 * t;
+  const __nv_bfloat16* wb = w + (size_t)row_b * K + 8 * t;
 
   // A ring of LSM_PRE steps of weights is requested before the wait on the
   // predecessor (weights are written by no kernel of the step); x, which the
@@ -107,6 +117,24 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   }
   __syncthreads();
 
+  if (GATED) {
+    const int half = N / 2;
+    for (int i = threadIdx.x; i < TPB * 8 * M; i += LSM_THREADS) {
+      const int tm = i / (8 * M);
+      const int m = (i / 8) % M, rr = i % 8;
+      const int n = (blockIdx.x * TPB + tm) * 8 + rr;
+      if (n >= half) continue;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int s = 0; s < TEAM; ++s) {
+        gate += part[tm * TEAM + s][rr][m];
+        up += part[tm * TEAM + s][rr + 8][m];
+      }
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * half + n] =
+          __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+    }
+    return;
+  }
   // each team's 16 x M results: consecutive threads take consecutive weight rows (n)
   const bool partial = gridDim.y > 1;
   for (int i = threadIdx.x; i < TPB * 16 * M; i += LSM_THREADS) {
@@ -128,6 +156,21 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 }
 
 template <int MT>
+static int launch_small_m_gated(const void* x, const void* w, void* out, int M, int N, int K,
+                                cudaStream_t stream) {
+  const int tiles = (N / 2 + 7) / 8;
+  const int k_per_split = (K + 31) / 32 * 32;
+  if (tiles >= 1024) {
+    return launch_dependent(linear_small_m_kernel<MT, 2, true>, dim3((tiles + 1) / 2), dim3(LSM_THREADS),
+                            0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                            (const float*)nullptr, out, 0, M, N, K, k_per_split);
+  }
+  return launch_dependent(linear_small_m_kernel<MT, 1, true>, dim3(tiles), dim3(LSM_THREADS), 0, stream,
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)nullptr, out,
+                          0, M, N, K, k_per_split);
+}
+
+template <int MT>
 static int launch_small_m(const void* x, const void* w, const float* bias, void* out,
                           int out_is_f32, int M, int N, int K, int k_splits,
                           cudaStream_t stream) {
@@ -137,12 +180,12 @@ static int launch_small_m(const void* x, const void* w, const float* bias, void*
   // many row tiles: two per block (teams of 4 warps); few: one per block (8 warps on its k)
   if (tiles >= 1024) {
     dim3 grid((tiles + 1) / 2, k_splits);
-    return launch_dependent(linear_small_m_kernel<MT, 2>, grid, dim3(LSM_THREADS), 0, stream,
+    return launch_dependent(linear_small_m_kernel<MT, 2, false>, grid, dim3(LSM_THREADS), 0, stream,
                             (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
                             M, N, K, k_per_split);
   }
   dim3 grid(tiles, k_splits);
-  return launch_dependent(linear_small_m_kernel<MT, 1>, grid, dim3(LSM_THREADS), 0, stream,
+  return launch_dependent(linear_small_m_kernel<MT, 1, false>, grid, dim3(LSM_THREADS), 0, stream,
                           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
                           M, N, K, k_per_split);
 }
@@ -160,4 +203,17 @@ TOKB200_API int tokb200_linear_small_m(const void* x, const void* w, const float
   if (M <= 16) return launch_small_m<2>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
   if (M <= 32) return launch_small_m<4>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
   return launch_small_m<8>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
+}
+
+// out[M, N/2] (bfloat16) = silu(x Wg^T) * (x Wu^T), w in the 128-gate / 128-up row
+// blocks described at the kernel (N a multiple of 256).
+TOKB200_API int tokb200_linear_small_m_gated(const void* x, const void* w, void* out, int M, int N,
+                                             int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (M > 64 || K <= 0 || K % 8 || N % 256) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M <= 8) return launch_small_m_gated<1>(x, w, out, M, N, K, stream);
+  if (M <= 16) return launch_small_m_gated<2>(x, w, out, M, N, K, stream);
+  if (M <= 32) return launch_small_m_gated<4>(x, w, out, M, N, K, stream);
+  return launch_small_m_gated<8>(x, w, out, M, N, K, stream);
 }

@@ -336,3 +336,33 @@ def gemm_tcgen05_check() -> None:
     flag = _lib("gemm_tcgen05").tokb200_gemm_tcgen05_error()
     if flag:
         raise KernelError("gemm_tcgen05: a wait on the device ran out (status %d)" % flag)
+
+
+def gated_linear_supported(K: int, N: int) -> bool:
+    """Gate and up products with the activation folded into the epilogue: the
+    stacked weight is laid out in blocks of 128 gate rows + 128 up rows."""
+    return K % 8 == 0 and N % 256 == 0
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[gate rows 0..127, up rows 0..127, gate rows 128..255, ...]: the layout the
+    gated kernels read (both have I rows, I a multiple of 128)."""
+    inner, k = gate.shape
+    return torch.stack([gate.view(inner // 128, 128, k), up.view(inner // 128, 128, k)], dim=1) \
+        .reshape(2 * inner, k).contiguous()
+
+
+def gated_linear(x, w, out) -> None:
+    """out[M, N/2] = silu(x Wg^T) * (x Wu^T) for w from `interleave_gate_up`."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise ValueError("gated_linear is the bfloat16 kernel")
+    if not gated_linear_supported(K, N) or w.shape[1] != K or tuple(out.shape) != (M, N // 2):
+        raise ValueError("gated_linear: K a multiple of 8, N of 256, out [M, N/2]")
+    if M <= 64:
+        _check(_lib("linear_small_m").tokb200_linear_small_m_gated(
+            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")
+    else:
+        _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_gated(
+            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")

@@ -28,14 +28,24 @@ class GatedMLP:
             raise ConfigError(f"gated feed-forward knows the silu activation, found {p['activation']}")
         self.runtime = runtime
         self.inner = int(p["intermediate_size"])
-        self.gate_up = Linear(runtime.matrix(torch.cat(
-            [store.get(x + ".gate_proj.weight"), store.get(x + ".up_proj.weight")], dim=0)))
+        gate, up = store.get(x + ".gate_proj.weight"), store.get(x + ".up_proj.weight")
+        hidden = int(p["hidden_size"])
+        # bfloat16 with sizes the gated kernels take: the activation is folded into the
+        # product's epilogue and the stacked weight is laid out for that
+        self.fused = runtime.dtype == torch.bfloat16 and self.inner % 128 == 0 and \
+            ops.gated_linear_supported(hidden, 2 * self.inner)
+        if self.fused:
+            self.gate_up_weight = ops.interleave_gate_up(runtime.matrix(gate), runtime.matrix(up))
+        else:
+            self.gate_up = Linear(runtime.matrix(torch.cat([gate, up], dim=0)))
         self.down = Linear(runtime.matrix(store.get(x + ".down_proj.weight")))
 
     def forward(self, h):
-        gu = self.gate_up.forward(h)
         act = self.runtime.empty(h.shape[0], self.inner)
-        ops.silu_gate(gu, act)
+        if self.fused:
+            ops.gated_linear(h, self.gate_up_weight, act)
+        else:
+            ops.silu_gate(self.gate_up.forward(h), act)
         return self.down.forward(act, partials_ok=True)
 
 

@@ -25,12 +25,10 @@ def choose_k_splits(M: int, N: int, K: int) -> int:
 
 def use_tcgen05(M: int, N: int, K: int) -> bool:
     """Which many-row products go to the framework's tcgen05 kernel.  TOKB200_GEMM
-    = tcgen05 or library forces one; by default the kernel takes the shapes it
-    wins (measured on B200: up to about 1,500 weight rows)."""
+    = library sends them to the vendor library instead (for comparisons); sizes
+    the kernel does not take (K not a multiple of 8) go there as well."""
     choice = os.environ.get("TOKB200_GEMM", "")
-    if not ops.gemm_tcgen05_supported(M, N, K) or choice == "library":
-        return False
-    return choice == "tcgen05" or N <= 1536
+    return ops.gemm_tcgen05_supported(M, N, K) and choice != "library"
 
 
 def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
