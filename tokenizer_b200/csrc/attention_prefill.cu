@@ -7,8 +7,8 @@
 // the tile can see to the tile's last position, and keep a running maximum, sum
 // and weighted value per row (the flash-attention recurrence).  Keys and values
 // are gathered from their pages into shared memory with 16-byte asynchronous
-// copies (two stages: the next block loads while this one is multiplied), so any
-// page size works.  q k^T and p v run on mma.sync m16n8k16 with fragments read by
+// copies, a ring of four blocks deep (the look-up in the block table runs one block
+// further ahead), so any page size works.  q k^T and p v run on mma.sync m16n8k16 with fragments read by
 // ldmatrix from rows padded by 16 bytes (conflict-free for every head size that
 // is a multiple of 16).  A row's arithmetic depends on its position, its window
 // and its place in its 64-row tile only.
@@ -24,6 +24,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 #define PF_ROWS 64          // rows of a tile (4 warps x 16)
 #define PF_KEYS 64          // keys of a block
 #define PF_THREADS 128
+#define PF_STAGES 4         // key/value blocks in flight
 constexpr int kStride = HEAD_DIM + 8;          // elements between rows in shared memory
 constexpr int kChunks = HEAD_DIM / 8;          // 16-byte pieces of a row
 constexpr int kTile = PF_KEYS * kStride;       // elements of one staged tile
@@ -59,28 +60,29 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Stage the keys and the values key0 .. key0 + 63 of one kv head.  Two threads
-// share a key: one look-up in the block table serves the key's and the value's row,
-// and all of a thread's copies are issued behind that single dependent load.  Keys
-// outside [first_ok, last_ok] are zero-filled and their pages are not touched.
+// Staging of the keys and the values key0 .. key0 + 63 of one kv head.  Two threads
+// share a key: one look-up in the block table serves the key's and the value's row.
+// The look-up (a dependent load) is made one block ahead of the copies that use it,
+// so the copies of a block are issued without waiting.  Keys outside [first_ok,
+// last_ok] are zero-filled and their pages are not touched (offset -1).
+__device__ __forceinline__ long long kv_row_offset(const int* __restrict__ table, int page, int nkv,
+                                                    int kvh, int key0, int first_ok, int last_ok) {
+  static_assert(PF_THREADS == 2 * PF_KEYS && kChunks % 2 == 0, "two threads a key");
+  const int key = key0 + (threadIdx.x >> 1);
+  if (key < first_ok || key > last_ok) return -1;
+  const int slot = table[key / page] * page + key % page;
+  return ((long long)slot * nkv + kvh) * HEAD_DIM;
+}
 __device__ __forceinline__ void stage_kv(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
                                          const __nv_bfloat16* __restrict__ k_pool,
-                                         const __nv_bfloat16* __restrict__ v_pool,
-                                         const int* __restrict__ table, int page, int nkv, int kvh,
-                                         int key0, int first_ok, int last_ok) {
-  static_assert(PF_THREADS == 2 * PF_KEYS && kChunks % 2 == 0, "two threads a key");
+                                         const __nv_bfloat16* __restrict__ v_pool, long long offset) {
   const int j = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * (kChunks / 2);
-  const int key = key0 + j;
-  const bool ok = key >= first_ok && key <= last_ok;
-  size_t offset = 0;
-  if (ok) {
-    const int slot = table[key / page] * page + key % page;
-    offset = ((size_t)slot * nkv + kvh) * HEAD_DIM;
-  }
+  const bool ok = offset >= 0;
+  const size_t at = ok ? (size_t)offset : 0;
 #pragma unroll
   for (int c = 0; c < kChunks / 2; ++c) {
-    cp_async16(k_dst + j * kStride + (c0 + c) * 8, k_pool + offset + (c0 + c) * 8, ok);
-    cp_async16(v_dst + j * kStride + (c0 + c) * 8, v_pool + offset + (c0 + c) * 8, ok);
+    cp_async16(k_dst + j * kStride + (c0 + c) * 8, k_pool + at + (c0 + c) * 8, ok);
+    cp_async16(v_dst + j * kStride + (c0 + c) * 8, v_pool + at + (c0 + c) * 8, ok);
   }
 }
 
@@ -93,8 +95,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          int window, float scale_log2) {
   extern __shared__ __align__(16) __nv_bfloat16 smem[];
   __nv_bfloat16* q_s = smem;                       // [64][kStride]
-  __nv_bfloat16* k_s = q_s + kTile;                // 2 stages
-  __nv_bfloat16* v_s = k_s + 2 * kTile;            // 2 stages
+  __nv_bfloat16* k_s = q_s + kTile;                // PF_STAGES tiles
+  __nv_bfloat16* v_s = k_s + PF_STAGES * kTile;    // PF_STAGES tiles
 
   // The host orders the tiles by the number of key blocks they walk, most first; a
   // block takes tile x and then tile n - 1 - x, so every block has about the same work.
@@ -123,8 +125,17 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   }
   const int kb_first = lo_first / PF_KEYS * PF_KEYS;
   const int n_blocks = (pos_last - kb_first) / PF_KEYS + 1;
-  stage_kv(k_s, v_s, k_pool, v_pool, table, page, nkv, kvh, kb_first, lo_first, pos_last);
-  cp_async_commit();
+  // fill the ring: blocks 0 .. PF_STAGES - 2 (q rides in the first group); a group is
+  // committed for every block, existing or not, so that group counts stay in step
+#pragma unroll
+  for (int b = 0; b < PF_STAGES - 1; ++b) {
+    if (b < n_blocks)
+      stage_kv(k_s + b * kTile, v_s + b * kTile, k_pool, v_pool,
+               kv_row_offset(table, page, nkv, kvh, kb_first + b * PF_KEYS, lo_first, pos_last));
+    cp_async_commit();
+  }
+  long long next_offset = PF_STAGES - 1 < n_blocks
+      ? kv_row_offset(table, page, nkv, kvh, kb_first + (PF_STAGES - 1) * PF_KEYS, lo_first, pos_last) : -1;
 
   // per thread: rows g and g + 8 of the warp's 16
   const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
@@ -142,16 +153,18 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 
   for (int b = 0; b < n_blocks; ++b) {
     const int kb = kb_first + b * PF_KEYS;
-    const int stage = b & 1;
-    if (b + 1 < n_blocks) {
-      stage_kv(k_s + (stage ^ 1) * kTile, v_s + (stage ^ 1) * kTile, k_pool, v_pool, table, page, nkv,
-               kvh, kb + PF_KEYS, lo_first, pos_last);
+    const int stage = b % PF_STAGES;
+    cp_async_wait<PF_STAGES - 2>();                 // block b has landed (for this thread)
+    __syncthreads();                                // ... for all; and block b - 1 is no longer read
+    {
+      const int nb = b + PF_STAGES - 1;             // goes where block b - 1 was
+      if (nb < n_blocks)
+        stage_kv(k_s + (nb % PF_STAGES) * kTile, v_s + (nb % PF_STAGES) * kTile, k_pool, v_pool,
+                 next_offset);
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+      next_offset = nb + 1 < n_blocks
+          ? kv_row_offset(table, page, nkv, kvh, kb_first + (nb + 1) * PF_KEYS, lo_first, pos_last) : -1;
     }
-    __syncthreads();
     if (b == 0) {
 #pragma unroll
       for (int ks = 0; ks < HEAD_DIM / 16; ++ks)
@@ -235,8 +248,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         mma16816(o[2 * dp + 1], pf, vf[2], vf[3]);
       }
     }
-    __syncthreads();   // this stage is overwritten by the load issued in the next iteration
   }
+  cp_async_wait<0>();
 
   // ---- write the rows that exist ----
 #pragma unroll
@@ -265,7 +278,7 @@ TOKB200_API int tokb200_prefill_attention(
     return TOKB200_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
     return TOKB200_BAD_ALIGNMENT;
-  const size_t smem = (size_t)5 * kTile * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(1 + 2 * PF_STAGES) * kTile * sizeof(__nv_bfloat16);
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;

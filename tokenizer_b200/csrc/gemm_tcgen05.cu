@@ -375,8 +375,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
             for (int e = 0; e < 4; ++e) {
               const float g0 = __uint_as_float(gate[8 * j + 2 * e]), g1 = __uint_as_float(gate[8 * j + 2 * e + 1]);
               const float u0 = __uint_as_float(up[8 * j + 2 * e]), u1 = __uint_as_float(up[8 * j + 2 * e + 1]);
-              __nv_bfloat162 pair = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0,
-                                                          g1 / (1.0f + expf(-g1)) * u1);
+              // silu in 32-bit with the fast exponential and reciprocal (a few ulp,
+              // far below the bfloat16 rounding of the result)
+              __nv_bfloat162 pair = __floats2bfloat162_rn(g0 * __frcp_rn(1.0f + __expf(-g0)) * u0,
+                                                          g1 * __frcp_rn(1.0f + __expf(-g1)) * u1);
               ow[e] = *reinterpret_cast<unsigned*>(&pair);
             }
             *reinterpret_cast<uint4*>(slab + (((piece0 + j) ^ (r & 7)) << 4)) = o;
