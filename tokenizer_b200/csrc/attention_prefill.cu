@@ -7,7 +7,7 @@
 // the tile can see to the tile's last position, and keep a running maximum, sum
 // and weighted value per row (the flash-attention recurrence).  Keys and values
 // are gathered from their pages into shared memory with 16-byte asynchronous
-// copies, a ring of four blocks deep (the look-up in the block table runs one block
+// copies, a ring of three blocks deep (the look-up in the block table runs one block
 // further ahead), so any page size works.  q k^T and p v run on mma.sync m16n8k16 with fragments read by
 // ldmatrix from rows padded by 16 bytes (conflict-free for every head size that
 // is a multiple of 16).  A row's arithmetic depends on its position, its window
@@ -24,7 +24,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 #define PF_ROWS 64          // rows of a tile (4 warps x 16)
 #define PF_KEYS 64          // keys of a block
 #define PF_THREADS 128
-#define PF_STAGES 4         // key/value blocks in flight
+#define PF_STAGES 3         // key/value blocks in flight
 constexpr int kStride = HEAD_DIM + 8;          // elements between rows in shared memory
 constexpr int kChunks = HEAD_DIM / 8;          // 16-byte pieces of a row
 constexpr int kTile = PF_KEYS * kStride;       // elements of one staged tile
@@ -98,16 +98,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   __nv_bfloat16* k_s = q_s + kTile;                // PF_STAGES tiles
   __nv_bfloat16* v_s = k_s + PF_STAGES * kTile;    // PF_STAGES tiles
 
-  // The host orders the tiles by the number of key blocks they walk, most first; a
-  // block takes tile x and then tile n - 1 - x, so every block has about the same work.
+  // The host orders the tiles by the number of key blocks they walk, most first, so
+  // the blocks that run longest start first and the short ones fill in behind them.
   const int h = blockIdx.y;
-  for (int which = 0; which < 2; ++which) {
-  const int tile = which == 0 ? (int)blockIdx.x : n_tiles - 1 - (int)blockIdx.x;
-  if (which == 1 && tile <= (int)blockIdx.x) break;
-  if (which == 1) __syncthreads();                 // the first tile's shared memory is reused
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles) return;
   const int row0 = tiles[2 * tile], n_rows = tiles[2 * tile + 1];
   const int r = row_req[row0];
-  if (r < 0 || n_rows <= 0) continue;
+  if (r < 0 || n_rows <= 0) return;
   const int kvh = h / (nh / nkv);
   const int pos0 = pos[row0];
   const int pos_last = pos0 + n_rows - 1;
@@ -189,33 +187,40 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         mma16816(s[2 * np + 1], q_frag[ks], kf[2], kf[3]);
       }
     }
-    // ---- scale, mask, running softmax (rows g and g + 8) ----
+    // ---- mask (only in blocks that reach past a row's position or before its window),
+    // running softmax on the raw scores: exp2(s * c - max * c), c = scale * log2(e) ----
+    const bool needs_mask = kb + PF_KEYS - 1 > pos0 || (window >= 0 && kb < pos_last - window);
+    if (needs_mask) {
+#pragma unroll
+      for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb + nt * 8 + 2 * t + (e & 1);
+          if (key > p_row[e >> 1] || key < lo_row[e >> 1]) s[nt][e] = -INFINITY;
+        }
+      }
+    }
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int key = kb + nt * 8 + 2 * t + (e & 1);
-        const bool seen = key <= p_row[i] && key >= lo_row[i];
-        s[nt][e] = seen ? s[nt][e] * scale_log2 : -INFINITY;
-        m_new[i] = fmaxf(m_new[i], s[nt][e]);
-      }
+      m_new[0] = fmaxf(m_new[0], fmaxf(s[nt][0], s[nt][1]));
+      m_new[1] = fmaxf(m_new[1], fmaxf(s[nt][2], s[nt][3]));
     }
-    float corr[2], m_use[2], sum[2] = {0.f, 0.f};
+    float corr[2], m_scaled[2], sum[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
       m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-      m_use[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];     // nothing seen yet: keep exp() finite
-      corr[i] = exp2f(m_run[i] - m_use[i]);                   // exp2(-inf) = 0
+      // nothing seen yet (all keys of the block hidden from this row): keep exp2() finite
+      m_scaled[i] = m_new[i] == -INFINITY ? 0.f : m_new[i] * scale_log2;
+      corr[i] = exp2f(m_run[i] * scale_log2 - m_scaled[i]);     // exp2(-inf) = 0 on the first block
       m_run[i] = m_new[i];
     }
 #pragma unroll
     for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float pe = exp2f(s[nt][e] - m_use[e >> 1]);
+        const float pe = exp2f(fmaf(s[nt][e], scale_log2, -m_scaled[e >> 1]));
         s[nt][e] = pe;
         sum[e >> 1] += pe;
       }
@@ -263,7 +268,6 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
           pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
     }
   }
-  }  // the two tiles of this block
 }
 
 TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
@@ -288,7 +292,7 @@ TOKB200_API int tokb200_prefill_attention(
     if (err != cudaSuccess) return (int)err;
     configured[device] = true;
   }
-  dim3 grid((n_tiles + 1) / 2, nh);
+  dim3 grid(n_tiles, nh);
   const float scale_log2 = scale * 1.4426950408889634f;
   prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,

@@ -79,6 +79,22 @@ __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(tc_smem(bar)) : "memory");
 }
+__device__ __forceinline__ void tmem_wait_loads() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// the same load without the wait: the caller waits once for several loads
+__device__ __forceinline__ void tmem_load_32_async(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+      "%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_load_32(unsigned taddr, unsigned (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -363,8 +379,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         for (int c0 = 0; c0 < 128; c0 += 32) {
           unsigned gate[32], up[32];
           const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BLOCK_N);
-          tmem_load_32(lane_base + (unsigned)c0, gate);
-          tmem_load_32(lane_base + (unsigned)(128 + c0), up);
+          tmem_load_32_async(lane_base + (unsigned)c0, gate);
+          tmem_load_32_async(lane_base + (unsigned)(128 + c0), up);
+          tmem_wait_loads();
           unsigned char* slab = staging + (c0 / 64) * S::kSlabBytes + r * 128;
           const int piece0 = (c0 / 32 % 2) * 4;
 #pragma unroll
@@ -377,8 +394,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
               const float u0 = __uint_as_float(up[8 * j + 2 * e]), u1 = __uint_as_float(up[8 * j + 2 * e + 1]);
               // silu in 32-bit with the fast exponential and reciprocal (a few ulp,
               // far below the bfloat16 rounding of the result)
-              __nv_bfloat162 pair = __floats2bfloat162_rn(g0 * __frcp_rn(1.0f + __expf(-g0)) * u0,
-                                                          g1 * __frcp_rn(1.0f + __expf(-g1)) * u1);
+              __nv_bfloat162 pair = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0,
+                                                          __fdividef(g1, 1.0f + __expf(-g1)) * u1);
               ow[e] = *reinterpret_cast<unsigned*>(&pair);
             }
             *reinterpret_cast<uint4*>(slab + (((piece0 + j) ^ (r & 7)) << 4)) = o;
