@@ -55,6 +55,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (one instruction; relative error about 2^-22,
+// far inside the bfloat16 rounding the probabilities get next)
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -213,14 +220,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
       // nothing seen yet (all keys of the block hidden from this row): keep exp2() finite
       m_scaled[i] = m_new[i] == -INFINITY ? 0.f : m_new[i] * scale_log2;
-      corr[i] = exp2f(m_run[i] * scale_log2 - m_scaled[i]);     // exp2(-inf) = 0 on the first block
+      corr[i] = exp2_approx(m_run[i] * scale_log2 - m_scaled[i]);     // exp2(-inf) = 0 on the first block
       m_run[i] = m_new[i];
     }
 #pragma unroll
     for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float pe = exp2f(fmaf(s[nt][e], scale_log2, -m_scaled[e >> 1]));
+        const float pe = exp2_approx(fmaf(s[nt][e], scale_log2, -m_scaled[e >> 1]));
         s[nt][e] = pe;
         sum[e >> 1] += pe;
       }
