@@ -542,3 +542,42 @@ def test_gated_linear(M, inner, K):
     close(out, (g * torch.sigmoid(g) * u).float(), torch.bfloat16)
     with pytest.raises(ValueError):
         o.gated_linear(x, w[:-8], torch.empty(M, inner - 4, dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("M,nh,nkv,d,K", [(1, 4, 2, 16, 64), (8, 14, 2, 64, 896), (5, 3, 1, 32, 96),
+                                           (16, 5, 5, 48, 80), (3, 2, 1, 128, 200)])
+def test_qkv_projection_with_rope_and_cache_write_folded_in(M, nh, nkv, d, K):
+    """The decoding step's q/k/v kernel against the unfused pieces' arithmetic:
+    product + bias in float64, rotation by the float32 tables, rows scattered to
+    their cache slots; one row writes no cache."""
+    o = ops()
+    heads = nh + 2 * nkv
+    x = rnd(M, K, seed=81, dtype=torch.bfloat16)
+    w = rnd(heads * d, K, seed=82, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(heads * d, seed=83, scale=0.3)
+    inv_freq = torch.tensor([1.0 / 1e4 ** (i / d) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 900)
+    pos = torch.tensor([(37 * i + 5) % 900 for i in range(M)], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([2 * i + 1 for i in range(M)], dtype=torch.int32, device=DEV)
+    if M > 1:
+        slot[M - 1] = -1
+    k_pool = torch.full((2 * M + 2, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((2 * M + 2, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(M, nh * d, dtype=torch.bfloat16, device=DEV)
+    o.qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d)
+    full = (x.double().cpu() @ w.double().cpu().t() + bias.double().cpu()).float().view(M, heads, d)
+    c, s = cos[pos.long()].cpu()[:, None, :], sin[pos.long()].cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :d // 2], v[..., d // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    close(q_out.view(M, nh, d), rotate(full[:, :nh]), torch.bfloat16)
+    k_want, v_want = rotate(full[:, nh:nh + nkv]), full[:, nh + nkv:]
+    for m in range(M):
+        if int(slot[m]) < 0:
+            continue
+        close(k_pool[int(slot[m])], k_want[m], torch.bfloat16)
+        close(v_pool[int(slot[m])], v_want[m], torch.bfloat16)
+    untouched = [i for i in range(2 * M + 2) if i not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())

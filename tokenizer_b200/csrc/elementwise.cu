@@ -309,6 +309,45 @@ __global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
   }
 }
 
+// the same for the interleaved layout of the gated kernels: for every 128 outputs,
+// 128 gate values followed by their 128 up values
+__global__ void silu_gate_interleaved_kernel(const __nv_bfloat16* __restrict__ gu,
+                                             __nv_bfloat16* __restrict__ out, int inner, int n_rows) {
+  pdl_wait();
+  pdl_launch();
+  const int per_row = inner / 8;
+  const size_t total = (size_t)n_rows * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / per_row;
+    const int c = (int)(i % per_row) * 8;                   // output column
+    const size_t at = t * 2 * inner + (size_t)(c / 128) * 256 + c % 128;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + at);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + at + 128);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+      o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * inner + c) = o4;
+  }
+}
+
+TOKB200_API int tokb200_silu_gate_interleaved(const void* gu, void* out, int n_tokens, int inner,
+                                              cudaStream_t stream) {
+  if (n_tokens <= 0) return TOKB200_OK;
+  if (inner <= 0 || inner % 128) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)gu | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
+  const size_t total = (size_t)n_tokens * (inner / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  return launch_dependent(silu_gate_interleaved_kernel, dim3(blocks), dim3(256), 0, stream,
+                          (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens);
+}
+
 TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_tokens, int inner,
                                   cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;

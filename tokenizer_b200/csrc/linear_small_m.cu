@@ -217,3 +217,132 @@ TOKB200_API int tokb200_linear_small_m_gated(const void* x, const void* w, void*
   if (M <= 32) return launch_small_m_gated<4>(x, w, out, M, N, K, stream);
   return launch_small_m_gated<8>(x, w, out, M, N, K, stream);
 }
+
+// ----------------------------------------------------------------------------
+// The query/key/value projection of a decoding step with everything that follows
+// it folded into the epilogue: bias, the rotary encoding of q and k at each row's
+// position, and the write of k and v into the row's cache slot.  w is the stacked
+// [q heads; k heads; v heads] x K weight.  A row tile is 8 lanes j0 .. j0 + 7 of a
+// head and their rotation partners j0 + d/2 .. (rows g and g + 8 of the mma), so a
+// thread of the epilogue holds both halves of a pair.  The rotary width must be
+// the whole head (d), d a multiple of 16.
+// ----------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(LSM_THREADS)
+qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const float* __restrict__ bias, const int* __restrict__ pos,
+                        const int* __restrict__ slot, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
+                        __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int M,
+                        int nh, int nkv, int d, int K) {
+  __shared__ float part[LSM_WARPS][16][8 * MT + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int tiles_per_head = d / 16;
+  const int head = blockIdx.x / tiles_per_head, j0 = (blockIdx.x % tiles_per_head) * 8;
+  const int row_a = head * d + j0 + g, row_b = row_a + d / 2;
+
+  float acc[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const __nv_bfloat16* wa = w + (size_t)row_a * K + 8 * t;
+  const __nv_bfloat16* wb = w + (size_t)row_b * K + 8 * t;
+
+  constexpr int step = LSM_WARPS * 32;
+  const int k_first = warp * 32;
+  uint4 a_ring[LSM_PRE], b_ring[LSM_PRE];
+#pragma unroll
+  for (int i = 0; i < LSM_PRE; ++i) {
+    const int kk = k_first + i * step;
+    const bool k_ok = kk + 8 * t + 8 <= K;
+    a_ring[i] = load16(wa + kk, k_ok);
+    b_ring[i] = load16(wb + kk, k_ok);
+  }
+  pdl_wait();
+  pdl_launch();
+  for (int k = k_first; k < K; k += LSM_PRE * step) {
+#pragma unroll
+    for (int i = 0; i < LSM_PRE; ++i) {
+      const int kk = k + i * step;
+      const uint4 a = a_ring[i], b = b_ring[i];
+      const int kn = kk + LSM_PRE * step;
+      const bool next_ok = kn + 8 * t + 8 <= K;
+      a_ring[i] = load16(wa + kn, next_ok);
+      b_ring[i] = load16(wb + kn, next_ok);
+      const bool k_ok = kk + 8 * t + 8 <= K;
+      if (kk < K) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          const int m = 8 * j + g;
+          const uint4 xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
+          mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
+          mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    part[warp][g][8 * j + 2 * t] = acc[j][0];
+    part[warp][g][8 * j + 2 * t + 1] = acc[j][1];
+    part[warp][g + 8][8 * j + 2 * t] = acc[j][2];
+    part[warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+
+  const int half = d / 2;
+  for (int i = threadIdx.x; i < 8 * M; i += LSM_THREADS) {
+    const int m = i / 8, rr = i % 8;
+    const int j = j0 + rr;
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int s = 0; s < LSM_WARPS; ++s) {
+      a += part[s][rr][m];
+      b += part[s][rr + 8][m];
+    }
+    if (bias) {
+      a += bias[head * d + j];
+      b += bias[head * d + j + half];
+    }
+    __nv_bfloat16* dst;
+    if (head < nh) {
+      dst = q_out + ((size_t)m * nh + head) * d;
+    } else {
+      const int s = slot ? slot[m] : -1;
+      if (s < 0) continue;                                    // no cache write for this row
+      const bool is_key = head < nh + nkv;
+      __nv_bfloat16* pool = is_key ? k_pool : v_pool;
+      if (!pool) continue;
+      dst = pool + ((size_t)s * nkv + (head - nh - (is_key ? 0 : nkv))) * d;
+    }
+    if (head < nh + nkv) {
+      const int p = pos[m];
+      const float c = cos_t[(size_t)p * half + j], sn = sin_t[(size_t)p * half + j];
+      const float ra = a * c - b * sn, rb = b * c + a * sn;
+      a = ra;
+      b = rb;
+    }
+    dst[j] = __float2bfloat16_rn(a);
+    dst[j + half] = __float2bfloat16_rn(b);
+  }
+}
+
+TOKB200_API int tokb200_qkv_rope_small_m(const void* x, const void* w, const float* bias, const int* pos,
+                                         const int* slot, const float* cos_t, const float* sin_t,
+                                         void* q_out, void* k_pool, void* v_pool, int M, int nh, int nkv,
+                                         int d, int K, cudaStream_t stream) {
+  if (M <= 0) return TOKB200_OK;
+  if (M > 64 || K <= 0 || K % 8 || d <= 0 || d % 16 || nh <= 0 || nkv <= 0) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
+  const dim3 grid((nh + 2 * nkv) * (d / 16));
+#define LAUNCH_QKV(MT)                                                                              \
+  return launch_dependent(qkv_rope_small_m_kernel<MT>, grid, dim3(LSM_THREADS), 0, stream,         \
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, pos, slot, cos_t, \
+                          sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, \
+                          M, nh, nkv, d, K)
+  if (M <= 8) LAUNCH_QKV(1);
+  if (M <= 16) LAUNCH_QKV(2);
+  if (M <= 32) LAUNCH_QKV(4);
+  LAUNCH_QKV(8);
+#undef LAUNCH_QKV
+}

@@ -241,6 +241,9 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(counters), _stream()), "decode_attention")
 
 
+SMALL_M_ROWS = 16     # up to here the streaming kernel leads; above it, the tensor-core tiles
+
+
 def linear_small_m_supported(M: int, K: int) -> bool:
     return 0 < M <= 64 and K % 8 == 0
 
@@ -360,9 +363,34 @@ def gated_linear(x, w, out) -> None:
         raise ValueError("gated_linear is the bfloat16 kernel")
     if not gated_linear_supported(K, N) or w.shape[1] != K or tuple(out.shape) != (M, N // 2):
         raise ValueError("gated_linear: K a multiple of 8, N of 256, out [M, N/2]")
-    if M <= 64:
+    if M <= SMALL_M_ROWS:
         _check(_lib("linear_small_m").tokb200_linear_small_m_gated(
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")
+    elif M <= 64:
+        # too few rows to fill the 256-wide gated tiles over the SMs: the plain tensor-core
+        # product over the same (interleaved) weight, then the activation on its output
+        gu = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        gemm_tcgen05(x, w, None, gu)
+        _check(_lib("elementwise").tokb200_silu_gate_interleaved(
+            _ptr(gu), _ptr(out), _i(M), _i(N // 2), _stream()), "silu_gate_interleaved")
     else:
         _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_gated(
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")
+
+
+def qkv_rope_small_m_supported(M: int, K: int, d: int, rotary: int) -> bool:
+    return 0 < M <= SMALL_M_ROWS and K % 8 == 0 and d % 16 == 0 and rotary == d
+
+
+def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d) -> None:
+    """The stacked q/k/v projection of few rows with bias, rotary encoding and the
+    cache write folded into its epilogue (bfloat16; the whole head is rotated)."""
+    M, K = x.shape
+    if w.shape != ((nh + 2 * nkv) * d, K) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ValueError("qkv_rope_small_m: w is the stacked [(heads + 2 kv heads) d, K] weight")
+    if not qkv_rope_small_m_supported(M, K, d, 2 * cos.shape[1]):
+        raise ValueError("qkv_rope_small_m: sizes it does not take")
+    _check(_lib("linear_small_m").tokb200_qkv_rope_small_m(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), _ptr(q_out),
+        _ptr(k_pool), _ptr(v_pool), _i(M), _i(nh), _i(nkv), _i(d), _i(K), _stream()),
+        "qkv_rope_small_m")

@@ -79,9 +79,20 @@ class GQAttention:
         return CacheNeed(kv=KVNeed(self.nkv, self.d, self.window))
 
     def forward(self, h, ctx, cache):
-        qkv = self.qkv.forward(h)
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
         group = ctx.groups[cache.group]
+        if h.dtype == torch.bfloat16 and ops.qkv_rope_small_m_supported(
+                h.shape[0], self.hidden, self.d, self.position.rotary_dim):
+            # few rows: projection, bias, rotation and cache write in one kernel
+            ops.qkv_rope_small_m(
+                h, self.qkv.weight, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
+                self.position.cos, self.position.sin, q,
+                cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None,
+                self.nh, self.nkv, self.d)
+            mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+            self.attend(q, mixed, ctx, group, cache)
+            return self.out.forward(mixed, partials_ok=True)
+        qkv = self.qkv.forward(h)
         ops.rope_store(
             qkv, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
             self.position.cos, self.position.sin, q,

@@ -37,7 +37,9 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     `partials_ok` the result may be float32 partial sums [S,M,N] instead."""
     M, K = a.shape
     N = weight.shape[0]
-    if ops.linear_small_m_supported(M, K):
+    # few rows: the streaming kernel; up to 64 rows it also keeps the narrow matrices,
+    # whose few tiles would leave most SMs of the tile kernel idle
+    if ops.linear_small_m_supported(M, K) and (M <= ops.SMALL_M_ROWS or N < 4096):
         splits = choose_k_splits(M, N, K) if (partials_ok and bias is None) else 1
         if splits > 1:
             out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
