@@ -539,7 +539,14 @@ def test_gated_linear(M, inner, K):
         o.gemm_tcgen05_check()
     g = x.double().cpu() @ gate.double().cpu().t()
     u = x.double().cpu() @ up.double().cpu().t()
-    close(out, (g * torch.sigmoid(g) * u).float(), torch.bfloat16)
+    want = (g * torch.sigmoid(g) * u).float()
+    if 16 < M <= 64:
+        # this range runs the plain product and then the activation: gate and up are
+        # rounded to bfloat16 on the way (three roundings of 2^-9 instead of one)
+        got = out.float().cpu()
+        assert torch.allclose(got, want, atol=4e-3, rtol=2 ** -6), float((got - want).abs().max())
+    else:
+        close(out, want, torch.bfloat16)
     with pytest.raises(ValueError):
         o.gated_linear(x, w[:-8], torch.empty(M, inner - 4, dtype=torch.bfloat16, device=DEV))
 

@@ -12,11 +12,11 @@
 // tile's values in shared memory and reads them with ldmatrix.trans.
 //
 // A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk
-// is 128 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
+// is 1024 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
 // function of the row's own position and window and does not change with the
-// batch around it.  The four warps of a block take tiles of 32 keys in turn, each
-// with its own running maximum, sum and weighted values; they are merged once at
-// the end.  Pieces of several blocks meet in scratch memory (max, sum, weighted
+// batch around it; up to 1024 keys are one block's work and need no merge across
+// blocks.  The eight warps of a block take tiles of 32 keys in turn, each with its
+// own running maximum, sum and weighted values; they are merged once at the end.  Pieces of several blocks meet in scratch memory (max, sum, weighted
 // values per (row, head, split)); the block that finishes last for a (row, kv
 // head) merges them in index order and writes the output.
 //
@@ -27,12 +27,13 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
 #endif
-#define DEC_WARPS 4
+#define DEC_WARPS 8
 #define DEC_THREADS (DEC_WARPS * 32)
 #define DEC_MAX_GROUP 16       // query heads per kv head: the rows of one mma
 #define DEC_MAX_SPLITS 32
 #define DEC_TILE 32            // keys a warp takes per pass
-#define DEC_BLOCK_KEYS (DEC_WARPS * DEC_TILE)
+#define DEC_BLOCK_KEYS (DEC_WARPS * DEC_TILE)   // keys a block takes per pass
+#define DEC_MIN_CHUNK 1024     // a row with no more keys than this is one block's work: no merge across blocks
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma
@@ -40,7 +41,7 @@ constexpr bool kTail16 = HEAD_DIM % 32 != 0;         // one more step of 16 lane
 constexpr int kVStride = HEAD_DIM + 8;               // elements between staged value rows
 
 __device__ __forceinline__ int split_chunk(int n_keys) {
-  int chunk = DEC_BLOCK_KEYS;
+  int chunk = DEC_MIN_CHUNK;
   while ((n_keys + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
   return chunk;
 }
@@ -329,7 +330,7 @@ TOKB200_API int tokb200_decode_attention(
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
     if (!configured[device]) {
       cudaError_t err = cudaFuncSetAttribute(decode_attention_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (err != cudaSuccess) return (int)err;
       configured[device] = true;
     }
