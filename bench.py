@@ -116,6 +116,8 @@ def main():
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--only-decode", action="store_true",
                         help="time the decode steps only and print a short line (for profiling)")
+    parser.add_argument("--only-prefill", action="store_true",
+                        help="time the 2,048-token prefill only and print a short line (for profiling)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -147,7 +149,7 @@ def main():
     with tempfile.TemporaryDirectory() as folder:
         tb.write_random_model(folder, config, seed=2)
         model = tb.load_model(folder, dtype="bfloat16", device="cuda:0")
-    biggest = max(args.batch, 1 if args.no_points else 64)
+    biggest = max(args.batch, 1 if (args.no_points or args.only_prefill) else 64)
     pool_tokens = max(biggest * (PROMPT_LEN + NEW_TOKENS + PAGE), PREFILL_TOKENS + PAGE)
     engine = tb.engine_for(model, pool_tokens, PAGE, max_requests=max(biggest, 1), share_prefixes=False)
 
@@ -170,6 +172,10 @@ def main():
             prefill_ms.append(start.elapsed_time(stop))
         engine.cache.close(cache)
     prefill_best = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
+    if args.only_prefill:
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": args.layers,
+                          "ms": prefill_best, "tok_s": PREFILL_TOKENS / (prefill_best / 1e3)}))
+        return 0
     prefill = {"value": PREFILL_TOKENS / (prefill_best / 1e3), "tokens": PREFILL_TOKENS,
                "ms": prefill_best,
                "frac": prefill_flops(cfg, args.layers, PREFILL_TOKENS) / (prefill_best / 1e3)
