@@ -24,7 +24,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 #define PF_ROWS 64          // rows of a tile (4 warps x 16)
 #define PF_KEYS 64          // keys of a block
 #define PF_THREADS 128
-#define PF_STAGES 3         // key/value blocks in flight
+#define PF_STAGES 4         // key/value blocks in flight
 constexpr int kStride = HEAD_DIM + 8;          // elements between rows in shared memory
 constexpr int kChunks = HEAD_DIM / 8;          // 16-byte pieces of a row
 constexpr int kTile = PF_KEYS * kStride;       // elements of one staged tile
