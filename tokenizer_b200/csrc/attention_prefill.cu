@@ -24,7 +24,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 #define PF_ROWS 64          // rows of a tile (4 warps x 16)
 #define PF_KEYS 64          // keys of a block
 #define PF_THREADS 128
-#define PF_STAGES 4         // key/value blocks in flight
+#define PF_STAGES 3         // key/value blocks in flight
 constexpr int kStride = HEAD_DIM + 8;          // elements between rows in shared memory
 constexpr int kChunks = HEAD_DIM / 8;          // 16-byte pieces of a row
 constexpr int kTile = PF_KEYS * kStride;       // elements of one staged tile
@@ -72,13 +72,20 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // The look-up (a dependent load) is made one block ahead of the copies that use it,
 // so the copies of a block are issued without waiting.  Keys outside [first_ok,
 // last_ok] are zero-filled and their pages are not touched (offset -1).
-__device__ __forceinline__ long long kv_row_offset(const int* __restrict__ table, int page, int nkv,
-                                                    int kvh, int key0, int first_ok, int last_ok) {
+// The page of this thread's key in the block starting at key0 (-1: the key is not to
+// be read).  Only the load is issued here; `kv_row_offset` turns it into an offset
+// when the copies are issued, one block later, so nothing waits for the load.
+__device__ __forceinline__ int kv_page(const int* __restrict__ table, int page, int key0, int first_ok,
+                                       int last_ok) {
   static_assert(PF_THREADS == 2 * PF_KEYS && kChunks % 2 == 0, "two threads a key");
   const int key = key0 + (threadIdx.x >> 1);
   if (key < first_ok || key > last_ok) return -1;
-  const int slot = table[key / page] * page + key % page;
-  return ((long long)slot * nkv + kvh) * HEAD_DIM;
+  return table[key / page];
+}
+__device__ __forceinline__ long long kv_row_offset(int pg, int page, int nkv, int kvh, int key0) {
+  if (pg < 0) return -1;
+  const int key = key0 + (threadIdx.x >> 1);
+  return ((long long)(pg * page + key % page) * nkv + kvh) * HEAD_DIM;
 }
 __device__ __forceinline__ void stage_kv(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
                                          const __nv_bfloat16* __restrict__ k_pool,
@@ -134,13 +141,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   // committed for every block, existing or not, so that group counts stay in step
 #pragma unroll
   for (int b = 0; b < PF_STAGES - 1; ++b) {
-    if (b < n_blocks)
+    if (b < n_blocks) {
+      const int key0 = kb_first + b * PF_KEYS;
       stage_kv(k_s + b * kTile, v_s + b * kTile, k_pool, v_pool,
-               kv_row_offset(table, page, nkv, kvh, kb_first + b * PF_KEYS, lo_first, pos_last));
+               kv_row_offset(kv_page(table, page, key0, lo_first, pos_last), page, nkv, kvh, key0));
+    }
     cp_async_commit();
   }
-  long long next_offset = PF_STAGES - 1 < n_blocks
-      ? kv_row_offset(table, page, nkv, kvh, kb_first + (PF_STAGES - 1) * PF_KEYS, lo_first, pos_last) : -1;
+  int next_page = PF_STAGES - 1 < n_blocks
+      ? kv_page(table, page, kb_first + (PF_STAGES - 1) * PF_KEYS, lo_first, pos_last) : -1;
 
   // per thread: rows g and g + 8 of the warp's 16
   const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
@@ -165,10 +174,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       const int nb = b + PF_STAGES - 1;             // goes where block b - 1 was
       if (nb < n_blocks)
         stage_kv(k_s + (nb % PF_STAGES) * kTile, v_s + (nb % PF_STAGES) * kTile, k_pool, v_pool,
-                 next_offset);
+                 kv_row_offset(next_page, page, nkv, kvh, kb_first + nb * PF_KEYS));
       cp_async_commit();
-      next_offset = nb + 1 < n_blocks
-          ? kv_row_offset(table, page, nkv, kvh, kb_first + (nb + 1) * PF_KEYS, lo_first, pos_last) : -1;
+      next_page = nb + 1 < n_blocks
+          ? kv_page(table, page, kb_first + (nb + 1) * PF_KEYS, lo_first, pos_last) : -1;
     }
     if (b == 0) {
 #pragma unroll
@@ -183,15 +192,24 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     float s[PF_KEYS / 8][4];
 #pragma unroll
     for (int i = 0; i < PF_KEYS / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    // the fragments of step ks + 1 are read while the products of step ks run
+    {
+      unsigned kf[2][PF_KEYS / 16][4];
+      const __nv_bfloat16* k_lane = kt + ((lane & 7) + (lane >> 4) * 8) * kStride + ((lane >> 3) & 1) * 8;
 #pragma unroll
-    for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+      for (int np = 0; np < PF_KEYS / 16; ++np) ldmatrix_x4(kf[0][np], k_lane + np * 16 * kStride);
 #pragma unroll
-      for (int np = 0; np < PF_KEYS / 16; ++np) {
-        unsigned kf[4];
-        ldmatrix_x4(kf, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * kStride + ks * 16 +
-                            ((lane >> 3) & 1) * 8);
-        mma16816(s[2 * np], q_frag[ks], kf[0], kf[1]);
-        mma16816(s[2 * np + 1], q_frag[ks], kf[2], kf[3]);
+      for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+        if (ks + 1 < HEAD_DIM / 16) {
+#pragma unroll
+          for (int np = 0; np < PF_KEYS / 16; ++np)
+            ldmatrix_x4(kf[(ks + 1) & 1][np], k_lane + np * 16 * kStride + (ks + 1) * 16);
+        }
+#pragma unroll
+        for (int np = 0; np < PF_KEYS / 16; ++np) {
+          mma16816(s[2 * np], q_frag[ks], kf[ks & 1][np][0], kf[ks & 1][np][1]);
+          mma16816(s[2 * np + 1], q_frag[ks], kf[ks & 1][np][2], kf[ks & 1][np][3]);
+        }
       }
     }
     // ---- mask (only in blocks that reach past a row's position or before its window),
@@ -244,20 +262,34 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
     // ---- o += p v ----
+    {
+      // value fragments are read in groups of four (64 lanes of the head) ahead of their products
+      constexpr int kGroups = (HEAD_DIM / 16 + 3) / 4;
+      const __nv_bfloat16* v_lane = vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * kStride + (lane >> 4) * 8;
 #pragma unroll
-    for (int ks = 0; ks < PF_KEYS / 16; ++ks) {
-      unsigned pf[4];
-      pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-      pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-      pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-      pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+      for (int ks = 0; ks < PF_KEYS / 16; ++ks) {
+        unsigned pf[4];
+        pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+        pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+        pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+        pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
 #pragma unroll
-      for (int dp = 0; dp < HEAD_DIM / 16; ++dp) {
-        unsigned vf[4];
-        ldmatrix_x4_trans(vf, vt + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kStride +
-                                  dp * 16 + (lane >> 4) * 8);
-        mma16816(o[2 * dp], pf, vf[0], vf[1]);
-        mma16816(o[2 * dp + 1], pf, vf[2], vf[3]);
+        for (int grp = 0; grp < kGroups; ++grp) {
+          unsigned vf[4][4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int dp = grp * 4 + i;
+            if (dp < HEAD_DIM / 16) ldmatrix_x4_trans(vf[i], v_lane + ks * 16 * kStride + dp * 16);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int dp = grp * 4 + i;
+            if (dp < HEAD_DIM / 16) {
+              mma16816(o[2 * dp], pf, vf[i][0], vf[i][1]);
+              mma16816(o[2 * dp + 1], pf, vf[i][2], vf[i][3]);
+            }
+          }
+        }
       }
     }
   }
