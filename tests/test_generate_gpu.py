@@ -162,3 +162,57 @@ def test_the_engine_refuses_what_it_cannot_run(folder):
     with pytest.raises(Exception, match="GPU"):
         tb.load_model(path, dtype="float32", device="cpu")
     assert engine.step([StepEntry(cache, [1, 2], [1])]).shape == (1, config.vocab_size)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scheduler_on_the_engine_with_too_few_pages(folder, dtype):
+    """Continuous batching on the real engine with a pool so small that requests are
+    preempted and recomputed: every request still gets the ids it gets alone, and
+    every page comes back."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine.scheduler import Scheduler
+    path, config, page = folder
+    model = tb.load_model(path, dtype=dtype)
+    lengths = [9, 30, 17, 44, 5]
+    new = 20
+    prompts = [random_ids(n, config.vocab_size, 500 + n) for n in lengths]
+    solo = [tb.generate(model, p, tb.GenerateParams.greedy(new)).tokens for p in prompts]
+    # room for about two and a half of the five requests at their final length
+    total = sum(-(-(n + new) // page) for n in lengths)
+    engine = tb.Engine(model, num_pages=max(total // 2, -(-(max(lengths) + new) // page) + 1),
+                       page_size=page, max_requests=4, share_prefixes=False)
+    scheduler = Scheduler(engine, max_batch_size=4, token_budget=24)
+    ids = [scheduler.add_request(p, tb.GenerateParams.greedy(new)) for p in prompts]
+    results = scheduler.run()
+    assert scheduler.stats.preemptions > 0
+    for rid, want in zip(ids, solo):
+        assert results[rid].reason == tb.StopReason.MAX_TOKENS
+        if dtype == "float32":
+            assert results[rid].tokens == want
+        else:
+            assert len(results[rid].tokens) == new
+    engine.cache.check()
+    assert all(a.all_released() and a.available == a.capacity for a in engine.cache.allocators)
+
+
+def test_shared_beginnings_on_the_engine(folder):
+    """Two requests with the same long beginning: the second adopts the first's
+    full pages, runs only its own tail, and gets the ids it gets alone."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine.scheduler import Scheduler
+    path, config, page = folder
+    if any(l.mixer.params["window"] is not None for l in config.model_spec().layers):
+        pytest.skip("pages are shared only when every layer keeps all keys")
+    model = tb.load_model(path, dtype="float32")
+    base = random_ids(3 * page + 5, config.vocab_size, 901)
+    a, b = base + [1, 2, 3], base + [4, 5]
+    alone = [tb.generate(model, p, tb.GenerateParams.greedy(6)).tokens for p in (a, b)]
+    engine = tb.Engine(model, num_pages=64, page_size=page, max_requests=4, share_prefixes=True)
+    scheduler = Scheduler(engine, max_batch_size=4, token_budget=512)
+    first = scheduler.add_request(a, tb.GenerateParams.greedy(6))
+    scheduler.step()
+    second = scheduler.add_request(b, tb.GenerateParams.greedy(6))
+    results = scheduler.run()
+    assert scheduler.stats.shared_prefix_tokens == 3 * page
+    assert results[first].tokens == alone[0] and results[second].tokens == alone[1]
+    engine.cache.check()
