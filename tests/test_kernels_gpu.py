@@ -588,3 +588,52 @@ def test_qkv_projection_with_rope_and_cache_write_folded_in(M, nh, nkv, d, K):
         close(v_pool[int(slot[m])], v_want[m], torch.bfloat16)
     untouched = [i for i in range(2 * M + 2) if i not in slot.tolist()]
     assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
+
+
+@pytest.mark.parametrize("hidden", [64, 896, 1000, 8192])
+def test_rms_norm_many_rows_vector_path(hidden):
+    rows = 100
+    x = rnd(rows, hidden, seed=91, scale=2.0)
+    delta = rnd(rows, hidden, seed=92, dtype=torch.bfloat16)
+    gain = 1 + rnd(hidden, seed=93, scale=0.1)
+    want_x = x + delta.float()
+    want = want_x / torch.sqrt((want_x * want_x).mean(-1, keepdim=True) + 1e-6) * gain
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=DEV)
+    x1 = x.clone()
+    ops().rms_norm(x1, gain, 1e-6, out, delta=delta)
+    assert torch.allclose(x1, want_x, atol=1e-6)
+    close(out, want, torch.bfloat16)
+    out2 = torch.empty_like(out)
+    ops().rms_norm(x1, gain, 1e-6, out2)
+    close(out2, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("nh,nkv,d", [(14, 2, 64), (5, 5, 48), (3, 1, 128), (4, 2, 16)])
+def test_rope_store_many_rows_vector_path(nh, nkv, d):
+    o = ops()
+    T = 130
+    inv_freq = torch.tensor([1.0 / 1e6 ** (i / d) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 3000)
+    qkv = rnd(T, (nh + 2 * nkv) * d, seed=94, dtype=torch.bfloat16)
+    bias = rnd((nh + 2 * nkv) * d, seed=95, scale=0.3)
+    pos = torch.arange(1500, 1500 + T, dtype=torch.int32, device=DEV)
+    slot = torch.randperm(T + 10, generator=torch.Generator().manual_seed(1))[:T].to(torch.int32).to(DEV)
+    slot[7] = -1
+    k_pool = torch.full((T + 10, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((T + 10, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=DEV)
+    o.rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d)
+    full = (qkv.float() + bias).view(T, nh + 2 * nkv, d).cpu()
+    c, s = cos[pos.long()].cpu()[:, None, :], sin[pos.long()].cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :d // 2], v[..., d // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    close(q_out.view(T, nh, d), rotate(full[:, :nh]), torch.bfloat16)
+    k_want, v_want = rotate(full[:, nh:nh + nkv]), full[:, nh + nkv:]
+    live = [t for t in range(T) if int(slot[t]) >= 0]
+    close(k_pool[slot[live].long()], k_want[live], torch.bfloat16)
+    close(v_pool[slot[live].long()], v_want[live], torch.bfloat16)
+    untouched = [i for i in range(T + 10) if i not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all())

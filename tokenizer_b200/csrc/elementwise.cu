@@ -112,12 +112,67 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ de
   }
 }
 
+// Many rows (portions of prompts), bfloat16 residual and output, width a multiple
+// of 8 up to 8192: one block a row, eight elements (16 bytes of bfloat16) a thread,
+// values kept in registers between the sum and the scaling.
+__global__ void rms_norm_rows_bf16_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                                          const float* __restrict__ gain, __nv_bfloat16* __restrict__ y,
+                                          int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const int c = threadIdx.x * 8;
+  const bool on = c < hidden;
+  float v[8];
+  float ss = 0.f;
+  if (on) {
+    const float4 a = *reinterpret_cast<const float4*>(x + base + c);
+    const float4 b = *reinterpret_cast<const float4*>(x + base + c + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    if (delta) {
+      const uint4 d4 = *reinterpret_cast<const uint4*>(delta + base + c);
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d = __bfloat1622float2(d2[e]);
+        v[2 * e] += d.x;
+        v[2 * e + 1] += d.y;
+      }
+      *reinterpret_cast<float4*>(x + base + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(x + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  if (on) {
+    const float4 ga = *reinterpret_cast<const float4*>(gain + c);
+    const float4 gb = *reinterpret_cast<const float4*>(gain + c + 4);
+    const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o2[e] = __floats2bfloat162_rn(v[2 * e] * inv * g[2 * e], v[2 * e + 1] * inv * g[2 * e + 1]);
+    *reinterpret_cast<uint4*>(y + base + c) = o4;
+  }
+}
+
 TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, int n_partials,
                                  long long partial_stride, const float* gain, void* y,
                                  int y_dtype, const int* rows, int n_rows, int hidden, float eps,
                                  cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (hidden <= 0 || n_partials < 1) return TOKB200_BAD_SIZE;
+  if (n_rows >= 64 && !rows && n_partials == 1 && y_dtype == TOKB200_BF16 &&
+      (!delta || delta_dtype == TOKB200_BF16) && hidden % 8 == 0 && hidden <= 8192 &&
+      (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)y) & 15) == 0) {
+    const int threads8 = ((hidden / 8 + 31) / 32) * 32;
+    return launch_dependent(rms_norm_rows_bf16_kernel, dim3(n_rows), dim3(threads8), 0, stream, x,
+                            (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)y, hidden, eps);
+  }
   int threads = 128;   // rows of up to 8 elements a thread stay in registers
   while (threads < 1024 && hidden > threads * 4) threads *= 2;
 #define LAUNCH(TD, TO)                                                                        \
@@ -244,6 +299,69 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, const float* __rest
   }
 }
 
+// The same for many rows in bfloat16 when the whole head is rotated and the head
+// size is a multiple of 16: a thread takes 8 lanes of a head and their 8 partners
+// (two 16-byte loads, two 16-byte stores).
+__global__ void rope_store_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
+                                         const int* __restrict__ pos, const int* __restrict__ slot,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
+                                         __nv_bfloat16* __restrict__ v_pool, int n_tokens, int nh, int nkv,
+                                         int d) {
+  pdl_wait();
+  pdl_launch();
+  const int heads = nh + 2 * nkv, half = d / 2, per_head = d / 16, per_token = heads * per_head;
+  const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= (size_t)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), rest = (int)(item % per_token);
+  const int head = rest / per_head, j = (rest % per_head) * 8;
+  const __nv_bfloat16* src = qkv + (size_t)t * heads * d + head * d + j;
+  const uint4 a4 = *reinterpret_cast<const uint4*>(src);
+  const uint4 b4 = *reinterpret_cast<const uint4*>(src + half);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a4);
+  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
+  float a[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
+    a[2 * e] = fa.x; a[2 * e + 1] = fa.y; b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
+  }
+  if (bias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a[e] += bias[head * d + j + e]; b[e] += bias[head * d + j + half + e]; }
+  }
+  __nv_bfloat16* dst;
+  if (head < nh) {
+    dst = q_out + ((size_t)t * nh + head) * d;
+  } else {
+    const int s = slot ? slot[t] : -1;
+    const bool is_key = head < nh + nkv;
+    __nv_bfloat16* pool = is_key ? k_pool : v_pool;
+    if (s < 0 || !pool) return;
+    dst = pool + ((size_t)s * nkv + (head - nh - (is_key ? 0 : nkv))) * d;
+  }
+  if (head < nh + nkv) {
+    const float* c = cos_t + (size_t)pos[t] * half + j;
+    const float* sn = sin_t + (size_t)pos[t] * half + j;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ra = a[e] * c[e] - b[e] * sn[e], rb = b[e] * c[e] + a[e] * sn[e];
+      a[e] = ra;
+      b[e] = rb;
+    }
+  }
+  uint4 oa, ob;
+  __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+  __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    oa2[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+    ob2[e] = __floats2bfloat162_rn(b[2 * e], b[2 * e + 1]);
+  }
+  *reinterpret_cast<uint4*>(dst + j) = oa;
+  *reinterpret_cast<uint4*>(dst + j + half) = ob;
+}
+
 TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int* pos,
                                    const int* slot, const float* cos_t, const float* sin_t,
                                    void* q_out, void* k_pool, void* v_pool, int dtype,
@@ -252,6 +370,14 @@ TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int
   if (n_tokens <= 0) return TOKB200_OK;
   if (d <= 0 || (d & 1) || rotary < 0 || rotary > d || (rotary & 1) || ((d - rotary) & 1))
     return TOKB200_BAD_SIZE;
+  if (dtype == TOKB200_BF16 && rotary == d && d % 16 == 0 && n_tokens >= 64 &&
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
+    const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (d / 16);
+    return launch_dependent(rope_store_bf16x8_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                            stream, (const __nv_bfloat16*)qkv, bias, pos, slot, cos_t, sin_t,
+                            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                            n_tokens, nh, nkv, d);
+  }
   const int items = (nh + 2 * nkv) * (d / 2);
   int threads = items < 256 ? ((items + 31) / 32) * 32 : 256;
   if (dtype == TOKB200_F32)
