@@ -394,3 +394,32 @@ def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh,
         _ptr(x), _ptr(w), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), _ptr(q_out),
         _ptr(k_pool), _ptr(v_pool), _i(M), _i(nh), _i(nkv), _i(d), _i(K), _stream()),
         "qkv_rope_small_m")
+
+
+WIDE_TILE_ROWS = 128
+
+
+def attention_tcgen05_supported(nh: int, nkv: int, d: int) -> bool:
+    return d in (64, 128) and nh % nkv == 0
+
+
+def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv, d,
+                      page, window, scale) -> None:
+    """Attention for portions of prompts on tcgen05 (bfloat16, head size 64 or 128).
+    `tiles` is int32 [n, 2]: (first row, rows <= 128) of consecutive rows of one request."""
+    if q.dtype != torch.bfloat16:
+        raise ValueError("attention_tcgen05 is the bfloat16 kernel")
+    if not attention_tcgen05_supported(nh, nkv, d):
+        raise ValueError(f"attention_tcgen05: head size {d} is not taken (64 or 128)")
+    lib = load_library("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",))
+    _check(lib.tokb200_attention_tcgen05(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
+        _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
+        _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
+        "attention_tcgen05")
+
+
+def attention_tcgen05_check(d: int) -> None:
+    flag = load_library("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",)).tokb200_attention_tcgen05_error()
+    if flag:
+        raise KernelError("attention_tcgen05: a wait on the device ran out (status %d)" % flag)
