@@ -637,3 +637,64 @@ def test_rope_store_many_rows_vector_path(nh, nkv, d):
     close(v_pool[slot[live].long()], v_want[live], torch.bfloat16)
     untouched = [i for i in range(T + 10) if i not in slot.tolist()]
     assert bool((k_pool[untouched] == 7.0).all())
+
+
+@pytest.mark.parametrize("nh,nkv,d,page,window", [
+    (4, 2, 64, 16, None), (14, 2, 64, 16, None), (3, 1, 64, 8, 100), (4, 1, 128, 16, None),
+    (6, 3, 128, 32, 40), (2, 2, 64, 64, None)])
+def test_attention_tcgen05_tiles(nh, nkv, d, page, window):
+    """The tcgen05 kernel for portions of prompts: portions that start at 0 and in the
+    middle of a page, of 1 to 400 rows (tiles of up to 128), beside single rows."""
+    dtype = torch.bfloat16
+    lengths = [1, 2, 70, 128, 129, 333, 520, 900]
+    starts = [0, 0, 7, 0, 64, 133, 519, 500]
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=101)
+    row_req, pos, tiles = [], [], []
+    for r, (n, s0) in enumerate(zip(lengths, starts)):
+        first = len(pos)
+        for p in range(s0, n):
+            row_req.append(r)
+            pos.append(p)
+        for off in range(0, n - s0, 128):
+            tiles.append([first + off, min(128, n - s0 - off)])
+    q = rnd(len(pos), nh, d, seed=102, dtype=dtype)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(d)
+    ops().attention_tcgen05(
+        q.view(len(pos), nh * d), k_pool, v_pool, out.view(len(pos), nh * d), tables,
+        torch.tensor(row_req, dtype=torch.int32, device=DEV),
+        torch.tensor(pos, dtype=torch.int32, device=DEV),
+        torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles), nh, nkv, d, page, window, scale)
+    torch.cuda.synchronize()
+    ops().attention_tcgen05_check(d)
+    want = attention_reference(q.float().cpu(), dense, row_req, pos, nh, nkv, window, scale)
+    assert torch.isfinite(out.float()).all()
+    close_tensor_core_attention(out, want)
+
+
+def test_attention_tcgen05_far_key_and_window_edge():
+    nh, nkv, d, page, n = 2, 1, 64, 16, 700
+    dtype = torch.bfloat16
+    k_pool, v_pool, tables, dense = paged_setup([n], nh, nkv, d, page, dtype, seed=103)
+    rows = 150
+    q = rnd(rows, nh, d, seed=104, dtype=dtype)
+    scale = 1.0 / math.sqrt(d)
+    tiles = torch.tensor([[0, 128], [128, 22]], dtype=torch.int32, device=DEV)
+    pos = list(range(n - rows, n))
+    for far in (0, 127, 128, 300, 699 - 30, 699 - 31, 640):
+        k, v = dense[0][0].clone(), dense[0][1]
+        k[far, 0] = (q[rows - 1, 0].float().cpu() * 40.0).to(dtype).float()
+        k_pool2 = k_pool.clone()
+        k_pool2[int(tables[0, far // page]) * page + far % page, 0] = k[far, 0].to(dtype).to(DEV)
+        for window in (None, 30):
+            out = torch.empty(rows, nh * d, dtype=dtype, device=DEV)
+            ops().attention_tcgen05(q.view(rows, nh * d), k_pool2, v_pool, out, tables,
+                                    torch.zeros(rows, dtype=torch.int32, device=DEV),
+                                    torch.tensor(pos, dtype=torch.int32, device=DEV), tiles, 2,
+                                    nh, nkv, d, page, window, scale)
+            got = out.view(rows, nh, d)[rows - 1, 0].float().cpu()
+            if window is None or far + window >= n - 1:
+                assert float((got - v[far, 0]).abs().max()) < 0.03
+            else:
+                assert float((got - v[far, 0]).abs().max()) > 0.1
+    ops().attention_tcgen05_check(d)

@@ -28,7 +28,8 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
-Q_TILE_ROWS = 64   # rows of one request that the prompt-attention kernel takes per block
+Q_TILE_ROWS = 64         # rows of one request that the mma.sync prompt-attention kernel takes per block
+Q_WIDE_TILE_ROWS = 128   # ... and the tcgen05 one
 
 
 def _round4(n: int) -> int:
@@ -52,6 +53,8 @@ class BatchLayout:
     want: int = 0
     tiles: int = 0
     max_tiles: int = 0
+    wide_tiles: int = 0
+    max_wide_tiles: int = 0
     slots: Optional[List[int]] = None
     tables: Optional[List[int]] = None
     total: int = 0
@@ -72,6 +75,8 @@ class BatchLayout:
         lay.want = take(W)
         lay.max_tiles = T // Q_TILE_ROWS + R
         lay.tiles = take(2 * lay.max_tiles)
+        lay.max_wide_tiles = T // Q_WIDE_TILE_ROWS + R
+        lay.wide_tiles = take(2 * lay.max_wide_tiles)
         lay.slots = [take(T) for _ in table_widths]
         lay.tables = [take(R * w) for w in table_widths]
         lay.total = at
@@ -161,6 +166,7 @@ class BatchBuilder:
         want_at = 0
         n_tiles = 0
         tiles = []   # (last position + 1: the keys the tile walks, first row, rows)
+        wide_tiles = []
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = e.cache.length
@@ -178,6 +184,9 @@ class BatchBuilder:
                 rows_here = min(Q_TILE_ROWS, n - first)
                 tiles.append((start + first + rows_here, row + first, rows_here))
                 n_tiles += 1
+            for first in range(0, n, Q_WIDE_TILE_ROWS):
+                rows_here = min(Q_WIDE_TILE_ROWS, n - first)
+                wide_tiles.append((start + first + rows_here, row + first, rows_here))
             for g in range(len(widths)):
                 table = np.asarray(e.cache.tables[g], dtype=np.int32)
                 buf[lay.tables[g] + r * widths[g]:lay.tables[g] + r * widths[g] + len(table)] = table
@@ -193,6 +202,10 @@ class BatchBuilder:
         for at, (_, first_row, rows_here) in enumerate(tiles):
             buf[lay.tiles + 2 * at] = first_row
             buf[lay.tiles + 2 * at + 1] = rows_here
+        wide_tiles.sort(key=lambda item: -item[0])
+        for at, (_, first_row, rows_here) in enumerate(wide_tiles):
+            buf[lay.wide_tiles + 2 * at] = first_row
+            buf[lay.wide_tiles + 2 * at + 1] = rows_here
         dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         self.last_bytes = lay.total * 4
         if dev.is_cuda:
@@ -210,5 +223,7 @@ class BatchBuilder:
             row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
             kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
             q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots,
-            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=n_tiles)
+            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=n_tiles,
+            q_wide_tiles=view(lay.wide_tiles, 2 * lay.max_wide_tiles).view(lay.max_wide_tiles, 2),
+            n_q_wide_tiles=len(wide_tiles))
         return ctx, view(lay.want, Wc), W

@@ -18,4 +18,6 @@ def all_variants():
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_prefill.cu", (f"HEAD_DIM={head_dim}",), ()))
+    for head_dim in (64, 128):
+        jobs.append(("attention_tcgen05.cu", (f"HEAD_DIM={head_dim}",), ()))
     return jobs

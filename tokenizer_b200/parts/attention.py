@@ -110,6 +110,14 @@ class GQAttention:
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
             return
+        if q.dtype == torch.bfloat16 and ctx.q_wide_tiles is not None and ctx.max_q_len >= 96 and \
+                ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
+            # long portions: the tcgen05 kernel (128-row tiles, scores in tensor memory)
+            ops.attention_tcgen05(
+                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                ctx.q_wide_tiles, ctx.n_q_wide_tiles, self.nh, self.nkv, self.d, group.page_size,
+                self.window, self.scale)
+            return
         if q.dtype == torch.bfloat16 and ctx.q_tiles is not None and \
                 ops.prefill_attention_supported(self.nh, self.nkv, self.d):
             ops.prefill_attention(

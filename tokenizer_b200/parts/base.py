@@ -133,6 +133,9 @@ class StepContext:
     # int32 [n_q_tiles, 2] = (first row, rows); None when the builder made none
     q_tiles: Optional[torch.Tensor] = None
     n_q_tiles: int = 0
+    # the same cut into tiles of up to 128 rows (the tcgen05 attention kernel's tile)
+    q_wide_tiles: Optional[torch.Tensor] = None
+    n_q_wide_tiles: int = 0
     # host copies, for choosing kernels and for mixers that loop over requests
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)
