@@ -35,7 +35,7 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size");
 #define FA_SOFTMAX_THREADS 128
 #define FA_LOADER_THREADS 128
 #define FA_THREADS (FA_SOFTMAX_THREADS + FA_LOADER_THREADS + 32)
-#define FA_WAIT_LIMIT (1u << 24)
+#define FA_WAIT_LIMIT (1u << 17)      // polls of up to 20 us each: seconds in all
 constexpr int kDBlocks = HEAD_DIM / 64;           // 64-lane pieces of the head (128 bytes a row)
 constexpr int kSubTile = 128 * 128;               // bytes of a [128 x 64] bfloat16 swizzled tile
 constexpr int kTmemCols = 256;                    // S: 128 columns, P V: up to 128
@@ -51,13 +51,16 @@ __device__ __forceinline__ void fa_mbar_arrive(unsigned long long* bar) {
 }
 __device__ __forceinline__ bool fa_mbar_wait(unsigned long long* bar, unsigned parity) {
   const unsigned addr = fa_smem(bar);
+  // the thread sleeps in hardware until the phase completes or the hint runs out, so
+  // waiting warps do not take issue slots from working ones
+  const unsigned suspend_ns = 20000u;
   for (unsigned spin = 0; spin < FA_WAIT_LIMIT; ++spin) {
     unsigned done;
     asm volatile(
         "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(suspend_ns) : "memory");
     if (done) return true;
   }
   atomicExch(&fa_error_flag, 1);
@@ -207,17 +210,13 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         fa_cp16(v_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), v_pool + offset + c * 8, ok);
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
-      // block b - 1 (and q with block 0) has landed for this thread once at most one group is pending
-      if (b == 0) continue;
-      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+      // say so as soon as the block has landed (q rides with block 0): the copies of
+      // block b run while block b - 1 is multiplied, so this wait is short
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (b == 1) fa_mbar_arrive(q_full);
-      fa_mbar_arrive(&kv_full[(b - 1) & 1]);
+      if (b == 0) fa_mbar_arrive(q_full);
+      fa_mbar_arrive(&kv_full[buf]);
     }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (n_blocks == 1) fa_mbar_arrive(q_full);
-    if (n_blocks >= 1) fa_mbar_arrive(&kv_full[(n_blocks - 1) & 1]);
   } else if (live && warp == 8) {
     // ---------------- products ----------------
     if (lane == 0) {
@@ -273,11 +272,15 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int c0 = 0; c0 < FA_KEYS; c0 += 32) {
         float s[32];
         fa_tmem_load32(tmem_s + lane_base + (unsigned)c0, s);
+        if (needs_mask) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = kb + c0 + j;
-          const bool seen = !needs_mask || (key <= p_row && key >= lo_row);
-          m_blk = fmaxf(m_blk, seen ? s[j] : -INFINITY);
+          for (int j = 0; j < 32; ++j) {
+            const int key = kb + c0 + j;
+            m_blk = fmaxf(m_blk, (key <= p_row && key >= lo_row) ? s[j] : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) m_blk = fmaxf(m_blk, s[j]);
         }
       }
       const float m_new = fmaxf(m_run, m_blk);
@@ -290,12 +293,19 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int c0 = 0; c0 < FA_KEYS; c0 += 32) {
         float s[32];
         fa_tmem_load32(tmem_s + lane_base + (unsigned)c0, s);
+        if (needs_mask) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = kb + c0 + j;
-          const bool seen = !needs_mask || (key <= p_row && key >= lo_row);
-          s[j] = seen ? fa_exp2(fmaf(s[j], scale_log2, -m_scaled)) : 0.f;
-          sum += s[j];
+          for (int j = 0; j < 32; ++j) {
+            const int key = kb + c0 + j;
+            s[j] = (key <= p_row && key >= lo_row) ? fa_exp2(fmaf(s[j], scale_log2, -m_scaled)) : 0.f;
+            sum += s[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            s[j] = fa_exp2(fmaf(s[j], scale_log2, -m_scaled));
+            sum += s[j];
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {                     // four 16-byte pieces of 8 keys

@@ -27,7 +27,7 @@
 #define TC_BLOCK_K 64          // 64 bfloat16 = 128 bytes = one swizzle row
 #define TC_UMMA_K 16
 #define TC_THREADS 192
-#define TC_WAIT_LIMIT (1u << 24)
+#define TC_WAIT_LIMIT (1u << 17)      // polls of up to 20 us each: seconds in all
 
 __device__ int tc_error_flag = 0;   // set when a bounded wait gave up
 
@@ -44,13 +44,16 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 // Waits for the phase with the given parity; false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
   const unsigned addr = tc_smem(bar);
+  // the thread sleeps in hardware until the phase completes or the hint runs out, so
+  // waiting warps do not take issue slots from working ones
+  const unsigned suspend_ns = 20000u;
   for (unsigned spin = 0; spin < TC_WAIT_LIMIT; ++spin) {
     unsigned done;
     asm volatile(
         "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(suspend_ns) : "memory");
     if (done) return true;
   }
   atomicExch(&tc_error_flag, 1);

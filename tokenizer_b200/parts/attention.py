@@ -12,6 +12,7 @@ through Wo (reference: qwen-infer/src/model.rs:262-328, 397-414, 119-129).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -22,6 +23,13 @@ from .base import CacheNeed, KVNeed, build_part, register_part
 from .linear import Linear
 
 _position_tables = {}
+
+# Which kernel takes long prompt portions in bfloat16.  The tcgen05 kernel (scores in
+# tensor memory) is complete and tested but, in its first form, its per-block chain
+# (product -> softmax -> product) is not yet overlapped, and it runs 80 us where the
+# mma.sync kernel runs 72 us on 2,048 tokens of 14 heads; TOKB200_ATTENTION=tcgen05
+# selects it.
+_PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "mma")
 
 
 class GQAttention:
@@ -110,9 +118,10 @@ class GQAttention:
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
             return
-        if q.dtype == torch.bfloat16 and ctx.q_wide_tiles is not None and ctx.max_q_len >= 96 and \
+        if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
+                ctx.q_wide_tiles is not None and ctx.max_q_len >= 96 and \
                 ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
-            # long portions: the tcgen05 kernel (128-row tiles, scores in tensor memory)
+            # long portions on the tcgen05 kernel (128-row tiles, scores in tensor memory)
             ops.attention_tcgen05(
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 ctx.q_wide_tiles, ctx.n_q_wide_tiles, self.nh, self.nkv, self.d, group.page_size,
