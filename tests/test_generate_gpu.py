@@ -216,3 +216,35 @@ def test_shared_beginnings_on_the_engine(folder):
     assert scheduler.stats.shared_prefix_tokens == 3 * page
     assert results[first].tokens == alone[0] and results[second].tokens == alone[1]
     engine.cache.check()
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_long_portions_on_either_prompt_kernel(tmp_path_factory, monkeypatch, kernel):
+    """Heads of 64 and portions of more than a hundred tokens reach the tensor-core
+    kernels for prompts; either of the two (mma.sync tiles of 64 rows, tcgen05 tiles of
+    128 rows) must give the plain logits, cut in portions that end inside a tile."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200 import Qwen2Config, write_random_model
+    from tokenizer_b200.engine import StepEntry
+    from tokenizer_b200.parts import attention
+    monkeypatch.setattr(attention, "_PROMPT_KERNEL", kernel)
+    config = Qwen2Config.from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=2, hidden_size=128,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=256, vocab_size=333,
+        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+        use_sliding_window=False, sliding_window=None, max_window_layers=2))
+    path = str(tmp_path_factory.mktemp("tiny_long"))
+    write_random_model(path, config, 5, scale=SHARPEN)
+    cfg, w = plain.load_folder(path)
+    ids = random_ids(421, config.vocab_size, 17)
+    want = plain.all_logits(cfg, w, ids)
+    model = tb.load_model(path, dtype="bfloat16")
+    engine = tb.engine_for(model, 512, 16, max_requests=2)
+    cache = engine.cache.open("x")
+    got, at = [], 0
+    for n in (150, 131, 140):
+        engine.cache.reserve(cache, n)
+        got.append(engine.step([StepEntry(cache, ids[at:at + n], list(range(n)))]).float().cpu())
+        at += n
+    bound = 2e-2 * float(want.abs().max())
+    assert float((torch.cat(got) - want).abs().max()) <= bound

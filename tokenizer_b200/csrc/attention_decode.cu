@@ -12,10 +12,11 @@
 // tile's values in shared memory and reads them with ldmatrix.trans.
 //
 // A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk
-// is 1024 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
+// is 256 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
 // function of the row's own position and window and does not change with the
-// batch around it; up to 1024 keys are one block's work and need no merge across
-// blocks.  The eight warps of a block take tiles of 32 keys in turn, each with its
+// batch around it; up to 256 keys are one block's work and need no merge across
+// blocks.  (A block's time is a chain of dependent loads per tile, table entry then
+// keys and values, so short pieces on many blocks beat long pieces on few.)  The eight warps of a block take tiles of 32 keys in turn, each with its
 // own running maximum, sum and weighted values; they are merged once at the end.  Pieces of several blocks meet in scratch memory (max, sum, weighted
 // values per (row, head, split)); the block that finishes last for a (row, kv
 // head) merges them in index order and writes the output.
@@ -33,7 +34,7 @@
 #define DEC_MAX_SPLITS 32
 #define DEC_TILE 32            // keys a warp takes per pass
 #define DEC_BLOCK_KEYS (DEC_WARPS * DEC_TILE)   // keys a block takes per pass
-#define DEC_MIN_CHUNK 1024     // a row with no more keys than this is one block's work: no merge across blocks
+#define DEC_MIN_CHUNK 256      // one pass of a block's warps; a row with no more keys needs no merge across blocks
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma

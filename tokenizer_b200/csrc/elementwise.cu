@@ -567,3 +567,31 @@ TOKB200_API int tokb200_advance_decode(int* ids, const int* drawn, int* pos, int
   if (status != TOKB200_OK) return status;
   return launch_dependent(bump_counter_kernel, dim3(1), dim3(1), 0, stream, step_counter);
 }
+
+// ---- bringing weights into L2 ahead of their use ------------------------------------
+// While a decoding step's kernels each wait on a short chain of loads, DRAM is mostly
+// idle.  This kernel asks the memory system to bring `bytes` at `base` into L2 and
+// returns at once; it runs on a second stream beside the layer that comes before the
+// one whose weights it names, so that layer's kernels then read L2 and not DRAM.
+constexpr int kPrefetchChunk = 8192;
+
+__global__ void prefetch_l2_kernel(const char* __restrict__ base, long long bytes) {
+  long long chunk = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long step = (long long)gridDim.x * blockDim.x;
+  for (long long at = chunk * kPrefetchChunk; at < bytes; at += step * kPrefetchChunk) {
+    long long left = bytes - at;
+    unsigned size = (unsigned)(left < kPrefetchChunk ? (left & ~15ll) : kPrefetchChunk);
+    if (size)
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + at), "r"(size) : "memory");
+  }
+}
+
+TOKB200_API int tokb200_prefetch_l2(const void* base, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return TOKB200_OK;
+  if (reinterpret_cast<uintptr_t>(base) % 16) return TOKB200_BAD_ALIGNMENT;
+  long long chunks = (bytes + kPrefetchChunk - 1) / kPrefetchChunk;
+  int blocks = (int)((chunks + 127) / 128);
+  if (blocks > 16) blocks = 16;
+  prefetch_l2_kernel<<<blocks, 128, 0, stream>>>(static_cast<const char*>(base), bytes);
+  return (int)cudaGetLastError();
+}

@@ -191,6 +191,12 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor],
         _ptr(uniform), _ptr(out), _stream()), "sample")
 
 
+def prefetch_l2(t: torch.Tensor) -> None:
+    """Ask for a tensor's bytes to be brought into L2; returns at once."""
+    _check(_lib("elementwise").tokb200_prefetch_l2(
+        _ptr(t), _ll(t.numel() * t.element_size()), _stream()), "prefetch_l2")
+
+
 def advance_decode(ids, drawn, pos, kv_len, row_req, slots, tables, page, history,
                    step_counter) -> None:
     """After a decoding step: the drawn ids become the next inputs and every

@@ -86,6 +86,9 @@ class GQAttention:
     def cache_need(self):
         return CacheNeed(kv=KVNeed(self.nkv, self.d, self.window))
 
+    def streamed_weights(self):
+        return [self.qkv.weight, self.out.weight]
+
     def forward(self, h, ctx, cache):
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
         group = ctx.groups[cache.group]

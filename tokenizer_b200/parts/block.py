@@ -11,6 +11,13 @@ class PreNormResidual:
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
+    def streamed_weights(self):
+        """The matrices a step with few rows reads once, in the order it reads them."""
+        out = []
+        for part in (self.mixer, self.feed_forward):
+            out += list(getattr(part, "streamed_weights", lambda: [])())
+        return out
+
     def forward(self, stream, ctx, cache):
         stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache))
         stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm)))

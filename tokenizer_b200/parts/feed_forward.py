@@ -40,6 +40,9 @@ class GatedMLP:
             self.gate_up = Linear(runtime.matrix(torch.cat([gate, up], dim=0)))
         self.down = Linear(runtime.matrix(store.get(x + ".down_proj.weight")))
 
+    def streamed_weights(self):
+        return [self.gate_up_weight if self.fused else self.gate_up.weight, self.down.weight]
+
     def forward(self, h):
         act = self.runtime.empty(h.shape[0], self.inner)
         if self.fused:

@@ -2,11 +2,13 @@
 the spec lists.  Nothing here names an architecture."""
 from __future__ import annotations
 
+import os
 from typing import List
 
 import torch
 
 from ..config.spec import ModelSpec
+from ..kernels import ops
 from ..weights.store import TensorSpec, WeightStore
 from .base import CacheBinding, ResidualStream, Runtime, StepContext, build_part, part_class
 
@@ -22,6 +24,28 @@ def declared_tensors(spec: ModelSpec) -> List[TensorSpec]:
     out += part_class("norm", spec.final_norm.kind).tensors(spec.final_norm)
     out += part_class("head", spec.head.kind).tensors(spec.head)
     return out
+
+
+_PREFETCH = os.environ.get("TOKB200_L2_PREFETCH", "1") != "0"
+
+
+class _Prefetcher:
+    """Launches L2 prefetches on a second stream, forked from and joined to the
+    stream the step runs on (which may be capturing a graph)."""
+
+    def __init__(self, side):
+        self.side, self.main, self.used = side, torch.cuda.current_stream(), False
+
+    def fetch(self, tensors):
+        self.side.wait_stream(self.main)
+        with torch.cuda.stream(self.side):
+            for t in tensors:
+                ops.prefetch_l2(t)
+        self.used = True
+
+    def join(self):
+        if self.used:
+            self.main.wait_stream(self.side)
 
 
 class DecoderModel:
@@ -45,6 +69,17 @@ class DecoderModel:
         tied = self.embedding.table if spec.head.params.get("tied_to") else None
         self.head = head_cls(spec.head, store, runtime, tied_table=tied)
         self.order = spec.order
+        self._side = None
+
+    def _prefetcher(self, ctx):
+        """Steps of few rows stream every weight once and wait on memory in each
+        kernel; for them the next layer's weights are brought into L2 on a second
+        stream while this layer runs."""
+        if not _PREFETCH or self.runtime.dtype != torch.bfloat16 or ctx.n_tokens > 64:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.runtime.device)
+        return _Prefetcher(self._side)
 
     def cache_needs(self):
         """One entry per call of the order: the need of the mixer that runs
@@ -60,8 +95,13 @@ class DecoderModel:
         """Run the rows of `ctx` through every call of the order and return the
         float32 logits of `want_rows` (int32 row indices), [len(want_rows), vocab]."""
         stream = ResidualStream(self.embedding.forward(ctx.ids))
-        for call, binding in zip(self.order, bindings):
+        ahead = self._prefetcher(ctx)
+        for at, (call, binding) in enumerate(zip(self.order, bindings)):
+            if ahead is not None and at + 1 < len(self.order):
+                ahead.fetch(self.blocks[self.order[at + 1].layer].streamed_weights())
             self.blocks[call.layer].forward(stream, ctx, binding)
+        if ahead is not None:
+            ahead.join()
         if want_rows.shape[0] == 0:
             stream.pending = None
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.runtime.device)
