@@ -50,6 +50,27 @@ class FakeEngine:
             self.cache.commit(e.cache, len(e.tokens))
         return np.stack(rows) if rows else np.zeros((0, self.vocab), dtype=np.float32)
 
+    def decode_steps(self, entries, n_steps):
+        """Greedy steps without the scheduler in between, as the engine offers them:
+        pages for all the steps are reserved first, or nothing happens."""
+        from tokenizer_b200.cache.manager import OutOfPages
+        from tokenizer_b200.engine.batch import StepEntry
+        missing = [0] * len(self.cache.groups)
+        for e in entries:
+            missing = [a + b for a, b in zip(missing, self.cache.pages_missing(e.cache, n_steps))]
+        if any(m > a.available for m, a in zip(missing, self.cache.allocators)):
+            raise OutOfPages("no pages for the burst")
+        for e in entries:
+            self.cache.reserve(e.cache, n_steps)
+        self.bursts = getattr(self, "bursts", 0) + 1
+        tokens = [e.tokens[0] for e in entries]
+        out = []
+        for _ in range(n_steps):
+            logits = self.step([StepEntry(e.cache, [t], [0]) for e, t in zip(entries, tokens)])
+            tokens = [int(np.argmax(row)) for row in logits]
+            out.append(tokens)
+        return out
+
     def _read_back(self, cache):
         out = []
         for position in range(cache.length):

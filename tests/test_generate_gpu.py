@@ -248,3 +248,21 @@ def test_long_portions_on_either_prompt_kernel(tmp_path_factory, monkeypatch, ke
         at += n
     bound = 2e-2 * float(want.abs().max())
     assert float((torch.cat(got) - want).abs().max()) <= bound
+
+
+def test_decode_bursts_on_the_engine(folder):
+    """Greedy requests run several steps on the device between visits to the host;
+    ids, reasons and counts equal those of single steps (one request ends by
+    max_tokens inside a burst, one by an EOS id)."""
+    import tokenizer_b200 as tb
+    path, config, page = folder
+    model = tb.load_model(path, dtype="float32")
+    prompts = [random_ids(n, config.vocab_size, 700 + n) for n in (6, 23, 40)]
+    free = tb.generate(model, prompts[2], tb.GenerateParams.greedy(20)).tokens
+    params = [tb.GenerateParams.greedy(21), tb.GenerateParams.greedy(10),
+              tb.GenerateParams(max_tokens=20, eos=[free[9]])]
+    single = tb.generate_batch(model, prompts, params, max_batch_size=3, page_size=page)
+    burst = tb.generate_batch(model, prompts, params, max_batch_size=3, page_size=page, decode_burst=8)
+    for a, b in zip(single, burst):
+        assert a.tokens == b.tokens and a.reason == b.reason
+        assert a.completion_tokens == b.completion_tokens

@@ -170,3 +170,33 @@ def test_windowed_groups_through_the_scheduler():
     out = run_checked(s)
     for rid, p in zip(ids, prompts):
         assert out[rid].tokens == solo(p, GenerateParams(max_tokens=7), page_size=4).tokens
+
+
+def test_decode_bursts_give_the_same_ids_and_fall_back_when_pages_are_short():
+    """Several steps on the device between visits to the host: same ids, same reasons
+    (max_tokens inside a burst, an EOS id inside a burst, a request that joins later),
+    and with a pool too small for a whole burst the single steps and preemption still work."""
+    prompts = [random_ids(n, 50, 70 + n) for n in (3, 8, 21, 5)]
+    free = [solo(p, GenerateParams(max_tokens=14)).tokens for p in prompts]
+    params = [GenerateParams(max_tokens=14), GenerateParams(max_tokens=9),
+              GenerateParams(max_tokens=14, eos=[free[2][6]]), GenerateParams(max_tokens=11)]
+    want = [solo(p, q) for p, q in zip(prompts, params)]
+    for pages, burst in ((256, 4), (256, 5), (12, 4)):
+        engine = FakeEngine(num_pages=pages)
+        s = Scheduler(engine, max_batch_size=4, token_budget=16, decode_burst=burst)
+        ids = [s.add_request(p, q) for p, q in zip(prompts[:3], params[:3])]
+        for _ in range(3):
+            s.step()
+            s.cache.check()
+        ids.append(s.add_request(prompts[3], params[3]))
+        out = run_checked(s)
+        for rid, w in zip(ids, want):
+            assert out[rid].tokens == w.tokens and out[rid].reason == w.reason
+            assert out[rid].completion_tokens == w.completion_tokens
+        assert engine.bursts > 0
+        if pages == 12:
+            assert s.stats.preemptions > 0
+    sampled = Scheduler(FakeEngine(num_pages=64), max_batch_size=2, token_budget=16, decode_burst=4)
+    sampled.add_request(prompts[0], GenerateParams(max_tokens=6, temperature=0.7, seed=3))
+    run_checked(sampled)
+    assert not hasattr(sampled.engine, "bursts")          # sampled requests take single steps

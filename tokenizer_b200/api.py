@@ -50,9 +50,11 @@ def generate_batch(model_or_engine, prompts: Sequence[Sequence[int]],
                    token_bytes: Optional[Callable[[int], bytes]] = None,
                    on_chunk: Optional[Callable[[int, str], Control]] = None,
                    max_batch_size: int = 64, token_budget: int = 2048,
-                   page_size: int = 16) -> List[Generated]:
+                   page_size: int = 16, decode_burst: int = 1) -> List[Generated]:
     """Run every prompt to its end with continuous batching; results in the
-    order of `prompts`.  `on_chunk(index, text)` may return Control.STOP."""
+    order of `prompts`.  `on_chunk(index, text)` may return Control.STOP.
+    `decode_burst` > 1 lets greedy decoding run that many steps on the device
+    between visits to the host (text then arrives in pieces of that many ids)."""
     if isinstance(params, GenerateParams):
         params = [params] * len(prompts)
     if len(params) != len(prompts):
@@ -65,7 +67,7 @@ def generate_batch(model_or_engine, prompts: Sequence[Sequence[int]],
         engine = engine_for(model_or_engine, need, page_size,
                             max_requests=max(1, min(max_batch_size, len(prompts))))
     scheduler = Scheduler(engine, max_batch_size=min(max_batch_size, engine.cache.max_requests),
-                          token_budget=token_budget)
+                          token_budget=token_budget, decode_burst=decode_burst)
     ids = []
     for index, (prompt, p) in enumerate(zip(prompts, params)):
         callback = (lambda text, index=index: on_chunk(index, text)) if on_chunk else None

@@ -336,7 +336,14 @@ TOKB200_API int tokb200_decode_attention(
       configured[device] = true;
     }
   }
-  dim3 grid(DEC_MAX_SPLITS, nkv, n_rows);
+  // no row sees more keys than its table reaches (or its window holds), so no row has
+  // more pieces than this; blocks beyond would only find that out and leave
+  long long reach = (long long)table_stride * page;
+  if (window >= 0 && window + 1 < reach) reach = window + 1;
+  long long most = (reach + DEC_MIN_CHUNK - 1) / DEC_MIN_CHUNK;
+  if (most > DEC_MAX_SPLITS) most = DEC_MAX_SPLITS;
+  if (most < 1) most = 1;
+  dim3 grid((unsigned)most, nkv, n_rows);
   return launch_dependent(decode_attention_kernel, grid, dim3(DEC_THREADS), smem, stream,
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,

@@ -160,7 +160,9 @@ static int launch_small_m_gated(const void* x, const void* w, void* out, int M, 
                                 cudaStream_t stream) {
   const int tiles = (N / 2 + 7) / 8;
   const int k_per_split = (K + 31) / 32 * 32;
-  if (tiles >= 1024) {
+  // two row tiles a block from 300 tiles on: with one, a feed-forward of a few thousand
+  // outputs needs more blocks than the device holds at once and runs a second, short wave
+  if (tiles >= 300) {
     return launch_dependent(linear_small_m_kernel<MT, 2, true>, dim3((tiles + 1) / 2), dim3(LSM_THREADS),
                             0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                             (const float*)nullptr, out, 0, M, N, K, k_per_split);

@@ -18,6 +18,14 @@ count of how much of that context the cache already holds.  One iteration:
  4. run the step, draw one id for each request whose context is now whole, let
     its cursor decide between going on and finishing, free what finished.
 
+With `decode_burst` > 1 an iteration in which nobody waits, every running
+request is decoding and draws greedily runs up to that many steps on the
+device in one go (`engine.decode_steps`: each step's drawn ids are the next
+step's inputs without a visit to the host) and then hands the ids to the
+cursors one by one; ids after a request's end are dropped with its cache.  The
+host's share of a step is paid once a burst.  When the pool has no pages for the
+whole burst the iteration runs a single step as above.
+
 The reference's scheduler (qwen-server/src/engine.rs:229-402, 455-704) admits
 and preempts in the same way but runs a whole prompt per iteration; the token
 budget and the portions are this engine's.
@@ -61,12 +69,16 @@ class _Request:
 
 
 class Scheduler:
-    def __init__(self, engine, max_batch_size: int = 8, token_budget: int = 512):
+    def __init__(self, engine, max_batch_size: int = 8, token_budget: int = 512,
+                 decode_burst: int = 1):
         """`engine` offers `cache` (a CachePlan), `step(entries) -> logits`,
         `sample(logits, temperature, top_p, uniform) -> ids` and
-        `max_positions`."""
+        `max_positions`; for bursts also `decode_steps(entries, n) -> ids[n][entries]`."""
         if max_batch_size < 1 or token_budget < 1:
             raise ValueError("the batch holds at least one request and one token")
+        if decode_burst < 1:
+            raise ValueError("a burst is at least one step")
+        self.decode_burst = decode_burst if hasattr(engine, "decode_steps") else 1
         self.engine = engine
         self.cache = engine.cache
         self.max_batch_size = max_batch_size
@@ -107,6 +119,9 @@ class Scheduler:
         """Run one iteration; returns the ids of the requests that finished."""
         done_before = set(self.finished)
         self._admit()
+        burst = self._burst_length()
+        if burst > 1 and self._run_burst(burst):
+            return [i for i in self.finished if i not in done_before]
         plan = self._plan_and_reserve()
         if plan:
             entries = [StepEntry(r.cache, r.context[r.cache.length:r.cache.length + n],
@@ -120,6 +135,43 @@ class Scheduler:
                 self.stats.peak_pages, max((a.live for a in self.cache.allocators), default=0))
             self._sample([r for r, n in plan if r.cache.length == len(r.context)], logits)
         return [i for i in self.finished if i not in done_before]
+
+    def _burst_length(self) -> int:
+        """How many steps the running requests can take together on the device:
+        0 unless nobody waits and all of them decode greedily."""
+        if self.decode_burst <= 1 or self.waiting or not self.running:
+            return 0
+        n = self.decode_burst
+        for r in self.running:
+            c = r.cursor
+            if len(r.context) - r.cache.length != 1 or c.params.temperature != 0.0 or c.done is not None:
+                return 0
+            n = min(n, c.params.max_tokens - c.produced, self.engine.max_positions - len(r.context))
+        return n
+
+    def _run_burst(self, n: int) -> bool:
+        ready = sorted(self.running, key=lambda r: r.id)
+        entries = [StepEntry(r.cache, [r.context[-1]]) for r in ready]
+        try:
+            ids = self.engine.decode_steps(entries, n)
+        except OutOfPages:
+            return False                  # nothing was reserved or run: take a single step
+        self.stats.steps += n
+        self.stats.tokens_run += n * len(ready)
+        self.stats.max_running = max(self.stats.max_running, len(self.running))
+        self.stats.peak_pages = max(
+            self.stats.peak_pages, max((a.live for a in self.cache.allocators), default=0))
+        now = time.perf_counter()
+        for at, r in enumerate(ready):
+            for k in range(n):
+                self.stats.tokens_sampled += 1
+                token = int(ids[k][at])
+                if not r.cursor.accept(token):
+                    break
+                r.context.append(token)
+            if r.cursor.done is not None:
+                self._retire(r, now)
+        return True
 
     def _context_pages(self, request: _Request) -> int:
         return self.cache.pages_for_tokens(len(request.context))
