@@ -262,6 +262,45 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   }
   pdl_wait();
   pdl_launch();
+  // what the epilogue needs from memory is asked for now, so that it has arrived by then:
+  // thread i of the epilogue serves row m = i / 8 and lane pair j0 + i % 8
+  constexpr int kEpi = (64 * MT + LSM_THREADS - 1) / LSM_THREADS;
+  const int half = d / 2;
+  float e_bias_a[kEpi], e_bias_b[kEpi], e_cos[kEpi], e_sin[kEpi];
+  int e_slot[kEpi];
+#pragma unroll
+  for (int e = 0; e < kEpi; ++e) {
+    const int i = threadIdx.x + e * LSM_THREADS;
+    const int m = i / 8, j = j0 + i % 8;
+    e_bias_a[e] = e_bias_b[e] = 0.f;
+    e_cos[e] = 1.f;
+    e_sin[e] = 0.f;
+    e_slot[e] = -1;
+    if (i < 8 * M) {
+      if (bias) {
+        e_bias_a[e] = bias[head * d + j];
+        e_bias_b[e] = bias[head * d + j + half];
+      }
+      if (head >= nh && slot) e_slot[e] = slot[m];
+      if (head < nh + nkv) {
+        const int p = pos[m];
+        e_cos[e] = cos_t[(size_t)p * half + j];
+        e_sin[e] = sin_t[(size_t)p * half + j];
+      }
+    }
+  }
+  constexpr bool kXRing = MT <= 2;
+  uint4 x_ring[kXRing ? LSM_PRE : 1][MT];
+  if (kXRing) {
+#pragma unroll
+    for (int i = 0; i < LSM_PRE; ++i) {
+      const int kk = k_first + i * step;
+      const bool k_ok = kk + 8 * t + 8 <= K;
+#pragma unroll
+      for (int j = 0; j < MT; ++j)
+        x_ring[i][j] = load16(x + (size_t)(8 * j + g) * K + kk + 8 * t, 8 * j + g < M && k_ok);
+    }
+  }
   for (int k = k_first; k < K; k += LSM_PRE * step) {
 #pragma unroll
     for (int i = 0; i < LSM_PRE; ++i) {
@@ -276,7 +315,13 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           const int m = 8 * j + g;
-          const uint4 xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
+          uint4 xv;
+          if (kXRing) {
+            xv = x_ring[i][j];
+            x_ring[i][j] = load16(x + (size_t)m * K + kn + 8 * t, m < M && next_ok);
+          } else {
+            xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
+          }
           mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
           mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
         }
@@ -292,8 +337,10 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   }
   __syncthreads();
 
-  const int half = d / 2;
-  for (int i = threadIdx.x; i < 8 * M; i += LSM_THREADS) {
+#pragma unroll
+  for (int e = 0; e < kEpi; ++e) {
+    const int i = threadIdx.x + e * LSM_THREADS;
+    if (i >= 8 * M) break;
     const int m = i / 8, rr = i % 8;
     const int j = j0 + rr;
     float a = 0.f, b = 0.f;
@@ -302,25 +349,21 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       a += part[s][rr][m];
       b += part[s][rr + 8][m];
     }
-    if (bias) {
-      a += bias[head * d + j];
-      b += bias[head * d + j + half];
-    }
+    a += e_bias_a[e];
+    b += e_bias_b[e];
     __nv_bfloat16* dst;
     if (head < nh) {
       dst = q_out + ((size_t)m * nh + head) * d;
     } else {
-      const int s = slot ? slot[m] : -1;
+      const int s = e_slot[e];
       if (s < 0) continue;                                    // no cache write for this row
       const bool is_key = head < nh + nkv;
       __nv_bfloat16* pool = is_key ? k_pool : v_pool;
       if (!pool) continue;
       dst = pool + ((size_t)s * nkv + (head - nh - (is_key ? 0 : nkv))) * d;
     }
-    if (head < nh + nkv) {
-      const int p = pos[m];
-      const float c = cos_t[(size_t)p * half + j], sn = sin_t[(size_t)p * half + j];
-      const float ra = a * c - b * sn, rb = b * c + a * sn;
+    if (head < nh + nkv) {                                    // values are not rotated: cos 1, sin 0
+      const float ra = a * e_cos[e] - b * e_sin[e], rb = b * e_cos[e] + a * e_sin[e];
       a = ra;
       b = rb;
     }
