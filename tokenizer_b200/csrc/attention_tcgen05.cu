@@ -2,23 +2,32 @@
 // (bfloat16, tcgen05 with the scores and the weighted values in tensor memory).
 //
 // A block takes one (tile of up to 128 consecutive rows of one request, query head)
-// and walks the request's keys in blocks of 128:
-//   * loader warps gather the block's keys and values from their cache pages with
+// and walks the request's keys in blocks of 128; it owns its SM (all 512 columns of
+// tensor memory: two score buffers and SPLITS output accumulators):
+//   * loader warps gather a block's keys and values from their cache pages with
 //     16-byte asynchronous copies into shared memory, in the 128-byte swizzled layout
-//     the tensor core reads (any page size works), one block ahead of its use;
+//     the tensor core reads (any page size works), several blocks ahead of their use;
 //   * one thread issues S = Q K^T (tcgen05.mma, M = 128 rows, N = 128 keys, both
-//     operands K-major) into tensor memory;
-//   * four softmax warps own one row per thread (thread r = row r = lane r of tensor
-//     memory): they read the row's scores, keep the running maximum and sum, write the
-//     probabilities as bfloat16 into shared memory (the A operand of the second
-//     product), and fold the block's P V (read back from tensor memory) into the
-//     row's output, which stays in registers: o = o * exp(m_old - m_new) + P V;
-//   * the same thread issues P V (M = 128, N = head size, K = 128 keys; V is the B
-//     operand in MN-major form, which is how the cache stores it: a key per row).
-// No row reduction crosses threads, so the softmax needs no shuffles.  Everything
-// but q, k, v, p and the output is 32-bit.  Every wait is bounded; when one runs
-// out an error flag is set and all roles fall through to the common exit, where
-// tensor memory is given back.
+//     operands K-major) into one of two score buffers, one block ahead, so the
+//     scores of block b + 1 are ready while the softmax of block b runs;
+//   * the softmax is cut by key columns: SPLITS threads share a row (thread = row r,
+//     columns 128/SPLITS * q ...), each with its OWN running maximum, sum and output
+//     accumulator in tensor memory, so no value crosses threads inside the walk; a
+//     thread reads its scores once (one tcgen05.ld), writes the probabilities as
+//     bfloat16 into shared memory (the A operand of the second product) and moves on;
+//   * the same issuing thread adds P V of each column split into that split's
+//     accumulator (M = 128, N = head size; V is the B operand in MN-major form, which
+//     is how the cache stores it: a key per row).  The accumulators stay in tensor
+//     memory over the whole walk.  A thread's reference maximum follows the true
+//     maximum lazily: only when the maximum has grown by more than 2^8 since it was
+//     set are the sum and the accumulator rescaled (read, multiplied, written back),
+//     which happens a few times per row, not per block; probabilities stay below 2^8;
+//   * at the end the SPLITS partial results of a row are merged: maxima and sums go
+//     through shared memory, and each thread reads its slice of the head from all
+//     accumulators.
+// Everything but q, k, v, p and the output is 32-bit.  Every wait is bounded; when
+// one runs out an error flag is set and all roles fall through to the common exit,
+// where tensor memory is given back.
 //
 // HEAD_DIM is a compile-time size (64 or 128), -DHEAD_DIM=...
 #include <cuda.h>
@@ -32,15 +41,22 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size");
 
 #define FA_ROWS 128
 #define FA_KEYS 128
-#define FA_SOFTMAX_THREADS 128
+#define FA_SPLITS (HEAD_DIM == 64 ? 4 : 2)        // threads (and accumulators) per row
+#define FA_SOFTMAX_THREADS (128 * FA_SPLITS)
 #define FA_LOADER_THREADS 128
 #define FA_THREADS (FA_SOFTMAX_THREADS + FA_LOADER_THREADS + 32)
+#define FA_KV_BUFFERS (HEAD_DIM == 64 ? 4 : 2)
 #define FA_WAIT_LIMIT (1u << 17)      // polls of up to 20 us each: seconds in all
+#define FA_RESCALE_AT 8.0f            // log2 units the maximum may lead its reference by
 constexpr int kDBlocks = HEAD_DIM / 64;           // 64-lane pieces of the head (128 bytes a row)
 constexpr int kSubTile = 128 * 128;               // bytes of a [128 x 64] bfloat16 swizzled tile
-constexpr int kTmemCols = 256;                    // S: 128 columns, P V: up to 128
+constexpr int kTmemCols = 512;                    // S0, S1: 128 columns each; SPLITS accumulators of HEAD_DIM
+constexpr int kSplitKeys = FA_KEYS / FA_SPLITS;   // key columns a softmax thread owns (32 or 64)
+constexpr int kSlice = HEAD_DIM / FA_SPLITS;      // output lanes a thread writes at the end (16 or 64)
+static_assert(256 + FA_SPLITS * HEAD_DIM == kTmemCols, "tensor memory plan");
 
 __device__ int fa_error_flag = 0;
+
 
 __device__ __forceinline__ unsigned fa_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void fa_mbar_init(unsigned long long* bar, unsigned count) {
@@ -112,19 +128,53 @@ __device__ __forceinline__ void fa_tmem_load32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void fa_tmem_load16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fa_tmem_store32(unsigned taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
+      "%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
 __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-// shared memory: q | k[2] | v[2] | p   (each a whole number of 16 KB sub-tiles), then barriers
+// shared memory: q | k[buffers] | v[buffers] | p   (each a whole number of 16 KB sub-tiles),
+// then the rows' maxima and sums for the final merge, then the barriers
 constexpr int kQBytes = kDBlocks * kSubTile;
 constexpr int kKVBytes = kDBlocks * kSubTile;
 constexpr int kPBytes = 2 * kSubTile;
-constexpr int kFaSmem = kQBytes + 4 * kKVBytes + kPBytes + 128;   // tiles, then the barriers
+constexpr int kStatBytes = FA_SPLITS * FA_ROWS * 2 * 4;
+constexpr int kFaSmem = kQBytes + 2 * FA_KV_BUFFERS * kKVBytes + kPBytes + kStatBytes + 256;
+static_assert(kFaSmem > 116 * 1024, "one block an SM: it takes all of tensor memory");
 
-__global__ void __launch_bounds__(FA_THREADS, HEAD_DIM == 64 ? 2 : 1)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                          const int* __restrict__ block_table, int table_stride,
@@ -132,21 +182,23 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page, int window,
                          float scale_log2) {
   extern __shared__ __align__(1024) unsigned char fa_raw[];      // swizzle atoms: 1024-byte aligned
-  unsigned char* base = fa_raw;
-  unsigned char* q_s = base;
-  unsigned char* k_s = q_s + kQBytes;                      // 2 buffers
-  unsigned char* v_s = k_s + 2 * kKVBytes;                 // 2 buffers
-  unsigned char* p_s = v_s + 2 * kKVBytes;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + kPBytes);
-  unsigned long long* kv_full = bars;                      // [2], 128 loader arrivals
-  unsigned long long* kv_empty = bars + 2;                 // [2], commit of the block's P V
-  unsigned long long* s_full = bars + 4;                   // commit of Q K^T
-  unsigned long long* p_ready = bars + 5;                  // 128 softmax arrivals
-  unsigned long long* o_full = bars + 6;                   // commit of P V
-  unsigned long long* q_full = bars + 7;                   // 128 loader arrivals
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 8);
+  unsigned char* q_s = fa_raw;
+  unsigned char* k_s = q_s + kQBytes;                            // FA_KV_BUFFERS buffers
+  unsigned char* v_s = k_s + FA_KV_BUFFERS * kKVBytes;           // FA_KV_BUFFERS buffers
+  unsigned char* p_s = v_s + FA_KV_BUFFERS * kKVBytes;
+  float* stat_s = reinterpret_cast<float*>(p_s + kPBytes);       // [split][row][max, sum]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + kPBytes + kStatBytes);
+  unsigned long long* kv_full = bars;                            // [buffers], an arrival per loader warp
+  unsigned long long* kv_empty = bars + FA_KV_BUFFERS;           // [buffers], commit of the block's P V
+  unsigned long long* s_full = bars + 2 * FA_KV_BUFFERS;         // [2], commit of Q K^T
+  unsigned long long* p_ready = s_full + 2;                      // an arrival per softmax warp
+  unsigned long long* pv_done = s_full + 3;                      // commit of P V
+  unsigned long long* q_full = s_full + 4;                       // an arrival per loader warp
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 5);
 
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // heads run fastest over the grid so that the tiles with the most keys (first in
+  // `tiles`) of all heads are placed first
+  const int h = blockIdx.x, tile = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = tiles[2 * tile], n_rows = tiles[2 * tile + 1];
   const int r_id = row_req[row0];
@@ -161,19 +213,22 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int kb_first = lo_first / FA_KEYS * FA_KEYS;
   const int n_blocks = live ? (pos_last - kb_first) / FA_KEYS + 1 : 0;
   const int* table = block_table + (size_t)(live ? r_id : 0) * table_stride;
+  constexpr int kSoftmaxWarps = FA_SOFTMAX_THREADS / 32;
+  constexpr int kMmaWarp = kSoftmaxWarps + FA_LOADER_THREADS / 32;
 
   if (threadIdx.x == 0) {
-    fa_mbar_init(&kv_full[0], FA_LOADER_THREADS);
-    fa_mbar_init(&kv_full[1], FA_LOADER_THREADS);
-    fa_mbar_init(&kv_empty[0], 1);
-    fa_mbar_init(&kv_empty[1], 1);
-    fa_mbar_init(s_full, 1);
-    fa_mbar_init(p_ready, FA_SOFTMAX_THREADS);
-    fa_mbar_init(o_full, 1);
-    fa_mbar_init(q_full, FA_LOADER_THREADS);
+    for (int i = 0; i < FA_KV_BUFFERS; ++i) {
+      fa_mbar_init(&kv_full[i], FA_LOADER_THREADS / 32);
+      fa_mbar_init(&kv_empty[i], 1);
+    }
+    fa_mbar_init(&s_full[0], 1);
+    fa_mbar_init(&s_full[1], 1);
+    fa_mbar_init(p_ready, FA_SOFTMAX_THREADS / 32);
+    fa_mbar_init(pv_done, 1);
+    fa_mbar_init(q_full, FA_LOADER_THREADS / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(fa_smem(tmem_slot)), "r"((unsigned)kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -181,11 +236,11 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const unsigned tmem_s = *tmem_slot;              // scores: columns 0 .. 127
-  const unsigned tmem_o = tmem_s + 128;            // the block's P V: columns 128 .. 128 + HEAD_DIM - 1
+  const unsigned tmem_base = *tmem_slot;           // scores: columns 0..127 and 128..255
+  const unsigned tmem_o = tmem_base + 256;         // accumulator of split j: columns 256 + j * HEAD_DIM ...
   pdl_wait();
 
-  if (live && warp >= 4 && warp < 8) {
+  if (live && warp >= kSoftmaxWarps && warp < kMmaWarp) {
     // ---------------- loaders: thread t brings row t of q, then key t of every block ----------------
     const int t = threadIdx.x - FA_SOFTMAX_THREADS;
     {
@@ -196,159 +251,217 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         fa_cp16(q_s + (c / 8) * kSubTile + swz(t, c % 8), src + c * 8, ok);
       asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
+    // kLag blocks are in flight at a time: before block b is asked for, block b - kLag is
+    // waited for and announced (q rides with block 0)
+    constexpr int kLag = FA_KV_BUFFERS / 2;
+    // a warp's copies have all landed once each of its lanes has waited: one arrival a warp
+    auto announce = [&](int e) {
+      __syncwarp();
+      if (lane == 0) {
+        if (e == 0) fa_mbar_arrive(q_full);
+        fa_mbar_arrive(&kv_full[e % FA_KV_BUFFERS]);
+      }
+    };
+    bool ok = true;
     for (int b = 0; b < n_blocks; ++b) {
-      const int buf = b & 1;
-      // the buffer is free once the P V of block b - 2 has read it
-      if (b >= 2 && !fa_mbar_wait(&kv_empty[buf], ((b >> 1) - 1) & 1)) break;
+      const int buf = b % FA_KV_BUFFERS, use = b / FA_KV_BUFFERS;
+      if (b >= kLag) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kLag - 1) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        announce(b - kLag);
+      }
+      // the buffer is free once the P V of the block that held it has read it
+      if (use > 0 && !__all_sync(0xffffffffu, fa_mbar_wait(&kv_empty[buf], (use - 1) & 1))) { ok = false; break; }   // a warp gives up together
       const int key = kb_first + b * FA_KEYS + t;
-      const bool ok = key >= lo_first && key <= pos_last;
+      const bool in = key >= lo_first && key <= pos_last;
       size_t offset = 0;
-      if (ok) offset = ((size_t)(table[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
+      if (in) offset = ((size_t)(table[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
 #pragma unroll
       for (int c = 0; c < HEAD_DIM / 8; ++c) {
-        fa_cp16(k_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), k_pool + offset + c * 8, ok);
-        fa_cp16(v_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), v_pool + offset + c * 8, ok);
+        fa_cp16(k_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), k_pool + offset + c * 8, in);
+        fa_cp16(v_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), v_pool + offset + c * 8, in);
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
-      // say so as soon as the block has landed (q rides with block 0): the copies of
-      // block b run while block b - 1 is multiplied, so this wait is short
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (b == 0) fa_mbar_arrive(q_full);
-      fa_mbar_arrive(&kv_full[buf]);
     }
-  } else if (live && warp == 8) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (ok)
+      for (int e = n_blocks > kLag ? n_blocks - kLag : 0; e < n_blocks; ++e) announce(e);
+  } else if (live && warp == kMmaWarp) {
     // ---------------- products ----------------
     if (lane == 0) {
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(FA_KEYS >> 3) << 17) |
                                ((unsigned)(FA_ROWS >> 4) << 24);
       const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* v is MN-major */ |
                                ((unsigned)(HEAD_DIM >> 3) << 17) | ((unsigned)(FA_ROWS >> 4) << 24);
-      bool ok = fa_mbar_wait(q_full, 0);
-      for (int b = 0; ok && b < n_blocks; ++b) {
-        const int buf = b & 1;
-        if (!fa_mbar_wait(&kv_full[buf], (b >> 1) & 1)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // S = Q K^T over the head's lanes, 16 at a time (32 bytes inside a swizzled row)
+      // S = Q K^T of block b into score buffer b & 1, 16 lanes of the head at a time
+      auto scores = [&](int b) {
+        const int buf = b % FA_KV_BUFFERS;
 #pragma unroll
         for (int kk = 0; kk < HEAD_DIM / 16; ++kk) {
           const unsigned long long a = desc_k_major(q_s + (kk / 4) * kSubTile) + 2 * (kk % 4);
           const unsigned long long bd = desc_k_major(k_s + buf * kKVBytes + (kk / 4) * kSubTile) + 2 * (kk % 4);
-          fa_mma(tmem_s, a, bd, idesc_s, kk != 0);
+          fa_mma(tmem_base + (unsigned)((b & 1) * 128), a, bd, idesc_s, kk != 0);
         }
-        fa_commit(s_full);
+        fa_commit(&s_full[b & 1]);
+      };
+      bool ok = fa_mbar_wait(q_full, 0) && fa_mbar_wait(&kv_full[0], 0);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        scores(0);
+      }
+      for (int b = 0; ok && b < n_blocks; ++b) {
+        const int buf = b % FA_KV_BUFFERS;
+        if (b + 1 < n_blocks) {
+          // the other score buffer held block b - 1, whose readers all arrived at p_ready(b - 1)
+          if (!fa_mbar_wait(&kv_full[(b + 1) % FA_KV_BUFFERS], ((b + 1) / FA_KV_BUFFERS) & 1)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          scores(b + 1);
+        }
         if (!fa_mbar_wait(p_ready, b & 1)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // P V over the block's keys, 16 at a time: p advances 32 bytes in its row (a new
-        // sub-tile after 64 keys), v advances two 8-key groups (2048 bytes)
+        // P V over the block's keys, 16 at a time, each column split into its own accumulator:
+        // p advances 32 bytes in its row (a new sub-tile after 64 keys), v two 8-key groups
+        constexpr int kStepsPerSplit = (FA_KEYS / 16) / FA_SPLITS;
 #pragma unroll
         for (int kk = 0; kk < FA_KEYS / 16; ++kk) {
           const unsigned long long a = desc_k_major(p_s + (kk / 4) * kSubTile) + 2 * (kk % 4);
           const unsigned long long bd = desc_mn_major(v_s + buf * kKVBytes) + (unsigned long long)(kk * 128);
-          fa_mma(tmem_o, a, bd, idesc_o, kk != 0);
+          fa_mma(tmem_o + (unsigned)((kk / kStepsPerSplit) * HEAD_DIM), a, bd, idesc_o,
+                 (b > 0 || kk % kStepsPerSplit != 0) ? 1u : 0u);
         }
-        fa_commit(o_full);
+        fa_commit(pv_done);
         fa_commit(&kv_empty[buf]);
       }
     }
-  } else if (live && warp < 4) {
-    // ---------------- softmax: thread r owns row r ----------------
-    const int r = threadIdx.x;
+  } else if (live && warp < kSoftmaxWarps) {
+    // ---------------- softmax: thread (r, split) owns columns split * kSplitKeys ... of row r ----------------
+    const int split = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
     const int p_row = pos0 + min(r, n_rows - 1);            // rows past the tile repeat its last row
     const int lo_row = (window >= 0 && p_row - window > 0) ? p_row - window : 0;
-    const unsigned lane_base = ((unsigned)(warp * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
-    float o[HEAD_DIM];
-#pragma unroll
-    for (int i = 0; i < HEAD_DIM; ++i) o[i] = 0.f;
+    const unsigned lane_base = ((unsigned)((warp & 3) * 32) << 16);
+    const unsigned my_o = tmem_o + lane_base + (unsigned)(split * HEAD_DIM);
+    float m_ref = -INFINITY, l_run = 0.f;     // reference maximum (raw score units) and running sum
+    bool ok = true;
     for (int b = 0; b < n_blocks; ++b) {
-      const int kb = kb_first + b * FA_KEYS;
-      if (!fa_mbar_wait(s_full, b & 1)) break;
+      const int kb = kb_first + b * FA_KEYS + split * kSplitKeys;
+      if (!__all_sync(0xffffffffu, fa_mbar_wait(&s_full[b & 1], (b >> 1) & 1))) { ok = false; break; }
+
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool needs_mask = kb + FA_KEYS - 1 > pos0 || (window >= 0 && kb < pos_last - window);
-      // first pass: the row's maximum over the block
+      float s[kSplitKeys];
+#pragma unroll
+      for (int c0 = 0; c0 < kSplitKeys; c0 += 32)
+        fa_tmem_load32(tmem_base + lane_base + (unsigned)((b & 1) * 128 + split * kSplitKeys + c0),
+                       *reinterpret_cast<float(*)[32]>(&s[c0]));
+      const bool needs_mask = kb + kSplitKeys - 1 > pos0 || (window >= 0 && kb < pos_last - window);
       float m_blk = -INFINITY;
+      if (needs_mask) {
+#pragma unroll
+        for (int j = 0; j < kSplitKeys; ++j) {
+          const int key = kb + j;
+          s[j] = (key <= p_row && key >= lo_row) ? s[j] : -INFINITY;
+          m_blk = fmaxf(m_blk, s[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kSplitKeys; ++j) m_blk = fmaxf(m_blk, s[j]);
+      }
+      // the reference moves only when the maximum has run away from it
+      const bool move = m_blk > -INFINITY &&
+                        (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > FA_RESCALE_AT);
+      float factor = 1.f;
+      if (move) {
+        factor = m_ref == -INFINITY ? 0.f : fa_exp2((m_ref - m_blk) * scale_log2);
+        m_ref = m_blk;
+        l_run *= factor;
+      }
+      if (b > 0) {
+        // the last block's P V must be through: it reads p, and it writes the accumulator
+        if (!__all_sync(0xffffffffu, fa_mbar_wait(pv_done, (b - 1) & 1))) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, move)) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < FA_KEYS; c0 += 32) {
-        float s[32];
-        fa_tmem_load32(tmem_s + lane_base + (unsigned)c0, s);
-        if (needs_mask) {
+          for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+            float acc[32];
+            fa_tmem_load32(my_o + (unsigned)c0, acc);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = kb + c0 + j;
-            m_blk = fmaxf(m_blk, (key <= p_row && key >= lo_row) ? s[j] : -INFINITY);
+            for (int j = 0; j < 32; ++j) acc[j] *= factor;
+            fa_tmem_store32(my_o + (unsigned)c0, acc);
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) m_blk = fmaxf(m_blk, s[j]);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      const float m_new = fmaxf(m_run, m_blk);
-      const float m_scaled = m_new == -INFINITY ? 0.f : m_new * scale_log2;
-      const float corr = fa_exp2(m_run * scale_log2 - m_scaled);      // 0 on the first block
-      m_run = m_new;
-      // second pass: probabilities, their sum, and the bfloat16 copy for the second product
+      // probabilities, their sum, and the bfloat16 copy for the second product
+      const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < FA_KEYS; c0 += 32) {
-        float s[32];
-        fa_tmem_load32(tmem_s + lane_base + (unsigned)c0, s);
-        if (needs_mask) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = kb + c0 + j;
-            s[j] = (key <= p_row && key >= lo_row) ? fa_exp2(fmaf(s[j], scale_log2, -m_scaled)) : 0.f;
-            sum += s[j];
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            s[j] = fa_exp2(fmaf(s[j], scale_log2, -m_scaled));
-            sum += s[j];
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {                     // four 16-byte pieces of 8 keys
-          uint4 piece;
-          unsigned* w = reinterpret_cast<unsigned*>(&piece);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 pair = __floats2bfloat162_rn(s[8 * c + 2 * e], s[8 * c + 2 * e + 1]);
-            w[e] = *reinterpret_cast<unsigned*>(&pair);
-          }
-          const int chunk = c0 / 8 + c;                   // 0 .. 15 over the 128 keys
-          *reinterpret_cast<uint4*>(p_s + (chunk / 8) * kSubTile + swz(r, chunk % 8)) = piece;
-        }
+      for (int j = 0; j < kSplitKeys; ++j) {
+        s[j] = fa_exp2(fmaf(s[j], scale_log2, -m_scaled));      // masked scores are -inf: 0
+        sum += s[j];
       }
-      l_run = l_run * corr + sum;
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // p in shared memory -> the tensor core
-      fa_mbar_arrive(p_ready);
-      // fold the block's P V into the row's output
-      if (!fa_mbar_wait(o_full, b & 1)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      l_run += sum;
 #pragma unroll
-      for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-        float pv[32];
-        fa_tmem_load32(tmem_o + lane_base + (unsigned)c0, pv);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = o[c0 + j] * corr + pv[j];
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    }
-    if (r < n_rows) {
-      const float inv = 1.0f / l_run;
-      __nv_bfloat16* dst = out + ((size_t)(row0 + r) * nh + h) * HEAD_DIM;
-#pragma unroll
-      for (int c = 0; c < HEAD_DIM / 8; ++c) {
+      for (int c = 0; c < kSplitKeys / 8; ++c) {            // 16-byte pieces of 8 keys
         uint4 piece;
         unsigned* w = reinterpret_cast<unsigned*>(&piece);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 pair = __floats2bfloat162_rn(o[8 * c + 2 * e] * inv, o[8 * c + 2 * e + 1] * inv);
+          __nv_bfloat162 pair = __floats2bfloat162_rn(s[8 * c + 2 * e], s[8 * c + 2 * e + 1]);
           w[e] = *reinterpret_cast<unsigned*>(&pair);
         }
-        *reinterpret_cast<uint4*>(dst + c * 8) = piece;
+        const int chunk = split * (kSplitKeys / 8) + c;     // 0 .. 15 over the 128 keys
+        *reinterpret_cast<uint4*>(p_s + (chunk / 8) * kSubTile + swz(r, chunk % 8)) = piece;
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // p in shared memory -> the tensor core
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(p_ready);                          // one arrival a warp
+    }
+    // ---------------- merge the row's splits ----------------
+    if (ok && n_blocks > 0) ok = fa_mbar_wait(pv_done, (n_blocks - 1) & 1);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    stat_s[(split * FA_ROWS + r) * 2] = m_ref;
+    stat_s[(split * FA_ROWS + r) * 2 + 1] = l_run;
+    asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_THREADS) : "memory");
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < FA_SPLITS; ++j) m_all = fmaxf(m_all, stat_s[(j * FA_ROWS + r) * 2]);
+    float weight[FA_SPLITS], den = 0.f;
+#pragma unroll
+    for (int j = 0; j < FA_SPLITS; ++j) {
+      const float m_j = stat_s[(j * FA_ROWS + r) * 2];
+      weight[j] = m_j == -INFINITY ? 0.f : fa_exp2((m_j - m_all) * scale_log2);
+      den += weight[j] * stat_s[(j * FA_ROWS + r) * 2 + 1];
+    }
+    if (ok) {
+      const float inv = 1.0f / den;
+      __nv_bfloat16* dst = out + ((size_t)(row0 + min(r, n_rows - 1)) * nh + h) * HEAD_DIM + split * kSlice;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kSlice; c0 += 16) {
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < FA_SPLITS; ++j) {
+          float part[16];
+          fa_tmem_load16(tmem_o + lane_base + (unsigned)(j * HEAD_DIM + split * kSlice + c0), part);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = fmaf(weight[j], part[i], acc[i]);
+        }
+        if (r < n_rows) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint4 piece;
+            unsigned* w = reinterpret_cast<unsigned*>(&piece);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(acc[8 * c + 2 * e] * inv, acc[8 * c + 2 * e + 1] * inv);
+              w[e] = *reinterpret_cast<unsigned*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + c * 8) = piece;
+          }
+        }
       }
     }
   }
@@ -356,9 +469,9 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   pdl_launch();
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s),
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((unsigned)kTmemCols) : "memory");
   }
 }
@@ -378,7 +491,7 @@ TOKB200_API int tokb200_attention_tcgen05(
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
     int nkv, int d, int page, int window, float scale, cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
-  if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || nh > 65535)
+  if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0)
     return TOKB200_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
     return TOKB200_BAD_ALIGNMENT;
@@ -391,7 +504,8 @@ TOKB200_API int tokb200_attention_tcgen05(
     if (err != cudaSuccess) return (int)err;
     configured[device] = true;
   }
-  dim3 grid(n_tiles, nh);
+  if (n_tiles > 65535) return TOKB200_BAD_SIZE;
+  dim3 grid(nh, n_tiles);
   return launch_dependent(attention_tcgen05_kernel, grid, dim3(FA_THREADS), (size_t)kFaSmem, stream,
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table, table_stride,

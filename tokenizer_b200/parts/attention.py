@@ -24,12 +24,11 @@ from .linear import Linear
 
 _position_tables = {}
 
-# Which kernel takes long prompt portions in bfloat16.  The tcgen05 kernel (scores in
-# tensor memory) is complete and tested but, in its first form, its per-block chain
-# (product -> softmax -> product) is not yet overlapped, and it runs 80 us where the
-# mma.sync kernel runs 72 us on 2,048 tokens of 14 heads; TOKB200_ATTENTION=tcgen05
-# selects it.
-_PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "mma")
+# Which kernel takes long prompt portions in bfloat16: the tcgen05 kernel (128-row
+# tiles, scores and outputs in tensor memory; 45 us on 2,048 tokens of 14 heads) or,
+# with TOKB200_ATTENTION=mma, the mma.sync kernel (64-row tiles; 73 us), which also
+# takes the short portions and the head sizes the first does not.
+_PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "tcgen05")
 
 
 class GQAttention:
