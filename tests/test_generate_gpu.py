@@ -266,3 +266,51 @@ def test_decode_bursts_on_the_engine(folder):
     for a, b in zip(single, burst):
         assert a.tokens == b.tokens and a.reason == b.reason
         assert a.completion_tokens == b.completion_tokens
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_factory, dtype):
+    """Steps that bring a whole number of 128-token tiles are captured once per shape
+    and replayed: the first use runs plainly, the second captures, later ones replay.
+    Each use here cuts its 256 tokens differently (two portions; a long portion beside
+    a decoding token of an older request) and must give the plain logits."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200 import Qwen2Config, write_random_model
+    from tokenizer_b200.engine import StepEntry
+    config = Qwen2Config.from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=2, hidden_size=128,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=256, vocab_size=333,
+        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+        use_sliding_window=False, sliding_window=None, max_window_layers=2))
+    path = str(tmp_path_factory.mktemp("tiny_shapes"))
+    write_random_model(path, config, 6, scale=SHARPEN)
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype=dtype)
+    engine = tb.engine_for(model, 2048, 16, max_requests=4)
+    old = engine.cache.open("old")
+    old_ids = random_ids(40, config.vocab_size, 1)
+    engine.cache.reserve(old, 39)
+    engine.step([StepEntry(old, old_ids[:39], [])])
+    for use, (n_a, n_b) in enumerate(((150, 106), (100, 156), (255, 0), (131, 125))):
+        a_ids = random_ids(n_a, config.vocab_size, 10 + use)
+        a = engine.cache.open(("a", use))
+        engine.cache.reserve(a, n_a)
+        entries = [StepEntry(a, a_ids, [n_a - 1, 0])]
+        wants = [plain.all_logits(cfg, w, a_ids)[[n_a - 1, 0]]]
+        if n_b:
+            b_ids = random_ids(n_b, config.vocab_size, 20 + use)
+            b = engine.cache.open(("b", use))
+            engine.cache.reserve(b, n_b)
+            entries.append(StepEntry(b, b_ids, []))
+        else:
+            engine.cache.reserve(old, 1)                      # one decoded token beside the portion
+            entries.append(StepEntry(old, old_ids[39:40], [0]))
+            wants.append(plain.all_logits(cfg, w, old_ids)[[39]])
+        got = engine.step(entries).float().cpu()
+        want = torch.cat(wants)
+        bound = 1e-4 if dtype == "float32" else 2e-2 * float(want.abs().max())
+        assert float((got - want).abs().max()) <= bound, f"use {use}"
+        for e in entries:
+            if e.cache is not old:
+                engine.cache.close(e.cache)
+    assert any(k[0] == "portions" and "graph" in v for k, v in engine._graphs.items())

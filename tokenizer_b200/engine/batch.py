@@ -125,9 +125,10 @@ class BatchBuilder:
                 raise ValueError(
                     f"positions {e.cache.length}..{e.cache.length + n} exceed "
                     f"max_position_embeddings {self.max_positions}")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+                bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
+                raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"wanted place {w} is not among the {n} tokens brought")
@@ -138,7 +139,10 @@ class BatchBuilder:
     def build(self, entries: List[StepEntry], pad_requests: int = 0, pad_tokens: int = 0,
               pad_want: int = 0, table_widths: Optional[List[int]] = None):
         """Pack the step.  The `pad_*` capacities (graph replay) extend the
-        batch with idle rows: request index -1, which every kernel skips."""
+        batch with idle rows: request index -1, which every kernel skips.  A padded
+        step also announces the most tiles its shape can have (the unused ones have
+        no rows), so that a captured launch fits every step of the shape."""
+        padded = bool(pad_requests or pad_tokens or pad_want or table_widths)
         plan = self.plan
         page = plan.page_size
         T = sum(len(e.tokens) for e in entries)
@@ -223,7 +227,8 @@ class BatchBuilder:
             row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
             kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
             q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots,
-            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=n_tiles,
+            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2),
+            n_q_tiles=lay.max_tiles if padded else n_tiles,
             q_wide_tiles=view(lay.wide_tiles, 2 * lay.max_wide_tiles).view(lay.max_wide_tiles, 2),
-            n_q_wide_tiles=len(wide_tiles))
+            n_q_wide_tiles=lay.max_wide_tiles if padded else len(wide_tiles))
         return ctx, view(lay.want, Wc), W

@@ -84,8 +84,9 @@ class Engine:
                                device=self.runtime.device)
         self.builder.validate(entries)
         with torch.cuda.device(self.runtime.device):
-            if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
-                logits = self._step_captured(entries)
+            shape = self._captured_shape(entries) if self.use_graphs else None
+            if shape is not None:
+                logits = self._step_captured(entries, *shape)
             else:
                 ctx, want_rows, n_want = self.builder.build(entries)
                 logits = self.model.forward(ctx, self.bindings, want_rows[:n_want])
@@ -102,24 +103,47 @@ class Engine:
             b *= 2
         return b
 
-    def _step_captured(self, entries: List[StepEntry]) -> torch.Tensor:
-        """A step of single tokens only.  Its launches are captured once per
-        (padded batch size, padded block-table widths) and replayed afterwards;
-        only the packed metadata changes between replays, at fixed addresses.
-        Idle rows of the padded batch carry request -1, which kernels skip."""
+    PORTION_GRAPHS = 6       # captured shapes of prompt steps kept (each holds its activations)
+
+    def _captured_shape(self, entries: List[StepEntry]):
+        """(key, padded tokens, padded requests) when steps of this shape are replayed
+        from a captured graph, else None.  Steps of single tokens always are.  Steps
+        with prompt portions are when they bring a whole number of 128-token tiles, at
+        least two: under a token budget most steps of a busy engine bring exactly the
+        budget, and a replay spares the host the launches (a quarter of such a step's
+        time otherwise).  The kernel choice that depends on the longest portion is
+        part of the key."""
+        widths = tuple(self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
+                       for g in range(len(self.cache.groups)))
+        longest = max(len(e.tokens) for e in entries)
+        if longest == 1:
+            rows = self._bucket(len(entries))
+            return (rows, widths), rows, rows
+        total = sum(len(e.tokens) for e in entries)
+        requests = self._bucket(len(entries))
+        if total < 256 or total % 128 or sum(len(e.want) for e in entries) > requests:
+            return None
+        return ("portions", total, requests, widths, longest >= 96), total, requests
+
+    def _step_captured(self, entries: List[StepEntry], key, tokens: int, requests: int) -> torch.Tensor:
+        """A step whose launches are captured once per shape (padded batch size,
+        padded block-table widths, token count) and replayed afterwards; only the
+        packed metadata changes between replays, at fixed addresses.  Idle rows of
+        the padded batch carry request -1, which kernels skip."""
         from ..kernels.ops import counter
-        rows = self._bucket(len(entries))
-        widths = [self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
-                  for g in range(len(self.cache.groups))]
-        key = (rows, tuple(widths))
+        widths = list(key[1] if len(key) == 2 else key[3])
         ctx, want_rows, n_want = self.builder.build(
-            entries, pad_requests=rows, pad_tokens=rows, pad_want=rows, table_widths=widths)
+            entries, pad_requests=requests, pad_tokens=tokens, pad_want=requests, table_widths=widths)
         if self._graph_buffer != self.builder.device_buffer_ptr():
             self._graphs.clear()           # the metadata moved: captured addresses are stale
             self._graph_buffer = self.builder.device_buffer_ptr()
         slot = self._graphs.get(key)
         if slot is None:
             # first use: run it once plainly (this also compiles what is missing)
+            if key[0] == "portions":
+                kept = [k for k in self._graphs if k[0] == "portions"]
+                if len(kept) >= self.PORTION_GRAPHS:
+                    del self._graphs[kept[0]]          # the oldest shape makes room
             self._graphs[key] = {}
             return self.model.forward(ctx, self.bindings, want_rows)[:n_want]
         if "graph" not in slot:
