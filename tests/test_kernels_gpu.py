@@ -698,3 +698,52 @@ def test_attention_tcgen05_far_key_and_window_edge():
             else:
                 assert float((got - v[far, 0]).abs().max()) > 0.1
     ops().attention_tcgen05_check(d)
+
+
+@pytest.mark.parametrize("M,hidden,inner,delta_kind", [
+    (1, 64, 128, "none"), (3, 96, 256, "partials"), (8, 896, 4864, "partials"), (8, 896, 4864, "bf16"),
+    (13, 160, 384, "partials"), (16, 896, 4864, "f32"), (5, 1536, 1280, "partials")])
+def test_ffn_small_m(M, hidden, inner, delta_kind):
+    """The whole feed-forward of few rows in one kernel (residual add, norm, gate/up with
+    the activation, the barrier over all blocks, down as partial sums), twice in a row so
+    that the barrier's counters are seen to come back to zero."""
+    o = ops()
+    splits = o.ffn_small_m_splits(M, hidden, inner)
+    assert splits > 0
+    x = rnd(M, hidden, seed=81)
+    if delta_kind == "none":
+        delta = None
+    elif delta_kind == "partials":
+        delta = rnd(3, M, hidden, seed=82, scale=0.3)
+    elif delta_kind == "f32":
+        delta = rnd(M, hidden, seed=82, scale=0.5)
+    else:
+        delta = rnd(M, hidden, seed=82, scale=0.5, dtype=torch.bfloat16)
+    gain = 1.0 + rnd(hidden, seed=83, scale=0.1)
+    gate = rnd(inner, hidden, seed=84, dtype=torch.bfloat16, scale=0.06)
+    up = rnd(inner, hidden, seed=85, dtype=torch.bfloat16, scale=0.06)
+    down = rnd(hidden, inner, seed=86, dtype=torch.bfloat16, scale=0.04)
+    w_gu = o.interleave_gate_up(gate, up)
+    eps = 1e-5
+    # the reference, rounding where the kernel rounds: h and the activation to bfloat16
+    xs = x.double().cpu()
+    if delta is not None:
+        xs = xs + (delta.double().cpu().sum(0) if delta.dim() == 3 else delta.double().cpu())
+    h = xs / torch.sqrt((xs * xs).mean(-1, keepdim=True) + eps) * gain.double().cpu()
+    h = h.float().to(torch.bfloat16).double()
+    g = h @ gate.double().cpu().t()
+    u = h @ up.double().cpu().t()
+    act = (g * torch.sigmoid(g) * u).float().to(torch.bfloat16).double()
+    want = (act @ down.double().cpu().t()).float()
+    for _ in range(2):
+        x_out = torch.full_like(x, 3.0)
+        out = torch.full((splits, M, hidden), 5.0, dtype=torch.float32, device=DEV)
+        o.ffn_small_m(x, x_out, delta, gain, eps, w_gu, down, out)
+        torch.cuda.synchronize()
+        o.ffn_small_m_check()
+        assert torch.allclose(x_out.cpu(), xs.float(), atol=1e-5, rtol=1e-6)
+        got = out.sum(0).cpu()
+        # h and the activation may round the other way on a tie's edge: 2^-8 of their size
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) <= 2e-3 * scale + 1e-5, float((got - want).abs().max())
+    assert o.ffn_small_m_splits(17, hidden, inner) == 0 and o.ffn_small_m_splits(4, 100, 128) == 0

@@ -247,6 +247,57 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(counters), _stream()), "decode_attention")
 
 
+_ffn_plans = {}
+_ffn_scratch = {}
+
+
+def ffn_small_m_splits(M: int, hidden: int, inner: int) -> int:
+    """Partial sums the fused feed-forward of few rows writes for these sizes on this
+    device; 0 when it does not take them (more than 16 rows, hidden not a multiple of
+    32, inner not a multiple of 128, too little shared memory)."""
+    key = (torch.cuda.current_device(), M <= 8, hidden, inner)
+    if M < 1 or M > 16:
+        return 0
+    if key not in _ffn_plans:
+        _ffn_plans[key] = int(_lib("ffn_small_m").tokb200_ffn_small_m_splits(_i(M), _i(hidden), _i(inner)))
+    return _ffn_plans[key]
+
+
+def ffn_small_m(x_in, x_out, delta, gain, eps, w_gate_up, w_down, out) -> None:
+    """The gated feed-forward of few rows in one kernel: x_out = x_in + delta (delta as
+    for rms_norm: [M, H] or float32 partial sums [S, M, H], or None), out [S', M, H] =
+    float32 partial sums over k of down(silu(gate(h)) * up(h)), h = rms_norm(x_out) * gain.
+    `w_gate_up` is in the interleaved row order of `interleave_gate_up`."""
+    M, hidden = x_in.shape
+    inner = w_down.shape[1]
+    if x_in.dtype != torch.float32 or x_out.dtype != torch.float32 or x_out.shape != x_in.shape:
+        raise ValueError("ffn_small_m: the residual stream is float32, in and out of one shape")
+    if w_gate_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16 or \
+            tuple(w_gate_up.shape) != (2 * inner, hidden) or tuple(w_down.shape) != (hidden, inner):
+        raise ValueError("ffn_small_m: bfloat16 weights [2 I, H] and [H, I]")
+    splits = ffn_small_m_splits(M, hidden, inner)
+    if splits == 0:
+        raise ValueError(f"ffn_small_m does not take {M} rows of {hidden} with inner size {inner}")
+    if tuple(out.shape) != (splits, M, hidden) or out.dtype != torch.float32:
+        raise ValueError(f"ffn_small_m: out must be float32 {(splits, M, hidden)}")
+    n_partials, stride = _partials(delta, x_in)
+    key = (x_in.device.index, inner)
+    if key not in _ffn_scratch:
+        _ffn_scratch[key] = (torch.empty((16, inner), dtype=torch.bfloat16, device=x_in.device),
+                             torch.zeros(2, dtype=torch.int32, device=x_in.device))
+    act, sync = _ffn_scratch[key]
+    _check(_lib("ffn_small_m").tokb200_ffn_small_m(
+        _ptr(x_in), _ptr(x_out), _ptr(delta), _i(1 if delta is not None and delta.dtype == torch.float32 else 0),
+        _i(n_partials), _ll(stride), _ptr(gain), _f(eps), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
+        _ptr(out), _i(M), _i(hidden), _i(inner), _ptr(sync), _stream()), "ffn_small_m")
+
+
+def ffn_small_m_check() -> None:
+    flag = _lib("ffn_small_m").tokb200_ffn_small_m_error()
+    if flag:
+        raise KernelError("ffn_small_m: a wait on the device ran out (status %d)" % flag)
+
+
 SMALL_M_ROWS = 16     # up to here the streaming kernel leads; above it, the tensor-core tiles
 
 

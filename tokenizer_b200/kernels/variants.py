@@ -13,6 +13,7 @@ def all_variants():
         ("sampling.cu", (), ()),
         ("linear_small_m.cu", (), ()),
         ("gemm_tcgen05.cu", (), ()),
+        ("ffn_small_m.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -20,7 +20,10 @@ class PreNormResidual:
 
     def forward(self, stream, ctx, cache):
         stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache))
-        stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm)))
+        # a feed-forward may take the stream as it is and fold the norm into its own kernel
+        fused = getattr(self.feed_forward, "fused_step", None)
+        if fused is None or not fused(stream, self.feed_forward_norm):
+            stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm)))
 
 
 register_part("block", "pre_norm_residual", PreNormResidual)

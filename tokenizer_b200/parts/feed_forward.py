@@ -3,6 +3,8 @@ products are one stacked product (reference: qwen-infer/src/model.rs:226-250,
 silu(z) = z * sigmoid(z))."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.spec import ConfigError
@@ -10,6 +12,10 @@ from ..kernels import ops
 from ..weights.store import TensorSpec
 from .base import register_part
 from .linear import Linear
+
+
+# TOKB200_FFN=separate runs the feed-forward of few rows as norm, gate/up and down kernels
+_FUSED_STEP = os.environ.get("TOKB200_FFN", "fused") != "separate"
 
 
 class GatedMLP:
@@ -40,7 +46,32 @@ class GatedMLP:
             self.gate_up = Linear(runtime.matrix(torch.cat([gate, up], dim=0)))
         self.down = Linear(runtime.matrix(store.get(x + ".down_proj.weight")))
 
+    def fused_step(self, stream, norm) -> bool:
+        """For few rows in bfloat16: residual add, norm, both products and the activation
+        in one kernel, straight from the stream (the norm must be one that can be folded:
+        it offers `folded() -> (gain, eps)` of an RMS norm).  True when it was done; the
+        stream then holds the new sum and this part's output as pending partial sums."""
+        fold = getattr(norm, "folded", None)
+        if not (_FUSED_STEP and self.fused and fold is not None):
+            return False
+        x = stream.x
+        rows, hidden = x.shape
+        splits = ops.ffn_small_m_splits(rows, hidden, self.inner)
+        if splits == 0:
+            return False
+        gain, eps = fold()
+        delta, stream.pending = stream.pending, None
+        x_out = torch.empty_like(x)
+        out = torch.empty((splits, rows, hidden), dtype=torch.float32, device=x.device)
+        ops.ffn_small_m(x, x_out, delta, gain, eps, self.gate_up_weight, self.down.weight, out)
+        stream.x, stream.pending = x_out, out
+        return True
+
     def streamed_weights(self):
+        """What a second stream may bring into L2 ahead of a step of few rows: nothing when
+        the fused kernel runs, which streams its weights itself from its first cycle."""
+        if _FUSED_STEP and self.fused:
+            return []
         return [self.gate_up_weight if self.fused else self.gate_up.weight, self.down.weight]
 
     def forward(self, h):

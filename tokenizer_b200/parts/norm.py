@@ -20,6 +20,10 @@ class RMSNorm:
         self.runtime = runtime
         self.gain = runtime.vector(store.get(spec.prefix + ".weight"))
 
+    def folded(self):
+        """(gain, eps) for a consumer that computes this norm inside its own kernel."""
+        return self.gain, self.eps
+
     def forward(self, x, delta=None, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.empty(n, self.size)
