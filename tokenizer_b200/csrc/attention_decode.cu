@@ -81,17 +81,26 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         float* __restrict__ scratch, int* __restrict__ counters) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   __shared__ int is_last;
-  pdl_wait();
-  pdl_launch();
+  // The rows' requests, positions and block tables were written before the predecessor (the
+  // projection that writes q and the newest key) started, so they are read while it still
+  // runs; q, keys and values only after the wait.
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int r = row_req[row];
-  if (r < 0) return;
-  const int p = pos[row];
+  const int p = r < 0 ? 0 : pos[row];
   const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
   const int n_keys = p - lo + 1;
   const int chunk = split_chunk(n_keys);
   const int n_splits = (n_keys + chunk - 1) / chunk;
-  if (split >= n_splits) return;
+  const bool idle = r < 0 || split >= n_splits;
+  if (!idle) {
+    // the block's table entries, into L1 for the lookups below
+    const int first_page = (lo + split * chunk) / page, last_page = min(p, lo + split * chunk + chunk - 1) / page;
+    for (int e = first_page + (int)threadIdx.x * 32; e <= last_page; e += DEC_THREADS * 32)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(block_table + (size_t)r * table_stride + e));
+  }
+  pdl_wait();
+  pdl_launch();
+  if (idle) return;
   const int group = nh / nkv;                       // <= DEC_MAX_GROUP, checked by the launcher
   const int first = lo + split * chunk;
   const int last = min(p, first + chunk - 1);

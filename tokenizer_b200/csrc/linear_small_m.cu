@@ -260,10 +260,9 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
     a_ring[i] = load16(wa + kk, k_ok);
     b_ring[i] = load16(wb + kk, k_ok);
   }
-  pdl_wait();
-  pdl_launch();
-  // what the epilogue needs from memory is asked for now, so that it has arrived by then:
-  // thread i of the epilogue serves row m = i / 8 and lane pair j0 + i % 8
+  // What the epilogue needs from memory is asked for now, so that it has arrived by then
+  // (thread i of the epilogue serves row m = i / 8 and lane pair j0 + i % 8), and before the
+  // wait: positions and slots were written before the predecessor (the norm) started.
   constexpr int kEpi = (64 * MT + LSM_THREADS - 1) / LSM_THREADS;
   const int half = d / 2;
   float e_bias_a[kEpi], e_bias_b[kEpi], e_cos[kEpi], e_sin[kEpi];
@@ -289,6 +288,8 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       }
     }
   }
+  pdl_wait();
+  pdl_launch();
   constexpr bool kXRing = MT <= 2;
   uint4 x_ring[kXRing ? LSM_PRE : 1][MT];
   if (kXRing) {
