@@ -71,6 +71,33 @@ class FakeEngine:
             out.append(tokens)
         return out
 
+    # ---- the engine's faces for a step packed ahead of its tokens (used when `ahead` is set) ----
+    def enable_ahead(self):
+        self.prepared_used = 0
+        self.prepare_decode = self._prepare_decode
+        self.step_prepared = self._step_prepared
+        self.sample_launch = self._sample_launch
+
+    def _prepare_decode(self, caches):
+        assert all(self.cache.pages_missing(c, 1) == [0] * len(self.cache.groups) for c in caches)
+        return (list(caches), [c.length for c in caches])
+
+    def _step_prepared(self, prepared, tokens):
+        from tokenizer_b200.engine.batch import StepEntry
+        caches, lengths = prepared
+        if any(c.closed or c.length != n for c, n in zip(caches, lengths)) or len(tokens) != len(caches):
+            return None
+        self.prepared_used += 1
+        return self.step([StepEntry(c, [t], [0]) for c, t in zip(caches, tokens)])
+
+    def _sample_launch(self, logits, temperature, top_p, uniform):
+        ids = self.sample(logits, temperature, top_p, uniform)
+
+        class Pending:
+            def result(self):
+                return ids
+        return Pending()
+
     def _read_back(self, cache):
         out = []
         for position in range(cache.length):

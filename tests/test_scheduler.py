@@ -200,3 +200,31 @@ def test_decode_bursts_give_the_same_ids_and_fall_back_when_pages_are_short():
     sampled.add_request(prompts[0], GenerateParams(max_tokens=6, temperature=0.7, seed=3))
     run_checked(sampled)
     assert not hasattr(sampled.engine, "bursts")          # sampled requests take single steps
+
+
+def test_steps_packed_ahead_of_their_tokens_change_nothing():
+    """While the ids of a step are drawn, the scheduler lets the engine pack the next
+    decoding step; it is used only if exactly the same requests go on.  Ends by EOS and
+    max_tokens, a late arrival, sampled requests and a pool that forces preemption all
+    give the ids of the plain path."""
+    prompts = [random_ids(n, 50, 90 + n) for n in (4, 9, 17, 6)]
+    free = [solo(p, GenerateParams(max_tokens=16)).tokens for p in prompts]
+    params = [GenerateParams(max_tokens=16), GenerateParams(max_tokens=7),
+              GenerateParams(max_tokens=16, eos=[free[2][9]]),
+              GenerateParams(max_tokens=12, temperature=0.9, top_p=0.8, seed=5)]
+    want = [solo(p, q) for p, q in zip(prompts, params)]
+    for pages in (256, 11):
+        engine = FakeEngine(num_pages=pages)
+        engine.enable_ahead()
+        s = Scheduler(engine, max_batch_size=4, token_budget=16)
+        ids = [s.add_request(p, q) for p, q in zip(prompts[:3], params[:3])]
+        for _ in range(4):
+            s.step()
+            s.cache.check()
+        ids.append(s.add_request(prompts[3], params[3]))
+        out = run_checked(s)
+        for rid, w in zip(ids, want):
+            assert out[rid].tokens == w.tokens and out[rid].reason == w.reason
+        assert engine.prepared_used > 0
+        if pages == 11:
+            assert s.stats.preemptions > 0

@@ -83,24 +83,46 @@ class BatchLayout:
         return lay
 
 
+@dataclass
+class PackedStep:
+    """A step packed into one of the builder's pinned buffers, not yet copied."""
+
+    layout: BatchLayout
+    turn: int
+    widths: List[int]
+    tokens: int
+    requests: int
+    wanted: int
+    n_want: int
+    q_lens: List[int]
+    kv_lens: List[int]
+    state_slots: List[int]
+    n_tiles: int
+    n_wide_tiles: int
+
+
 class BatchBuilder:
     def __init__(self, plan, vocab_size: int, max_positions: int, device):
         self.plan = plan
         self.vocab_size = vocab_size
         self.max_positions = max_positions
         self.device = device
-        self._host: Optional[torch.Tensor] = None
+        # two pinned buffers used in turn: the next step can be packed while the copy of
+        # the one before may still be reading its buffer
+        self._hosts: List[Optional[torch.Tensor]] = [None, None]
+        self._copied: List[Optional[torch.cuda.Event]] = [None, None]
+        self._turn = 0
         self._dev: Optional[torch.Tensor] = None
-        self._copied: Optional[torch.cuda.Event] = None
         self.last_bytes = 0
 
     def _buffers(self, total: int):
-        if self._host is None or self._host.numel() < total:
+        if self._dev is None or self._dev.numel() < total:
             capacity = max(total * 2, 4096)
             pin = self.device.type == "cuda"
-            self._host = torch.empty(capacity, dtype=torch.int32, pin_memory=pin)
+            self._hosts = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+            self._copied = [None, None]
             self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
-        return self._host, self._dev
+        return self._dev
 
     def device_buffer_ptr(self) -> int:
         return 0 if self._dev is None else self._dev.data_ptr()
@@ -142,6 +164,11 @@ class BatchBuilder:
         batch with idle rows: request index -1, which every kernel skips.  A padded
         step also announces the most tiles its shape can have (the unused ones have
         no rows), so that a captured launch fits every step of the shape."""
+        return self.upload(self.pack(entries, pad_requests, pad_tokens, pad_want, table_widths))
+
+    def pack(self, entries: List[StepEntry], pad_requests: int = 0, pad_tokens: int = 0,
+             pad_want: int = 0, table_widths: Optional[List[int]] = None) -> "PackedStep":
+        """The host's half of `build`: fill a pinned buffer; nothing touches the device."""
         padded = bool(pad_requests or pad_tokens or pad_want or table_widths)
         plan = self.plan
         page = plan.page_size
@@ -156,10 +183,13 @@ class BatchBuilder:
                 raise ValueError("the captured block-table width is too small for this step")
         Tc, Rc, Wc = max(T, pad_tokens), max(R, pad_requests), max(W, pad_want)
         lay = BatchLayout.compute(Tc, Rc, Wc, widths)
-        if self._copied is not None:
-            self._copied.synchronize()  # the last step's copy still reads the host buffer
-        host, dev = self._buffers(lay.total)
-        buf = host.numpy()
+        self._buffers(lay.total)
+        turn = self._turn
+        self._turn ^= 1
+        if self._copied[turn] is not None:
+            self._copied[turn].synchronize()  # the copy of two steps ago still reads this buffer
+            self._copied[turn] = None
+        buf = self._hosts[turn].numpy()
         buf[:lay.total] = 0
         buf[lay.row_req:lay.row_req + Tc] = -1
         for g in range(len(widths)):
@@ -210,11 +240,26 @@ class BatchBuilder:
         for at, (_, first_row, rows_here) in enumerate(wide_tiles):
             buf[lay.wide_tiles + 2 * at] = first_row
             buf[lay.wide_tiles + 2 * at + 1] = rows_here
+        return PackedStep(lay, turn, widths, Tc, Rc, Wc, W, q_lens, kv_lens, state_slots,
+                          lay.max_tiles if padded else n_tiles,
+                          lay.max_wide_tiles if padded else len(wide_tiles))
+
+    def set_ids(self, packed: "PackedStep", ids: Sequence[int]) -> None:
+        """Put the token ids of a packed step of single tokens in place (row = entry)."""
+        lay = packed.layout
+        self._hosts[packed.turn].numpy()[lay.ids:lay.ids + len(ids)] = np.asarray(ids, dtype=np.int32)
+
+    def upload(self, packed: "PackedStep"):
+        """The device's half: one copy, and the views the parts receive."""
+        lay, widths = packed.layout, packed.widths
+        Tc, Rc, Wc = packed.tokens, packed.requests, packed.wanted
+        dev, host = self._dev, self._hosts[packed.turn]
+        page = self.plan.page_size
         dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         self.last_bytes = lay.total * 4
         if dev.is_cuda:
-            self._copied = torch.cuda.Event()
-            self._copied.record()
+            self._copied[packed.turn] = torch.cuda.Event()
+            self._copied[packed.turn].record()
 
         def view(offset, n):
             return dev[offset:offset + n]
@@ -226,9 +271,8 @@ class BatchBuilder:
             n_tokens=Tc, n_requests=Rc, ids=view(lay.ids, Tc), pos=view(lay.pos, Tc),
             row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
             kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
-            q_lens=q_lens, kv_lens=kv_lens, state_slots=state_slots,
-            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2),
-            n_q_tiles=lay.max_tiles if padded else n_tiles,
+            q_lens=packed.q_lens, kv_lens=packed.kv_lens, state_slots=packed.state_slots,
+            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=packed.n_tiles,
             q_wide_tiles=view(lay.wide_tiles, 2 * lay.max_wide_tiles).view(lay.max_wide_tiles, 2),
-            n_q_wide_tiles=lay.max_wide_tiles if padded else len(wide_tiles))
-        return ctx, view(lay.want, Wc), W
+            n_q_wide_tiles=packed.n_wide_tiles)
+        return ctx, view(lay.want, Wc), packed.n_want

@@ -88,6 +88,7 @@ class Scheduler:
         self.finished: Dict[int, Generated] = {}
         self.stats = SchedulerStats()
         self._next_id = 0
+        self._ahead = None            # (requests, step packed ahead of its tokens)
 
     # ---- requests -------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: GenerateParams,
@@ -119,15 +120,24 @@ class Scheduler:
         """Run one iteration; returns the ids of the requests that finished."""
         done_before = set(self.finished)
         self._admit()
+        ahead, self._ahead = self._ahead, None
         burst = self._burst_length()
         if burst > 1 and self._run_burst(burst):
             return [i for i in self.finished if i not in done_before]
-        plan = self._plan_and_reserve()
+        plan, logits = None, None
+        if ahead is not None and self._still_holds(ahead[0]):
+            # the step was packed while the last one ran: only the tokens were missing
+            logits = self.engine.step_prepared(ahead[1], [r.context[-1] for r in ahead[0]])
+            if logits is not None:
+                plan = [(r, 1) for r in ahead[0]]
+        if logits is None:
+            plan = self._plan_and_reserve()
+            if plan:
+                entries = [StepEntry(r.cache, r.context[r.cache.length:r.cache.length + n],
+                                     [n - 1] if r.cache.length + n == len(r.context) else [])
+                           for r, n in plan]
+                logits = self.engine.step(entries)
         if plan:
-            entries = [StepEntry(r.cache, r.context[r.cache.length:r.cache.length + n],
-                                 [n - 1] if r.cache.length + n == len(r.context) else [])
-                       for r, n in plan]
-            logits = self.engine.step(entries)
             self.stats.steps += 1
             self.stats.tokens_run += sum(n for _, n in plan)
             self.stats.max_running = max(self.stats.max_running, len(self.running))
@@ -135,6 +145,35 @@ class Scheduler:
                 self.stats.peak_pages, max((a.live for a in self.cache.allocators), default=0))
             self._sample([r for r, n in plan if r.cache.length == len(r.context)], logits)
         return [i for i in self.finished if i not in done_before]
+
+    def _still_holds(self, requests) -> bool:
+        """A step packed ahead is good if exactly these requests run, nobody waits, and each
+        is one token short of its context."""
+        if self.waiting or len(requests) != len(self.running):
+            return False
+        running = sorted(self.running, key=lambda r: r.id)
+        return all(a is b and a.cursor.done is None and len(a.context) - a.cache.length == 1
+                   for a, b in zip(running, requests))
+
+    def _pack_ahead(self, ready: List[_Request]) -> None:
+        """While the device still draws this step's ids: if the next step will be one token
+        for each of the requests that run now, reserve its pages and let the engine pack it.
+        Should a request end with the id it is about to get, the packed step is dropped."""
+        prepare = getattr(self.engine, "prepare_decode", None)
+        if prepare is None or self.waiting or len(ready) != len(self.running) or self.decode_burst > 1:
+            return
+        if any(r.cursor.produced + 1 >= r.cursor.params.max_tokens or
+               len(r.context) + 1 >= self.engine.max_positions for r in ready):
+            return
+        requests = sorted(ready, key=lambda r: r.id)
+        try:
+            for r in requests:
+                self.cache.reserve(r.cache, 1)
+        except OutOfPages:
+            return                       # the next iteration decides who gives way
+        prepared = prepare([r.cache for r in requests])
+        if prepared is not None:
+            self._ahead = (requests, prepared)
 
     def _burst_length(self) -> int:
         """How many steps the running requests can take together on the device:
@@ -256,10 +295,17 @@ class Scheduler:
                 drawing.append(r)
         if drawing:
             picked = logits if len(rows) == len(ready) else logits[rows]
-            ids = self.engine.sample(
-                picked, [r.cursor.params.temperature for r in drawing],
-                [r.cursor.params.top_p for r in drawing],
-                [r.cursor.next_uniform() for r in drawing])
+            draw = [picked, [r.cursor.params.temperature for r in drawing],
+                    [r.cursor.params.top_p for r in drawing],
+                    [r.cursor.next_uniform() for r in drawing]]
+            launch = getattr(self.engine, "sample_launch", None)
+            if launch is None:
+                ids = self.engine.sample(*draw)
+            else:
+                pending = launch(*draw)
+                if len(drawing) == len(ready):
+                    self._pack_ahead(ready)          # beside the device
+                ids = pending.result()
             self.stats.tokens_sampled += len(ids)
             for r, token in zip(drawing, ids):
                 if r.cursor.accept(int(token)):

@@ -10,7 +10,7 @@ as the reference's paged forwards do not (qwen-infer/src/model.rs:1015-1053).
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -49,6 +49,13 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
         model = DecoderModel(config.model_spec(), store, Runtime(device, parse_dtype(dtype)))
     model.config = config
     return model
+
+
+class PreparedDecode:
+    """A decoding step whose metadata is packed and whose tokens are still to come."""
+
+    def __init__(self, entries, key, packed, lengths):
+        self.entries, self.key, self.packed, self.lengths = entries, key, packed, lengths
 
 
 class Engine:
@@ -235,5 +242,49 @@ class Engine:
 
     def sample(self, logits: torch.Tensor, temperature, top_p, uniform) -> List[int]:
         """Draw one id per row of `logits` on the device."""
+        return self.sample_launch(logits, temperature, top_p, uniform).result()
+
+    def sample_launch(self, logits: torch.Tensor, temperature, top_p, uniform):
+        """Start the draw; `.result()` of what is returned waits for the ids."""
         with torch.cuda.device(self.runtime.device):
-            return self.sampler.sample(logits, temperature, top_p, uniform)
+            return self.sampler.sample_launch(logits, temperature, top_p, uniform)
+
+    # ---- a decoding step packed ahead of its tokens --------------------------------
+    def prepare_decode(self, caches) -> Optional["PreparedDecode"]:
+        """Pack, on the host only, a step that will run one token (not yet known) for each
+        cache, wanting its logits; pages for the token must be reserved.  None when steps of
+        this shape are not replayed from a graph yet.  The scheduler calls this while the
+        device still runs the step before, so that the host's share of a step is hidden."""
+        if not self.use_graphs or not caches:
+            return None
+        entries = [StepEntry(c, [0], [0]) for c in caches]
+        key, tokens, requests = self._captured_shape(entries)
+        slot = self._graphs.get(key)
+        if slot is None or "graph" not in slot or self._graph_buffer != self.builder.device_buffer_ptr():
+            return None
+        self.builder.validate(entries)
+        packed = self.builder.pack(entries, pad_requests=requests, pad_tokens=tokens,
+                                   pad_want=requests, table_widths=list(key[1]))
+        return PreparedDecode(entries, key, packed, [c.length for c in caches])
+
+    def step_prepared(self, prepared: "PreparedDecode", tokens: Sequence[int]) -> Optional[torch.Tensor]:
+        """Run a step packed by `prepare_decode` with the tokens now known.  None when it can
+        no longer be used as packed (a cache moved on, the graph is gone): run `step` instead."""
+        from ..kernels.ops import counter
+        slot = self._graphs.get(prepared.key)
+        if slot is None or "graph" not in slot or self._graph_buffer != self.builder.device_buffer_ptr() or \
+                len(tokens) != len(prepared.entries) or \
+                any(e.cache.closed or e.cache.length != n for e, n in zip(prepared.entries, prepared.lengths)):
+            return None
+        for t in tokens:
+            if not 0 <= int(t) < self.model.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.model.vocab_size}")
+        self.builder.set_ids(prepared.packed, tokens)
+        with torch.cuda.device(self.runtime.device):
+            _, _, n_want = self.builder.upload(prepared.packed)
+            slot["graph"].replay()
+            counter.launches += slot["launches"]
+        for e in prepared.entries:
+            self.cache.commit(e.cache, 1)
+        self.steps_run += 1
+        return slot["out"][:n_want]

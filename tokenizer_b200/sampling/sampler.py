@@ -25,16 +25,36 @@ def validate_sampling(temperature: float, top_p: float) -> None:
         raise ValueError(f"top_p {top_p} is negative")
 
 
+class PendingIds:
+    """Ids on their way from the device; one outstanding draw per sampler at a time."""
+
+    def __init__(self, host, done):
+        self._host, self._done = host, done
+
+    def result(self) -> List[int]:
+        if self._host is None:
+            return []
+        self._done.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._pinned = None
 
     def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_p: Sequence[float],
                uniform: Sequence[float]) -> List[int]:
         """One id per row.  All-greedy batches skip the parameter upload."""
+        return self.sample_launch(logits, temperature, top_p, uniform).result()
+
+    def sample_launch(self, logits: torch.Tensor, temperature: Sequence[float],
+                      top_p: Sequence[float], uniform: Sequence[float]) -> "PendingIds":
+        """Start the draw and the copy of the ids to pinned host memory; `result()` waits for
+        them.  What the host does in between runs beside the device."""
         n = logits.shape[0]
         if n == 0:
-            return []
+            return PendingIds(None, None)
         if logits.shape[1] == 0:
             raise ValueError("no logits to sample")
         out = torch.empty(n, dtype=torch.int32, device=self.device)
@@ -44,7 +64,13 @@ class Sampler:
             params = torch.tensor([list(temperature), list(top_p), list(uniform)],
                                   dtype=torch.float32).to(self.device, non_blocking=True)
             ops.sample(logits, params[0], params[1], params[2], out)
-        return out.tolist()
+        if self._pinned is None or self._pinned.numel() < n:
+            self._pinned = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
+        host = self._pinned[:n]
+        host.copy_(out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return PendingIds(host, done)
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
