@@ -71,9 +71,11 @@ class Engine:
         self.sampler = Sampler(model.runtime.device)
         self.max_positions = model.max_positions
         self.steps_run = 0
-        # a captured step bakes its launches: only mixers that say so may be replayed
+        # a captured step bakes its launches: only mixers that say so may be replayed, and a
+        # feed-forward may say that it cannot (a choice made on the host, say)
         self.use_graphs = bool(use_graphs) and all(
-            getattr(block.mixer, "graph_safe", False) for block in model.blocks)
+            getattr(block.mixer, "graph_safe", False) and getattr(block.feed_forward, "graph_safe", True)
+            for block in model.blocks)
         self._graphs = {}
         self._graph_buffer = 0
         tables = sum(max_requests * (model.max_positions // page_size + 8) for _ in self.cache.groups)
