@@ -165,13 +165,13 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
-// shared memory: q | k[buffers] | v[buffers] | p   (each a whole number of 16 KB sub-tiles),
+// shared memory: q | k[buffers] | v[buffers] | p[2]   (each a whole number of 16 KB sub-tiles),
 // then the rows' maxima and sums for the final merge, then the barriers
 constexpr int kQBytes = kDBlocks * kSubTile;
 constexpr int kKVBytes = kDBlocks * kSubTile;
 constexpr int kPBytes = 2 * kSubTile;
 constexpr int kStatBytes = FA_SPLITS * FA_ROWS * 2 * 4;
-constexpr int kFaSmem = kQBytes + 2 * FA_KV_BUFFERS * kKVBytes + kPBytes + kStatBytes + 256;
+constexpr int kFaSmem = kQBytes + 2 * FA_KV_BUFFERS * kKVBytes + 2 * kPBytes + kStatBytes + 256;
 static_assert(kFaSmem > 116 * 1024, "one block an SM: it takes all of tensor memory");
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
@@ -185,9 +185,9 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   unsigned char* q_s = fa_raw;
   unsigned char* k_s = q_s + kQBytes;                            // FA_KV_BUFFERS buffers
   unsigned char* v_s = k_s + FA_KV_BUFFERS * kKVBytes;           // FA_KV_BUFFERS buffers
-  unsigned char* p_s = v_s + FA_KV_BUFFERS * kKVBytes;
-  float* stat_s = reinterpret_cast<float*>(p_s + kPBytes);       // [split][row][max, sum]
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + kPBytes + kStatBytes);
+  unsigned char* p_s = v_s + FA_KV_BUFFERS * kKVBytes;           // two buffers, blocks in turn
+  float* stat_s = reinterpret_cast<float*>(p_s + 2 * kPBytes);   // [split][row][max, sum]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + 2 * kPBytes + kStatBytes);
   unsigned long long* kv_full = bars;                            // [buffers], an arrival per loader warp
   unsigned long long* kv_empty = bars + FA_KV_BUFFERS;           // [buffers], commit of the block's P V
   unsigned long long* s_full = bars + 2 * FA_KV_BUFFERS;         // [2], commit of Q K^T
@@ -325,7 +325,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         constexpr int kStepsPerSplit = (FA_KEYS / 16) / FA_SPLITS;
 #pragma unroll
         for (int kk = 0; kk < FA_KEYS / 16; ++kk) {
-          const unsigned long long a = desc_k_major(p_s + (kk / 4) * kSubTile) + 2 * (kk % 4);
+          const unsigned long long a = desc_k_major(p_s + (b & 1) * kPBytes + (kk / 4) * kSubTile) + 2 * (kk % 4);
           const unsigned long long bd = desc_mn_major(v_s + buf * kKVBytes) + (unsigned long long)(kk * 128);
           fa_mma(tmem_o + (unsigned)((kk / kStepsPerSplit) * HEAD_DIM), a, bd, idesc_o,
                  (b > 0 || kk % kStepsPerSplit != 0) ? 1u : 0u);
@@ -376,21 +376,22 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         m_ref = m_blk;
         l_run *= factor;
       }
-      if (b > 0) {
-        // the last block's P V must be through: it reads p, and it writes the accumulator
+      // The probabilities of blocks b and b - 1 have buffers of their own, and the scores of
+      // block b were committed after the P V of block b - 2 was issued, so p's buffer is free
+      // by now.  Only a rescaling has to wait for the last block's P V, which writes the
+      // accumulator.
+      if (b > 0 && __any_sync(0xffffffffu, move)) {
         if (!__all_sync(0xffffffffu, fa_mbar_wait(pv_done, (b - 1) & 1))) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, move)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-            float acc[32];
-            fa_tmem_load32(my_o + (unsigned)c0, acc);
+        for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+          float acc[32];
+          fa_tmem_load32(my_o + (unsigned)c0, acc);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] *= factor;
-            fa_tmem_store32(my_o + (unsigned)c0, acc);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int j = 0; j < 32; ++j) acc[j] *= factor;
+          fa_tmem_store32(my_o + (unsigned)c0, acc);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       // probabilities, their sum, and the bfloat16 copy for the second product
       const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
@@ -411,7 +412,7 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
           w[e] = *reinterpret_cast<unsigned*>(&pair);
         }
         const int chunk = split * (kSplitKeys / 8) + c;     // 0 .. 15 over the 128 keys
-        *reinterpret_cast<uint4*>(p_s + (chunk / 8) * kSubTile + swz(r, chunk % 8)) = piece;
+        *reinterpret_cast<uint4*>(p_s + (b & 1) * kPBytes + (chunk / 8) * kSubTile + swz(r, chunk % 8)) = piece;
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // p in shared memory -> the tensor core
