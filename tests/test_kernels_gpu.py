@@ -747,3 +747,26 @@ def test_ffn_small_m(M, hidden, inner, delta_kind):
         scale = float(want.abs().max())
         assert float((got - want).abs().max()) <= 2e-3 * scale + 1e-5, float((got - want).abs().max())
     assert o.ffn_small_m_splits(17, hidden, inner) == 0 and o.ffn_small_m_splits(4, 100, 128) == 0
+
+
+@pytest.mark.parametrize("M,N,K,S", [(64, 896, 4864, 19), (33, 100, 264, 2), (200, 256, 1024, 4),
+                                     (17, 1152, 896, 7), (128, 132, 640, 5)])
+def test_gemm_tcgen05_partials(M, N, K, S):
+    """The tcgen05 product cut along k into S pieces (units of work = tile x piece, so that
+    a narrow matrix still fills the device): the pieces add up to the product, rows past M
+    of a tile stay out of the next piece's plane, and a piece count that would leave a
+    piece empty is refused."""
+    o = ops()
+    a = rnd(M, K, seed=91, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=92, dtype=torch.bfloat16, scale=0.1)
+    out = torch.full((S, M, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_tcgen05_partials(a, w, out)
+    torch.cuda.synchronize()
+    o.gemm_tcgen05_check()
+    want = (a.double().cpu() @ w.double().cpu().t()).float()
+    got = out.sum(0).cpu()
+    assert torch.allclose(got, want, atol=2e-4 * float(want.abs().max()), rtol=1e-5), float((got - want).abs().max())
+    # the pieces are different sums, none of them the fill value
+    assert not bool((out == 9.0).any())
+    with pytest.raises(ValueError):
+        o.gemm_tcgen05_partials(a, w, torch.empty(K, M, N, dtype=torch.float32, device=DEV))

@@ -268,6 +268,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                ::"l"(map), "r"(tc_smem(src)), "r"(x), "r"(y) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(tc_smem(src)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
 template <int BLOCK_N, int STAGES, bool OUT_F32>
 struct TcPersistentSmem {
   static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2;
@@ -288,7 +293,10 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_out,
-                               const float* __restrict__ bias, int M, int N, int K) {
+                               const float* __restrict__ bias, int M, int N, int K, int k_splits) {
+  // k_splits > 1 (32-bit output only): a unit of work is (tile, piece of k); the output is
+  // [k_splits, M, N] partial sums that the consumer adds in index order, written through a
+  // three-dimensional map so that a tile's rows past M fall outside its piece's plane.
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
   static_assert(!GATED || (BLOCK_N == 256 && !OUT_F32), "the gated epilogue pairs two halves of a 256 tile");
   extern __shared__ unsigned char tc_raw[];
@@ -306,6 +314,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
   const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
+  const int kb_per_split = (k_blocks + k_splits - 1) / k_splits;
+  const int total_units = total_tiles * k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -327,9 +337,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0) {
       int it = 0;                                   // k blocks issued so far, over all tiles
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+        const int tile = unit % total_tiles, split = unit / total_tiles;
         const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int kb_end = min(k_blocks, (split + 1) * kb_per_split);
+        for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { ok = false; break; }   // fresh barriers pass
           unsigned char* a_tile = tiles + s * S::kStage;
@@ -345,12 +357,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                              ((unsigned)(TC_BLOCK_M >> 4) << 24);
       int it = 0, round = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++round) {
+      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x, ++round) {
+        const int split = unit / total_tiles;
+        const int kb_begin = split * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
         const int buf = round & 1;
         if (!mbar_wait(&acc_empty[buf], ((round >> 1) & 1) ^ 1)) break;     // the epilogue has drained it
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned tmem_d = tmem_base + (unsigned)(buf * BLOCK_N);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -358,7 +372,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
           const unsigned long long a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + S::kABytes);
 #pragma unroll
           for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k)
-            umma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+            umma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb_begin) | k) != 0);
           umma_commit(&empty[s]);
         }
         umma_commit(&acc_full[buf]);
@@ -369,7 +383,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
     const int r = quarter * 32 + lane;              // this thread's row of the tile
     const bool issuer = warp == 2 && lane == 0;     // the thread that issues the TMA stores
     int round = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++round) {
+      const int tile = unit % total_tiles, split = unit / total_tiles;
       const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
       const int buf = round & 1;
       if (!mbar_wait(&acc_full[buf], (round >> 1) & 1)) break;
@@ -456,8 +471,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         } else {
 #pragma unroll 1
           for (int sl = 0; sl < S::kSlabs; ++sl)
-            if (n0 + sl * S::kSlabCols < N)
-              tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+            if (n0 + sl * S::kSlabCols < N) {
+              if (OUT_F32) tma_store_3d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0, split);
+              else tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+            }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
@@ -507,9 +524,19 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 }
 
 // A map over the row-major [M, N] output, boxes of 128 rows x 128 bytes, 128-byte swizzle.
-static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, bool f32) {
+static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, bool f32, int planes = 1) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return TOKB200_BAD_SIZE;
+  if (f32) {   // [planes, M, N]: a plane per piece of k (one plane for a whole product)
+    const cuuint64_t dims3[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)planes};
+    const cuuint64_t strides3[2] = {(cuuint64_t)N * 4, (cuuint64_t)M * (cuuint64_t)N * 4};
+    const cuuint32_t box3[3] = {32, TC_BLOCK_M, 1};
+    const cuuint32_t elem3[3] = {1, 1, 1};
+    CUresult r3 = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims3, strides3, box3, elem3,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r3 == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
+  }
   const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
   const cuuint64_t strides[1] = {(cuuint64_t)N * (f32 ? 4 : 2)};
   const cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : 64), TC_BLOCK_M};
@@ -522,7 +549,7 @@ static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, 
 
 template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false>
 static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
-                                int K, cudaStream_t stream) {
+                                int K, cudaStream_t stream, int k_splits = 1) {
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
   CUtensorMap map_x, map_w, map_out;
@@ -530,7 +557,8 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   if (status != TOKB200_OK) return status;
   status = make_map(&map_w, w, N, K, BLOCK_N);
   if (status != TOKB200_OK) return status;
-  status = make_out_map(&map_out, out, M, GATED ? N / 2 : N, OUT_F32);
+  if (k_splits < 1 || (k_splits > 1 && (!OUT_F32 || bias))) return TOKB200_BAD_SIZE;
+  status = make_out_map(&map_out, out, M, GATED ? N / 2 : N, OUT_F32, k_splits);
   if (status != TOKB200_OK) return status;
   static bool configured[64] = {};
   static int sm_count[64] = {};
@@ -544,11 +572,11 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
     if (err != cudaSuccess) return (int)err;
     configured[device] = true;
   }
-  const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
+  const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N) * k_splits;
   dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
   return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED>, grid,
                           dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out, bias, M, N,
-                          K);
+                          K, k_splits);
 }
 
 template <int BLOCK_N, int STAGES>
@@ -610,6 +638,21 @@ TOKB200_API int tokb200_gemm_tcgen05(const void* x, const void* w, const float* 
     case 256: return launch_tc<256, 4>(x, w, bias, out, out_is_f32, M, N, K, stream);
     default: return TOKB200_BAD_SIZE;
   }
+}
+
+// out[k_splits, M, N] (float32) = partial sums of x w^T over k_splits pieces of k (of whole
+// 64-element blocks; every piece must get at least one), for products with too few output
+// tiles to fill the device; the consumer adds the pieces in index order.
+TOKB200_API int tokb200_gemm_tcgen05_partials(const void* x, const void* w, void* out, int M, int N, int K,
+                                              int k_splits, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (K <= 0 || K % 8 || N % 4 || k_splits < 1) return TOKB200_BAD_SIZE;
+  const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
+  const int per = (k_blocks + k_splits - 1) / k_splits;
+  if ((k_splits - 1) * per >= k_blocks) return TOKB200_BAD_SIZE;        // an empty piece
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  return launch_tc_persistent<128, 4, true>(x, w, nullptr, out, M, N, K, stream, k_splits);
 }
 
 // out[M, N/2] = silu(x Wg^T) * (x Wu^T) where w [N, K] holds, for every 128 outputs,

@@ -383,12 +383,29 @@ def gemm_tcgen05(a, w, bias, out, block_n: int = 0) -> None:
         pitch_ok = N % (4 if out.dtype == torch.float32 else 8) == 0
         if pitch_ok and M * N >= 128 * 128 * 32:
             # persistent kernel, TMA-stored output: the wide tile where it divides the work well
-            block_n = 1256 if (out.dtype == torch.bfloat16 and N >= 2048) else 1128
+            # (with one tile of rows, the narrow tile gives twice the blocks to stream the weights)
+            block_n = 1256 if (out.dtype == torch.bfloat16 and N >= 2048 and M > 128) else 1128
         else:
             block_n = 128 if N > 64 else 64
     _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05(
         _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
         _i(M), _i(N), _i(K), _i(block_n), _stream()), "gemm_tcgen05")
+
+
+def gemm_tcgen05_partials(a, w, out) -> None:
+    """out[S,M,N] (float32) = partial sums of a[M,K] w[N,K]^T over S pieces of k, for products
+    with too few output tiles to fill the device; the consumer adds the pieces in index order."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("gemm_tcgen05_partials: bfloat16 a [M,K] and w [N,K]")
+    if out.dim() != 3 or tuple(out.shape[1:]) != (M, N) or out.dtype != torch.float32:
+        raise ValueError("gemm_tcgen05_partials: out is float32 [S,M,N]")
+    if K % 8 or N % 4:
+        raise ValueError("gemm_tcgen05_partials: K a multiple of 8 and N a multiple of 4")
+    _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_partials(
+        _ptr(a), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _i(out.shape[0]), _stream()),
+        "gemm_tcgen05_partials")
 
 
 def gemm_tcgen05_check() -> None:

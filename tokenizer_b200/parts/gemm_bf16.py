@@ -23,6 +23,18 @@ def choose_k_splits(M: int, N: int, K: int) -> int:
     return max(1, min(-(-_TARGET_BLOCKS // blocks), K // 256, 16))
 
 
+def choose_tile_k_splits(M: int, N: int, K: int) -> int:
+    """Pieces of k for a many-row product whose output tiles (128 x 128) are too few for the
+    device: about one unit of work per SM, at least two 64-element blocks of k a piece."""
+    tiles = -(-M // 128) * -(-N // 128)
+    k_blocks = -(-K // 64)
+    if tiles * 2 > 148 or N % 4 or k_blocks < 4:
+        return 1
+    want = min(148 // tiles, k_blocks // 2, 8)      # more pieces cost the consumer more than they save here
+    per = -(-k_blocks // max(want, 1))
+    return -(-k_blocks // per)
+
+
 def use_tcgen05(M: int, N: int, K: int) -> bool:
     """Which many-row products go to the framework's tcgen05 kernel.  TOKB200_GEMM
     = library sends them to the vendor library instead (for comparisons); sizes
@@ -39,6 +51,14 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     N = weight.shape[0]
     # few rows: the streaming kernel; up to 64 rows it also keeps the narrow matrices,
     # whose few tiles would leave most SMs of the tile kernel idle
+    tiles_cut = 1
+    if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):
+        tiles_cut = choose_tile_k_splits(M, N, K)
+    if tiles_cut > 1:
+        # few output tiles (a narrow matrix, a few dozen rows): pieces of k over all SMs
+        out = torch.empty((tiles_cut, M, N), dtype=torch.float32, device=a.device)
+        ops.gemm_tcgen05_partials(a, weight, out)
+        return out
     if ops.linear_small_m_supported(M, K) and (M <= ops.SMALL_M_ROWS or N < 4096):
         splits = choose_k_splits(M, N, K) if (partials_ok and bias is None) else 1
         if splits > 1:
