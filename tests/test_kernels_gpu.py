@@ -770,3 +770,36 @@ def test_gemm_tcgen05_partials(M, N, K, S):
     assert not bool((out == 9.0).any())
     with pytest.raises(ValueError):
         o.gemm_tcgen05_partials(a, w, torch.empty(K, M, N, dtype=torch.float32, device=DEV))
+
+
+@pytest.mark.parametrize("nh,nkv,d,S,T", [(14, 2, 64, 7, 40), (3, 1, 32, 2, 70), (4, 4, 128, 5, 17)])
+def test_rope_store_from_partial_sums(nh, nkv, d, S, T):
+    """Bias, rotation and the cache write straight from float32 partial sums [S, T, width]."""
+    o = ops()
+    width = (nh + 2 * nkv) * d
+    inv_freq = torch.tensor([1.0 / 1e4 ** (i / d) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 600)
+    parts = rnd(S, T, width, seed=96)
+    bias = rnd(width, seed=97, scale=0.3)
+    pos = torch.arange(500, 500 + T, dtype=torch.int32, device=DEV)
+    slot = torch.randperm(T + 5, generator=torch.Generator().manual_seed(2))[:T].to(torch.int32).to(DEV)
+    slot[3] = -1
+    k_pool = torch.full((T + 5, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((T + 5, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=DEV)
+    o.rope_store(parts, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d)
+    full = (parts.sum(0) + bias).view(T, nh + 2 * nkv, d).cpu()
+    c, s = cos[pos.long()].cpu()[:, None, :], sin[pos.long()].cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :d // 2], v[..., d // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    close(q_out.view(T, nh, d), rotate(full[:, :nh]), torch.bfloat16)
+    live = [t for t in range(T) if int(slot[t]) >= 0]
+    close(k_pool[slot[live].long()], rotate(full[:, nh:nh + nkv])[live], torch.bfloat16)
+    close(v_pool[slot[live].long()], full[:, nh + nkv:][live], torch.bfloat16)
+    untouched = [i for i in range(T + 5) if i not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all())
+    with pytest.raises(ValueError):
+        o.rope_store(parts, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d - 2)

@@ -362,6 +362,87 @@ __global__ void rope_store_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, 
   *reinterpret_cast<uint4*>(dst + j + half) = ob;
 }
 
+// The same from float32 partial sums [S, T, heads d] of a product that was cut along k: the
+// pieces are added in index order, then bias, rotation and the cache write as above.
+__global__ void rope_store_partials_kernel(const float* __restrict__ parts, int n_partials, size_t stride,
+                                           const float* __restrict__ bias, const int* __restrict__ pos,
+                                           const int* __restrict__ slot, const float* __restrict__ cos_t,
+                                           const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
+                                           __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+                                           int n_tokens, int nh, int nkv, int d) {
+  pdl_wait();
+  pdl_launch();
+  const int heads = nh + 2 * nkv, half = d / 2, per_head = d / 16, per_token = heads * per_head;
+  const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= (size_t)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), rest = (int)(item % per_token);
+  const int head = rest / per_head, j = (rest % per_head) * 8;
+  const float* src = parts + (size_t)t * heads * d + head * d + j;
+  float a[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] = b[e] = 0.f;
+  for (int s = 0; s < n_partials; ++s) {
+    const float4 a0 = *reinterpret_cast<const float4*>(src + s * stride);
+    const float4 a1 = *reinterpret_cast<const float4*>(src + s * stride + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(src + s * stride + half);
+    const float4 b1 = *reinterpret_cast<const float4*>(src + s * stride + half + 4);
+    a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w; a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+    b[0] += b0.x; b[1] += b0.y; b[2] += b0.z; b[3] += b0.w; b[4] += b1.x; b[5] += b1.y; b[6] += b1.z; b[7] += b1.w;
+  }
+  if (bias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a[e] += bias[head * d + j + e]; b[e] += bias[head * d + j + half + e]; }
+  }
+  __nv_bfloat16* dst;
+  if (head < nh) {
+    dst = q_out + ((size_t)t * nh + head) * d;
+  } else {
+    const int sl = slot ? slot[t] : -1;
+    const bool is_key = head < nh + nkv;
+    __nv_bfloat16* pool = is_key ? k_pool : v_pool;
+    if (sl < 0 || !pool) return;
+    dst = pool + ((size_t)sl * nkv + (head - nh - (is_key ? 0 : nkv))) * d;
+  }
+  if (head < nh + nkv) {
+    const float* c = cos_t + (size_t)pos[t] * half + j;
+    const float* sn = sin_t + (size_t)pos[t] * half + j;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ra = a[e] * c[e] - b[e] * sn[e], rb = b[e] * c[e] + a[e] * sn[e];
+      a[e] = ra;
+      b[e] = rb;
+    }
+  }
+  uint4 oa, ob;
+  __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+  __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    oa2[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+    ob2[e] = __floats2bfloat162_rn(b[2 * e], b[2 * e + 1]);
+  }
+  *reinterpret_cast<uint4*>(dst + j) = oa;
+  *reinterpret_cast<uint4*>(dst + j + half) = ob;
+}
+
+// parts: float32 [n_partials, n_tokens, (nh + 2 nkv) d]; outputs bfloat16; the whole head is
+// rotated (d a multiple of 16).
+TOKB200_API int tokb200_rope_store_partials(const float* parts, int n_partials, const float* bias,
+                                            const int* pos, const int* slot, const float* cos_t,
+                                            const float* sin_t, void* q_out, void* k_pool, void* v_pool,
+                                            int n_tokens, int nh, int nkv, int d, cudaStream_t stream) {
+  if (n_tokens <= 0) return TOKB200_OK;
+  if (d <= 0 || d % 16 || n_partials < 1) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)parts | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15)
+    return TOKB200_BAD_ALIGNMENT;
+  const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (d / 16);
+  const size_t stride = (size_t)n_tokens * (nh + 2 * nkv) * d;
+  return launch_dependent(rope_store_partials_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                          stream, parts, n_partials, stride, bias, pos, slot, cos_t, sin_t,
+                          (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_tokens,
+                          nh, nkv, d);
+}
+
 TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int* pos,
                                    const int* slot, const float* cos_t, const float* sin_t,
                                    void* q_out, void* k_pool, void* v_pool, int dtype,

@@ -131,6 +131,20 @@ def rope_table(inv_freq: torch.Tensor, n_positions: int):
 
 
 def rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, rotary) -> None:
+    """Bias, rotation and the write of k and v to their cache slots.  `qkv` is [T, width] or
+    float32 partial sums [S, T, width] of a product cut along k (bfloat16 outputs, the whole
+    head rotated, head size a multiple of 16)."""
+    if qkv.dim() == 3:
+        n = qkv.shape[1]
+        if qkv.dtype != torch.float32 or qkv.shape[2] != (nh + 2 * nkv) * d or rotary != d or d % 16 or \
+                q_out.dtype != torch.bfloat16 or cos.shape[1] != d // 2:
+            raise ValueError("rope_store: partial sums are float32 [S, T, width], for bfloat16 "
+                             "outputs and a whole-head rotation with head size a multiple of 16")
+        _check(_lib("elementwise").tokb200_rope_store_partials(
+            _ptr(qkv), _i(qkv.shape[0]), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin),
+            _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _i(n), _i(nh), _i(nkv), _i(d), _stream()),
+            "rope_store_partials")
+        return
     n = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * d:
         raise ValueError("rope_store: qkv width is not (heads + 2 kv heads) * head_dim")

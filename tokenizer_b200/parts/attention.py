@@ -102,7 +102,10 @@ class GQAttention:
             mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
             self.attend(q, mixed, ctx, group, cache)
             return self.out.forward(mixed, partials_ok=True)
-        qkv = self.qkv.forward(h)
+        # in bfloat16 with a whole-head rotation the product may come as partial sums over k
+        # (a few dozen rows and a narrow matrix fill the device only that way)
+        sums_ok = h.dtype == torch.bfloat16 and self.position.rotary_dim == self.d and self.d % 16 == 0
+        qkv = self.qkv.forward(h, partials_ok=sums_ok)
         ops.rope_store(
             qkv, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
             self.position.cos, self.position.sin, q,
