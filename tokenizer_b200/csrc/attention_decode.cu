@@ -138,15 +138,20 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 
   for (int k0 = first + warp * DEC_TILE; k0 <= last; k0 += DEC_BLOCK_KEYS) {
     // ---- request the values of this tile (a lane per key) and the keys (mma layout) ----
-    uint4 vreg[HEAD_DIM / 8];
     {
+      // the values go straight to their staging rows (asynchronous 16-byte copies, zeros for
+      // idle keys): no registers hold them while the scores are computed
       const int key = k0 + lane;
       const bool ok = key <= last;
       const int key_ok = ok ? key : k0;
       const int slot = table[key_ok / page] * page + key_ok % page;
       const __nv_bfloat16* vrow = v_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(v_s + lane * kVStride);
+      const int bytes = ok ? 16 : 0;
 #pragma unroll
-      for (int c = 0; c < HEAD_DIM / 8; ++c) vreg[c] = dec_load16(vrow + c * 8, ok);   // idle keys: zeros
+      for (int c = 0; c < HEAD_DIM / 8; ++c)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + c * 16), "l"(vrow + c * 8), "r"(bytes));
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
     float s[DEC_TILE / 8][4];
 #pragma unroll
@@ -168,10 +173,6 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         dec_mma(s[nt], qt, kv.x, kv.y);
       }
     }
-    // ---- stage the values for the transposed read ----
-#pragma unroll
-    for (int c = 0; c < HEAD_DIM / 8; ++c)
-      *reinterpret_cast<uint4*>(v_s + lane * kVStride + c * 8) = vreg[c];
     // ---- scale, mask, running softmax: rows g (heads 0..7) and g + 8 (heads 8..15) ----
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
@@ -211,6 +212,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       o[i][0] *= corr[0]; o[i][1] *= corr[0];
       o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // the tile's values have landed
     __syncwarp();
     // ---- o += p v ----
 #pragma unroll
