@@ -72,6 +72,26 @@ __device__ __forceinline__ uint2 dec_load8(const __nv_bfloat16* p, bool ok) {
   return v;
 }
 
+#define DEC_CLUSTER_MAX 8      // pieces that can meet through distributed shared memory
+
+__device__ __forceinline__ void dec_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// a float of block `rank` of this cluster, at the place `local` has in this block's shared memory
+__device__ __forceinline__ float dec_peer_load(const float* local, unsigned rank) {
+  const unsigned mine = (unsigned)__cvta_generic_to_shared(local);
+  unsigned theirs;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(theirs) : "r"(mine), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(theirs) : "memory");
+  return v;
+}
+
+// CLUSTER: the grid's x (the pieces of a row) is one thread-block cluster; the pieces meet in
+// the first block through distributed shared memory instead of scratch memory, a fence and a
+// counter.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
@@ -100,7 +120,14 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
   pdl_wait();
   pdl_launch();
-  if (idle) return;
+  if (idle) {
+    // in a cluster whose row is live, a block without keys still keeps the two appointments
+    if (CLUSTER && r >= 0) {
+      dec_cluster_sync();
+      dec_cluster_sync();
+    }
+    return;
+  }
   const int group = nh / nkv;                       // <= DEC_MAX_GROUP, checked by the launcher
   const int first = lo + split * chunk;
   const int last = min(p, first + chunk - 1);
@@ -256,6 +283,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   // scratch layout per (row, head): [split][HEAD_DIM + 2] = weighted values, max (log2 units), sum
   const size_t per_head = (size_t)DEC_MAX_SPLITS * kRow;
   float* base = scratch + ((size_t)row * nh + kvh * group) * per_head;
+  float* piece_s = acc_s + (size_t)DEC_WARPS * group * kRow;     // CLUSTER: this block's piece, [head][kRow]
   for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
     const int head = i / HEAD_DIM, c = i % HEAD_DIM;
     float m = -INFINITY;
@@ -269,13 +297,46 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       num += f * src[c];
       den += f * src[HEAD_DIM + 1];
     }
-    if (n_splits == 1) {
+    if (CLUSTER) {
+      float* piece = piece_s + (size_t)head * kRow;
+      piece[c] = num;
+      if (c == 0) { piece[HEAD_DIM] = m; piece[HEAD_DIM + 1] = den; }
+    } else if (n_splits == 1) {
       out[((size_t)row * nh + kvh * group + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
     } else {
       float* piece = base + head * per_head + (size_t)split * kRow;
       piece[c] = num;
       if (c == 0) { piece[HEAD_DIM] = m; piece[HEAD_DIM + 1] = den; }
     }
+  }
+  if (CLUSTER) {
+    // ---- the pieces meet in the first block, read from their blocks' shared memory ----
+    dec_cluster_sync();
+    if (split == 0) {
+      for (int head = warp; head < group; head += DEC_WARPS) {
+        const float* piece = piece_s + (size_t)head * kRow;
+        const bool on = lane < n_splits;
+        const float m_s = on ? dec_peer_load(piece + HEAD_DIM, (unsigned)lane) : -INFINITY;
+        const float l_s = on ? dec_peer_load(piece + HEAD_DIM + 1, (unsigned)lane) : 0.f;
+        const float m_all = warp_max(m_s);
+        const float f = exp2f(m_s - m_all);                 // 0 for lanes without a piece
+        const float den = warp_sum(f * l_s);
+        for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+          const int c = c0 + lane;
+          const bool have = c < HEAD_DIM;
+          float v[DEC_CLUSTER_MAX];
+#pragma unroll
+          for (int sp = 0; sp < DEC_CLUSTER_MAX; ++sp)
+            v[sp] = (have && sp < n_splits) ? dec_peer_load(piece + c, (unsigned)sp) : 0.f;
+          float num = 0.f;
+#pragma unroll
+          for (int sp = 0; sp < DEC_CLUSTER_MAX; ++sp) num += __shfl_sync(0xffffffffu, f, sp) * v[sp];
+          if (have) out[((size_t)row * nh + kvh * group + head) * HEAD_DIM + c] = __float2bfloat16_rn(num / den);
+        }
+      }
+    }
+    dec_cluster_sync();            // nobody leaves while its piece may still be read
+    return;
   }
   if (n_splits == 1) return;
   // ---- the last block to finish merges the pieces, in index order ----
@@ -334,19 +395,8 @@ TOKB200_API int tokb200_decode_attention(
     return TOKB200_BAD_ALIGNMENT;
   const int group = nh / nkv;
   const size_t stage = (size_t)DEC_WARPS * DEC_TILE * kVStride * sizeof(__nv_bfloat16);
-  const size_t merge = (size_t)DEC_WARPS * group * (HEAD_DIM + 2) * sizeof(float);
+  const size_t merge = (size_t)(DEC_WARPS + 1) * group * (HEAD_DIM + 2) * sizeof(float);
   const size_t smem = stage > merge ? stage : merge;
-  if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
-    static bool configured[64] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
-    if (!configured[device]) {
-      cudaError_t err = cudaFuncSetAttribute(decode_attention_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      if (err != cudaSuccess) return (int)err;
-      configured[device] = true;
-    }
-  }
   // no row sees more keys than its table reaches (or its window holds), so no row has
   // more pieces than this; blocks beyond would only find that out and leave
   long long reach = (long long)table_stride * page;
@@ -354,10 +404,55 @@ TOKB200_API int tokb200_decode_attention(
   long long most = (reach + DEC_MIN_CHUNK - 1) / DEC_MIN_CHUNK;
   if (most > DEC_MAX_SPLITS) most = DEC_MAX_SPLITS;
   if (most < 1) most = 1;
+  // up to DEC_CLUSTER_MAX pieces: one cluster a (row, kv head), pieces merged through
+  // distributed shared memory; more: scratch memory and the last block.  TOKB200_DECODE_MERGE
+  // = scratch always takes the second way.
+  static const bool clusters_allowed = [] {
+    const char* v = getenv("TOKB200_DECODE_MERGE");
+    return !(v && v[0] == 's');
+  }();
+  const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX;
+  void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
+                 int, const int*, const int*, int, int, int, int, float, float*, int*) =
+      cluster ? decode_attention_kernel<true> : decode_attention_kernel<false>;
+  if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
+    static bool configured[64][2] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+    if (!configured[device][cluster]) {
+      cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (err != cudaSuccess) return (int)err;
+      configured[device][cluster] = true;
+    }
+  }
   dim3 grid((unsigned)most, nkv, n_rows);
-  return launch_dependent(decode_attention_kernel, grid, dim3(DEC_THREADS), smem, stream,
-                          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-                          (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
-                          table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                          counters);
+  if (!cluster)
+    return launch_dependent(kernel, grid, dim3(DEC_THREADS), smem, stream,
+                            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+                            (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
+                            table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
+                            counters);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(DEC_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  static const int overlap = [] {
+    const char* v = getenv("TOKB200_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = overlap;
+  attribute[1].id = cudaLaunchAttributeClusterDimension;
+  attribute[1].val.clusterDim.x = (unsigned)most;
+  attribute[1].val.clusterDim.y = 1;
+  attribute[1].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 2;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+                                       (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
+                                       table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
+                                       counters);
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
