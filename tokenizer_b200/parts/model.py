@@ -26,7 +26,11 @@ def declared_tensors(spec: ModelSpec) -> List[TensorSpec]:
     return out
 
 
-_PREFETCH = os.environ.get("TOKB200_L2_PREFETCH", "1") != "0"
+# TOKB200_L2_PREFETCH=1: while a step of few rows runs a layer, a second stream brings the next
+# layer's streamed weights into L2.  It gained 3 % before kernels started under programmatic
+# dependent launch and asked for their weights ahead of their wait; since then it gains
+# nothing (0.771 against 0.769 ms a step at batch 8) and is off unless asked for.
+_PREFETCH = os.environ.get("TOKB200_L2_PREFETCH", "0") == "1"
 
 
 class _Prefetcher:
