@@ -803,3 +803,27 @@ def test_rope_store_from_partial_sums(nh, nkv, d, S, T):
     assert bool((k_pool[untouched] == 7.0).all())
     with pytest.raises(ValueError):
         o.rope_store(parts, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d, d - 2)
+
+
+@pytest.mark.parametrize("M,N,K,out_dtype,with_bias", [
+    (1, 16, 32, torch.float32, False), (8, 151936, 896, torch.float32, False), (5, 3001, 96, torch.bfloat16, True),
+    (16, 20000, 1536, torch.float32, True), (13, 777, 2080, torch.bfloat16, False)])
+def test_linear_stream(M, N, K, out_dtype, with_bias):
+    """The ring-streaming product for few rows and many weight rows: tiles that end inside
+    the matrix (N not a multiple of 16), K longer than a stage (2080 > 1024), both output
+    types, blocks with no tile at all (16 rows on a whole device)."""
+    o = ops()
+    assert o.linear_stream_supported(M, N, K)
+    x = rnd(M, K, seed=111, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=112, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=113) if with_bias else None
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device=DEV)
+    for _ in range(2):
+        o.linear_stream(x, w, bias, out)
+    torch.cuda.synchronize()
+    o.linear_stream_check()
+    want = x.double().cpu() @ w.double().cpu().t()
+    if with_bias:
+        want = want + bias.double().cpu()
+    close(out, want.float(), out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+    assert not o.linear_stream_supported(17, N, K) and not o.linear_stream_supported(4, N, 100)

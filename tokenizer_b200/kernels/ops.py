@@ -261,6 +261,42 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(counters), _stream()), "decode_attention")
 
 
+_stream_plans = {}
+
+
+def linear_stream_supported(M: int, N: int, K: int) -> bool:
+    """Sizes the ring-streaming product takes on this device (up to 16 rows, K a multiple of
+    32 up to 8192); it pays for matrices of many rows (several tiles of 16 per SM)."""
+    if M < 1 or M > 16 or K % 32 or K > 8192:
+        return False
+    key = (torch.cuda.current_device(), M <= 8, N, K)
+    if key not in _stream_plans:
+        _stream_plans[key] = bool(_lib("linear_stream").tokb200_linear_stream_supported(_i(M), _i(N), _i(K)))
+    return _stream_plans[key]
+
+
+def linear_stream(x, w, bias, out) -> None:
+    """out[M,N] = x w^T (+ bias float32) for up to 16 rows of bfloat16 x and a weight of many
+    rows, streamed through shared memory by bulk copies; out is bfloat16 or float32."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("linear_stream: bfloat16 x [M,K] and w [N,K]")
+    if tuple(out.shape) != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("linear_stream: out is [M,N] bfloat16 or float32")
+    if not linear_stream_supported(M, N, K):
+        raise ValueError(f"linear_stream does not take {M} rows with K = {K}")
+    _check(_lib("linear_stream").tokb200_linear_stream(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0),
+        _i(M), _i(N), _i(K), _stream()), "linear_stream")
+
+
+def linear_stream_check() -> None:
+    flag = _lib("linear_stream").tokb200_linear_stream_error()
+    if flag:
+        raise KernelError("linear_stream: a wait on the device ran out (status %d)" % flag)
+
+
 _ffn_plans = {}
 _ffn_scratch = {}
 

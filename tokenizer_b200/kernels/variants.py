@@ -14,6 +14,7 @@ def all_variants():
         ("linear_small_m.cu", (), ()),
         ("gemm_tcgen05.cu", (), ()),
         ("ffn_small_m.cu", (), ()),
+        ("linear_stream.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -10,6 +10,9 @@ import torch
 
 from ..kernels import ops
 
+# TOKB200_STREAM=0 keeps the vocabulary projection of few rows on the kernel for single products
+_STREAM = os.environ.get("TOKB200_STREAM", "1") != "0"
+
 # blocks wanted in flight before a product with few weight rows is also cut along k
 _TARGET_BLOCKS = 296
 
@@ -51,6 +54,12 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     N = weight.shape[0]
     # few rows: the streaming kernel; up to 64 rows it also keeps the narrow matrices,
     # whose few tiles would leave most SMs of the tile kernel idle
+    # few rows and a weight of many rows (the vocabulary projection): one block an SM streams
+    # its run of the weight through a shared-memory ring
+    if _STREAM and M <= ops.SMALL_M_ROWS and N >= 16 * 148 * 4 and ops.linear_stream_supported(M, N, K):
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        ops.linear_stream(a, weight, bias, out)
+        return out
     tiles_cut = 1
     if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):
         tiles_cut = choose_tile_k_splits(M, N, K)
