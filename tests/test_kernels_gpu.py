@@ -827,3 +827,60 @@ def test_linear_stream(M, N, K, out_dtype, with_bias):
         want = want + bias.double().cpu()
     close(out, want.float(), out_dtype if out_dtype == torch.bfloat16 else torch.float32)
     assert not o.linear_stream_supported(17, N, K) and not o.linear_stream_supported(4, N, 100)
+
+
+@pytest.mark.parametrize("M,nh,nkv,d,K,delta_kind", [
+    (1, 4, 2, 16, 64, "none"), (8, 14, 2, 64, 896, "partials5"), (5, 3, 1, 32, 96, "bf16"),
+    (7, 5, 5, 48, 160, "partials5"), (3, 2, 1, 128, 1024, "f32")])
+def test_qkv_projection_with_the_norm_in_front_folded_in(M, nh, nkv, d, K, delta_kind):
+    """The q/k/v kernel that also adds the pending residual and computes the RMS norm: the
+    new residual sum, and the rotated projections of the normed rows (rounded to bfloat16
+    where the kernel rounds them) in their cache slots."""
+    o = ops()
+    heads = nh + 2 * nkv
+    x = rnd(M, K, seed=121)
+    delta = {"none": None, "partials5": rnd(5, M, K, seed=122, scale=0.3),
+             "f32": rnd(M, K, seed=122, scale=0.5),
+             "bf16": rnd(M, K, seed=122, scale=0.5, dtype=torch.bfloat16)}[delta_kind]
+    gain = 1.0 + rnd(K, seed=123, scale=0.1)
+    eps = 1e-5
+    w = rnd(heads * d, K, seed=124, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(heads * d, seed=125, scale=0.3)
+    inv_freq = torch.tensor([1.0 / 1e4 ** (i / d) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 900)
+    pos = torch.tensor([(37 * i + 5) % 900 for i in range(M)], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([2 * i + 1 for i in range(M)], dtype=torch.int32, device=DEV)
+    if M > 1:
+        slot[M - 1] = -1
+    k_pool = torch.full((2 * M + 2, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((2 * M + 2, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty(M, nh * d, dtype=torch.bfloat16, device=DEV)
+    x_out = torch.full_like(x, 3.0)
+    o.qkv_norm_rope_small_m(x, x_out, delta, gain, eps, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool,
+                            nh, nkv, d)
+    xs = x.double().cpu()
+    if delta is not None:
+        xs = xs + (delta.double().cpu().sum(0) if delta.dim() == 3 else delta.double().cpu())
+    assert torch.allclose(x_out.cpu(), xs.float(), atol=1e-5, rtol=1e-6)
+    h = (xs / torch.sqrt((xs * xs).mean(-1, keepdim=True) + eps) * gain.double().cpu()).float().to(torch.bfloat16)
+    full = (h.double() @ w.double().cpu().t() + bias.double().cpu()).float().view(M, heads, d)
+    c, s = cos[pos.long()].cpu()[:, None, :], sin[pos.long()].cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :d // 2], v[..., d // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    def near(got, want):   # h may round the other way on a tie's edge: 2^-8 of the sum's terms
+        got, want = got.float().cpu(), want.float().cpu()
+        assert torch.allclose(got, want, atol=3e-3 * float(want.abs().max()) + 1e-3, rtol=2 ** -7), \
+            float((got - want).abs().max())
+
+    near(q_out.view(M, nh, d), rotate(full[:, :nh]))
+    k_want, v_want = rotate(full[:, nh:nh + nkv]), full[:, nh + nkv:]
+    for m in range(M):
+        if int(slot[m]) >= 0:
+            near(k_pool[int(slot[m])], k_want[m])
+            near(v_pool[int(slot[m])], v_want[m])
+    untouched = [i for i in range(2 * M + 2) if i not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
+    assert not o.qkv_norm_rope_small_m_supported(9, K, d, d) and not o.qkv_norm_rope_small_m_supported(4, 2048, d, d)

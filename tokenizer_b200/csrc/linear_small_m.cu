@@ -229,15 +229,110 @@ TOKB200_API int tokb200_linear_small_m_gated(const void* x, const void* w, void*
 // thread of the epilogue holds both halves of a pair.  The rotary width must be
 // the whole head (d), d a multiple of 16.
 // ----------------------------------------------------------------------------
-template <int MT>
+// The residual sum and the norm in front of a projection, for kernels that compute them
+// themselves (every block for all rows: a few KB): x' = x + pending (float32; the pending
+// part is [M, K] bfloat16 or float32, or float32 partial sums [S, M, K], added in index order),
+// h = x' / sqrt(mean(x'^2) + eps) * gain as bfloat16 rows in shared memory.
+struct NormInput {
+  const float* x;          // [M, K]
+  float* x_out;            // [M, K]: x' (written by block 0)
+  const void* delta;       // may be null
+  int delta_is_f32, n_partials;
+  long long partial_stride;
+  const float* gain;
+  float eps;
+  int h_pitch;             // bytes between rows of h in shared memory
+};
+
+// One warp, one row of up to 1024 elements (K a multiple of 4): the row goes in two halves; a
+// half's loads of x and of up to three partial sums are all asked for before the first is used.
+__device__ __forceinline__ void norm_row_to_shared(const NormInput& in, int m, int K, int lane,
+                                                   bool write_x, __nv_bfloat16* hrow) {
+  constexpr int kVec = 8;
+  const float* xr = in.x + (size_t)m * K;
+  const float* df = reinterpret_cast<const float*>(in.delta) + (size_t)m * K;
+  const __nv_bfloat16* dh = reinterpret_cast<const __nv_bfloat16*>(in.delta) + (size_t)m * K;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v[kVec];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    constexpr int kHalf = kVec / 2;
+    float4 a[3][kHalf];
+    uint2 raw[kHalf];
+#pragma unroll
+    for (int e = 0; e < kHalf; ++e) {
+      const int i = (lane + 32 * (half * kHalf + e)) * 4;
+      const bool inside = i < K;
+      v[half * kHalf + e] = inside ? *reinterpret_cast<const float4*>(xr + i) : zero4;
+      raw[e] = make_uint2(0u, 0u);
+      if (in.delta && !in.delta_is_f32 && inside) raw[e] = *reinterpret_cast<const uint2*>(dh + i);
+#pragma unroll
+      for (int s = 0; s < 3; ++s)
+        a[s][e] = (in.delta && in.delta_is_f32 && s < in.n_partials && inside)
+                      ? *reinterpret_cast<const float4*>(df + (size_t)s * in.partial_stride + i) : zero4;
+    }
+#pragma unroll
+    for (int e = 0; e < kHalf; ++e) {
+      float4& t4 = v[half * kHalf + e];
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[e].x));
+      const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[e].y));
+      t4.x += lo.x; t4.y += lo.y; t4.z += hi.x; t4.w += hi.y;
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        t4.x += a[s][e].x; t4.y += a[s][e].y; t4.z += a[s][e].z; t4.w += a[s][e].w;
+      }
+    }
+    if (in.delta && in.delta_is_f32) {
+      for (int s = 3; s < in.n_partials; ++s) {
+#pragma unroll
+        for (int e = 0; e < kHalf; ++e) {
+          const int i = (lane + 32 * (half * kHalf + e)) * 4;
+          if (i < K) {
+            const float4 more = *reinterpret_cast<const float4*>(df + (size_t)s * in.partial_stride + i);
+            float4& t4 = v[half * kHalf + e];
+            t4.x += more.x; t4.y += more.y; t4.z += more.z; t4.w += more.w;
+          }
+        }
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    ss += v[e].x * v[e].x + v[e].y * v[e].y + v[e].z * v[e].z + v[e].w * v[e].w;
+    const int i = (lane + 32 * e) * 4;
+    if (write_x && i < K) *reinterpret_cast<float4*>(in.x_out + (size_t)m * K + i) = v[e];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = 1.0f / sqrtf(ss / (float)K + in.eps);
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    const int i = (lane + 32 * e) * 4;
+    if (i < K) {
+      const float4 gn = *reinterpret_cast<const float4*>(in.gain + i);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[e].x * inv * gn.x, v[e].y * inv * gn.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[e].z * inv * gn.z, v[e].w * inv * gn.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<unsigned*>(&lo);
+      packed.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(hrow + i) = packed;
+    }
+  }
+}
+
+// NORM: the kernel is handed the residual stream instead of normed rows and computes the
+// norm itself (`x` is then unused): one launch and one trip through memory less per layer.
+template <int MT, bool NORM>
 __global__ void __launch_bounds__(LSM_THREADS)
-qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+qkv_rope_small_m_kernel(const NormInput norm, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                         const float* __restrict__ bias, const int* __restrict__ pos,
                         const int* __restrict__ slot, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
                         __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int M,
                         int nh, int nkv, int d, int K) {
   __shared__ float part[LSM_WARPS][16][8 * MT + 1];
+  extern __shared__ __align__(16) unsigned char qkv_h[];        // NORM: [8 MT][norm.h_pitch]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int tiles_per_head = d / 16;
@@ -290,7 +385,15 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   }
   pdl_wait();
   pdl_launch();
-  constexpr bool kXRing = MT <= 2;
+  if (NORM) {
+    for (int m = warp; m < 8 * MT; m += LSM_WARPS) {
+      __nv_bfloat16* hrow = reinterpret_cast<__nv_bfloat16*>(qkv_h + (size_t)m * norm.h_pitch);
+      if (m < M) norm_row_to_shared(norm, m, K, lane, blockIdx.x == 0, hrow);
+      else for (int i = lane * 2; i < K; i += 64) *reinterpret_cast<unsigned*>(hrow + i) = 0u;
+    }
+    __syncthreads();
+  }
+  constexpr bool kXRing = MT <= 2 && !NORM;
   uint4 x_ring[kXRing ? LSM_PRE : 1][MT];
   if (kXRing) {
 #pragma unroll
@@ -316,8 +419,10 @@ qkv_rope_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           const int m = 8 * j + g;
-          uint4 xv;
-          if (kXRing) {
+          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+          if (NORM) {
+            if (k_ok) xv = *reinterpret_cast<const uint4*>(qkv_h + (size_t)m * norm.h_pitch + (kk + 8 * t) * 2);
+          } else if (kXRing) {
             xv = x_ring[i][j];
             x_ring[i][j] = load16(x + (size_t)m * K + kn + 8 * t, m < M && next_ok);
           } else {
@@ -381,9 +486,10 @@ TOKB200_API int tokb200_qkv_rope_small_m(const void* x, const void* w, const flo
   if (M > 64 || K <= 0 || K % 8 || d <= 0 || d % 16 || nh <= 0 || nkv <= 0) return TOKB200_BAD_SIZE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
   const dim3 grid((nh + 2 * nkv) * (d / 16));
+  const NormInput none = {};
 #define LAUNCH_QKV(MT)                                                                              \
-  return launch_dependent(qkv_rope_small_m_kernel<MT>, grid, dim3(LSM_THREADS), 0, stream,         \
-                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, pos, slot, cos_t, \
+  return launch_dependent(qkv_rope_small_m_kernel<MT, false>, grid, dim3(LSM_THREADS), 0, stream,  \
+                          none, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, pos, slot, cos_t, \
                           sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, \
                           M, nh, nkv, d, K)
   if (M <= 8) LAUNCH_QKV(1);
@@ -391,4 +497,37 @@ TOKB200_API int tokb200_qkv_rope_small_m(const void* x, const void* w, const flo
   if (M <= 32) LAUNCH_QKV(4);
   LAUNCH_QKV(8);
 #undef LAUNCH_QKV
+}
+
+// The same with the residual add and the RMS norm in front computed by the kernel itself:
+// x_out = x + delta (delta as for the norm kernel: [M, K] or float32 partial sums [S, M, K], or
+// null); the projection is taken of norm(x_out) * gain.  Up to 16 rows, K a multiple of 32 up to
+// 1024.
+TOKB200_API int tokb200_qkv_norm_rope_small_m(const float* x, float* x_out, const void* delta,
+                                              int delta_is_f32, int n_partials, long long partial_stride,
+                                              const float* gain, float eps, const void* w,
+                                              const float* bias, const int* pos, const int* slot,
+                                              const float* cos_t, const float* sin_t, void* q_out,
+                                              void* k_pool, void* v_pool, int M, int nh, int nkv, int d,
+                                              int K, cudaStream_t stream) {
+  if (M <= 0) return TOKB200_OK;
+  if (M > 16 || K <= 0 || K % 32 || K > 1024 || d <= 0 || d % 16 || nh <= 0 || nkv <= 0) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)x_out | (uintptr_t)w | (uintptr_t)delta | (uintptr_t)gain) & 15)
+    return TOKB200_BAD_ALIGNMENT;
+  NormInput norm;
+  norm.x = x; norm.x_out = x_out; norm.delta = delta; norm.delta_is_f32 = delta_is_f32;
+  norm.n_partials = n_partials; norm.partial_stride = partial_stride; norm.gain = gain; norm.eps = eps;
+  norm.h_pitch = (2 * K + 127) / 128 * 128 + 64;      // 64 mod 128: rows g and g + 1 miss each other's banks
+  const dim3 grid((nh + 2 * nkv) * (d / 16));
+  const int MT = M <= 8 ? 1 : 2;
+  const size_t smem = (size_t)8 * MT * norm.h_pitch;
+  if (MT == 1)
+    return launch_dependent(qkv_rope_small_m_kernel<1, true>, grid, dim3(LSM_THREADS), smem, stream, norm,
+                            (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)w, bias, pos, slot, cos_t,
+                            sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                            M, nh, nkv, d, K);
+  return launch_dependent(qkv_rope_small_m_kernel<2, true>, grid, dim3(LSM_THREADS), smem, stream, norm,
+                          (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)w, bias, pos, slot, cos_t,
+                          sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                          M, nh, nkv, d, K);
 }

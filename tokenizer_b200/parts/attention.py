@@ -29,6 +29,8 @@ _position_tables = {}
 # with TOKB200_ATTENTION=mma, the mma.sync kernel (64-row tiles; 73 us), which also
 # takes the short portions and the head sizes the first does not.
 _PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "tcgen05")
+# TOKB200_QKV_NORM=separate keeps the norm in front of the projection of few rows a kernel of its own
+_FUSED_NORM = os.environ.get("TOKB200_QKV_NORM", "fused") != "separate"
 
 
 class GQAttention:
@@ -87,6 +89,32 @@ class GQAttention:
 
     def streamed_weights(self):
         return [self.qkv.weight, self.out.weight]
+
+    def fused_step(self, stream, norm, ctx, cache):
+        """For few rows in bfloat16: the residual add and the norm in front are computed by
+        the projection kernel itself, straight from the stream (the norm must offer
+        `folded() -> (gain, eps)` of an RMS norm).  Returns this part's output, or None when
+        the sizes are not taken (the block then norms and calls `forward`)."""
+        fold = getattr(norm, "folded", None)
+        x = stream.x
+        if not (_FUSED_NORM and fold is not None and self.runtime.dtype == torch.bfloat16 and
+                ops.qkv_norm_rope_small_m_supported(x.shape[0], self.hidden, self.d,
+                                                    self.position.rotary_dim)):
+            return None
+        gain, eps = fold()
+        group = ctx.groups[cache.group]
+        delta, stream.pending = stream.pending, None
+        x_out = torch.empty_like(x)
+        q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+        ops.qkv_norm_rope_small_m(
+            x, x_out, delta, gain, eps, self.qkv.weight, self.qkv_bias, ctx.pos,
+            group.slots if cache.writes else None, self.position.cos, self.position.sin, q,
+            cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None,
+            self.nh, self.nkv, self.d)
+        stream.x = x_out
+        mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+        self.attend(q, mixed, ctx, group, cache)
+        return self.out.forward(mixed, partials_ok=True)
 
     def forward(self, h, ctx, cache):
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)

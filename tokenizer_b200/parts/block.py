@@ -19,7 +19,12 @@ class PreNormResidual:
         return out
 
     def forward(self, stream, ctx, cache):
-        stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache))
+        # a mixer may take the stream as it is and fold the norm into its own kernel
+        fused = getattr(self.mixer, "fused_step", None)
+        delta = fused(stream, self.mixer_norm, ctx, cache) if fused is not None else None
+        if delta is None:
+            delta = self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache)
+        stream.add(delta)
         # a feed-forward may take the stream as it is and fold the norm into its own kernel
         fused = getattr(self.feed_forward, "fused_step", None)
         if fused is None or not fused(stream, self.feed_forward_norm):
