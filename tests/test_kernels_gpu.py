@@ -884,3 +884,42 @@ def test_qkv_projection_with_the_norm_in_front_folded_in(M, nh, nkv, d, K, delta
     untouched = [i for i in range(2 * M + 2) if i not in slot.tolist()]
     assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
     assert not o.qkv_norm_rope_small_m_supported(9, K, d, d) and not o.qkv_norm_rope_small_m_supported(4, 2048, d, d)
+
+
+@pytest.mark.parametrize("M,nh,nkv,d,K", [(130, 4, 2, 64, 128), (2048, 14, 2, 64, 896), (300, 2, 1, 128, 200),
+                                           (129, 6, 4, 64, 72)])
+def test_gemm_qkv_rope(M, nh, nkv, d, K):
+    """The tcgen05 q/k/v product of many rows with bias, rotation and cache write in its
+    epilogue, against the unfused arithmetic; some rows write no cache."""
+    o = ops()
+    heads = nh + 2 * nkv
+    assert o.gemm_qkv_rope_supported(K, nh, nkv, d, d)
+    x = rnd(M, K, seed=131, dtype=torch.bfloat16)
+    w = rnd(heads * d, K, seed=132, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(heads * d, seed=133, scale=0.3)
+    inv_freq = torch.tensor([1.0 / 1e4 ** (i / d) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, 3000)
+    pos = torch.tensor([(37 * i + 5) % 3000 for i in range(M)], dtype=torch.int32, device=DEV)
+    slot = torch.randperm(M + 9, generator=torch.Generator().manual_seed(3))[:M].to(torch.int32).to(DEV)
+    slot[5] = -1
+    slot[M - 1] = -1
+    k_pool = torch.full((M + 9, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((M + 9, nkv, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((M, nh * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_qkv_rope(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d)
+    torch.cuda.synchronize()
+    o.gemm_tcgen05_check()
+    full = (x.double().cpu() @ w.double().cpu().t() + bias.double().cpu()).float().view(M, heads, d)
+    c, s = cos[pos.long()].cpu()[:, None, :], sin[pos.long()].cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :d // 2], v[..., d // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    close(q_out.view(M, nh, d), rotate(full[:, :nh]), torch.bfloat16)
+    live = [t for t in range(M) if int(slot[t]) >= 0]
+    close(k_pool[slot[live].long()], rotate(full[:, nh:nh + nkv])[live], torch.bfloat16)
+    close(v_pool[slot[live].long()], full[:, nh + nkv:][live], torch.bfloat16)
+    untouched = [i for i in range(M + 9) if i not in slot.tolist()]
+    assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
+    assert not o.gemm_qkv_rope_supported(K, 3, 1, 64, 64) and not o.gemm_qkv_rope_supported(K, nh, nkv, 48, 48)

@@ -285,15 +285,33 @@ struct TcPersistentSmem {
   static constexpr int kTotal = STAGES * kStage + kOutBytes + 1024 + 256;
 };
 
+// What the QKV epilogue needs besides the product: each row's position and cache slot, the
+// rotary tables, the key/value pools and the head geometry.  `heads` null: not a QKV product.
+struct QkvEpilogue {
+  const int* pos;
+  const int* slot;              // may be null: no cache write
+  const float* cos_t;
+  const float* sin_t;           // [positions, d / 2]
+  __nv_bfloat16* k_pool;
+  __nv_bfloat16* v_pool;        // [slots, nkv, d]; may be null
+  int nh, nkv, d;
+};
+
 // GATED: the weight rows come in blocks of 256 = 128 "gate" rows followed by the 128
 // "up" rows of the same outputs; the epilogue writes silu(gate) * up, 128 columns a
 // tile, and the 2 N wide product never goes to memory.
-template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED>
+// QKV: w is the stacked [q heads; k heads; v heads] weight; the epilogue adds the bias, rotates
+// q and k by each row's position (half-split pairs (j, j + d/2), the whole head) and writes q to
+// its matrix (TMA store) and k and v to the rows' cache slots, so the stacked product never goes
+// to memory.  Tiles of 128 columns hold whole heads (d = 64 or 128) of one kind.
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED, bool QKV = false>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_out,
-                               const float* __restrict__ bias, int M, int N, int K, int k_splits) {
+                               const float* __restrict__ bias, int M, int N, int K, int k_splits,
+                               const QkvEpilogue qkv) {
+  static_assert(!QKV || (BLOCK_N == 128 && !OUT_F32 && !GATED), "the QKV epilogue works on 128-column bfloat16 tiles");
   // k_splits > 1 (32-bit output only): a unit of work is (tile, piece of k); the output is
   // [k_splits, M, N] partial sums that the consumer adds in index order, written through a
   // three-dimensional map so that a tile's rows past M fall outside its piece's plane.
@@ -392,7 +410,83 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
       // the stores of the previous tile must have read the staging area
       if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       epilogue_barrier();
-      if (GATED) {
+      if (QKV) {
+        const int row = m0 + r;
+        const bool row_ok = row < M;
+        const int d = qkv.d, half = d / 2;
+        const int q_cols = qkv.nh * d, k_cols = qkv.nkv * d;
+        const int kind = n0 < q_cols ? 0 : (n0 < q_cols + k_cols ? 1 : 2);      // q, k, v
+        const int p = row_ok ? qkv.pos[row] : 0;
+        const int sl = (row_ok && qkv.slot) ? qkv.slot[row] : -1;
+        const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BLOCK_N);
+#pragma unroll 1
+        for (int h0 = 0; h0 < 128; h0 += d) {                 // the heads of this tile
+#pragma unroll 1
+          for (int j0 = 0; j0 < half; j0 += 32) {             // 32 lanes and their partners
+            unsigned a[32], b[32];
+            tmem_load_32_async(lane_base + (unsigned)(h0 + j0), a);
+            tmem_load_32_async(lane_base + (unsigned)(h0 + half + j0), b);
+            tmem_wait_loads();
+            float fa[32], fb[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              fa[i] = __uint_as_float(a[i]) + (bias ? bias[n0 + h0 + j0 + i] : 0.f);
+              fb[i] = __uint_as_float(b[i]) + (bias ? bias[n0 + h0 + half + j0 + i] : 0.f);
+            }
+            if (kind != 2 && row_ok) {
+              const float4* c4 = reinterpret_cast<const float4*>(qkv.cos_t + (size_t)p * half + j0);
+              const float4* s4 = reinterpret_cast<const float4*>(qkv.sin_t + (size_t)p * half + j0);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 c = c4[i], sn = s4[i];
+                const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float ra = fa[4 * i + e] * cs[e] - fb[4 * i + e] * ss[e];
+                  const float rb = fb[4 * i + e] * cs[e] + fa[4 * i + e] * ss[e];
+                  fa[4 * i + e] = ra;
+                  fb[4 * i + e] = rb;
+                }
+              }
+            }
+            uint4 oa[4], ob[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              unsigned* wa = reinterpret_cast<unsigned*>(&oa[j]);
+              unsigned* wb = reinterpret_cast<unsigned*>(&ob[j]);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 pa = __floats2bfloat162_rn(fa[8 * j + 2 * e], fa[8 * j + 2 * e + 1]);
+                __nv_bfloat162 pb = __floats2bfloat162_rn(fb[8 * j + 2 * e], fb[8 * j + 2 * e + 1]);
+                wa[e] = *reinterpret_cast<unsigned*>(&pa);
+                wb[e] = *reinterpret_cast<unsigned*>(&pb);
+              }
+            }
+            if (kind == 0) {
+              // into the staging slabs (64 columns each, 128-byte swizzled rows) for the TMA store
+              const int ca = h0 + j0, cb = h0 + half + j0;
+              unsigned char* slab_a = staging + (ca / 64) * S::kSlabBytes + r * 128;
+              unsigned char* slab_b = staging + (cb / 64) * S::kSlabBytes + r * 128;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                *reinterpret_cast<uint4*>(slab_a + ((((ca / 32) % 2) * 4 + j) ^ (r & 7)) * 16) = oa[j];
+                *reinterpret_cast<uint4*>(slab_b + ((((cb / 32) % 2) * 4 + j) ^ (r & 7)) * 16) = ob[j];
+              }
+            } else {
+              __nv_bfloat16* pool = kind == 1 ? qkv.k_pool : qkv.v_pool;
+              if (row_ok && sl >= 0 && pool) {
+                const int kv_head = (n0 + h0 - q_cols - (kind == 2 ? k_cols : 0)) / d;
+                __nv_bfloat16* dst = pool + ((size_t)sl * qkv.nkv + kv_head) * d;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  *reinterpret_cast<uint4*>(dst + j0 + 8 * j) = oa[j];
+                  *reinterpret_cast<uint4*>(dst + half + j0 + 8 * j) = ob[j];
+                }
+              }
+            }
+          }
+        }
+      } else if (GATED) {
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           unsigned gate[32], up[32];
@@ -468,10 +562,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
           for (int sl = 0; sl < 2; ++sl)
             if (n0 / 2 + sl * 64 < N / 2)
               tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 / 2 + sl * 64, m0);
-        } else {
+        } else if (!QKV || n0 < qkv.nh * qkv.d) {
 #pragma unroll 1
           for (int sl = 0; sl < S::kSlabs; ++sl)
-            if (n0 + sl * S::kSlabCols < N) {
+            if (n0 + sl * S::kSlabCols < (QKV ? qkv.nh * qkv.d : N)) {
               if (OUT_F32) tma_store_3d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0, split);
               else tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
             }
@@ -547,9 +641,10 @@ static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, 
   return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
 }
 
-template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false>
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false, bool QKV = false>
 static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
-                                int K, cudaStream_t stream, int k_splits = 1) {
+                                int K, cudaStream_t stream, int k_splits = 1,
+                                const QkvEpilogue* qkv_in = nullptr) {
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
   CUtensorMap map_x, map_w, map_out;
@@ -558,14 +653,16 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   status = make_map(&map_w, w, N, K, BLOCK_N);
   if (status != TOKB200_OK) return status;
   if (k_splits < 1 || (k_splits > 1 && (!OUT_F32 || bias))) return TOKB200_BAD_SIZE;
-  status = make_out_map(&map_out, out, M, GATED ? N / 2 : N, OUT_F32, k_splits);
+  QkvEpilogue qkv = {};
+  if (QKV) qkv = *qkv_in;
+  status = make_out_map(&map_out, out, M, GATED ? N / 2 : (QKV ? (long long)qkv.nh * qkv.d : N), OUT_F32, k_splits);
   if (status != TOKB200_OK) return status;
   static bool configured[64] = {};
   static int sm_count[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
   if (!configured[device]) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED>,
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED, QKV>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (err != cudaSuccess) return (int)err;
     err = cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device);
@@ -574,9 +671,9 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   }
   const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N) * k_splits;
   dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
-  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED>, grid,
+  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED, QKV>, grid,
                           dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out, bias, M, N,
-                          K, k_splits);
+                          K, k_splits, qkv);
 }
 
 template <int BLOCK_N, int STAGES>
@@ -664,4 +761,28 @@ TOKB200_API int tokb200_gemm_tcgen05_gated(const void* x, const void* w, void* o
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   if (M > 128 * 65535) return TOKB200_BAD_SIZE;
   return launch_tc_persistent<256, 3, false, true>(x, w, nullptr, out, M, N, K, stream);
+}
+
+// The stacked q/k/v projection of many rows with bias, rotary encoding (the whole head, half-split
+// pairs) and the cache write in the epilogue: q_out [M, nh d] bfloat16; k and v go to
+// pool[slot[row], kv head, :] (a negative slot, a null slot array or a null pool skip the write).
+// Head size 64 or 128, and both nh d and nkv d multiples of 128, so that a tile holds whole heads
+// of one kind.
+TOKB200_API int tokb200_gemm_tcgen05_qkv_rope(const void* x, const void* w, const float* bias,
+                                              const int* pos, const int* slot, const float* cos_t,
+                                              const float* sin_t, void* q_out, void* k_pool, void* v_pool,
+                                              int M, int nh, int nkv, int d, int K, cudaStream_t stream) {
+  if (M <= 0) return TOKB200_OK;
+  if (K <= 0 || K % 8 || (d != 64 && d != 128) || nh <= 0 || nkv <= 0 || (nh * d) % 128 || (nkv * d) % 128)
+    return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool |
+       (uintptr_t)cos_t | (uintptr_t)sin_t) & 15)
+    return TOKB200_BAD_ALIGNMENT;
+  if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  QkvEpilogue qkv;
+  qkv.pos = pos; qkv.slot = slot; qkv.cos_t = cos_t; qkv.sin_t = sin_t;
+  qkv.k_pool = (__nv_bfloat16*)k_pool; qkv.v_pool = (__nv_bfloat16*)v_pool;
+  qkv.nh = nh; qkv.nkv = nkv; qkv.d = d;
+  return launch_tc_persistent<128, 5, false, false, true>(x, w, bias, q_out, M, (nh + 2 * nkv) * d, K, stream,
+                                                          1, &qkv);
 }

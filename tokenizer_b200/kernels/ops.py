@@ -520,6 +520,25 @@ def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh,
         "qkv_rope_small_m")
 
 
+def gemm_qkv_rope_supported(K: int, nh: int, nkv: int, d: int, rotary: int) -> bool:
+    """Sizes the tcgen05 q/k/v product with the rotary epilogue takes: head size 64 or 128, the
+    whole head rotated, and q and k/v regions of whole 128-column tiles."""
+    return K % 8 == 0 and d in (64, 128) and rotary == d and (nh * d) % 128 == 0 and (nkv * d) % 128 == 0
+
+
+def gemm_qkv_rope(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d) -> None:
+    """The stacked q/k/v projection of many rows on tcgen05 with bias, rotary encoding and the
+    cache write folded into the epilogue (bfloat16)."""
+    M, K = x.shape
+    if w.shape != ((nh + 2 * nkv) * d, K) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ValueError("gemm_qkv_rope: w is the stacked [(heads + 2 kv heads) d, K] weight")
+    if not gemm_qkv_rope_supported(K, nh, nkv, d, 2 * cos.shape[1]) or tuple(q_out.shape) != (M, nh * d):
+        raise ValueError("gemm_qkv_rope: sizes it does not take")
+    _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_qkv_rope(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), _ptr(q_out),
+        _ptr(k_pool), _ptr(v_pool), _i(M), _i(nh), _i(nkv), _i(d), _i(K), _stream()), "gemm_qkv_rope")
+
+
 def qkv_norm_rope_small_m_supported(M: int, K: int, d: int, rotary: int) -> bool:
     """Up to 8 rows (a row a warp; with 16, the norm that every block repeats costs more than
     the launch it saves: 1.03 against 0.92 ms a step), K a multiple of 32 up to 1024."""

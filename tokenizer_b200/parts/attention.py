@@ -20,6 +20,7 @@ from ..config.spec import ConfigError
 from ..kernels import ops
 from ..weights.store import TensorSpec
 from .base import CacheNeed, KVNeed, build_part, register_part
+from . import gemm_bf16
 from .linear import Linear
 
 _position_tables = {}
@@ -30,6 +31,11 @@ _position_tables = {}
 # takes the short portions and the head sizes the first does not.
 _PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "tcgen05")
 # TOKB200_QKV_NORM=separate keeps the norm in front of the projection of few rows a kernel of its own
+# TOKB200_QKV_ROPE=fused folds rotation and cache write of many rows into the tcgen05 product's
+# epilogue.  With one tile a block the longer epilogue is not hidden behind other tiles, and it
+# costs what the separate kernel costs (3.27 against 3.26 ms for 2,048 tokens), so it is off
+# unless asked for.
+_FUSED_QKV = os.environ.get("TOKB200_QKV_ROPE", "separate") == "fused"
 _FUSED_NORM = os.environ.get("TOKB200_QKV_NORM", "fused") != "separate"
 
 
@@ -123,6 +129,19 @@ class GQAttention:
                 h.shape[0], self.hidden, self.d, self.position.rotary_dim):
             # few rows: projection, bias, rotation and cache write in one kernel
             ops.qkv_rope_small_m(
+                h, self.qkv.weight, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
+                self.position.cos, self.position.sin, q,
+                cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None,
+                self.nh, self.nkv, self.d)
+            mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
+            self.attend(q, mixed, ctx, group, cache)
+            return self.out.forward(mixed, partials_ok=True)
+        if h.dtype == torch.bfloat16 and _FUSED_QKV and \
+                gemm_bf16.choose_tile_k_splits(h.shape[0], self.qkv.out_features, self.hidden) == 1 and \
+                gemm_bf16.use_tcgen05(h.shape[0], self.qkv.out_features, self.hidden) and \
+                ops.gemm_qkv_rope_supported(self.hidden, self.nh, self.nkv, self.d, self.position.rotary_dim):
+            # many rows: the tcgen05 product with bias, rotation and cache write in its epilogue
+            ops.gemm_qkv_rope(
                 h, self.qkv.weight, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
                 self.position.cos, self.position.sin, q,
                 cache.k_pool if cache.writes else None, cache.v_pool if cache.writes else None,
