@@ -159,6 +159,26 @@ __device__ __forceinline__ void fa_tmem_store32(unsigned taddr, const float (&v)
         "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+// two 32-bit values in one 64-bit register, for the packed arithmetic of sm_100
+__device__ __forceinline__ unsigned long long fa_pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void fa_unpack2(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fa_fma2(unsigned long long a, unsigned long long b,
+                                                      unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long fa_add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -395,13 +415,21 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       }
       // probabilities, their sum, and the bfloat16 copy for the second product
       const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
-      float sum = 0.f;
+      // two columns an instruction where the hardware has it (scale and shift, the sum); the
+      // exponential is one column each.  Masked scores are -inf: probability 0.
+      const unsigned long long scale2 = fa_pack2(scale_log2, scale_log2), shift2 = fa_pack2(-m_scaled, -m_scaled);
+      unsigned long long sum2 = fa_pack2(0.f, 0.f);
 #pragma unroll
-      for (int j = 0; j < kSplitKeys; ++j) {
-        s[j] = fa_exp2(fmaf(s[j], scale_log2, -m_scaled));      // masked scores are -inf: 0
-        sum += s[j];
+      for (int j = 0; j < kSplitKeys; j += 2) {
+        float x0, x1;
+        fa_unpack2(fa_fma2(fa_pack2(s[j], s[j + 1]), scale2, shift2), x0, x1);
+        s[j] = fa_exp2(x0);
+        s[j + 1] = fa_exp2(x1);
+        sum2 = fa_add2(sum2, fa_pack2(s[j], s[j + 1]));
       }
-      l_run += sum;
+      float sum_even, sum_odd;
+      fa_unpack2(sum2, sum_even, sum_odd);
+      l_run += sum_even + sum_odd;
 #pragma unroll
       for (int c = 0; c < kSplitKeys / 8; ++c) {            // 16-byte pieces of 8 keys
         uint4 piece;
