@@ -43,7 +43,7 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size");
 #define FA_KEYS 128
 #define FA_SPLITS (HEAD_DIM == 64 ? 4 : 2)        // threads (and accumulators) per row
 #define FA_SOFTMAX_THREADS (128 * FA_SPLITS)
-#define FA_LOADER_THREADS 128
+#define FA_LOADER_THREADS 64            // two rows a thread: 19 warps in all leave 96 registers a thread
 #define FA_THREADS (FA_SOFTMAX_THREADS + FA_LOADER_THREADS + 32)
 #define FA_KV_BUFFERS (HEAD_DIM == 64 ? 4 : 2)
 #define FA_WAIT_LIMIT (1u << 17)      // polls of up to 20 us each: seconds in all
@@ -261,16 +261,17 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   pdl_wait();
 
   if (live && warp >= kSoftmaxWarps && warp < kMmaWarp) {
-    // ---------------- loaders: thread t brings row t of q, then key t of every block ----------------
-    const int t = threadIdx.x - FA_SOFTMAX_THREADS;
-    {
+    // ---------------- loaders: a thread brings rows t0, t0 + 64 of q, then those keys of every block ----------------
+    const int t0 = threadIdx.x - FA_SOFTMAX_THREADS;
+#pragma unroll
+    for (int t = t0; t < FA_ROWS; t += FA_LOADER_THREADS) {
       const bool ok = t < n_rows;
       const __nv_bfloat16* src = q + ((size_t)(row0 + (ok ? t : 0)) * nh + h) * HEAD_DIM;
 #pragma unroll
       for (int c = 0; c < HEAD_DIM / 8; ++c)
         fa_cp16(q_s + (c / 8) * kSubTile + swz(t, c % 8), src + c * 8, ok);
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
     // kLag blocks are in flight at a time: before block b is asked for, block b - kLag is
     // waited for and announced (q rides with block 0)
     constexpr int kLag = FA_KV_BUFFERS / 2;
@@ -292,14 +293,17 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       }
       // the buffer is free once the P V of the block that held it has read it
       if (use > 0 && !__all_sync(0xffffffffu, fa_mbar_wait(&kv_empty[buf], (use - 1) & 1))) { ok = false; break; }   // a warp gives up together
-      const int key = kb_first + b * FA_KEYS + t;
-      const bool in = key >= lo_first && key <= pos_last;
-      size_t offset = 0;
-      if (in) offset = ((size_t)(table[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
 #pragma unroll
-      for (int c = 0; c < HEAD_DIM / 8; ++c) {
-        fa_cp16(k_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), k_pool + offset + c * 8, in);
-        fa_cp16(v_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), v_pool + offset + c * 8, in);
+      for (int t = t0; t < FA_KEYS; t += FA_LOADER_THREADS) {
+        const int key = kb_first + b * FA_KEYS + t;
+        const bool in = key >= lo_first && key <= pos_last;
+        size_t offset = 0;
+        if (in) offset = ((size_t)(table[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
+#pragma unroll
+        for (int c = 0; c < HEAD_DIM / 8; ++c) {
+          fa_cp16(k_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), k_pool + offset + c * 8, in);
+          fa_cp16(v_s + buf * kKVBytes + (c / 8) * kSubTile + swz(t, c % 8), v_pool + offset + c * 8, in);
+        }
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
