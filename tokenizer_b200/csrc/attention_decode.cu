@@ -11,12 +11,13 @@
 // same permutation for q and k); p v needs v transposed, so each warp stages its
 // tile's values in shared memory and reads them with ldmatrix.trans.
 //
-// A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk
-// is 256 * 2^k, the smallest that needs at most MAX_SPLITS pieces, so the cut is a
-// function of the row's own position and window and does not change with the
-// batch around it; up to 256 keys are one block's work and need no merge across
-// blocks.  (A block's time is a chain of dependent loads per tile, table entry then
-// keys and values, so short pieces on many blocks beat long pieces on few.)  The eight warps of a block take tiles of 32 keys in turn, each with its
+// A row's visible keys lo..pos are cut into n_splits pieces of `chunk` keys; chunk is
+// min_chunk * 2^k, the smallest that needs at most MAX_SPLITS pieces.  The launcher picks
+// min_chunk (256 .. 2048) for the launch as a whole from the number of (row, kv head) pairs
+// and the table's reach: with few pairs, short pieces on many blocks win (a block's time is
+// a chain of dependent loads per pass); with many pairs, long pieces win (fewer blocks than
+// the device holds at once cost no second wave, and fewer pieces cost less merging).  The
+// cut thus changes with the batch, which changes the order of the 32-bit merge, nothing else.  The eight warps of a block take tiles of 32 keys in turn, each with its
 // own running maximum, sum and weighted values; they are merged once at the end.  Pieces of several blocks meet in scratch memory (max, sum, weighted
 // values per (row, head, split)); the block that finishes last for a (row, kv
 // head) merges them in index order and writes the output.
@@ -34,15 +35,15 @@
 #define DEC_MAX_SPLITS 32
 #define DEC_TILE 32            // keys a warp takes per pass
 #define DEC_BLOCK_KEYS (DEC_WARPS * DEC_TILE)   // keys a block takes per pass
-#define DEC_MIN_CHUNK 256      // one pass of a block's warps; a row with no more keys needs no merge across blocks
+#define DEC_MIN_CHUNK 256      // one pass of a block's warps: the shortest piece a launch may choose
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma
 constexpr bool kTail16 = HEAD_DIM % 32 != 0;         // one more step of 16 lanes: an 8-byte load
 constexpr int kVStride = HEAD_DIM + 8;               // elements between staged value rows
 
-__device__ __forceinline__ int split_chunk(int n_keys) {
-  int chunk = DEC_MIN_CHUNK;
+__device__ __forceinline__ int split_chunk(int n_keys, int min_chunk) {
+  int chunk = min_chunk;
   while ((n_keys + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
   return chunk;
 }
@@ -98,7 +99,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
                         int nkv, int page, int window, float scale,
-                        float* __restrict__ scratch, int* __restrict__ counters) {
+                        float* __restrict__ scratch, int* __restrict__ counters, int min_chunk) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   __shared__ int is_last;
   // The rows' requests, positions and block tables were written before the predecessor (the
@@ -109,7 +110,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int p = r < 0 ? 0 : pos[row];
   const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
   const int n_keys = p - lo + 1;
-  const int chunk = split_chunk(n_keys);
+  const int chunk = split_chunk(n_keys, min_chunk);
   const int n_splits = (n_keys + chunk - 1) / chunk;
   const bool idle = r < 0 || split >= n_splits;
   if (!idle) {
@@ -401,7 +402,32 @@ TOKB200_API int tokb200_decode_attention(
   // more pieces than this; blocks beyond would only find that out and leave
   long long reach = (long long)table_stride * page;
   if (window >= 0 && window + 1 < reach) reach = window + 1;
-  long long most = (reach + DEC_MIN_CHUNK - 1) / DEC_MIN_CHUNK;
+  // The shortest piece for this launch: the candidate with the least estimated time, from a
+  // block's fixed cost (3), 2 per pass of 256 keys, 3 for a merge across blocks, and as many
+  // waves as the blocks need at two a multiprocessor (figures in microseconds, fitted to
+  // measurements at 8 and 64 rows, contexts of 600 to 16,000).
+  static int slots = 0;
+  if (!slots) {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    slots = 2 * sms;
+  }
+  const long long pairs = (long long)n_rows * nkv;
+  int min_chunk = DEC_MIN_CHUNK;
+  double best = 1e30;
+  for (int c = DEC_MIN_CHUNK; c <= 2048; c <<= 1) {
+    int chunk = c;
+    while ((reach + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
+    const long long pieces = (reach + chunk - 1) / chunk;
+    const long long passes = ((reach < chunk ? reach : chunk) + DEC_BLOCK_KEYS - 1) / DEC_BLOCK_KEYS;
+    const long long waves = (pairs * pieces + slots - 1) / slots;
+    const double t = (double)waves * (3.0 + 2.0 * (double)passes + (pieces > 1 ? 3.0 : 0.0));
+    if (t < best - 1e-9) { best = t; min_chunk = c; }
+  }
+  // no row has more pieces than this (a row a little shorter than the reach may be cut finer
+  // than the reach itself would be: its pieces are counted from min_chunk, not from the
+  // reach's chunk)
+  long long most = (reach + min_chunk - 1) / min_chunk;
   if (most > DEC_MAX_SPLITS) most = DEC_MAX_SPLITS;
   if (most < 1) most = 1;
   // up to DEC_CLUSTER_MAX pieces: one cluster a (row, kv head), pieces merged through
@@ -413,7 +439,7 @@ TOKB200_API int tokb200_decode_attention(
   }();
   const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
-                 int, const int*, const int*, int, int, int, int, float, float*, int*) =
+                 int, const int*, const int*, int, int, int, int, float, float*, int*, int) =
       cluster ? decode_attention_kernel<true> : decode_attention_kernel<false>;
   if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
     static bool configured[64][2] = {};
@@ -431,7 +457,7 @@ TOKB200_API int tokb200_decode_attention(
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                             table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                            counters);
+                            counters, min_chunk);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = dim3(DEC_THREADS);
@@ -453,6 +479,6 @@ TOKB200_API int tokb200_decode_attention(
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                        (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                                        table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                                       counters);
+                                       counters, min_chunk);
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
