@@ -270,10 +270,11 @@ def test_decode_bursts_on_the_engine(folder):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_factory, dtype):
-    """Steps that bring a whole number of 128-token tiles are captured once per shape
-    and replayed: the first use runs plainly, the second captures, later ones replay.
-    Each use here cuts its 256 tokens differently (two portions; a long portion beside
-    a decoding token of an older request) and must give the plain logits."""
+    """Steps that bring a whole number of 128-token tiles, or a few rows less (the rest are
+    idle rows), are captured once per shape and replayed: the first use runs plainly, the
+    second captures, later ones replay.  Each use here cuts its 249 to 256 tokens
+    differently (two portions; a long portion beside a decoding token of an older request)
+    and must give the plain logits."""
     import tokenizer_b200 as tb
     from tokenizer_b200 import Qwen2Config, write_random_model
     from tokenizer_b200.engine import StepEntry
@@ -288,10 +289,12 @@ def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_fac
     model = tb.load_model(path, dtype=dtype)
     engine = tb.engine_for(model, 2048, 16, max_requests=4)
     old = engine.cache.open("old")
-    old_ids = random_ids(40, config.vocab_size, 1)
+    old_ids = random_ids(42, config.vocab_size, 1)
+    old_want = plain.all_logits(cfg, w, old_ids)
     engine.cache.reserve(old, 39)
     engine.step([StepEntry(old, old_ids[:39], [])])
-    for use, (n_a, n_b) in enumerate(((150, 106), (100, 156), (255, 0), (131, 125))):
+    old_at = 39
+    for use, (n_a, n_b) in enumerate(((150, 106), (100, 156), (255, 0), (131, 125), (140, 109), (251, 0))):
         a_ids = random_ids(n_a, config.vocab_size, 10 + use)
         a = engine.cache.open(("a", use))
         engine.cache.reserve(a, n_a)
@@ -304,8 +307,9 @@ def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_fac
             entries.append(StepEntry(b, b_ids, []))
         else:
             engine.cache.reserve(old, 1)                      # one decoded token beside the portion
-            entries.append(StepEntry(old, old_ids[39:40], [0]))
-            wants.append(plain.all_logits(cfg, w, old_ids)[[39]])
+            entries.append(StepEntry(old, old_ids[old_at:old_at + 1], [0]))
+            wants.append(old_want[[old_at]])
+            old_at += 1
         got = engine.step(entries).float().cpu()
         want = torch.cat(wants)
         bound = 1e-4 if dtype == "float32" else 2e-2 * float(want.abs().max())

@@ -130,9 +130,11 @@ class Engine:
             return (rows, widths), rows, rows
         total = sum(len(e.tokens) for e in entries)
         requests = self._bucket(len(entries))
-        if total < 256 or total % 128 or sum(len(e.want) for e in entries) > requests:
+        # up to the next whole tile with idle rows, where that wastes little (a sixteenth)
+        padded = -(-total // 128) * 128
+        if total < 256 or padded - total > total // 16 or sum(len(e.want) for e in entries) > requests:
             return None
-        return ("portions", total, requests, widths, longest >= 96), total, requests
+        return ("portions", padded, requests, widths, longest >= 96), padded, requests
 
     def _step_captured(self, entries: List[StepEntry], key, tokens: int, requests: int) -> torch.Tensor:
         """A step whose launches are captured once per shape (padded batch size,
