@@ -83,8 +83,12 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
     a_ring[i] = load16(wa + kk, row_a_ok && k_ok);
     b_ring[i] = load16(wb + kk, row_b_ok && k_ok);
   }
-  pdl_wait();
+  // The successor may start now, before this kernel has even waited for its own predecessor:
+  // the kernels that follow a plain product (a norm, the fused feed-forward, the sampler) touch
+  // only weights before their own wait, and that wait still covers this kernel whole.  The
+  // feed-forward thus streams its weights while the attention before this product still runs.
   pdl_launch();
+  pdl_wait();
   for (int k = k_first; k < k_end; k += LSM_PRE * step) {
 #pragma unroll
     for (int i = 0; i < LSM_PRE; ++i) {
