@@ -249,17 +249,25 @@ class BatchBuilder:
         lay = packed.layout
         self._hosts[packed.turn].numpy()[lay.ids:lay.ids + len(ids)] = np.asarray(ids, dtype=np.int32)
 
-    def upload(self, packed: "PackedStep"):
-        """The device's half: one copy, and the views the parts receive."""
-        lay, widths = packed.layout, packed.widths
-        Tc, Rc, Wc = packed.tokens, packed.requests, packed.wanted
+    def copy(self, packed: "PackedStep") -> int:
+        """Only the copy to the device (a replayed graph has the views baked in); returns the
+        number of wanted rows."""
+        lay = packed.layout
         dev, host = self._dev, self._hosts[packed.turn]
-        page = self.plan.page_size
         dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         self.last_bytes = lay.total * 4
         if dev.is_cuda:
             self._copied[packed.turn] = torch.cuda.Event()
             self._copied[packed.turn].record()
+        return packed.n_want
+
+    def upload(self, packed: "PackedStep"):
+        """The device's half: one copy, and the views the parts receive."""
+        lay, widths = packed.layout, packed.widths
+        Tc, Rc, Wc = packed.tokens, packed.requests, packed.wanted
+        dev = self._dev
+        page = self.plan.page_size
+        self.copy(packed)
 
         def view(offset, n):
             return dev[offset:offset + n]

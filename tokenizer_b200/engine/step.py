@@ -285,7 +285,7 @@ class Engine:
                 raise ValueError(f"token id {t} is outside the vocabulary of {self.model.vocab_size}")
         self.builder.set_ids(prepared.packed, tokens)
         with torch.cuda.device(self.runtime.device):
-            _, _, n_want = self.builder.upload(prepared.packed)
+            n_want = self.builder.copy(prepared.packed)
             slot["graph"].replay()
             counter.launches += slot["launches"]
         for e in prepared.entries:
