@@ -106,6 +106,14 @@ class Engine:
 
     # ---- decoding steps replayed from CUDA graphs ---------------------------------
     @staticmethod
+    def _width(pages: int) -> int:
+        """Captured block-table widths: powers of two up to 64 pages, then whole 64s (kernels
+        size their grids from the table's reach, so a width twice the need costs idle blocks)."""
+        if pages <= 64:
+            return Engine._bucket(pages, 8)
+        return -(-pages // 64) * 64
+
+    @staticmethod
     def _bucket(n: int, least: int = 1) -> int:
         b = least
         while b < n:
@@ -122,7 +130,7 @@ class Engine:
         budget, and a replay spares the host the launches (a quarter of such a step's
         time otherwise).  The kernel choice that depends on the longest portion is
         part of the key."""
-        widths = tuple(self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
+        widths = tuple(self._width(max(len(e.cache.tables[g]) for e in entries))
                        for g in range(len(self.cache.groups)))
         longest = max(len(e.tokens) for e in entries)
         if longest == 1:
@@ -196,7 +204,7 @@ class Engine:
         device = self.runtime.device
         with torch.cuda.device(device):
             rows = self._bucket(len(entries))
-            widths = [self._bucket(max(len(e.cache.tables[g]) for e in entries), 8)
+            widths = [self._width(max(len(e.cache.tables[g]) for e in entries))
                       for g in range(len(self.cache.groups))]
             ctx, want_rows, n_want = self.builder.build(
                 entries, pad_requests=rows, pad_tokens=rows, pad_want=rows, table_widths=widths)
