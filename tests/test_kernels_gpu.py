@@ -552,7 +552,8 @@ def test_gated_linear(M, inner, K):
 
 
 @pytest.mark.parametrize("M,nh,nkv,d,K", [(1, 4, 2, 16, 64), (8, 14, 2, 64, 896), (5, 3, 1, 32, 96),
-                                           (16, 5, 5, 48, 80), (3, 2, 1, 128, 200)])
+                                           (16, 5, 5, 48, 80), (3, 2, 1, 128, 200), (32, 14, 2, 64, 896),
+                                           (23, 3, 3, 16, 72)])
 def test_qkv_projection_with_rope_and_cache_write_folded_in(M, nh, nkv, d, K):
     """The decoding step's q/k/v kernel against the unfused pieces' arithmetic:
     product + bias in float64, rotation by the float32 tables, rows scattered to

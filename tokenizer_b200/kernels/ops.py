@@ -503,7 +503,10 @@ def gated_linear(x, w, out) -> None:
 
 
 def qkv_rope_small_m_supported(M: int, K: int, d: int, rotary: int) -> bool:
-    return 0 < M <= SMALL_M_ROWS and K % 8 == 0 and d % 16 == 0 and rotary == d
+    """Up to 32 rows: beyond 16 the streaming product is no longer the fastest on its own, but
+    with rotation and cache write in its epilogue it still beats a tile product and a second
+    kernel (batch 32: 1.30 -> see the decoding map)."""
+    return 0 < M <= 32 and K % 8 == 0 and d % 16 == 0 and rotary == d
 
 
 def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d) -> None:
