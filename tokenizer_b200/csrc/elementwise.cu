@@ -69,16 +69,24 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ de
       v[e] = i < hidden ? xr[i] : 0.f;
     }
     if (dr) {
-      // the pending residual may come as partial sums of a product cut along k
-      for (int s = 0; s < n_partials; ++s) {
-        float d[RMS_MAX_PER_THREAD];
+      // the pending residual may come as partial sums of a product cut along k; four of
+      // them are asked for at a time (a trip to memory per group, not per partial sum) and
+      // added in index order
+      for (int s0 = 0; s0 < n_partials; s0 += 4) {
+        float d[4][RMS_MAX_PER_THREAD];
 #pragma unroll
-        for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
-          const int i = threadIdx.x + e * blockDim.x;
-          d[e] = i < hidden ? to_float(dr[(size_t)s * partial_stride + i]) : 0.f;
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
+            const int i = threadIdx.x + e * blockDim.x;
+            d[u][e] = (s0 + u < n_partials && i < hidden) ? to_float(dr[(size_t)(s0 + u) * partial_stride + i]) : 0.f;
+          }
         }
 #pragma unroll
-        for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) v[e] += d[e];
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) v[e] += d[u][e];
+        }
       }
 #pragma unroll
       for (int e = 0; e < RMS_MAX_PER_THREAD; ++e) {
