@@ -47,7 +47,7 @@ TOKB200_API int tokb200_embed(const int* ids, const void* table, int table_dtype
 #define RMS_MAX_PER_THREAD 8
 
 template <typename TD, typename TO>
-__global__ void rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void __launch_bounds__(1024) rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                 const float* __restrict__ gain, TO* __restrict__ y,
                                 const int* __restrict__ rows, int hidden, float eps,
                                 int n_partials, size_t partial_stride) {
