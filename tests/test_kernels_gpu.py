@@ -773,6 +773,68 @@ def test_gemm_tcgen05_partials(M, N, K, S):
         o.gemm_tcgen05_partials(a, w, torch.empty(K, M, N, dtype=torch.float32, device=DEV))
 
 
+@pytest.mark.parametrize("M,N,K,S", [(2048, 896, 4864, 2), (300, 520, 200, 1), (100, 264, 1032, 3),
+                                     (1100, 136, 640, 4), (513, 4, 128, 2)])
+def test_gemm_tcgen05_pair_partials(M, N, K, S):
+    """Two CTAs on a tile of 256 rows (each loads half of the weight tile, one thread issues the
+    products for both): partial sums over S pieces of k, written in two passes of 128 columns.
+    Row counts that leave the second CTA of the last pair with some or no rows; widths that end
+    inside a tile and inside a pass."""
+    o = ops()
+    a = rnd(M, K, seed=93, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=94, dtype=torch.bfloat16, scale=0.1)
+    out = torch.full((S, M, N), 9.0, dtype=torch.float32, device=DEV)
+    o.gemm_tcgen05_pair(a, w, None, out, o.PAIR_PARTIALS)
+    torch.cuda.synchronize()
+    o.gemm_tcgen05_check()
+    want = (a.double().cpu() @ w.double().cpu().t()).float()
+    got = out.sum(0).cpu()
+    assert torch.allclose(got, want, atol=2e-4 * float(want.abs().max()), rtol=1e-5), float((got - want).abs().max())
+    assert not bool((out == 9.0).any())
+    with pytest.raises(ValueError):
+        o.gemm_tcgen05_pair(a, w, None, torch.empty(K, M, N, dtype=torch.float32, device=DEV), o.PAIR_PARTIALS)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1152, 896), (257, 520, 72), (90, 256, 264), (640, 1032, 512)])
+@pytest.mark.parametrize("narrow", [False, True])
+def test_gemm_tcgen05_pair_plain(M, N, K, narrow):
+    """The pair form with bfloat16 output and bias, on 256- and on 128-column tiles; the output
+    past M and N stays untouched."""
+    o = ops()
+    a = rnd(M, K, seed=95, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=96, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=97)
+    room = torch.full((M + 3, N), 5.0, dtype=torch.bfloat16, device=DEV)
+    out = room[:M]
+    o.gemm_tcgen05_pair(a, w, bias, out, o.PAIR_PLAIN_128 if narrow else o.PAIR_PLAIN)
+    torch.cuda.synchronize()
+    o.gemm_tcgen05_check()
+    want = (a.double().cpu() @ w.double().cpu().t() + bias.double().cpu()).float()
+    got = out.float().cpu()
+    assert float((got - want).abs().max()) <= 2 ** -8 * float(want.abs().max()) + 1e-3
+    assert bool((room[M:] == 5.0).all())
+
+
+@pytest.mark.parametrize("M,inner,K", [(2048, 4864, 896), (256, 128, 64), (300, 384, 200), (1000, 1280, 512)])
+def test_gemm_tcgen05_pair_gated(M, inner, K):
+    """silu(gate) * up in the epilogue of the pair form, against the lone-CTA kernel's rule:
+    the products in 32-bit, one rounding of the result."""
+    o = ops()
+    x = rnd(M, K, seed=98, dtype=torch.bfloat16)
+    gate = rnd(inner, K, seed=99, dtype=torch.bfloat16, scale=0.1)
+    up = rnd(inner, K, seed=100, dtype=torch.bfloat16, scale=0.1)
+    w = o.interleave_gate_up(gate, up)
+    out = torch.full((M, inner), 3.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tcgen05_pair(x, w, None, out, o.PAIR_GATED)
+    torch.cuda.synchronize()
+    o.gemm_tcgen05_check()
+    g = x.double().cpu() @ gate.double().cpu().t()
+    u = x.double().cpu() @ up.double().cpu().t()
+    want = (g / (1 + torch.exp(-g)) * u).float()
+    got = out.float().cpu()
+    assert float((got - want).abs().max()) <= 2 ** -7 * float(want.abs().max()) + 1e-3, float((got - want).abs().max())
+
+
 @pytest.mark.parametrize("nh,nkv,d,S,T", [(14, 2, 64, 7, 40), (3, 1, 32, 2, 70), (4, 4, 128, 5, 17)])
 def test_rope_store_from_partial_sums(nh, nkv, d, S, T):
     """Bias, rotation and the cache write straight from float32 partial sums [S, T, width]."""

@@ -20,6 +20,7 @@ SWITCHES = [
     {}, {"TOKB200_ATTENTION": "mma"}, {"TOKB200_FFN": "separate"}, {"TOKB200_QKV_NORM": "separate"},
     {"TOKB200_DECODE_MERGE": "scratch"}, {"TOKB200_STREAM": "0"}, {"TOKB200_PDL": "0"},
     {"TOKB200_GEMM": "library"}, {"TOKB200_QKV_ROPE": "fused"}, {"TOKB200_L2_PREFETCH": "1"},
+    {"TOKB200_GEMM_PAIR": "0"},
 ]
 
 

@@ -273,13 +273,78 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
                ::"l"(map), "r"(tc_smem(src)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
-template <int BLOCK_N, int STAGES, bool OUT_F32>
+// ---- two CTAs on one tile (cta_group::2) ----------------------------------------
+// A pair of CTAs (a cluster of two, on the two SMs of one TPC) works on a tile of 256 rows x
+// BLOCK_N columns: each CTA loads its 128 rows of x and HALF of the tile's rows of W, the even
+// CTA's thread issues products of M = 256 that read both halves of W, and each CTA's tensor
+// memory gets the accumulator of its own 128 rows.  A k block then costs each SM 32 KB of
+// shared-memory fill for 512 cycles of products (BLOCK_N = 256) where a lone CTA needs 48 KB,
+// which is what the fill rate from L2 allows.
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's window, of the same shared-memory location in CTA 0 of the pair
+__device__ __forceinline__ unsigned leader_address(const void* p) {
+  unsigned a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(tc_smem(p)), "r"(0u));
+  return a;
+}
+// a load into this CTA's shared memory whose bytes are counted on a barrier of the pair's CTA 0
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, unsigned leader_bar,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(tc_smem(dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long a_desc,
+                                               unsigned long long b_desc, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this offset in BOTH CTAs of the pair once the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(tc_smem(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+// the bounded wait, acquiring at cluster scope (arrivals come from the other CTA of the pair)
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned long long* bar, unsigned parity) {
+  const unsigned addr = tc_smem(bar);
+  const unsigned suspend_ns = 20000u;
+  for (unsigned spin = 0; spin < TC_WAIT_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(suspend_ns) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&tc_error_flag, 2);
+  return false;
+}
+
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false, bool PAIR = false>
 struct TcPersistentSmem {
   static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2;
-  static constexpr int kBBytes = BLOCK_N * TC_BLOCK_K * 2;
+  static constexpr int kBBytes = (PAIR ? BLOCK_N / 2 : BLOCK_N) * TC_BLOCK_K * 2;
   static constexpr int kStage = kABytes + kBBytes;
   static constexpr int kSlabCols = OUT_F32 ? 32 : 64;                  // 128 bytes of output
-  static constexpr int kSlabs = BLOCK_N / kSlabCols;
+  // slabs staged at a time: the gated tile has 128 output columns; the pair's 256-column
+  // 32-bit tile goes out in two passes of 128 columns
+  static constexpr int kSlabs = GATED ? 2 : ((PAIR && OUT_F32 && BLOCK_N == 256) ? 4 : BLOCK_N / kSlabCols);
+  static constexpr int kPassCols = GATED ? BLOCK_N : kSlabs * kSlabCols;   // accumulator columns a pass
   static constexpr int kSlabBytes = TC_BLOCK_M * 128;
   static constexpr int kOutBytes = kSlabs * kSlabBytes;
   static constexpr int kTotal = STAGES * kStage + kOutBytes + 1024 + 256;
@@ -304,7 +369,7 @@ struct QkvEpilogue {
 // q and k by each row's position (half-split pairs (j, j + d/2), the whole head) and writes q to
 // its matrix (TMA store) and k and v to the rows' cache slots, so the stacked product never goes
 // to memory.  Tiles of 128 columns hold whole heads (d = 64 or 128) of one kind.
-template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED, bool QKV = false>
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED, bool QKV = false, bool PAIR = false>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                                const __grid_constant__ CUtensorMap map_w,
@@ -315,8 +380,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
   // k_splits > 1 (32-bit output only): a unit of work is (tile, piece of k); the output is
   // [k_splits, M, N] partial sums that the consumer adds in index order, written through a
   // three-dimensional map so that a tile's rows past M fall outside its piece's plane.
-  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
+  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32, GATED, PAIR>;
   static_assert(!GATED || (BLOCK_N == 256 && !OUT_F32), "the gated epilogue pairs two halves of a 256 tile");
+  static_assert(!PAIR || !QKV, "the QKV epilogue has no pair form");
+  // PAIR: the grid is clusters of two CTAs; a tile has 256 rows, of which this CTA owns 128
+  constexpr int kTileM = PAIR ? 2 * TC_BLOCK_M : TC_BLOCK_M;
+  const int rank = PAIR ? (int)cluster_rank() : 0;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ unsigned char tc_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
@@ -328,7 +399,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + TC_BLOCK_M - 1) / TC_BLOCK_M;
+  const int m_tiles = (M + kTileM - 1) / kTileM;
   const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
@@ -336,17 +407,26 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
   const int total_units = total_tiles * k_splits;
 
   if (threadIdx.x == 0) {
+    // PAIR: the loads of both CTAs count on CTA 0's "full"; a commit arrives on "empty" and
+    // "acc_full" of both; the epilogue warps of both CTAs arrive on CTA 0's "acc_empty"
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 8 : 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(tc_smem(tmem_slot)), "r"((unsigned)(2 * BLOCK_N)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {      // the warps of both CTAs take part: the same columns in both tensor memories
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(tc_smem(tmem_slot)), "r"((unsigned)(2 * BLOCK_N)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(tc_smem(tmem_slot)), "r"((unsigned)(2 * BLOCK_N)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if (PAIR) cluster_sync_all();        // the other CTA's barriers are ready before anything arrives there
+  else __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
   pdl_wait();
@@ -355,45 +435,62 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0) {
       int it = 0;                                   // k blocks issued so far, over all tiles
       bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x) {
+      for (int unit = worker; ok && unit < total_units; unit += workers) {
         const int tile = unit % total_tiles, split = unit / total_tiles;
-        const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
+        const int m0 = (tile % m_tiles) * kTileM + rank * TC_BLOCK_M;
+        const int n0 = (tile / m_tiles) * BLOCK_N + (PAIR ? rank * (BLOCK_N / 2) : 0);
         const int kb_end = min(k_blocks, (split + 1) * kb_per_split);
         for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) { ok = false; break; }   // fresh barriers pass
           unsigned char* a_tile = tiles + s * S::kStage;
-          mbar_expect_tx(&full[s], S::kStage);
-          tma_load_2d(a_tile, &map_x, &full[s], kb * TC_BLOCK_K, m0);
-          tma_load_2d(a_tile + S::kABytes, &map_w, &full[s], kb * TC_BLOCK_K, n0);
+          if (PAIR) {
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * S::kStage);      // the bytes of both CTAs
+            const unsigned bar = leader_address(&full[s]);
+            tma_load_2d_pair(a_tile, &map_x, bar, kb * TC_BLOCK_K, m0);
+            tma_load_2d_pair(a_tile + S::kABytes, &map_w, bar, kb * TC_BLOCK_K, n0);
+          } else {
+            mbar_expect_tx(&full[s], S::kStage);
+            tma_load_2d(a_tile, &map_x, &full[s], kb * TC_BLOCK_K, m0);
+            tma_load_2d(a_tile + S::kABytes, &map_w, &full[s], kb * TC_BLOCK_K, n0);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {        // PAIR: CTA 0's thread issues for both
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BLOCK_N >> 3) << 17) |
-                             ((unsigned)(TC_BLOCK_M >> 4) << 24);
+                             ((unsigned)(kTileM >> 4) << 24);
       int it = 0, round = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; ok && unit < total_units; unit += gridDim.x, ++round) {
+      for (int unit = worker; ok && unit < total_units; unit += workers, ++round) {
         const int split = unit / total_tiles;
         const int kb_begin = split * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
         const int buf = round & 1;
-        if (!mbar_wait(&acc_empty[buf], ((round >> 1) & 1) ^ 1)) break;     // the epilogue has drained it
+        // the epilogue (of both CTAs) has drained it
+        if (!(PAIR ? mbar_wait_cluster(&acc_empty[buf], ((round >> 1) & 1) ^ 1)
+                   : mbar_wait(&acc_empty[buf], ((round >> 1) & 1) ^ 1))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned tmem_d = tmem_base + (unsigned)(buf * BLOCK_N);
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
+          if (!(PAIR ? mbar_wait_cluster(&full[s], (it / STAGES) & 1) : mbar_wait(&full[s], (it / STAGES) & 1))) {
+            ok = false;
+            break;
+          }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned char* a_tile = tiles + s * S::kStage;
           const unsigned long long a_desc = umma_desc(a_tile), b_desc = umma_desc(a_tile + S::kABytes);
 #pragma unroll
-          for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k)
-            umma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb_begin) | k) != 0);
-          umma_commit(&empty[s]);
+          for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k) {
+            if (PAIR) umma_bf16_pair(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb_begin) | k) != 0);
+            else umma_bf16(tmem_d, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb_begin) | k) != 0);
+          }
+          if (PAIR) umma_commit_pair(&empty[s]);
+          else umma_commit(&empty[s]);
         }
-        umma_commit(&acc_full[buf]);
+        if (PAIR) umma_commit_pair(&acc_full[buf]);
+        else umma_commit(&acc_full[buf]);
       }
     }
   } else {
@@ -401,13 +498,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
     const int r = quarter * 32 + lane;              // this thread's row of the tile
     const bool issuer = warp == 2 && lane == 0;     // the thread that issues the TMA stores
     int round = 0;
-    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++round) {
+    for (int unit = worker; unit < total_units; unit += workers, ++round) {
       const int tile = unit % total_tiles, split = unit / total_tiles;
-      const int m0 = (tile % m_tiles) * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
+      const int m0 = (tile % m_tiles) * kTileM + rank * TC_BLOCK_M, n0 = (tile / m_tiles) * BLOCK_N;
       const int buf = round & 1;
       if (!mbar_wait(&acc_full[buf], (round >> 1) & 1)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // the stores of the previous tile must have read the staging area
+#pragma unroll 1
+      for (int c_base = 0; c_base < BLOCK_N; c_base += S::kPassCols) {    // the tile in passes of staged columns
+      // the stores of the previous pass or tile must have read the staging area
       if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
       epilogue_barrier();
       if (QKV) {
@@ -515,12 +614,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+      for (int c0 = c_base; c0 < c_base + S::kPassCols; c0 += 32) {
         unsigned v[32];
         tmem_load_32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BLOCK_N + c0), v);
         if (OUT_F32) {
           // a slab is 32 columns: row r holds 8 pieces of 16 bytes, piece j at (j ^ (r % 8))
-          unsigned char* slab = staging + (c0 / 32) * S::kSlabBytes + r * 128;
+          unsigned char* slab = staging + ((c0 - c_base) / 32) * S::kSlabBytes + r * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float4 o;
@@ -532,7 +631,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
           }
         } else {
           // a slab is 64 columns: these 32 are pieces 4 * (c0 / 32 % 2) .. + 3 of row r
-          unsigned char* slab = staging + (c0 / 64) * S::kSlabBytes + r * 128;
+          unsigned char* slab = staging + ((c0 - c_base) / 64) * S::kSlabBytes + r * 128;
           const int piece0 = (c0 / 32 % 2) * 4;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -551,12 +650,17 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       }
       }
-      // the accumulator buffer is free for the products of the tile after next
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (c_base + S::kPassCols >= BLOCK_N) {
+        // the accumulator buffer is free for the products of the tile after next
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(leader_address(&acc_empty[buf]));
+          else mbar_arrive(&acc_empty[buf]);
+        }
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> TMA reads
       epilogue_barrier();
-      if (issuer) {
+      if (issuer && m0 < M) {
         if (GATED) {   // the tile's 128 output columns start at n0 / 2
 #pragma unroll 1
           for (int sl = 0; sl < 2; ++sl)
@@ -564,24 +668,33 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
               tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 / 2 + sl * 64, m0);
         } else if (!QKV || n0 < qkv.nh * qkv.d) {
 #pragma unroll 1
-          for (int sl = 0; sl < S::kSlabs; ++sl)
-            if (n0 + sl * S::kSlabCols < (QKV ? qkv.nh * qkv.d : N)) {
-              if (OUT_F32) tma_store_3d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0, split);
-              else tma_store_2d(&map_out, staging + sl * S::kSlabBytes, n0 + sl * S::kSlabCols, m0);
+          for (int sl = 0; sl < S::kSlabs; ++sl) {
+            const int col = n0 + c_base + sl * S::kSlabCols;
+            if (col < (QKV ? qkv.nh * qkv.d : N)) {
+              if (OUT_F32) tma_store_3d(&map_out, staging + sl * S::kSlabBytes, col, m0, split);
+              else tma_store_2d(&map_out, staging + sl * S::kSlabBytes, col, m0);
             }
+          }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
       }
     }
     if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // before the CTA's memory goes
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  __syncwarp();
+  if (PAIR) cluster_sync_all();       // neither CTA's shared or tensor memory goes while the other may use it
+  else __syncthreads();
   pdl_launch();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((unsigned)(2 * BLOCK_N)) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((unsigned)(2 * BLOCK_N)) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"((unsigned)(2 * BLOCK_N)) : "memory");
   }
 }
 
@@ -641,16 +754,16 @@ static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, 
   return r == CUDA_SUCCESS ? TOKB200_OK : TOKB200_BAD_ALIGNMENT;
 }
 
-template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false, bool QKV = false>
+template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false, bool QKV = false, bool PAIR = false>
 static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
                                 int K, cudaStream_t stream, int k_splits = 1,
                                 const QkvEpilogue* qkv_in = nullptr) {
-  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32>;
+  using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32, GATED, PAIR>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
   CUtensorMap map_x, map_w, map_out;
   int status = make_map(&map_x, x, M, K, TC_BLOCK_M);
   if (status != TOKB200_OK) return status;
-  status = make_map(&map_w, w, N, K, BLOCK_N);
+  status = make_map(&map_w, w, N, K, PAIR ? BLOCK_N / 2 : BLOCK_N);      // a pair's CTA loads half the rows
   if (status != TOKB200_OK) return status;
   if (k_splits < 1 || (k_splits > 1 && (!OUT_F32 || bias))) return TOKB200_BAD_SIZE;
   QkvEpilogue qkv = {};
@@ -661,19 +774,43 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   static int sm_count[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
+  auto kernel = gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED, QKV, PAIR>;
   if (!configured[device]) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED, QKV>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (err != cudaSuccess) return (int)err;
     err = cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device);
     if (err != cudaSuccess) return (int)err;
     configured[device] = true;
   }
-  const int tiles = ((M + TC_BLOCK_M - 1) / TC_BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N) * k_splits;
-  dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
-  return launch_dependent(gemm_tcgen05_persistent_kernel<BLOCK_N, STAGES, OUT_F32, GATED, QKV>, grid,
-                          dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out, bias, M, N,
-                          K, k_splits, qkv);
+  const int tile_m = PAIR ? 2 * TC_BLOCK_M : TC_BLOCK_M;
+  const int tiles = ((M + tile_m - 1) / tile_m) * ((N + BLOCK_N - 1) / BLOCK_N) * k_splits;
+  if (!PAIR) {
+    dim3 grid(tiles < sm_count[device] ? tiles : sm_count[device]);
+    return launch_dependent(kernel, grid, dim3(TC_THREADS), (size_t)S::kTotal, stream, map_x, map_w, map_out,
+                            bias, M, N, K, k_splits, qkv);
+  }
+  // clusters of two CTAs, one cluster per pair of SMs at most
+  const int pairs = sm_count[device] / 2;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(2 * (tiles < pairs ? tiles : pairs));
+  config.blockDim = dim3(TC_THREADS);
+  config.dynamicSmemBytes = (size_t)S::kTotal;
+  config.stream = stream;
+  static const int overlap = [] {
+    const char* v = getenv("TOKB200_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = overlap;
+  attribute[1].id = cudaLaunchAttributeClusterDimension;
+  attribute[1].val.clusterDim.x = 2;
+  attribute[1].val.clusterDim.y = 1;
+  attribute[1].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 2;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, bias, M, N, K, k_splits, qkv);
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
 
 template <int BLOCK_N, int STAGES>
@@ -750,6 +887,37 @@ TOKB200_API int tokb200_gemm_tcgen05_partials(const void* x, const void* w, void
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   if (M > 128 * 65535) return TOKB200_BAD_SIZE;
   return launch_tc_persistent<128, 4, true>(x, w, nullptr, out, M, N, K, stream, k_splits);
+}
+
+// The pair form (two CTAs a tile of 256 rows x 256 columns; see the kernel).  kind 0: out [M,N]
+// bfloat16 (+ bias); kind 1: the gated product, out [M, N/2] bfloat16 (N a multiple of 256, no
+// bias); kind 2: float32 partial sums out [k_splits, M, N] (no bias); kind 3: as kind 0 with
+// 128-column tiles.
+TOKB200_API int tokb200_gemm_tcgen05_pair(const void* x, const void* w, const float* bias, void* out,
+                                          int kind, int M, int N, int K, int k_splits,
+                                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return TOKB200_OK;
+  if (K <= 0 || K % 8 || k_splits < 1) return TOKB200_BAD_SIZE;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
+  if (M > 128 * 65535) return TOKB200_BAD_SIZE;
+  const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
+  const int per = (k_blocks + k_splits - 1) / k_splits;
+  if ((k_splits - 1) * per >= k_blocks) return TOKB200_BAD_SIZE;        // an empty piece
+  switch (kind) {
+    case 0:
+      if (N % 8 || k_splits != 1) return TOKB200_BAD_SIZE;
+      return launch_tc_persistent<256, 5, false, false, false, true>(x, w, bias, out, M, N, K, stream);
+    case 1:
+      if (N % 256 || k_splits != 1 || bias) return TOKB200_BAD_SIZE;
+      return launch_tc_persistent<256, 6, false, true, false, true>(x, w, nullptr, out, M, N, K, stream);
+    case 2:
+      if (N % 4 || bias) return TOKB200_BAD_SIZE;
+      return launch_tc_persistent<256, 5, true, false, false, true>(x, w, nullptr, out, M, N, K, stream, k_splits);
+    case 3:
+      if (N % 8 || k_splits != 1) return TOKB200_BAD_SIZE;
+      return launch_tc_persistent<128, 6, false, false, false, true>(x, w, bias, out, M, N, K, stream);
+    default: return TOKB200_BAD_SIZE;
+  }
 }
 
 // out[M, N/2] = silu(x Wg^T) * (x Wu^T) where w [N, K] holds, for every 128 outputs,

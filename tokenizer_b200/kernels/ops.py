@@ -5,6 +5,7 @@ refuses.  There is no CPU path: a tensor that is not on a GPU is an error."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -61,8 +62,31 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_bound_stream = None
+
+
 def _stream():
+    if _bound_stream is not None:
+        return _bound_stream
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class bound_stream:
+    """Within the block every launch goes to the stream that is current at its entry, looked
+    up once (asking torch for the current stream costs several microseconds, and a step has a
+    few hundred launches).  Nest it anew where the current stream changes (a second stream, a
+    graph capture)."""
+
+    def __enter__(self):
+        global _bound_stream
+        self._outer = _bound_stream
+        _bound_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _bound_stream
+        _bound_stream = self._outer
+        return False
 
 
 _i, _f, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_longlong
@@ -458,6 +482,40 @@ def gemm_tcgen05_partials(a, w, out) -> None:
         "gemm_tcgen05_partials")
 
 
+PAIR_PLAIN, PAIR_GATED, PAIR_PARTIALS, PAIR_PLAIN_128 = 0, 1, 2, 3
+# TOKB200_GEMM_PAIR=0 keeps every tensor-core product on lone CTAs
+_PAIR = os.environ.get("TOKB200_GEMM_PAIR", "1") != "0"
+
+
+def gemm_tcgen05_pair(a, w, bias, out, kind: int) -> None:
+    """The product on pairs of CTAs (two SMs a tile of 256 rows x 256 columns, each loading half
+    of the tile's rows of w).  PAIR_PLAIN: out [M,N] bfloat16 (+ bias); PAIR_GATED: out [M,N/2]
+    bfloat16 = silu(gate) * up for w from `interleave_gate_up`; PAIR_PARTIALS: out [S,M,N]
+    float32 partial sums over S pieces of k; PAIR_PLAIN_128: as PAIR_PLAIN with 128-column tiles."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("gemm_tcgen05_pair: bfloat16 a [M,K] and w [N,K]")
+    splits = 1
+    if kind == PAIR_PARTIALS:
+        if out.dim() != 3 or tuple(out.shape[1:]) != (M, N) or out.dtype != torch.float32 or bias is not None:
+            raise ValueError("gemm_tcgen05_pair: partial sums are float32 [S,M,N] without bias")
+        splits = out.shape[0]
+    elif kind == PAIR_GATED:
+        if tuple(out.shape) != (M, N // 2) or out.dtype != torch.bfloat16 or N % 256 or bias is not None:
+            raise ValueError("gemm_tcgen05_pair: the gated product is bfloat16 [M,N/2], N a multiple of 256")
+    elif kind in (PAIR_PLAIN, PAIR_PLAIN_128):
+        if tuple(out.shape) != (M, N) or out.dtype != torch.bfloat16:
+            raise ValueError("gemm_tcgen05_pair: out is bfloat16 [M,N]")
+    else:
+        raise ValueError(f"gemm_tcgen05_pair: kind {kind}")
+    if K % 8 or N % (4 if kind == PAIR_PARTIALS else 8):
+        raise ValueError("gemm_tcgen05_pair: K a multiple of 8, N of 8 (4 for partial sums)")
+    _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_pair(
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(kind), _i(M), _i(N), _i(K), _i(splits), _stream()),
+        "gemm_tcgen05_pair")
+
+
 def gemm_tcgen05_check() -> None:
     """Raise if a bounded wait inside the tensor-core product ran out since the last check."""
     flag = _lib("gemm_tcgen05").tokb200_gemm_tcgen05_error()
@@ -497,6 +555,12 @@ def gated_linear(x, w, out) -> None:
         gemm_tcgen05(x, w, None, gu)
         _check(_lib("elementwise").tokb200_silu_gate_interleaved(
             _ptr(gu), _ptr(out), _i(M), _i(N // 2), _stream()), "silu_gate_interleaved")
+    elif M >= 256 and _PAIR:
+        # two tiles of rows and more: pairs of CTAs on tiles of 256 rows, each loading half of the
+        # weight tile (a sixth fewer cycles than lone CTAs at 2,048 rows)
+        _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_pair(
+            _ptr(x), _ptr(w), None, _ptr(out), _i(PAIR_GATED), _i(M), _i(N), _i(K), _i(1), _stream()),
+            "gated_linear")
     else:
         _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_gated(
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")

@@ -38,6 +38,14 @@ def choose_tile_k_splits(M: int, N: int, K: int) -> int:
     return -(-k_blocks // per)
 
 
+def use_pair(M: int, N: int, K: int) -> bool:
+    """Many rows, a long k and enough tiles of 256 x 256 for most of a device's 74 pairs of SMs
+    (the down projection from 3,840 rows on): the product goes to pairs of CTAs, each loading half
+    of the weight tile.  With fewer tiles the pair form would need pieces of k as float32 partial
+    sums, and the consumer's cost of adding the planes outweighs what the product saves."""
+    return ops._PAIR and K >= 2048 and N % 8 == 0 and -(-M // 256) * -(-N // 256) >= 60
+
+
 def use_tcgen05(M: int, N: int, K: int) -> bool:
     """Which many-row products go to the framework's tcgen05 kernel.  TOKB200_GEMM
     = library sends them to the vendor library instead (for comparisons); sizes
@@ -59,6 +67,10 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if _STREAM and M <= ops.SMALL_M_ROWS and N >= 16 * 148 * 4 and ops.linear_stream_supported(M, N, K):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         ops.linear_stream(a, weight, bias, out)
+        return out
+    if out_dtype == torch.bfloat16 and use_tcgen05(M, N, K) and use_pair(M, N, K):
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        ops.gemm_tcgen05_pair(a, weight, bias, out, ops.PAIR_PLAIN)
         return out
     tiles_cut = 1
     if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):

@@ -42,7 +42,7 @@ class _Prefetcher:
 
     def fetch(self, tensors):
         self.side.wait_stream(self.main)
-        with torch.cuda.stream(self.side):
+        with torch.cuda.stream(self.side), ops.bound_stream():
             for t in tensors:
                 ops.prefetch_l2(t)
         self.used = True
@@ -98,6 +98,10 @@ class DecoderModel:
                 want_rows: torch.Tensor) -> torch.Tensor:
         """Run the rows of `ctx` through every call of the order and return the
         float32 logits of `want_rows` (int32 row indices), [len(want_rows), vocab]."""
+        with ops.bound_stream():
+            return self._forward(ctx, bindings, want_rows)
+
+    def _forward(self, ctx, bindings, want_rows):
         stream = ResidualStream(self.embedding.forward(ctx.ids))
         ahead = self._prefetcher(ctx)
         for at, (call, binding) in enumerate(zip(self.order, bindings)):
