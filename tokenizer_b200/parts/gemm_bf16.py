@@ -34,6 +34,11 @@ def choose_tile_k_splits(M: int, N: int, K: int) -> int:
     if tiles * 2 > 148 or N % 4 or k_blocks < 4:
         return 1
     want = min(148 // tiles, k_blocks // 2, 8)      # more pieces cost the consumer more than they save here
+    # the consumer reads every plane: beyond 8 MB of partial sums, or with planes of more than
+    # 3 MB (1,024 rows of 896), adding them costs more than the idle SMs did (512 rows: 1.98 ->
+    # 1.91 ms a step with at most 4 planes; 1,024 rows: 2.52 -> 2.49 ms with none)
+    plane = M * N * 4
+    want = 1 if plane > 3_000_000 else max(1, min(want, 8_000_000 // plane))
     per = -(-k_blocks // max(want, 1))
     return -(-k_blocks // per)
 
