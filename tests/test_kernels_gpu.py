@@ -609,6 +609,26 @@ def test_rms_norm_many_rows_vector_path(hidden):
     close(out2, want, torch.bfloat16)
 
 
+@pytest.mark.parametrize("hidden,S", [(64, 1), (896, 2), (896, 5), (1000, 4), (8192, 3), (132, 2)])
+def test_rms_norm_many_rows_of_partial_sums(hidden, S):
+    """Many rows whose pending residual is float32 partial sums [S, rows, hidden]: the planes are
+    added in index order (the sum below adds them the same way), the stream is updated, the
+    output is bfloat16.  132 is no multiple of 8: the general kernel."""
+    rows = 100
+    x = rnd(rows, hidden, seed=94, scale=2.0)
+    delta = rnd(S, rows, hidden, seed=95, scale=0.7)
+    gain = 1 + rnd(hidden, seed=96, scale=0.1)
+    want_x = x.clone()
+    for s in range(S):
+        want_x = want_x + delta[s]
+    want = want_x / torch.sqrt((want_x * want_x).mean(-1, keepdim=True) + 1e-6) * gain
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=DEV)
+    x1 = x.clone()
+    ops().rms_norm(x1, gain, 1e-6, out, delta=delta)
+    assert torch.equal(x1, want_x)
+    close(out, want, torch.bfloat16)
+
+
 @pytest.mark.parametrize("nh,nkv,d", [(14, 2, 64), (5, 5, 48), (3, 1, 128), (4, 2, 16)])
 def test_rope_store_many_rows_vector_path(nh, nkv, d):
     o = ops()

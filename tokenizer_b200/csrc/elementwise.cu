@@ -168,6 +168,63 @@ __global__ void rms_norm_rows_bf16_kernel(float* __restrict__ x, const __nv_bflo
   }
 }
 
+// The same for a pending residual that comes as float32 partial sums [n_partials, rows, hidden]
+// of a product cut along k: all planes of a thread's eight elements are asked for at once and
+// added in index order.
+__global__ void rms_norm_rows_partials_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                              const float* __restrict__ gain, __nv_bfloat16* __restrict__ y,
+                                              int hidden, float eps, int n_partials, size_t partial_stride) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const int c = threadIdx.x * 8;
+  const bool on = c < hidden;
+  float v[8];
+  float ss = 0.f;
+  if (on) {
+    const float4 a = *reinterpret_cast<const float4*>(x + base + c);
+    const float4 b = *reinterpret_cast<const float4*>(x + base + c + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    for (int s0 = 0; s0 < n_partials; s0 += 4) {
+      float4 lo[4], hi[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < n_partials) {
+          const float* plane = delta + (size_t)(s0 + u) * partial_stride + base + c;
+          lo[u] = *reinterpret_cast<const float4*>(plane);
+          hi[u] = *reinterpret_cast<const float4*>(plane + 4);
+        } else {
+          lo[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          hi[u] = lo[u];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[0] += lo[u].x; v[1] += lo[u].y; v[2] += lo[u].z; v[3] += lo[u].w;
+        v[4] += hi[u].x; v[5] += hi[u].y; v[6] += hi[u].z; v[7] += hi[u].w;
+      }
+    }
+    *reinterpret_cast<float4*>(x + base + c) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(x + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  if (on) {
+    const float4 ga = *reinterpret_cast<const float4*>(gain + c);
+    const float4 gb = *reinterpret_cast<const float4*>(gain + c + 4);
+    const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o2[e] = __floats2bfloat162_rn(v[2 * e] * inv * g[2 * e], v[2 * e + 1] * inv * g[2 * e + 1]);
+    *reinterpret_cast<uint4*>(y + base + c) = o4;
+  }
+}
+
 TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, int n_partials,
                                  long long partial_stride, const float* gain, void* y,
                                  int y_dtype, const int* rows, int n_rows, int hidden, float eps,
@@ -180,6 +237,14 @@ TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, i
     const int threads8 = ((hidden / 8 + 31) / 32) * 32;
     return launch_dependent(rms_norm_rows_bf16_kernel, dim3(n_rows), dim3(threads8), 0, stream, x,
                             (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)y, hidden, eps);
+  }
+  if (n_rows >= 64 && !rows && delta && delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16 &&
+      hidden % 8 == 0 && hidden <= 8192 && partial_stride % 4 == 0 &&
+      (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)y) & 15) == 0) {
+    const int threads8 = ((hidden / 8 + 31) / 32) * 32;
+    return launch_dependent(rms_norm_rows_partials_kernel, dim3(n_rows), dim3(threads8), 0, stream, x,
+                            (const float*)delta, gain, (__nv_bfloat16*)y, hidden, eps, n_partials,
+                            (size_t)partial_stride);
   }
   int threads = 128;   // rows of up to 8 elements a thread stay in registers
   while (threads < 1024 && hidden > threads * 4) threads *= 2;

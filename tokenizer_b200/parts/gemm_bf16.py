@@ -34,21 +34,27 @@ def choose_tile_k_splits(M: int, N: int, K: int) -> int:
     if tiles * 2 > 148 or N % 4 or k_blocks < 4:
         return 1
     want = min(148 // tiles, k_blocks // 2, 8)      # more pieces cost the consumer more than they save here
-    # the consumer reads every plane: beyond 8 MB of partial sums, or with planes of more than
-    # 3 MB (1,024 rows of 896), adding them costs more than the idle SMs did (512 rows: 1.98 ->
-    # 1.91 ms a step with at most 4 planes; 1,024 rows: 2.52 -> 2.49 ms with none)
+    # the consumer reads every plane: beyond 8 MB of partial sums adding them costs more than the
+    # idle SMs did (a step of 512 rows: 1.98 -> 1.81 ms with at most 4 planes of 1.8 MB)
     plane = M * N * 4
-    want = 1 if plane > 3_000_000 else max(1, min(want, 8_000_000 // plane))
+    want = 1 if plane > 4_000_000 else max(1, min(want, 8_000_000 // plane))
     per = -(-k_blocks // max(want, 1))
     return -(-k_blocks // per)
 
 
 def use_pair(M: int, N: int, K: int) -> bool:
     """Many rows, a long k and enough tiles of 256 x 256 for most of a device's 74 pairs of SMs
-    (the down projection from 3,840 rows on): the product goes to pairs of CTAs, each loading half
-    of the weight tile.  With fewer tiles the pair form would need pieces of k as float32 partial
-    sums, and the consumer's cost of adding the planes outweighs what the product saves."""
-    return ops._PAIR and K >= 2048 and N % 8 == 0 and -(-M // 256) * -(-N // 256) >= 60
+    (the down projection from 2,816 rows on, where tiles of 128 x 128 need a second round of
+    CTAs and take 48 us at 3,072 rows): the product goes to pairs of CTAs, each loading half of
+    the weight tile."""
+    return ops._PAIR and K >= 2048 and N % 8 == 0 and -(-M // 256) * -(-N // 256) >= 44
+
+
+def use_pair_halves(M: int, N: int, K: int) -> bool:
+    """Between 1,536 rows and half the pairs' worth of tiles (the down projection of a portion of
+    2,048 tokens: 32 tiles): the pair form with k cut in two, float32 partial sums for a consumer
+    that adds them (product 25.2 -> 22.1 us, the norm behind it 3.6 -> 3.9 us)."""
+    return ops._PAIR and M >= 1536 and K >= 2048 and N % 4 == 0 and -(-M // 256) * -(-N // 256) <= 37
 
 
 def use_tcgen05(M: int, N: int, K: int) -> bool:
@@ -76,6 +82,10 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if out_dtype == torch.bfloat16 and use_tcgen05(M, N, K) and use_pair(M, N, K):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         ops.gemm_tcgen05_pair(a, weight, bias, out, ops.PAIR_PLAIN)
+        return out
+    if partials_ok and bias is None and use_tcgen05(M, N, K) and use_pair_halves(M, N, K):
+        out = torch.empty((2, M, N), dtype=torch.float32, device=a.device)
+        ops.gemm_tcgen05_pair(a, weight, None, out, ops.PAIR_PARTIALS)
         return out
     tiles_cut = 1
     if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):
