@@ -609,12 +609,12 @@ def test_rms_norm_many_rows_vector_path(hidden):
     close(out2, want, torch.bfloat16)
 
 
+@pytest.mark.parametrize("rows", [100, 17])
 @pytest.mark.parametrize("hidden,S", [(64, 1), (896, 2), (896, 5), (1000, 4), (8192, 3), (132, 2)])
-def test_rms_norm_many_rows_of_partial_sums(hidden, S):
+def test_rms_norm_many_rows_of_partial_sums(hidden, S, rows):
     """Many rows whose pending residual is float32 partial sums [S, rows, hidden]: the planes are
     added in index order (the sum below adds them the same way), the stream is updated, the
     output is bfloat16.  132 is no multiple of 8: the general kernel."""
-    rows = 100
     x = rnd(rows, hidden, seed=94, scale=2.0)
     delta = rnd(S, rows, hidden, seed=95, scale=0.7)
     gain = 1 + rnd(hidden, seed=96, scale=0.1)

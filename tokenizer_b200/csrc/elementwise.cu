@@ -238,7 +238,7 @@ TOKB200_API int tokb200_rms_norm(float* x, const void* delta, int delta_dtype, i
     return launch_dependent(rms_norm_rows_bf16_kernel, dim3(n_rows), dim3(threads8), 0, stream, x,
                             (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)y, hidden, eps);
   }
-  if (n_rows >= 64 && !rows && delta && delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16 &&
+  if (n_rows > 16 && !rows && delta && delta_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16 &&
       hidden % 8 == 0 && hidden <= 8192 && partial_stride % 4 == 0 &&
       (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)y) & 15) == 0) {
     const int threads8 = ((hidden / 8 + 31) / 32) * 32;
