@@ -6,9 +6,10 @@ weights on one B200.  Prints ONE JSON line.
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
-(`Engine.decode_steps`); `e2e` is the same through the Python entry point
-(`generate_batch`: token ids come from the host and sampled ids go back to it
-every step).  The line also carries the prefill of 2,048 tokens, the decode
+(`Engine.decode_steps`); `e2e` is the same through the scheduler that the Python
+entry point (`generate_batch`) runs: prompts come from the host, every step's
+positions, slots and block tables are copied from pinned host memory and its
+sampled ids are read back by the host, which judges the ends one step behind.  The line also carries the prefill of 2,048 tokens, the decode
 roofline and decode at batch 1 and 64.
 """
 import argparse
@@ -277,7 +278,10 @@ def main():
                    "peaks": pk["source"]},
         "clocks": main_run["clocks"],
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps},
+                "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps,
+                "note": "every step: its positions, slots and block tables from pinned host memory, its drawn "
+                        "ids back to the host; a step's token ids reach it on the device, so the host reads "
+                        "a draw while the next step runs"},
         "e2e_burst": {"value": burst_value, "unit": "tokens/s", "steps": burst_steps, "burst": 8,
                       "note": "8 greedy steps on the device between visits to the host: "
                               "one input copy and one read of 8 steps' ids per burst"},

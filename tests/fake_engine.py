@@ -72,11 +72,23 @@ class FakeEngine:
         return out
 
     # ---- the engine's faces for a step packed ahead of its tokens (used when `ahead` is set) ----
-    def enable_ahead(self):
+    def enable_ahead(self, launch=False):
+        """`launch`: the engine also runs a packed step with the ids of a draw that the host
+        has not read yet."""
         self.prepared_used = 0
+        self.launched_ahead = 0
         self.prepare_decode = self._prepare_decode
         self.step_prepared = self._step_prepared
         self.sample_launch = self._sample_launch
+        if launch:
+            self.step_prepared_device = self._step_prepared_device
+
+    def _step_prepared_device(self, prepared, pending):
+        assert not pending.read, "the step is launched before the host reads the draw"
+        logits = self._step_prepared(prepared, pending.device_ids)
+        if logits is not None:
+            self.launched_ahead += 1
+        return logits
 
     def _prepare_decode(self, caches):
         assert all(self.cache.pages_missing(c, 1) == [0] * len(self.cache.groups) for c in caches)
@@ -94,7 +106,11 @@ class FakeEngine:
         ids = self.sample(logits, temperature, top_p, uniform)
 
         class Pending:
+            device_ids = ids
+            read = False
+
             def result(self):
+                self.read = True
                 return ids
         return Pending()
 

@@ -269,6 +269,37 @@ def test_decode_bursts_on_the_engine(folder):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_fed_with_the_draw_on_the_device(folder, dtype):
+    """Once a decoding shape is captured, the scheduler launches the next step with the ids the
+    sampler has just drawn, before the host has read them.  Ids, reasons and counts equal those
+    of the same batch stepped only after the host has read each draw: one request ends by an
+    end-of-sequence id (its extra token is dropped and the batch shrinks), one by max_tokens;
+    in 32-bit a third is sampled with a temperature, and every request equals itself alone."""
+    import tokenizer_b200 as tb
+    path, config, page = folder
+    model = tb.load_model(path, dtype=dtype)
+    prompts = [random_ids(n, config.vocab_size, 900 + n) for n in (5, 19, 33)]
+    free = tb.generate(model, prompts[1], tb.GenerateParams.greedy(30)).tokens
+    last = tb.GenerateParams(max_tokens=25, temperature=0.8, top_p=0.9, seed=11) if dtype == "float32" \
+        else tb.GenerateParams.greedy(25)
+    params = [tb.GenerateParams.greedy(40), tb.GenerateParams(max_tokens=30, eos=[free[17]]), last]
+    fed = tb.engine_for(model, 64 * 3 + 64, page, max_requests=3)
+    together = tb.generate_batch(fed, prompts, params, max_batch_size=3, page_size=page)
+    waiting = tb.engine_for(model, 64 * 3 + 64, page, max_requests=3)
+    waiting.step_prepared_device = lambda prepared, pending: None
+    stepwise = tb.generate_batch(waiting, prompts, params, max_batch_size=3, page_size=page)
+    for a, b in zip(stepwise, together):
+        assert a.tokens == b.tokens and a.reason == b.reason
+        assert a.completion_tokens == b.completion_tokens
+    if dtype == "float32":
+        for p, q, b in zip(prompts, params, together):
+            assert tb.generate(model, p, q).tokens == b.tokens
+    assert together[1].reason == tb.StopReason.EOS and len(together[1].tokens) == free.index(free[17])
+    assert fed.steps_fed_on_device > 20 and waiting.steps_fed_on_device == 0
+    assert all(a.live == 0 for a in fed.cache.allocators)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_factory, dtype):
     """Steps that bring a whole number of 128-token tiles, or a few rows less (the rest are
     idle rows), are captured once per shape and replayed: the first use runs plainly, the

@@ -204,7 +204,9 @@ def test_decode_bursts_give_the_same_ids_and_fall_back_when_pages_are_short():
 
 def test_steps_packed_ahead_of_their_tokens_change_nothing():
     """While the ids of a step are drawn, the scheduler lets the engine pack the next
-    decoding step; it is used only if exactly the same requests go on.  Ends by EOS and
+    decoding step; it is used only if exactly the same requests go on (or, where the engine
+    can feed it the drawn ids on the device, launched at once and its rows for ended requests
+    dropped).  Ends by EOS and
     max_tokens, a late arrival, sampled requests and a pool that forces preemption all
     give the ids of the plain path."""
     prompts = [random_ids(n, 50, 90 + n) for n in (4, 9, 17, 6)]
@@ -213,9 +215,9 @@ def test_steps_packed_ahead_of_their_tokens_change_nothing():
               GenerateParams(max_tokens=16, eos=[free[2][9]]),
               GenerateParams(max_tokens=12, temperature=0.9, top_p=0.8, seed=5)]
     want = [solo(p, q) for p, q in zip(prompts, params)]
-    for pages in (256, 11):
+    for pages, launch in ((256, False), (11, False), (256, True), (11, True)):
         engine = FakeEngine(num_pages=pages)
-        engine.enable_ahead()
+        engine.enable_ahead(launch)
         s = Scheduler(engine, max_batch_size=4, token_budget=16)
         ids = [s.add_request(p, q) for p, q in zip(prompts[:3], params[:3])]
         for _ in range(4):
@@ -226,5 +228,8 @@ def test_steps_packed_ahead_of_their_tokens_change_nothing():
         for rid, w in zip(ids, want):
             assert out[rid].tokens == w.tokens and out[rid].reason == w.reason
         assert engine.prepared_used > 0
+        # with `launch` the packed step runs on the draw's ids before the host has read them;
+        # a request that ends with such an id leaves one token run for nothing
+        assert (engine.launched_ahead > 0) == launch
         if pages == 11:
             assert s.stats.preemptions > 0

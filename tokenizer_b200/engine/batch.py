@@ -249,6 +249,12 @@ class BatchBuilder:
         lay = packed.layout
         self._hosts[packed.turn].numpy()[lay.ids:lay.ids + len(ids)] = np.asarray(ids, dtype=np.int32)
 
+    def copy_ids(self, packed: "PackedStep", ids: torch.Tensor) -> None:
+        """Put token ids that are still on the device (int32, row = entry) in the place of a
+        packed step of single tokens, after `copy` and before the step runs."""
+        lay = packed.layout
+        self._dev[lay.ids:lay.ids + ids.numel()].copy_(ids, non_blocking=True)
+
     def copy(self, packed: "PackedStep") -> int:
         """Only the copy to the device (a replayed graph has the views baked in); returns the
         number of wanted rows."""

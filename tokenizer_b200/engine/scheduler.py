@@ -89,6 +89,7 @@ class Scheduler:
         self.stats = SchedulerStats()
         self._next_id = 0
         self._ahead = None            # (requests, step packed ahead of its tokens)
+        self._in_flight = None        # (requests, logits) of a step launched ahead of its tokens
 
     # ---- requests -------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: GenerateParams,
@@ -120,6 +121,16 @@ class Scheduler:
         """Run one iteration; returns the ids of the requests that finished."""
         done_before = set(self.finished)
         self._admit()
+        in_flight, self._in_flight = self._in_flight, None
+        if in_flight is not None:
+            # this step already runs (or ran) on the device, fed with the last draw's ids there;
+            # what it computed for requests that ended with those ids is dropped
+            requests, logits = in_flight
+            alive = [i for i, r in enumerate(requests) if r.cursor.done is None]
+            if alive:
+                self._sample([requests[i] for i in alive],
+                             logits if len(alive) == len(requests) else logits[alive])
+                return [i for i in self.finished if i not in done_before]
         ahead, self._ahead = self._ahead, None
         burst = self._burst_length()
         if burst > 1 and self._run_burst(burst):
@@ -174,6 +185,26 @@ class Scheduler:
         prepared = prepare([r.cache for r in requests])
         if prepared is not None:
             self._ahead = (requests, prepared)
+
+    def _launch_ahead(self, drawing: List[_Request], pending) -> None:
+        """If the next step is packed and the engine can take its tokens from the draw on the
+        device, launch it now: the host reads the drawn ids, extends the contexts and judges
+        the ends while that step runs, instead of the device waiting for the host.  A request
+        that ends with the id being drawn (an end-of-sequence id, a stop text, a callback; never
+        `max_tokens`, which `_pack_ahead` sees coming) has then run one token that nobody reads."""
+        run = getattr(self.engine, "step_prepared_device", None)
+        if run is None or self._ahead is None:
+            return
+        requests, prepared = self._ahead
+        if len(requests) != len(drawing) or any(a is not b for a, b in zip(requests, drawing)):
+            return                        # the draw's rows are in another order than the packed step's
+        logits = run(prepared, pending)
+        if logits is None:
+            return
+        self._ahead = None
+        self._in_flight = (requests, logits)
+        self.stats.steps += 1
+        self.stats.tokens_run += len(requests)
 
     def _burst_length(self) -> int:
         """How many steps the running requests can take together on the device:
@@ -305,6 +336,7 @@ class Scheduler:
                 pending = launch(*draw)
                 if len(drawing) == len(ready):
                     self._pack_ahead(ready)          # beside the device
+                    self._launch_ahead(drawing, pending)
                 ids = pending.result()
             self.stats.tokens_sampled += len(ids)
             for r, token in zip(drawing, ids):

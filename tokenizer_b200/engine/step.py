@@ -71,6 +71,7 @@ class Engine:
         self.sampler = Sampler(model.runtime.device)
         self.max_positions = model.max_positions
         self.steps_run = 0
+        self.steps_fed_on_device = 0      # of them: launched with a draw's ids before the host read them
         # a captured step bakes its launches: only mixers that say so may be replayed, and a
         # feed-forward may say that it cannot (a choice made on the host, say)
         self.use_graphs = bool(use_graphs) and all(
@@ -278,6 +279,30 @@ class Engine:
         packed = self.builder.pack(entries, pad_requests=requests, pad_tokens=tokens,
                                    pad_want=requests, table_widths=list(key[1]))
         return PreparedDecode(entries, key, packed, [c.length for c in caches])
+
+    def step_prepared_device(self, prepared: "PreparedDecode", pending) -> Optional[torch.Tensor]:
+        """As `step_prepared`, with the tokens taken on the device from a draw that was launched
+        (`sample_launch`) and not read yet: the step starts right behind the draw, and the host
+        reads and judges the drawn ids while it runs.  A request that turns out to have ended
+        with its drawn id has then run one token too many, which nobody reads.  None when the
+        step cannot be used as packed."""
+        from ..kernels.ops import counter
+        ids = getattr(pending, "device_ids", None)
+        slot = self._graphs.get(prepared.key)
+        if ids is None or ids.numel() != len(prepared.entries) or ids.dtype != torch.int32 or \
+                slot is None or "graph" not in slot or self._graph_buffer != self.builder.device_buffer_ptr() or \
+                any(e.cache.closed or e.cache.length != n for e, n in zip(prepared.entries, prepared.lengths)):
+            return None
+        with torch.cuda.device(self.runtime.device):
+            n_want = self.builder.copy(prepared.packed)
+            self.builder.copy_ids(prepared.packed, ids)
+            slot["graph"].replay()
+            counter.launches += slot["launches"]
+        for e in prepared.entries:
+            self.cache.commit(e.cache, 1)
+        self.steps_run += 1
+        self.steps_fed_on_device += 1
+        return slot["out"][:n_want]
 
     def step_prepared(self, prepared: "PreparedDecode", tokens: Sequence[int]) -> Optional[torch.Tensor]:
         """Run a step packed by `prepare_decode` with the tokens now known.  None when it can

@@ -26,10 +26,12 @@ def validate_sampling(temperature: float, top_p: float) -> None:
 
 
 class PendingIds:
-    """Ids on their way from the device; one outstanding draw per sampler at a time."""
+    """Ids on their way from the device; one outstanding draw per sampler at a time.
+    `device_ids` (int32, one a row) can feed the next step before the host has read them."""
 
-    def __init__(self, host, done):
+    def __init__(self, host, done, device_ids=None):
         self._host, self._done = host, done
+        self.device_ids = device_ids
 
     def result(self) -> List[int]:
         if self._host is None:
@@ -70,7 +72,7 @@ class Sampler:
         host.copy_(out, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return PendingIds(host, done)
+        return PendingIds(host, done, out)
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
