@@ -96,3 +96,38 @@ def test_malformed_files(tmp_path):
     p.write_bytes(len(header).to_bytes(8, "little") + header + b"\0" * 8)
     with pytest.raises(WeightError, match="x has 8 bytes"):
         read_safetensors(str(p))
+
+
+def test_a_folder_of_several_files_with_an_index(tmp_path):
+    """`model.safetensors.index.json` names the file of each tensor; the store reads them all and
+    the check sees one set of names.  A tensor in two files, a file outside the folder and an
+    index without a map are refused."""
+    config = TINY["a"]()[0]
+    whole = tmp_path / "whole"
+    write_random_model(str(whole), config, 3)
+    tensors = read_safetensors(str(whole / "model.safetensors"))
+    names = sorted(tensors)
+    parts = tmp_path / "parts"
+    parts.mkdir()
+    cut = len(names) // 2
+    files = {"model-00001-of-00002.safetensors": names[:cut], "model-00002-of-00002.safetensors": names[cut:]}
+    for file, held in files.items():
+        write_safetensors(str(parts / file), {n: tensors[n] for n in held})
+    index = {"metadata": {}, "weight_map": {n: f for f, held in files.items() for n in held}}
+    (parts / "model.safetensors.index.json").write_text(json.dumps(index))
+    store = WeightStore.from_folder(str(parts))
+    assert store.names() == names
+    assert all(torch.equal(store.get(n), tensors[n]) for n in names)
+    store.check(declared_tensors(config.model_spec()))
+    # the same tensor in a second file
+    write_safetensors(str(parts / "model-00002-of-00002.safetensors"),
+                      {n: tensors[n] for n in names[cut - 1:]})
+    with pytest.raises(WeightError, match="more than one file"):
+        WeightStore.from_folder(str(parts))
+    index["weight_map"][names[0]] = "../whole/model.safetensors"
+    (parts / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightError, match="not a file name inside the folder"):
+        WeightStore.from_folder(str(parts))
+    (parts / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}}))
+    with pytest.raises(WeightError, match="weight_map"):
+        WeightStore.from_folder(str(parts))

@@ -9,6 +9,7 @@ and a tensor stored in 32-bit stays 32-bit.
 """
 from __future__ import annotations
 
+import json
 import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Tuple
@@ -48,8 +49,28 @@ class WeightStore:
 
     @classmethod
     def from_folder(cls, folder: str) -> "WeightStore":
+        """`model.safetensors`, or the files that `model.safetensors.index.json` names (its
+        "weight_map": tensor name -> file).  A tensor that the index sends to a file which does
+        not hold it counts as missing; one that two files hold is an error here."""
         path = os.path.join(folder, "model.safetensors")
-        return cls(read_safetensors(path), path)
+        index = os.path.join(folder, "model.safetensors.index.json")
+        if os.path.exists(path) or not os.path.exists(index):
+            return cls(read_safetensors(path), path)
+        try:
+            with open(index) as f:
+                weight_map = json.load(f)["weight_map"]
+            files = sorted(set(weight_map.values()))
+        except (OSError, ValueError, KeyError, TypeError, AttributeError) as err:
+            raise WeightError(f"{index}: no usable \"weight_map\" ({err})")
+        tensors: Dict[str, torch.Tensor] = {}
+        for name in files:
+            if not isinstance(name, str) or os.path.basename(name) != name:
+                raise WeightError(f"{index}: {name!r} is not a file name inside the folder")
+            for key, tensor in read_safetensors(os.path.join(folder, name)).items():
+                if key in tensors:
+                    raise WeightError(f"{index}: tensor {key} is stored in more than one file")
+                tensors[key] = tensor
+        return cls(tensors, index)
 
     def names(self) -> List[str]:
         return sorted(self.tensors)
