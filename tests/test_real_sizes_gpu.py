@@ -1,7 +1,8 @@
-"""The kernels at the sizes the benchmark runs (Qwen2.5-0.5B widths, a few layers): tiny
-configurations do not reach the tcgen05 tiles of 128, the streamed vocabulary projection or
-the fused feed-forward at their real shapes.  One plain float32 forward on the CPU over one
-long id sequence serves every request, because each request's prompt is a beginning of it."""
+"""The kernels at the widths of real checkpoints (Qwen2.5-0.5B, the benchmark's; 1.5B and 7B with
+head size 128, the latter with four key/value heads and an untied head), a few
+layers each: tiny configurations do not reach the tcgen05 tiles of 128, the streamed vocabulary
+projection or the fused feed-forward at their real shapes.  One plain float32 forward on the CPU
+over one long id sequence serves every request, because each request's prompt is a beginning of it."""
 import pytest
 import torch
 
@@ -11,14 +12,26 @@ from tiny import random_ids
 pytestmark = pytest.mark.gpu
 
 
-def test_prompt_and_decoding_at_benchmark_widths(tmp_path_factory):
+WIDTHS = {
+    "0.5B": dict(num_hidden_layers=3, hidden_size=896, num_attention_heads=14, num_key_value_heads=2,
+                 intermediate_size=4864, vocab_size=151936, tie_word_embeddings=True),
+    "1.5B": dict(num_hidden_layers=2, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                 intermediate_size=8960, vocab_size=151936, tie_word_embeddings=True),
+    # the 7B widths with a third of its vocabulary (the two tables are most of a one-layer model)
+    "7B": dict(num_hidden_layers=1, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, vocab_size=50021, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("widths", list(WIDTHS))
+def test_prompt_and_decoding_at_real_widths(tmp_path_factory, widths):
     import tokenizer_b200 as tb
     from tokenizer_b200.engine import StepEntry
+    sizes = WIDTHS[widths]
     config = tb.Qwen2Config.from_dict(dict(
-        architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=3, hidden_size=896,
-        num_attention_heads=14, num_key_value_heads=2, intermediate_size=4864, vocab_size=151936,
-        rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
-        use_sliding_window=False, sliding_window=4096, max_window_layers=3))
+        sizes, architectures=["Qwen2ForCausalLM"], hidden_act="silu",
+        rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=4096,
+        use_sliding_window=False, sliding_window=4096, max_window_layers=sizes["num_hidden_layers"]))
     path = str(tmp_path_factory.mktemp("real_sizes"))
     # Attention is left as flat as random weights make it: sharpened fourfold, the rounding of q
     # and k to bfloat16 alone moves these logits by 4 % of their largest (0.13; the same with the
@@ -33,13 +46,17 @@ def test_prompt_and_decoding_at_benchmark_widths(tmp_path_factory):
     cache = exact.cache.open("exact")
     exact.cache.reserve(cache, 256)
     got = exact.step([StepEntry(cache, ids[:256], [0, 100, 255])]).cpu()
-    assert float((got - want[[0, 100, 255]]).abs().max()) <= 1e-4
+    off = float((got - want[[0, 100, 255]]).abs().max())
+    print(f"{widths}: largest logit {float(want.abs().max()):.3f}, 32-bit path off by {off:.2e}")
+    assert off <= 1e-4
     del exact
+    torch.cuda.empty_cache()
     model = tb.load_model(path, dtype="bfloat16")
     engine = tb.engine_for(model, 8 * 320, 16, max_requests=8)
 
     def check(got, rows, what):
         err = (got.float().cpu() - want[rows]).abs().max(dim=1).values
+        print(f"{widths}: {what}: off by {float(err.max()):.4f} of {bound:.4f} allowed")
         assert float(err.max()) <= bound, f"{what}: row {rows[int(err.argmax())]} is off by {float(err.max())}"
 
     # a prompt of 256 tokens three times over (run plainly, captured, replayed), then single tokens

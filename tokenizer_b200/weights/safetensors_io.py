@@ -79,7 +79,7 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
 def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
     header = {}
     offset = 0
-    blobs = []
+    flats = []
     for name in sorted(tensors):
         tensor = tensors[name].detach().cpu().contiguous()
         if tensor.dtype not in _TORCH_TO_FILE:
@@ -87,20 +87,21 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
         flat = tensor.reshape(-1)
         if tensor.dtype == torch.bfloat16:
             flat = flat.view(torch.int16)
-        blob = flat.numpy().tobytes()
+        size = flat.numel() * flat.element_size()
         header[name] = {
             "dtype": _TORCH_TO_FILE[tensor.dtype],
             "shape": list(tensor.shape),
-            "data_offsets": [offset, offset + len(blob)],
+            "data_offsets": [offset, offset + size],
         }
-        offset += len(blob)
-        blobs.append(blob)
+        offset += size
+        flats.append(flat)
     encoded = json.dumps(header, separators=(",", ":")).encode()
     encoded += b" " * (-len(encoded) % 8)
     tmp = path + ".tmp"
     with open(tmp, "wb") as fh:
         fh.write(struct.pack("<Q", len(encoded)))
         fh.write(encoded)
-        for blob in blobs:
-            fh.write(blob)
+        for flat in flats:
+            if flat.numel():
+                fh.write(memoryview(flat.numpy()).cast("B"))     # straight from the tensor's memory
     os.replace(tmp, path)
