@@ -14,8 +14,10 @@
 //     quarter of the 128 lanes), add the bias, convert and store.
 //
 // Warp roles: warp 0 loads, warp 1 allocates TMEM and issues the products, warps
-// 2..5 are the epilogue.  No operand tile is shared between CTAs (no cluster, no
-// multicast).  Rows and columns past M, N or K are zero-filled by TMA and masked
+// 2..5 are the epilogue.  In these forms no operand tile is shared between CTAs; the
+// persistent kernel further down also has a form in which two CTAs of a cluster work
+// on one tile (cta_group::2), each loading half of the W tile - still without any
+// multicast load.  Rows and columns past M, N or K are zero-filled by TMA and masked
 // at the store.  Every wait on an mbarrier is bounded: when it runs out the
 // thread records an error flag, and all roles fall through to the common exit,
 // where TMEM is given back.
