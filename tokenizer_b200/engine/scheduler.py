@@ -18,6 +18,12 @@ count of how much of that context the cache already holds.  One iteration:
  4. run the step, draw one id for each request whose context is now whole, let
     its cursor decide between going on and finishing, free what finished.
 
+While the device draws the ids of a step in which every running request decodes, the
+scheduler already reserves and packs the next step (`engine.prepare_decode`), and where the
+engine can feed a step with drawn ids on the device (`engine.step_prepared_device`) it launches
+that step before it has read the ids.  The next iteration then starts at 4 with the logits of
+the step in flight; the rows of requests that ended with the ids read in between are dropped.
+
 With `decode_burst` > 1 an iteration in which nobody waits, every running
 request is decoding and draws greedily runs up to that many steps on the
 device in one go (`engine.decode_steps`: each step's drawn ids are the next
