@@ -233,3 +233,51 @@ def test_steps_packed_ahead_of_their_tokens_change_nothing():
         assert (engine.launched_ahead > 0) == launch
         if pages == 11:
             assert s.stats.preemptions > 0
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_arrivals_and_ends_in_every_mode(seed):
+    """Random prompts, lengths, ends (max_tokens, an end-of-sequence id from the request's own
+    free run, sampled with a temperature), arrivals spread over the run and a pool that may or may
+    not force preemption: single steps, steps packed ahead, steps launched on the draw's ids before
+    the host has read them, and bursts all give each request the ids it gets alone, and every page
+    comes back."""
+    import random
+    rng = random.Random(seed)
+    n = rng.randint(3, 7)
+    prompts = [random_ids(rng.randint(1, 30), 50, 1000 * seed + i) for i in range(n)]
+    params = []
+    for i, p in enumerate(prompts):
+        kind = rng.choice(["max", "eos", "sampled"])
+        most = rng.randint(1, 14)
+        if kind == "eos":
+            free = solo(p, GenerateParams(max_tokens=most)).tokens
+            params.append(GenerateParams(max_tokens=most, eos=[free[rng.randrange(len(free))]]))
+        elif kind == "sampled":
+            params.append(GenerateParams(max_tokens=most, temperature=0.9, top_p=0.85, seed=seed * 31 + i))
+        else:
+            params.append(GenerateParams(max_tokens=most))
+    want = [solo(p, q) for p, q in zip(prompts, params)]
+    arrivals = sorted(rng.randint(0, 12) for _ in range(n))
+    pages = rng.choice([256, 24, 16])          # 16 pages of 4 tokens: less than what all hold together
+    for mode in ("single", "ahead", "launch", "burst"):
+        engine = FakeEngine(num_pages=pages)
+        if mode in ("ahead", "launch"):
+            engine.enable_ahead(launch=mode == "launch")
+        s = Scheduler(engine, max_batch_size=rng.choice([2, 4, 8]), token_budget=rng.choice([5, 16, 64]),
+                      decode_burst=4 if mode == "burst" else 1)
+        ids, at, step = [], 0, 0
+        while at < n or s.has_work():
+            while at < n and arrivals[at] <= step:
+                ids.append(s.add_request(prompts[at], params[at]))
+                at += 1
+            if s.has_work():
+                s.step()
+                s.cache.check()
+            step += 1
+        for a in s.cache.allocators:
+            assert a.all_released() and a.available == a.capacity
+        for rid, w in zip(ids, want):
+            got = s.finished[rid]
+            assert got.tokens == w.tokens and got.reason == w.reason, (mode, rid)
+            assert got.completion_tokens == w.completion_tokens
