@@ -109,9 +109,14 @@ class CachePlan:
     def pages_missing(self, cache: RequestCache, n_new: int) -> List[int]:
         """Per group, the pages a step of `n_new` more tokens still needs."""
         missing = []
+        end_block = pages_for(cache.length + n_new, self.page_size)
         for g in range(len(self.groups)):
             table = cache.tables[g]
-            end_block = pages_for(cache.length + n_new, self.page_size)
+            if self.groups[g].window is None:
+                # a table of all keys has no holes (every reserve fills it from block 0 on and
+                # nothing is given back before the end): only blocks past its end are missing
+                missing.append(max(0, end_block - len(table)))
+                continue
             first = self.first_needed_block(g, cache.length)
             count = sum(1 for b in range(first, end_block) if b >= len(table) or table[b] < 0)
             missing.append(count)
@@ -132,9 +137,13 @@ class CachePlan:
             if m > allocator.available:
                 raise OutOfPages(
                     f"request {cache.request_id!r} needs {m} more pages, {allocator.available} are left")
+        end_block = pages_for(cache.length + n_new, self.page_size)
         for g, allocator in enumerate(self.allocators):
             table = cache.tables[g]
-            end_block = pages_for(cache.length + n_new, self.page_size)
+            if self.groups[g].window is None:
+                while len(table) < end_block:          # no holes below the table's end (see pages_missing)
+                    table.append(allocator.take())
+                continue
             first = self.first_needed_block(g, cache.length)
             while len(table) < end_block:
                 table.append(-1)
@@ -200,6 +209,9 @@ class CachePlan:
                 for page in cache.tables[g]:
                     if page >= 0:
                         counts[page] = counts.get(page, 0) + 1
+                    elif self.groups[g].window is None:
+                        raise PageError(f"group {g} keeps all keys, yet request "
+                                        f"{cache.request_id!r} has a hole in its table")
             for page in range(allocator.capacity):
                 if allocator.holders(page) != counts.get(page, 0):
                     raise PageError(

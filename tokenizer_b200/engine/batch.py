@@ -101,6 +101,10 @@ class PackedStep:
     n_wide_tiles: int
 
 
+# False sends steps of single tokens through the general packing loop too (tests compare the two)
+_SINGLE_TOKEN_PATH = True
+
+
 class BatchBuilder:
     def __init__(self, plan, vocab_size: int, max_positions: int, device):
         self.plan = plan
@@ -147,14 +151,18 @@ class BatchBuilder:
                 raise ValueError(
                     f"positions {e.cache.length}..{e.cache.length + n} exceed "
                     f"max_position_embeddings {self.max_positions}")
-            ids = np.asarray(e.tokens, dtype=np.int64)
-            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
-                bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
-                raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+            if n == 1:
+                if not 0 <= int(e.tokens[0]) < self.vocab_size:
+                    raise ValueError(f"token id {int(e.tokens[0])} is outside the vocabulary of {self.vocab_size}")
+            else:
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+                    bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
+                    raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"wanted place {w} is not among the {n} tokens brought")
-            if self.plan.pages_missing(e.cache, n) != [0] * len(self.plan.groups):
+            if any(self.plan.pages_missing(e.cache, n)):
                 raise ValueError(
                     f"request {e.cache.request_id!r} has no pages reserved for {n} more tokens")
 
@@ -195,6 +203,36 @@ class BatchBuilder:
         for g in range(len(widths)):
             buf[lay.slots[g]:lay.slots[g] + Tc] = -1
             buf[lay.tables[g]:lay.tables[g] + Rc * widths[g]] = -1
+        if T == R and _SINGLE_TOKEN_PATH:
+            # a decoding step: one row a request, so whole columns are written at once
+            starts = np.fromiter((e.cache.length for e in entries), dtype=np.int32, count=R)
+            rows = np.arange(R, dtype=np.int32)
+            state_slots = [e.cache.state_slot for e in entries]
+            buf[lay.ids:lay.ids + R] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=R)
+            buf[lay.pos:lay.pos + R] = starts
+            buf[lay.row_req:lay.row_req + R] = rows
+            buf[lay.q_start:lay.q_start + R] = rows
+            buf[lay.kv_len:lay.kv_len + R] = starts + 1
+            buf[lay.state_slot:lay.state_slot + R] = state_slots
+            wanted = [r for r, e in enumerate(entries) for _ in e.want]
+            buf[lay.want:lay.want + len(wanted)] = wanted
+            for g in range(len(widths)):
+                at, width, slots = lay.tables[g], widths[g], lay.slots[g]
+                for r, e in enumerate(entries):
+                    table = e.cache.tables[g]
+                    buf[at + r * width:at + r * width + len(table)] = table
+                    position = e.cache.length
+                    buf[slots + r] = table[position // page] * page + position % page
+            buf[lay.q_start + R:lay.q_start + Rc + 1] = R
+            # one tile of one row a request, most keys first (a stable order, as a sort of tuples gives)
+            order = np.argsort(-starts, kind="stable").astype(np.int32)
+            pairs = np.empty(2 * R, dtype=np.int32)
+            pairs[0::2] = order
+            pairs[1::2] = 1
+            buf[lay.tiles:lay.tiles + 2 * R] = pairs
+            buf[lay.wide_tiles:lay.wide_tiles + 2 * R] = pairs
+            return PackedStep(lay, turn, widths, Tc, Rc, Wc, W, [1] * R, (starts + 1).tolist(), state_slots,
+                              lay.max_tiles if padded else R, lay.max_wide_tiles if padded else R)
         q_lens, kv_lens, state_slots = [], [], []
         row = 0
         want_at = 0

@@ -139,6 +139,9 @@ class SampleCursor:
         return self.done is None
 
     def next_uniform(self) -> float:
+        """The draw for the next id; the greedy choice uses none (sample.rs:43-56)."""
+        if self.params.temperature == 0:
+            return 0.0
         return uniform(self.params.seed, self.drawn)
 
     def _observe(self, piece: str) -> Control:
