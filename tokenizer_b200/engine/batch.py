@@ -203,7 +203,7 @@ class BatchBuilder:
         for g in range(len(widths)):
             buf[lay.slots[g]:lay.slots[g] + Tc] = -1
             buf[lay.tables[g]:lay.tables[g] + Rc * widths[g]] = -1
-        if T == R and _SINGLE_TOKEN_PATH:
+        if T == R and _SINGLE_TOKEN_PATH and all(len(e.tokens) == 1 for e in entries):
             # a decoding step: one row a request, so whole columns are written at once
             starts = np.fromiter((e.cache.length for e in entries), dtype=np.int32, count=R)
             rows = np.arange(R, dtype=np.int32)
