@@ -95,9 +95,16 @@ def mask_value(query, key, window):
 
 
 def attention_mask(seq, window):
-    """model.rs:923-940 for a whole sequence (query and key origin equal)."""
-    rows = [[mask_value(q, k, window) for k in range(seq)] for q in range(seq)]
-    return torch.tensor(rows, dtype=torch.float32)
+    """model.rs:923-940 for a whole sequence (query and key origin equal): the matrix of
+    `mask_value(query, key, window)`, filled by comparisons over whole index arrays so that
+    sequences of thousands of tokens stay affordable (tests/test_plain.py compares it with
+    the entry-by-entry rule)."""
+    query = torch.arange(seq).reshape(-1, 1)
+    key = torch.arange(seq).reshape(1, -1)
+    hidden = key > query
+    if window is not None:
+        hidden = hidden | (key + int(window) < query)
+    return torch.zeros((seq, seq), dtype=torch.float32).masked_fill(hidden, -math.inf)
 
 
 def window_for_layer(cfg, index):
@@ -154,10 +161,11 @@ def decoder_layer(x, w, index, cfg, cos, sin):
     return swiglu_mlp(h, w, p + "mlp.") + x
 
 
-def all_logits(cfg, w, ids):
+def all_logits(cfg, w, ids, rows=None):
     """Logits at every position of `ids`, (seq, vocab), by a full recompute
     (model.rs:832-848 keeps the last row only; every row is the same product).
-    Head: model.rs:1224-1242, tied to the embedding or `lm_head.weight`."""
+    Head: model.rs:1224-1242, tied to the embedding or `lm_head.weight`.  With `rows`
+    (positions), only those rows go through the final norm and the head: (len(rows), vocab)."""
     seq = len(ids)
     if seq == 0 or seq > cfg["max_position_embeddings"]:
         raise ValueError("positions exceed max_position_embeddings")
@@ -165,6 +173,8 @@ def all_logits(cfg, w, ids):
     x = embed(ids, w["model.embed_tokens.weight"])
     for index in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, index, cfg, cos, sin)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     h = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return linear(h, head)

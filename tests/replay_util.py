@@ -25,16 +25,25 @@ def rounded64(n):
     return (n + 63) // 64 * 64
 
 
-def run_trace(folder, dtype, steps, out_dir, max_tokens, page_size, timeout=600):
-    """Feed `steps` (list of dicts) and return {step: array [wanted, vocab]}."""
+def run_trace(folder, dtype, steps, out_dir, max_tokens, page_size, timeout=600, share=False,
+              adopted=None):
+    """Feed `steps` (list of dicts) and return {step: array [wanted, vocab]}.  With `share`
+    the program may share pages between requests; `adopted` (a dict) is then filled with
+    {request: tokens it took over instead of computing}."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
            "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    if share:
+        cmd.append("--share-prefixes")
     text = "".join(json.dumps(s) + "\n" for s in steps)
     proc = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
     assert proc.returncode == 0, f"trace_run failed:\n{proc.stdout[-2000:]}\n{proc.stderr[-4000:]}"
     done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
     assert [d.split()[1] for d in done] == [str(s["step"]) for s in steps], proc.stdout[-2000:]
+    if adopted is not None:
+        for line in proc.stdout.splitlines():
+            if line.startswith("adopted "):
+                adopted[line.split()[1]] = int(line.split()[2])
     vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
     out = {}
     for s in steps:
@@ -133,21 +142,34 @@ def steps_portions(requests, sizes=(2, 7, 3, 16, 2, 33, 5, 2, 64, 9)):
 
 
 def steps_mixed(requests, max_live=4, prompt_fraction=0.6, portion=(11, 2, 24, 5, 17),
-                seed=0):
+                seed=0, share=None, page=16):
     """Up to `max_live` requests at a time: a request's first part goes in
     portions of changing size, the rest token by token; each step carries the
     portions of some beside the single tokens of others, one request is left out
     of a step now and then.  Returns the steps and the most tokens (each request
-    rounded up to 64) that were live at once."""
+    rounded up to 64) that were live at once.
+
+    `share` = {adopter: (donor, n)}: the adopter's first n tokens equal the donor's.  The
+    donor's pages are published in the step that completes its first n tokens; the adopter
+    starts only after that, while the donor is still live, with an entry that asks to adopt
+    and wants logits only behind the whole pages it takes over.  Returns also
+    {adopter: tokens it is expected to adopt}."""
     rng = np.random.RandomState(seed)
+    share = share or {}
     waiting = list(requests.items())
     live = []   # [name, ids, done, prompt_len, k]
     steps, at, peak = [], 0, 0
+    published = set()
+    expect = {}
     while waiting or live:
         while waiting and len(live) < max_live:
+            name = waiting[0][0]
+            if name in share and share[name][0] not in published:
+                assert any(item[0] == share[name][0] for item in live), "the donor must run first"
+                break                      # its donor has not published yet
             name, ids = waiting.pop(0)
             live.append([name, ids, 0, max(2, int(len(ids) * prompt_fraction)), 0])
-        entries, ended = [], []
+        entries, ended, publish = [], [], []
         for item in live:
             name, ids, done, prompt_len, k = item
             if len(live) > 1 and rng.rand() < 0.15:
@@ -156,15 +178,31 @@ def steps_mixed(requests, max_live=4, prompt_fraction=0.6, portion=(11, 2, 24, 5
                 n = min(portion[(k + len(name)) % len(portion)], prompt_len - done)
             else:
                 n = 1
+            entry = {"id": name}
+            first = 0
+            if done == 0 and name in share:
+                n = share[name][1] + 1 + n             # the shared beginning and a little more
+                first = min(share[name][1], n - 1) // page * page
+                expect[name] = first
+                entry["adopt"] = True
             n = min(n, len(ids) - done)
-            entries.append({"id": name, "tokens": ids[done:done + n], "want": list(range(n))})
+            entry.update(tokens=ids[done:done + n], want=list(range(first, n)))
+            entries.append(entry)
             item[2] += n
             item[4] += 1
             if item[2] == len(ids):
                 ended.append(name)
+            for adopter, (donor, shared) in share.items():
+                if donor == name and donor not in published and item[2] >= shared:
+                    published.add(donor)
+                    publish.append(donor)
         peak = max(peak, sum(rounded64(item[2]) for item in live))
         if entries:
             steps.append({"step": at, "entries": entries, "end": ended})
+            if publish:
+                steps[-1]["publish"] = publish
             at += 1
         live = [item for item in live if item[0] not in ended]
+    if share:
+        return steps, peak, expect
     return steps, peak

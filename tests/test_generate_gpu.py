@@ -25,6 +25,18 @@ def margins_ok(cfg, w, ids, n_prompt, least):
     return bool(((top2[:, 0] - top2[:, 1]) > least).all())
 
 
+def assert_near_best(cfg, w, prompt, tokens, dtype, what=""):
+    """Every id is the best of the plain logits given the ids before it, up to the rounding
+    of the precision (in bfloat16 two ids whose logits lie closer than that may swap)."""
+    logits = plain.all_logits(cfg, w, list(prompt) + list(tokens))
+    lead = logits[len(prompt) - 1:-1]
+    chosen = lead.gather(1, torch.tensor(tokens)[:, None])[:, 0]
+    slack = 1e-4 if dtype == "float32" else 0.04 * float(logits.abs().max())
+    gap = lead.max(dim=1).values - chosen
+    assert float(gap.max()) <= slack, \
+        f"{what}: token {int(gap.argmax())} lies {float(gap.max())} below the best logit (slack {slack})"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_equals_the_plain_implementation(folder, dtype):
     import tokenizer_b200 as tb
@@ -43,6 +55,7 @@ def test_greedy_generation_equals_the_plain_implementation(folder, dtype):
         elif margins_ok(cfg, w, prompt + want, n, 0.05 * float(plain.all_logits(cfg, w, prompt + want).abs().max())):
             assert out.tokens == want
             checked += 1
+        assert_near_best(cfg, w, prompt, out.tokens, dtype, f"prompt of {n}")
         assert tb.greedy_tokens(model, prompt, 16) == out.tokens     # the same call twice
     assert dtype == "bfloat16" or checked == 3
 
@@ -172,6 +185,7 @@ def test_scheduler_on_the_engine_with_too_few_pages(folder, dtype):
     import tokenizer_b200 as tb
     from tokenizer_b200.engine.scheduler import Scheduler
     path, config, page = folder
+    cfg, w = plain.load_folder(path)
     model = tb.load_model(path, dtype=dtype)
     lengths = [9, 30, 17, 44, 5]
     new = 20
@@ -185,12 +199,13 @@ def test_scheduler_on_the_engine_with_too_few_pages(folder, dtype):
     ids = [scheduler.add_request(p, tb.GenerateParams.greedy(new)) for p in prompts]
     results = scheduler.run()
     assert scheduler.stats.preemptions > 0
-    for rid, want in zip(ids, solo):
+    for rid, want, prompt in zip(ids, solo, prompts):
         assert results[rid].reason == tb.StopReason.MAX_TOKENS
+        assert len(results[rid].tokens) == new
         if dtype == "float32":
             assert results[rid].tokens == want
-        else:
-            assert len(results[rid].tokens) == new
+        # a context recomputed after a preemption must still lead to ids the plain logits back
+        assert_near_best(cfg, w, prompt, results[rid].tokens, dtype, f"request {rid}")
     engine.cache.check()
     assert all(a.all_released() and a.available == a.capacity for a in engine.cache.allocators)
 
@@ -216,6 +231,55 @@ def test_shared_beginnings_on_the_engine(folder):
     assert scheduler.stats.shared_prefix_tokens == 3 * page
     assert results[first].tokens == alone[0] and results[second].tokens == alone[1]
     engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_shared_pages_are_read_and_never_rewritten(folder, dtype):
+    """A second and a third request take over the published pages of a first: their logits
+    behind the shared beginning are the plain ones, and what the shared pages hold, in every
+    layer, is bit for bit what the first request wrote (the reference snapshots a shared
+    block around the second sharer's run in the same way: qwen-server/src/engine.rs:2208-2320)."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    path, config, page = folder
+    if any(l.mixer.params["window"] is not None for l in config.model_spec().layers):
+        pytest.skip("pages are shared only when every layer keeps all keys")
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype=dtype)
+    engine = tb.Engine(model, num_pages=40, page_size=page, max_requests=4, share_prefixes=True)
+    base = random_ids(3 * page + 5, config.vocab_size, 911)
+    first = engine.cache.open("first")
+    engine.cache.reserve(first, len(base))
+    engine.step([StepEntry(first, base, [])])
+    engine.cache.publish_prompt(first, base)
+    shared_pages = list(first.tables[0][:3])
+
+    def snapshot():
+        pool = engine.cache.pools[0]            # [calls, 2, pages * page, kv heads, head size]
+        return torch.stack([pool[:, :, p * page:(p + 1) * page].clone() for p in shared_pages])
+
+    before = snapshot()
+    bound_of = lambda want: 1e-4 if dtype == "float32" else 2e-2 * float(want.abs().max())
+    for name, tail in (("second", [1, 2, 3, 4, 5, 6, 7]), ("third", random_ids(2 * page + 3, config.vocab_size, 5))):
+        ids = base + tail
+        want = plain.all_logits(cfg, w, ids)
+        cache = engine.cache.open(name)
+        adopted = engine.cache.adopt_prefix(cache, ids[:-1])
+        assert adopted == 3 * page and cache.tables[0][:3] == shared_pages
+        cut = adopted + 4                        # a portion that starts right behind the shared pages
+        engine.cache.reserve(cache, cut - adopted)
+        got = [engine.step([StepEntry(cache, ids[adopted:cut], list(range(cut - adopted)))]).float().cpu()]
+        for t in ids[cut:]:                      # then token by token, beside the first request's decoding
+            engine.cache.reserve(cache, 1)
+            engine.cache.reserve(first, 1)
+            got.append(engine.step([StepEntry(cache, [t], [0]), StepEntry(first, [t], [])]).float().cpu())
+        err = float((torch.cat(got) - want[adopted:]).abs().max())
+        assert err <= bound_of(want), f"{name}: {err}"
+        assert torch.equal(snapshot(), before), f"{name} changed a shared page"
+    engine.cache.check()
+    for name in ("second", "third", "first"):
+        engine.cache.close(engine.cache.requests[name])
+    assert all(a.live == 0 for a in engine.cache.allocators)
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])

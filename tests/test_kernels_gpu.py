@@ -350,6 +350,30 @@ def test_decode_attention_splits_and_merges(nh, nkv, d, page, window):
         out.fill_(9.0)
 
 
+@pytest.mark.parametrize("nh,nkv,d", [(14, 2, 64), (28, 4, 128)])
+def test_decode_attention_with_64_rows_of_8192_keys(nh, nkv, d):
+    """The benchmark's widest decoding shape: 64 rows whose block tables hold 512 pages, most of
+    them near 8,192 keys and a few short ones between (the length of a row's pieces doubles
+    with its keys; pieces beyond a cluster's eight meet through scratch)."""
+    dtype, page = torch.bfloat16, 16
+    lengths = [8192 - 61 * i for i in range(56)] + [1, 17, 255, 256, 257, 1000, 3000, 5000]
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=31)
+    assert tables.shape[1] > 512
+    pos = [n - 1 for n in lengths]
+    q = rnd(64, nh, d, seed=32, dtype=dtype)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(d)
+    for _ in range(2):
+        ops().decode_attention(
+            q.view(64, nh * d), k_pool, v_pool, out.view(64, nh * d), tables,
+            torch.arange(64, dtype=torch.int32, device=DEV),
+            torch.tensor(pos, dtype=torch.int32, device=DEV), nh, nkv, d, page, None, scale)
+        want = attention_reference(q.float().cpu(), dense, list(range(64)), pos, nh, nkv, None, scale)
+        assert torch.isfinite(out.float()).all()
+        close_tensor_core_attention(out, want)
+        out.fill_(9.0)
+
+
 def test_decode_attention_far_key_across_splits():
     nh, nkv, d, page, n = 7, 1, 64, 16, 1500
     dtype = torch.bfloat16
@@ -513,8 +537,6 @@ def test_gemm_tcgen05(M, N, K, block_n, out_dtype):
             assert float((out.cpu() - ref).abs().max()) <= 2e-5 * float(ref.abs().max()) + 1e-6 * K
         else:
             close(out, ref, torch.bfloat16)
-    if N % 8:   # an output pitch that is not a multiple of 16 bytes is refused, not mis-stored
-        pass
     with pytest.raises(ValueError):
         o.gemm_tcgen05(rnd(M, 12, dtype=torch.bfloat16), rnd(N, 12, dtype=torch.bfloat16), None,
                        torch.empty(M, N, dtype=out_dtype, device=DEV))
@@ -1006,3 +1028,70 @@ def test_gemm_qkv_rope(M, nh, nkv, d, K):
     untouched = [i for i in range(M + 9) if i not in slot.tolist()]
     assert bool((k_pool[untouched] == 7.0).all()) and bool((v_pool[untouched] == 7.0).all())
     assert not o.gemm_qkv_rope_supported(K, 3, 1, 64, 64) and not o.gemm_qkv_rope_supported(K, nh, nkv, 48, 48)
+
+
+def test_a_wait_that_runs_out_returns_and_is_reported(monkeypatch, tmp_path):
+    """The barrier between the two products of the fused feed-forward waits for a count in
+    global memory.  Built with short limits and given a count that can never be met, every
+    block's wait runs out: the kernel must come back by itself, the host must learn of it
+    through the error word (`raise_if_error`, and through the engine: the draw that follows a
+    failed step raises), the barrier's counters must be left ready, and the next launch must
+    be right.  No copy is in flight when the wait gives up and nothing is read out of bounds:
+    the blocks only skip their second product."""
+    o = ops()
+    monkeypatch.setattr(o, "_FFN_DEFINES", ("FFN_GRID_WAIT_LIMIT=2048u", "FFN_WAIT_LIMIT=2048u"))
+    M, hidden, inner = 4, 128, 256
+    splits = o.ffn_small_m_splits(M, hidden, inner)
+    x = rnd(M, hidden, seed=1)
+    gain = 1.0 + rnd(hidden, seed=2, scale=0.1)
+    gate = rnd(inner, hidden, seed=3, dtype=torch.bfloat16, scale=0.06)
+    up = rnd(inner, hidden, seed=4, dtype=torch.bfloat16, scale=0.06)
+    down = rnd(hidden, inner, seed=5, dtype=torch.bfloat16, scale=0.04)
+    w_gu = o.interleave_gate_up(gate, up)
+    space = o.ScratchSpace()
+
+    def run():
+        x_out = torch.empty_like(x)
+        out = torch.zeros((splits, M, hidden), dtype=torch.float32, device=DEV)
+        with o.scratch_scope(space):
+            o.ffn_small_m(x, x_out, None, gain, 1e-6, w_gu, down, out)
+        torch.cuda.synchronize()
+        return out.sum(0).cpu()
+
+    o.raise_if_error()
+    good = run()
+    o.raise_if_error()                       # the short limits are long enough for a sound run
+    (act, sync), = space.ffn.values()
+    sync[0] = -1_000_000                     # the count of arrived blocks can never reach the grid's size
+    bad = run()
+    assert o.error_code() != 0
+    with pytest.raises(o.KernelError, match="ffn_small_m"):
+        o.raise_if_error("in the test")
+    assert o.error_code() == 0 and sync.tolist() == [0, 0]
+    o.ffn_small_m_check()                    # the library's own flag was cleared with the word
+    assert not torch.equal(bad, good)        # the failed launch did not produce the result...
+    assert torch.equal(run(), good)          # ...and the one after it does
+    o.raise_if_error()
+
+    # the same through an engine: the step runs to its end, reading its ids raises
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    config = tb.Qwen2Config.from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=2, hidden_size=128,
+        num_attention_heads=2, num_key_value_heads=1, intermediate_size=256, vocab_size=320,
+        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=256,
+        use_sliding_window=False, sliding_window=64, max_window_layers=2))
+    tb.write_random_model(str(tmp_path), config, seed=5)
+    engine = tb.engine_for(tb.load_model(str(tmp_path), dtype="bfloat16"), 128, 16, max_requests=2)
+    cache = engine.cache.open("x")
+    engine.cache.reserve(cache, 3)
+    first = engine.step([StepEntry(cache, [5], [0])]).clone()
+    assert engine.sample(first, [0.0], [1.0], [0.0])
+    (act, sync), = engine.model.scratch.ffn.values()
+    sync[0] = -1_000_000
+    logits = engine.step([StepEntry(cache, [6], [0])])
+    with pytest.raises(o.KernelError, match="ffn_small_m"):
+        engine.sample(logits, [0.0], [1.0], [0.0])
+    engine.check()                           # reported once; the engine goes on
+    after = engine.step([StepEntry(cache, [7], [0])])
+    assert engine.sample(after, [0.0], [1.0], [0.0]) and bool(torch.isfinite(after).all())

@@ -10,6 +10,20 @@ from tiny import TINY, random_ids
 from tokenizer_b200 import write_random_model
 
 
+def test_mask_matrix_is_the_rule_entry_by_entry():
+    for seq, window in ((1, None), (7, None), (9, 3), (12, 0), (6, 100)):
+        rule = torch.tensor([[plain.mask_value(q, k, window) for k in range(seq)] for q in range(seq)])
+        assert torch.equal(plain.attention_mask(seq, window), rule)
+
+
+def test_logits_of_chosen_rows_are_rows_of_all_logits(tmp_path):
+    folder = write_random_model(str(tmp_path / "m"), TINY["a"]()[0], 3)
+    cfg, w = plain.load_folder(folder)
+    ids = [3, 1, 4, 1, 5, 9, 2, 6]
+    full = plain.all_logits(cfg, w, ids)
+    assert torch.equal(plain.all_logits(cfg, w, ids, rows=[0, 5, 7]), full[[0, 5, 7]])
+
+
 def test_mask_truth_table():
     # model.rs:1389-1399
     inf = -math.inf

@@ -85,10 +85,8 @@ def test_prompt_and_decoding_at_real_widths(tmp_path_factory, widths):
               f"eight decoded together, step {step}")
     # the same eight through steps that stay on the device: ids must be those of the plain argmax
     # where it leads clearly
-    first = [int(want[n + 3].argmax()) for n in lengths]
     drawn = engine.decode_steps([StepEntry(c, [ids[n + 4]]) for c, n in zip(caches, lengths)], 1)
     top2 = torch.topk(want[[n + 4 for n in lengths]], 2, dim=-1).values
     for i, n in enumerate(lengths):
         if float(top2[i, 0] - top2[i, 1]) > 2 * bound:
             assert drawn[0][i] == int(want[n + 4].argmax())
-    assert len(first) == 8

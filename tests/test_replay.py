@@ -59,3 +59,40 @@ def test_mixed_with_page_reuse(model, dtype, tmp_path):
     got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), peak, page))
     assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
     ru.compare(got, want, dtype, "mixed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_with_shared_pages(model, dtype, tmp_path):
+    """As above, and two of the requests begin with the first tokens of another that is still
+    running: they take its published pages over instead of computing them, while pages of
+    ended requests are used again around them.  The logits behind the shared pages must be
+    what the plain implementation gives for the whole sequence."""
+    folder, config, page, requests, want = model
+    if config.use_sliding_window:
+        pytest.skip("a cache with a windowed group shares no pages")
+    names = sorted(requests)
+    donor = max(names, key=lambda n: len(requests[n]))
+    shared = (len(requests[donor]) * 2 // 3) // page * page
+    assert shared >= 2 * page
+    requests = dict(requests)
+    extra = {}
+    for k, n_shared in enumerate((shared, shared - page)):
+        tail = random_ids(23 + 9 * k, config.vocab_size, 900 + k)
+        extra[f"s{k}"] = requests[donor][:n_shared] + tail
+    # the donor first, then one other, then the two sharers, then the rest
+    others = [n for n in names if n != donor]
+    ordered = {donor: requests[donor], others[0]: requests[others[0]]}
+    ordered.update(extra)
+    ordered.update({n: requests[n] for n in others[1:]})
+    share = {"s0": (donor, shared), "s1": (donor, shared - page)}
+    want = dict(want)
+    want.update(ru.reference_logits(folder, extra))
+    steps, peak, expect = ru.steps_mixed(ordered, max_live=4, share=share, page=page)
+    assert all(n >= 2 * page or n == shared - page for n in expect.values()) and min(expect.values()) >= page
+    adopted = {}
+    got = ru.collect(steps, ru.run_trace(folder, dtype, steps, str(tmp_path), peak, page,
+                                         share=True, adopted=adopted))
+    assert adopted == expect, f"pages were not shared as planned: {adopted} vs {expect}"
+    for name, ids in ordered.items():
+        assert len(got[name]) == len(ids) - expect.get(name, 0)
+    ru.compare(got, want, dtype, "mixed with shared pages")

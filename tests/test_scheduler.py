@@ -281,3 +281,24 @@ def test_random_arrivals_and_ends_in_every_mode(seed):
             got = s.finished[rid]
             assert got.tokens == w.tokens and got.reason == w.reason, (mode, rid)
             assert got.completion_tokens == w.completion_tokens
+
+
+def test_a_batch_larger_than_the_request_slots_is_refused():
+    with pytest.raises(ValueError, match="request slots"):
+        Scheduler(FakeEngine(num_pages=64, max_requests=2), max_batch_size=3)
+
+
+def test_the_head_waits_while_every_request_slot_is_held_elsewhere():
+    """Slots held outside the scheduler (another user of the same cache): the head of the line
+    waits instead of the iteration failing, and runs once a slot is free."""
+    engine = FakeEngine(num_pages=64, max_requests=2)
+    held = [engine.cache.open(("outside", i)) for i in range(2)]
+    s = Scheduler(engine, max_batch_size=2, token_budget=64)
+    prompt, params = random_ids(5, 50, 3), GenerateParams(max_tokens=4)
+    rid = s.add_request(prompt, params)
+    assert s.step() == [] and not s.running and len(s.waiting) == 1
+    engine.cache.close(held[0])
+    out = s.run()
+    assert out[rid].tokens == solo(prompt, params).tokens
+    engine.cache.close(held[1])
+    engine.cache.check()

@@ -71,15 +71,15 @@ def test_nfc_and_digits():
     (lambda r: r["normalizer"].update(type="NFKC"), "NFC"),
     (lambda r: r["pre_tokenizer"].update(type="ByteLevel"), "Sequence"),
     (lambda r: r["pre_tokenizer"]["pretokenizers"][0].update(behavior="Removed"), "Isolated"),
-    (lambda r: r["pre_tokenizer"]["pretokenizers"][0].update(invert=True), "invert"),
+    (lambda r: r["pre_tokenizer"]["pretokenizers"][0].update(invert=True), "inverted"),
     (lambda r: r["pre_tokenizer"]["pretokenizers"][1].update(use_regex=True), "use_regex"),
     (lambda r: r["model"].update(type="WordPiece"), "BPE"),
-    (lambda r: r["model"]["vocab"].pop("A"), "missing single-byte token 65"),
-    (lambda r: r["model"]["merges"].append("q q"), "concatenation"),
-    (lambda r: r["model"]["merges"].append("hello"), "two bytes_to_unicode"),
-    (lambda r: r["added_tokens"][0].update(normalized=True), "normalized"),
-    (lambda r: r["added_tokens"][0].update(id=65), "already belongs"),
-    (lambda r: r["model"]["vocab"].update({"中": 999}), "bytes_to_unicode scalar"),
+    (lambda r: r["model"]["vocab"].pop("A"), "no token for the single byte 65"),
+    (lambda r: r["model"]["merges"].append("q q"), "produces bytes the vocab does not hold"),
+    (lambda r: r["model"]["merges"].append("hello"), "not a pair of tokens"),
+    (lambda r: r["added_tokens"][0].update(normalized=True), "normalization"),
+    (lambda r: r["added_tokens"][0].update(id=65), "taken by a vocab token"),
+    (lambda r: r["model"]["vocab"].update({"中": 999}), "stands for no byte"),
 ])
 def test_the_file_must_say_what_the_reader_does(change, message):
     raw = json.loads(json.dumps(synthetic()))
@@ -92,10 +92,20 @@ def test_command_line_options():
     args = parse_args(["--max-tokens", "5", "--temperature", "0.7", "--top-p", "0.9", "--seed", "3",
                        "--stop", "a", "--stop", "b", "The capital"])
     assert (args["max_tokens"], args["temperature"], args["top_p"], args["seed"]) == (5, 0.7, 0.9, 3)
-    assert args["stop"] == ["a", "b"] and args["prompt"] == "The capital"
+    assert args["stop"] == ["a", "b"] and args["prompts"] == ["The capital"]
     d = parse_args(["x"])
     assert (d["max_tokens"], d["temperature"], d["top_p"], d["seed"], d["stop"]) == (20, 0.0, 1.0, 0, [])
-    assert parse_args(["--ids", "1,2,3"])["ids"] == [1, 2, 3]
-    for bad in (["--nope"], ["a", "b"], ["--max-tokens"], ["--max-tokens", "x", "p"]):
+    assert parse_args(["--ids", "1,2,3"])["ids"] == [[1, 2, 3]]
+    assert (d["num_pages"], d["page_size"], d["max_batch_size"], d["token_budget"]) == (None, 16, 8, 2048)
+    # several prompts, and the sizes of the cache and of the scheduler (under either name)
+    many = parse_args(["--ids", "1,2", "--ids", "3", "--num-pages", "7", "--page-size", "8",
+                       "--max-batch-size", "2", "--token-budget", "24"])
+    assert many["ids"] == [[1, 2], [3]]
+    assert (many["num_pages"], many["page_size"], many["max_batch_size"], many["token_budget"]) == (7, 8, 2, 24)
+    alias = parse_args(["--num-blocks", "9", "--block-size", "4", "--prefill-chunk", "5", "a", "b"])
+    assert (alias["num_pages"], alias["page_size"], alias["token_budget"]) == (9, 4, 5)
+    assert alias["prompts"] == ["a", "b"]
+    for bad in (["--nope"], ["a", "--ids", "1"], ["--max-tokens"], ["--max-tokens", "x", "p"],
+                ["--num-pages", "0", "p"], ["--page-size", "x", "p"]):
         with pytest.raises(UsageError):
             parse_args(bad)

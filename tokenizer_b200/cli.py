@@ -2,7 +2,16 @@
 (qwen-infer/src/main.rs:12-148): the same options with the same meanings and
 defaults, text on standard output, ids and timings on standard error.  The
 model comes from a local folder; a prompt is text when the folder has a
-tokenizer.json, or ids with --ids."""
+tokenizer.json, or ids with --ids.
+
+Beyond the reference's options: several prompts (positional arguments or `--ids` given more
+than once) run together through the scheduler, and the scheduler's and the cache's sizes can
+be set: --num-pages N (pages of the cache; default: room for every prompt to its end),
+--page-size N (tokens a page, default 16), --max-batch-size N (requests that run together,
+default 8 as the reference's server: qwen-server/src/lib.rs:47-55), --token-budget N (tokens a
+step may run: prompts are cut into portions under it; default 2048).  --num-blocks,
+--block-size and --prefill-chunk are other names for the first, second and fourth.  With a
+small --num-pages requests are preempted and recomputed; the ids do not change."""
 from __future__ import annotations
 
 import os
@@ -12,7 +21,8 @@ import time
 
 USAGE = ("usage: qwen-infer [--max-tokens N] [--temperature T] [--top-p P] [--seed N] "
          "[--stop STRING]... [--model DIR | --random-weights CONFIG.json] [--dtype bfloat16|float32] "
-         "[--ids 1,2,3 | <prompt>]")
+         "[--num-pages N] [--page-size N] [--max-batch-size N] [--token-budget N] "
+         "[--ids 1,2,3]... [<prompt>]...")
 
 
 class UsageError(Exception):
@@ -20,9 +30,10 @@ class UsageError(Exception):
 
 
 def parse_args(argv):
-    args = dict(prompt=None, ids=None, max_tokens=20, temperature=0.0, top_p=1.0, seed=0, stop=[],
+    args = dict(prompts=[], ids=[], max_tokens=20, temperature=0.0, top_p=1.0, seed=0, stop=[],
                 model=os.environ.get("QWEN_INFER_MODEL"), random_weights=None, dtype="bfloat16",
-                weights_seed=0, device="cuda:0")
+                weights_seed=0, device="cuda:0", num_pages=None, page_size=16, max_batch_size=8,
+                token_budget=2048)
     it = iter(argv)
 
     def value(flag):
@@ -55,14 +66,29 @@ def parse_args(argv):
         elif arg == "--device":
             args["device"] = value(arg)
         elif arg == "--ids":
-            args["ids"] = [_number(int, v, arg) for v in value(arg).split(",") if v.strip()]
+            args["ids"].append([_number(int, v, arg) for v in value(arg).split(",") if v.strip()])
+        elif arg in ("--num-pages", "--num-blocks"):
+            args["num_pages"] = _positive(value(arg), arg)
+        elif arg in ("--page-size", "--block-size"):
+            args["page_size"] = _positive(value(arg), arg)
+        elif arg == "--max-batch-size":
+            args["max_batch_size"] = _positive(value(arg), arg)
+        elif arg in ("--token-budget", "--prefill-chunk"):
+            args["token_budget"] = _positive(value(arg), arg)
         elif arg.startswith("-") and arg != "-":
             raise UsageError(f"unknown argument {arg}")
         else:
-            if args["prompt"] is not None:
-                raise UsageError(f"only one prompt is accepted (got {arg!r} as well)")
-            args["prompt"] = arg
+            args["prompts"].append(arg)
+    if args["prompts"] and args["ids"]:
+        raise UsageError("prompts come as text or as --ids, not both")
     return args
+
+
+def _positive(text, flag):
+    n = _number(int, text, flag)
+    if n < 1:
+        raise UsageError(f"{flag} {text}: must be at least 1")
+    return n
 
 
 def _number(kind, text, flag):
@@ -82,7 +108,7 @@ def main(argv=None) -> int:
     if args.get("help"):
         print(USAGE, file=sys.stderr)
         return 0
-    if (args["prompt"] is None) == (args["ids"] is None):
+    if not args["prompts"] and not args["ids"]:
         print(USAGE, file=sys.stderr)
         return 1
 
@@ -107,29 +133,43 @@ def main(argv=None) -> int:
     tokenizer_path = os.path.join(folder, "tokenizer.json")
     if os.path.exists(tokenizer_path):
         tokenizer = ByteLevelBPE.from_file(tokenizer_path)
-    if args["ids"] is not None:
-        prompt_ids = args["ids"]
+    if args["ids"]:
+        prompts = args["ids"]
     elif tokenizer is None:
         print(f"{folder} has no tokenizer.json: give the prompt as --ids 1,2,3", file=sys.stderr)
         return 1
     else:
-        prompt_ids = tokenizer.encode(args["prompt"])
-    if not prompt_ids:
+        prompts = [tokenizer.encode(text) for text in args["prompts"]]
+    if any(not ids for ids in prompts):
         print("prompt encoded to no tokens", file=sys.stderr)
         return 1
-    print(f"prompt ids ({len(prompt_ids)}): {prompt_ids}", file=sys.stderr)
+    several = len(prompts) > 1
+    for index, ids in enumerate(prompts):
+        label = f"prompt {index} ids" if several else "prompt ids"
+        print(f"{label} ({len(ids)}): {ids}", file=sys.stderr)
 
     params = tb.GenerateParams(max_tokens=args["max_tokens"], temperature=args["temperature"],
                                top_p=args["top_p"], seed=args["seed"],
                                eos=tb.load_eos_token_ids(folder), stop=args["stop"])
     print(f"max_tokens {params.max_tokens} temperature {params.temperature} top_p {params.top_p} "
           f"seed {params.seed} eos {list(params.eos)}", file=sys.stderr)
+    scheduler = None
     try:
         params.validate()
         model = tb.load_model(folder, dtype=args["dtype"], device=args["device"])
+        page = args["page_size"]
+        pages = args["num_pages"]
+        if pages is None:
+            pages = sum(-(-(len(ids) + params.max_tokens + 1) // page) for ids in prompts)
+        batch = min(args["max_batch_size"], len(prompts))
+        engine = tb.Engine(model, num_pages=pages, page_size=page, max_requests=batch,
+                           share_prefixes=True)
         started = time.perf_counter()
         token_bytes = (lambda t: tokenizer.decode_bytes([t])) if tokenizer else None
-        generated = tb.generate(model, prompt_ids, params, token_bytes)
+        scheduler = tb.Scheduler(engine, max_batch_size=batch, token_budget=args["token_budget"])
+        ids = [scheduler.add_request(p, params, token_bytes) for p in prompts]
+        finished = scheduler.run()
+        results = [finished[i] for i in ids]
         elapsed = time.perf_counter() - started
     except (ValueError, RuntimeError) as err:
         print(f"error: {err}", file=sys.stderr)
@@ -137,20 +177,33 @@ def main(argv=None) -> int:
     finally:
         if scratch is not None:
             scratch.cleanup()
-    print(generated.text if tokenizer else " ".join(str(t) for t in generated.tokens))
-    print(f"generated ids: {generated.tokens}", file=sys.stderr)
-    print(f"stop: {generated.reason.name}", file=sys.stderr)
-    n = len(generated.tokens)
-    if n == 0 or generated.decode == 0.0:
-        print(f"prefill {generated.prefill:.4f} s, decode {generated.decode:.4f} s, {n} tokens "
-              f"(KV cache, total {elapsed:.4f} s)", file=sys.stderr)
-    else:
-        print(f"prefill {generated.prefill:.4f} s, decode {generated.decode:.4f} s, "
-              f"{n / generated.decode:.4f} tok/s ({n} tokens, KV cache, total {elapsed:.4f} s)",
-              file=sys.stderr)
-    if generated.reason == tb.StopReason.EOS:
-        print("stopped on eos before max_tokens", file=sys.stderr)
-    return 0
+    status = 0
+    for index, generated in enumerate(results):
+        tag = f"[{index}] " if several else ""
+        if generated.reason == tb.StopReason.FAILED:
+            print(f"{tag}error: {generated.error}", file=sys.stderr)
+            print("")
+            status = 1
+            continue
+        print(generated.text if tokenizer else " ".join(str(t) for t in generated.tokens))
+        print(f"{tag}generated ids: {generated.tokens}", file=sys.stderr)
+        print(f"{tag}stop: {generated.reason.name}", file=sys.stderr)
+        n = len(generated.tokens)
+        if n == 0 or generated.decode == 0.0:
+            print(f"{tag}prefill {generated.prefill:.4f} s, decode {generated.decode:.4f} s, {n} tokens "
+                  f"(KV cache, total {elapsed:.4f} s)", file=sys.stderr)
+        else:
+            print(f"{tag}prefill {generated.prefill:.4f} s, decode {generated.decode:.4f} s, "
+                  f"{n / generated.decode:.4f} tok/s ({n} tokens, KV cache, total {elapsed:.4f} s)",
+                  file=sys.stderr)
+        if generated.reason == tb.StopReason.EOS:
+            print(f"{tag}stopped on eos before max_tokens", file=sys.stderr)
+    if several or args["num_pages"] is not None:
+        stats = scheduler.stats
+        print(f"scheduler: {stats.steps} steps, most running {stats.max_running}, preemptions "
+              f"{stats.preemptions}, most pages held {stats.peak_pages} of {pages}, shared prefix "
+              f"tokens {stats.shared_prefix_tokens}", file=sys.stderr)
+    return status
 
 
 if __name__ == "__main__":

@@ -80,6 +80,7 @@ __device__ __forceinline__ bool fa_mbar_wait(unsigned long long* bar, unsigned p
     if (done) return true;
   }
   atomicExch(&fa_error_flag, 1);
+  tokb200_report_error(TOKB200_LIB_ATTENTION_TCGEN05, 1);
   return false;
 }
 __device__ __forceinline__ void fa_cp16(void* dst, const void* src, bool ok) {
@@ -224,7 +225,10 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int r_id = row_req[row0];
   // uniform over the block; a misaligned base (never seen) is reported instead of used
   const bool aligned = (fa_smem(fa_raw) & 1023u) == 0;
-  if (!aligned && threadIdx.x == 0) atomicExch(&fa_error_flag, 2);
+  if (!aligned && threadIdx.x == 0) {
+    atomicExch(&fa_error_flag, 2);
+    tokb200_report_error(TOKB200_LIB_ATTENTION_TCGEN05, 2);
+  }
   const bool live = aligned && tile < n_tiles && r_id >= 0 && n_rows > 0;
   const int kvh = h / (nh / nkv);
   const int pos0 = live ? pos[row0] : 0;

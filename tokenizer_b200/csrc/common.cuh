@@ -26,6 +26,50 @@ static inline int tokb200_launch_status() {
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
 
+// ---- one error word for all libraries ------------------------------------------
+// Every wait on the device is bounded.  A wait that gives up sets its library's own flag
+// (read and cleared by that library's `..._error()` function) AND stores a non-zero code in
+// one word of mapped pinned host memory that all libraries of a process share: the host
+// hands each library the word's device address once, after loading it
+// (`tokb200_set_error_word`), and reads the word without any CUDA call wherever it has
+// just synchronised with the device (after it read a step's ids or logits).  The code is
+// library * 16 + reason; a later code may overwrite an earlier one, the flags keep both.
+enum : int {
+  TOKB200_LIB_GEMM_TCGEN05 = 1,
+  TOKB200_LIB_ATTENTION_TCGEN05 = 2,
+  TOKB200_LIB_FFN_SMALL_M = 3,
+  TOKB200_LIB_LINEAR_STREAM = 4,
+  TOKB200_LIB_ATTENTION_LAYER = 5,
+};
+__device__ int* tokb200_error_word = nullptr;
+
+__device__ __forceinline__ void tokb200_report_error(int library, int reason) {
+  int* word = tokb200_error_word;
+  if (word != nullptr) {
+    *reinterpret_cast<volatile int*>(word) = library * 16 + reason;
+    __threadfence_system();
+  }
+}
+
+// `device_pointer`: the device-side address of the shared word (or null to detach).  A
+// synchronous copy: call it outside stream capture.
+TOKB200_API int tokb200_set_error_word(int* device_pointer) {
+  cudaError_t err = cudaMemcpyToSymbol(tokb200_error_word, &device_pointer, sizeof(int*));
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
+}
+
+// One int of mapped pinned host memory, zeroed: its host and device addresses.
+TOKB200_API int tokb200_error_word_alloc(int** host_pointer, int** device_pointer) {
+  int* host = nullptr;
+  cudaError_t err = cudaHostAlloc((void**)&host, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (err != cudaSuccess) return (int)err;
+  *host = 0;
+  err = cudaHostGetDevicePointer((void**)device_pointer, host, 0);
+  if (err != cudaSuccess) return (int)err;
+  *host_pointer = host;
+  return TOKB200_OK;
+}
+
 // ---- programmatic dependent launch -------------------------------------------
 // The step's kernels are launched with the attribute below: a kernel may start
 // while its predecessor in the stream still runs, so that its launch and its

@@ -689,7 +689,10 @@ __global__ void advance_decode_kernel(int* __restrict__ ids, const int* __restri
     pos[r] = p;
     kv_len[r] += 1;
     for (int g = 0; g < groups.count; ++g) {
-      const int pg = groups.tables[g][(size_t)r * groups.widths[g] + p / page];
+      // after the last step of a burst the next position may lie one block past the row's
+      // table (a length of exactly width * page): nothing will be written there
+      const int block = p / page;
+      const int pg = block < groups.widths[g] ? groups.tables[g][(size_t)r * groups.widths[g] + block] : -1;
       groups.slots[g][r] = pg < 0 ? -1 : pg * page + p % page;
     }
   }

@@ -37,8 +37,13 @@
 #define FFN_ROW_PITCH (FFN_KC * 2 + 64)      // bytes between a stage's rows: 64 mod 128, so that
                                              // 16-byte reads of 8 rows x 4 pieces miss each other's banks
 #define FFN_STAGE_BYTES (16 * FFN_ROW_PITCH)
+// the bounds of the waits; a test build makes them small so that a wait that nothing ends runs out quickly
+#ifndef FFN_WAIT_LIMIT
 #define FFN_WAIT_LIMIT (1u << 16)            // polls of up to 20 us
+#endif
+#ifndef FFN_GRID_WAIT_LIMIT
 #define FFN_GRID_WAIT_LIMIT (1u << 22)
+#endif
 
 __device__ int ffn_error_flag = 0;
 
@@ -66,6 +71,7 @@ __device__ __forceinline__ bool ffn_mbar_wait(unsigned long long* bar, unsigned 
     if (done) return true;
   }
   atomicExch(&ffn_error_flag, 1);
+  tokb200_report_error(TOKB200_LIB_FFN_SMALL_M, 1);
   return false;
 }
 __device__ __forceinline__ void ffn_bulk_copy(void* dst, const void* src, unsigned bytes,
@@ -363,6 +369,7 @@ ffn_small_m_kernel(const FfnParams p) {
     }
     if (!met) {
       atomicExch(&ffn_error_flag, 2);
+      tokb200_report_error(TOKB200_LIB_FFN_SMALL_M, 2);
       grid_ok = 0;
     }
     __threadfence();

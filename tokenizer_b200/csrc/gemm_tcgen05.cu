@@ -59,6 +59,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     if (done) return true;
   }
   atomicExch(&tc_error_flag, 1);
+  tokb200_report_error(TOKB200_LIB_GEMM_TCGEN05, 1);
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar,
@@ -334,6 +335,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(unsigned long long* bar, unsig
     if (done) return true;
   }
   atomicExch(&tc_error_flag, 2);
+  tokb200_report_error(TOKB200_LIB_GEMM_TCGEN05, 2);
   return false;
 }
 

@@ -46,6 +46,7 @@ __device__ __forceinline__ bool ls_mbar_wait(unsigned long long* bar, unsigned p
     if (done) return true;
   }
   atomicExch(&ls_error_flag, 1);
+  tokb200_report_error(TOKB200_LIB_LINEAR_STREAM, 1);
   return false;
 }
 __device__ __forceinline__ void ls_bulk_copy(void* dst, const void* src, unsigned bytes,

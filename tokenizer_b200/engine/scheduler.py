@@ -87,6 +87,9 @@ class Scheduler:
         self.decode_burst = decode_burst if hasattr(engine, "decode_steps") else 1
         self.engine = engine
         self.cache = engine.cache
+        if max_batch_size > self.cache.max_requests:
+            raise ValueError(f"a batch of {max_batch_size} requests needs as many request slots; "
+                             f"the cache has {self.cache.max_requests}")
         self.max_batch_size = max_batch_size
         self.token_budget = token_budget
         self.waiting: Deque[_Request] = deque()
@@ -260,7 +263,10 @@ class Scheduler:
                 self._fail(head, f"the cache has {self.cache.num_pages} pages of "
                                  f"{self.cache.page_size}; this request needs {self._context_pages(head)}")
                 continue
-            cache = self.cache.open(head.id)
+            try:
+                cache = self.cache.open(head.id)
+            except OutOfPages:
+                break                    # every request slot is held (some outside this scheduler): wait
             adopted = self.cache.adopt_prefix(cache, head.context[:-1])
             if not self.cache.can_reserve(cache, len(head.context) - cache.length):
                 self.cache.close(cache)

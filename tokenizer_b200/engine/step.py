@@ -16,6 +16,7 @@ import torch
 
 from ..cache.device import DeviceCache
 from ..config.registry import load_config
+from ..kernels import ops
 from ..kernels.ops import KernelError
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
@@ -86,9 +87,22 @@ class Engine:
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
         return cls(load_model(folder, dtype, device), **kw)
 
+    def check(self) -> None:
+        """Raise `KernelError` if a bounded wait inside a kernel ran out since the last check
+        (the kernel then ran on without its data and what the steps since wrote is wrong).
+        It reads one word of host memory; it is meaningful for the work the host has already
+        waited for, so callers that read logits or ids themselves call it after that read.
+        `step`, `decode_steps`, the prepared steps and the sampler's `result()` call it."""
+        ops.raise_if_error()
+
     def step(self, entries: List[StepEntry]) -> torch.Tensor:
         """Run one batch; returns logits [wanted, vocab] float32 on the device,
-        in the order of the entries and of their `want`."""
+        in the order of the entries and of their `want`.
+
+        The logits are valid until the engine's next step: a step replayed from a captured
+        graph returns a view of that graph's output buffer, which the next replay of the same
+        shape overwrites.  A caller that keeps logits across steps clones them."""
+        self.check()
         if not entries:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32,
                                device=self.runtime.device)
@@ -225,14 +239,27 @@ class Engine:
 
             def iteration():
                 logits = self.model.forward(ctx, self.bindings, want_rows)
-                ops.sample(logits, None, None, None, slot["drawn"])
+                with ops.scratch_scope(self.sampler.scratch):
+                    ops.sample(logits, None, None, None, slot["drawn"])
                 ops.advance_decode(ctx.ids, slot["drawn"], ctx.pos, ctx.kv_len, ctx.row_req,
                                    [g.slots for g in ctx.groups],
                                    [g.block_table for g in ctx.groups], self.cache.page_size,
                                    slot["history"], slot["counter"])
+                # a mixer that keeps more than keys and values between steps moves it on here
+                for call, binding in zip(self.model.order, self.bindings):
+                    advance = getattr(self.model.blocks[call.layer].mixer, "advance_decode", None)
+                    if advance is not None:
+                        advance(ctx, binding)
 
             done = 0
-            if "graph" not in slot:
+            if not self.use_graphs:
+                # a part whose launches depend on host-side values cannot be replayed: every
+                # step is launched anew (still without a visit to the host for the ids)
+                for _ in range(n_steps):
+                    iteration()
+                    ctx.kv_lens = [n + 1 for n in ctx.kv_lens]      # the host's copies follow
+                done = n_steps
+            elif "graph" not in slot:
                 iteration()              # plainly once: compiles and warms
                 done = 1
                 if n_steps > 1:
@@ -248,6 +275,7 @@ class Engine:
                 slot["graph"].replay()
                 counter.launches += slot["launches"]
             history = slot["history"][:n_steps * rows].view(n_steps, rows)[:, :len(entries)].tolist()
+        self.check()
         for e in entries:
             self.cache.commit(e.cache, n_steps)
         self.steps_run += n_steps
@@ -287,6 +315,7 @@ class Engine:
         with its drawn id has then run one token too many, which nobody reads.  None when the
         step cannot be used as packed."""
         from ..kernels.ops import counter
+        self.check()
         ids = getattr(pending, "device_ids", None)
         slot = self._graphs.get(prepared.key)
         if ids is None or ids.numel() != len(prepared.entries) or ids.dtype != torch.int32 or \
@@ -308,6 +337,7 @@ class Engine:
         """Run a step packed by `prepare_decode` with the tokens now known.  None when it can
         no longer be used as packed (a cache moved on, the graph is gone): run `step` instead."""
         from ..kernels.ops import counter
+        self.check()
         slot = self._graphs.get(prepared.key)
         if slot is None or "graph" not in slot or self._graph_buffer != self.builder.device_buffer_ptr() or \
                 len(tokens) != len(prepared.entries) or \

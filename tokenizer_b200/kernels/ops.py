@@ -92,8 +92,112 @@ class bound_stream:
 _i, _f, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
 
+class ScratchSpace:
+    """Device memory that kernels use beyond their inputs and outputs: the pieces and counters
+    of the decode attention, the activation and barrier counters of the fused feed-forward,
+    the partial results of the greedy choice.  Counters are zero between launches, and two
+    launches that overlap on the device must not share them, so a space belongs to ONE order
+    of launches: a model (its forward runs on one stream) and a sampler each own theirs
+    (`scratch_scope`), and die with them.  Launches outside any scope (kernel tests) share
+    the module's default space, on one stream.  Buffers are made at a shape's first use,
+    which is never inside a captured graph: a shape's first step runs plainly."""
+
+    def __init__(self):
+        self.decode, self.ffn, self.argmax = {}, {}, {}
+
+
+_default_space = ScratchSpace()
+_space = _default_space
+
+
+class scratch_scope:
+    """Within the block, kernels take their scratch from `space`."""
+
+    def __init__(self, space: ScratchSpace):
+        self.space = space
+
+    def __enter__(self):
+        global _space
+        self._outer = _space
+        _space = self.space
+        return self
+
+    def __exit__(self, *exc):
+        global _space
+        _space = self._outer
+        return False
+
+
+# ---- the error word ----------------------------------------------------------------
+# A wait on the device that runs out does not hang: the kernel sets its library's flag, stores a
+# code in one word of mapped pinned host memory and runs to its end WITHOUT the data it waited
+# for, so what it wrote is wrong.  Every library gets the word's device address when it is
+# loaded; the host reads the word (plain memory, no CUDA call) wherever it has just
+# synchronised with the device, and raises.
+_LIBRARY_NAMES = {1: "gemm_tcgen05", 2: "attention_tcgen05", 3: "ffn_small_m", 4: "linear_stream",
+                  5: "attention_layer"}
+_REASONS = {1: "a wait on a shared-memory barrier ran out", 2: "a wait between blocks ran out"}
+_error_word = None          # (ctypes int at the host address, device address)
+_registered = {}            # id(library handle) -> handle: libraries that know the word
+
+
+def _error_word_pointers():
+    global _error_word
+    if _error_word is None:
+        lib = load_library("elementwise.cu")
+        host, dev = ctypes.c_void_p(0), ctypes.c_void_p(0)
+        status = lib.tokb200_error_word_alloc(ctypes.byref(host), ctypes.byref(dev))
+        if status != 0 or not host.value:
+            raise KernelError(f"the error word could not be allocated (CUDA error {status})")
+        _error_word = (ctypes.c_int.from_address(host.value), dev.value)
+    return _error_word
+
+
+def _load(source: str, defines=()):
+    """Load (compile at first use) a library and hand it the error word."""
+    lib = load_library(source, defines=defines)
+    if id(lib) not in _registered:
+        _, dev = _error_word_pointers()
+        status = lib.tokb200_set_error_word(ctypes.c_void_p(dev))
+        if status != 0:
+            raise KernelError(f"{source}: the error word could not be set (CUDA error {status})")
+        _registered[id(lib)] = lib
+    return lib
+
+
 def _lib(name):
-    return load_library(name + ".cu")
+    return _load(name + ".cu")
+
+
+def error_code() -> int:
+    """The word as it stands (0: no bounded wait has run out); meaningful once the device has
+    finished the work in question."""
+    return 0 if _error_word is None else int(_error_word[0].value)
+
+
+def raise_if_error(where: str = "") -> None:
+    """Raise KernelError if a bounded wait on the device ran out since the last check.  The
+    word and the libraries' flags are cleared, so the next step starts clean.  Costs a read of
+    host memory when nothing happened; call it after a synchronisation with the device."""
+    code = error_code()
+    if code == 0:
+        return
+    _error_word[0].value = 0
+    library, reason = _LIBRARY_NAMES.get(code // 16, f"library {code // 16}"), code % 16
+    if reason == 2 and code // 16 == 2:
+        text = "a shared-memory base was not aligned as the kernel needs"
+    else:
+        text = _REASONS.get(reason, f"reason {reason}")
+    for lib in _registered.values():          # clear the per-library flags too
+        for name in ("tokb200_gemm_tcgen05_error", "tokb200_attention_tcgen05_error",
+                     "tokb200_ffn_small_m_error", "tokb200_linear_stream_error",
+                     "tokb200_attention_layer_error"):
+            try:
+                getattr(lib, name)()
+            except AttributeError:
+                pass
+    raise KernelError(f"{library}: {text}{' (' + where + ')' if where else ''}; the results of the "
+                      f"steps since the last check are not valid")
 
 
 # --------------------------------------------------------------------------- #
@@ -252,7 +356,6 @@ def advance_decode(ids, drawn, pos, kv_len, row_req, slots, tables, page, histor
 
 
 DECODE_MAX_GROUP = 16
-_decode_scratch = {}
 
 
 def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
@@ -269,15 +372,15 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         raise ValueError("decode_attention is the bfloat16 kernel")
     if not decode_attention_supported(nh, nkv, d):
         raise ValueError(f"decode_attention: {nh} heads over {nkv} groups of size {d} is not taken")
-    lib = load_library("attention_decode.cu", defines=(f"HEAD_DIM={d}",))
+    lib = _load("attention_decode.cu", defines=(f"HEAD_DIM={d}",))
     n_rows = q.shape[0]
     key = (q.device.index, n_rows, nh, nkv, d)
-    if key not in _decode_scratch:
+    if key not in _space.decode:
         lib.tokb200_decode_attention_scratch_floats.restype = ctypes.c_longlong
         floats = lib.tokb200_decode_attention_scratch_floats(_i(n_rows), _i(nh))
-        _decode_scratch[key] = (torch.empty(floats, dtype=torch.float32, device=q.device),
-                                torch.zeros(n_rows * nkv, dtype=torch.int32, device=q.device))
-    scratch, counters = _decode_scratch[key]
+        _space.decode[key] = (torch.empty(floats, dtype=torch.float32, device=q.device),
+                              torch.zeros(n_rows * nkv, dtype=torch.int32, device=q.device))
+    scratch, counters = _space.decode[key]
     _check(lib.tokb200_decode_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
@@ -322,7 +425,12 @@ def linear_stream_check() -> None:
 
 
 _ffn_plans = {}
-_ffn_scratch = {}
+# compile-time switches of the fused feed-forward's library (a test builds it with short wait limits)
+_FFN_DEFINES = ()
+
+
+def _ffn_lib():
+    return _load("ffn_small_m.cu", defines=_FFN_DEFINES)
 
 
 def ffn_small_m_splits(M: int, hidden: int, inner: int) -> int:
@@ -333,7 +441,7 @@ def ffn_small_m_splits(M: int, hidden: int, inner: int) -> int:
     if M < 1 or M > 16:
         return 0
     if key not in _ffn_plans:
-        _ffn_plans[key] = int(_lib("ffn_small_m").tokb200_ffn_small_m_splits(_i(M), _i(hidden), _i(inner)))
+        _ffn_plans[key] = int(_ffn_lib().tokb200_ffn_small_m_splits(_i(M), _i(hidden), _i(inner)))
     return _ffn_plans[key]
 
 
@@ -356,18 +464,18 @@ def ffn_small_m(x_in, x_out, delta, gain, eps, w_gate_up, w_down, out) -> None:
         raise ValueError(f"ffn_small_m: out must be float32 {(splits, M, hidden)}")
     n_partials, stride = _partials(delta, x_in)
     key = (x_in.device.index, inner)
-    if key not in _ffn_scratch:
-        _ffn_scratch[key] = (torch.empty((16, inner), dtype=torch.bfloat16, device=x_in.device),
-                             torch.zeros(2, dtype=torch.int32, device=x_in.device))
-    act, sync = _ffn_scratch[key]
-    _check(_lib("ffn_small_m").tokb200_ffn_small_m(
+    if key not in _space.ffn:
+        _space.ffn[key] = (torch.empty((16, inner), dtype=torch.bfloat16, device=x_in.device),
+                           torch.zeros(2, dtype=torch.int32, device=x_in.device))
+    act, sync = _space.ffn[key]
+    _check(_ffn_lib().tokb200_ffn_small_m(
         _ptr(x_in), _ptr(x_out), _ptr(delta), _i(1 if delta is not None and delta.dtype == torch.float32 else 0),
         _i(n_partials), _ll(stride), _ptr(gain), _f(eps), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
         _ptr(out), _i(M), _i(hidden), _i(inner), _ptr(sync), _stream()), "ffn_small_m")
 
 
 def ffn_small_m_check() -> None:
-    flag = _lib("ffn_small_m").tokb200_ffn_small_m_error()
+    flag = _ffn_lib().tokb200_ffn_small_m_error()
     if flag:
         raise KernelError("ffn_small_m: a wait on the device ran out (status %d)" % flag)
 
@@ -411,15 +519,12 @@ def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
         raise ValueError("prefill_attention is the bfloat16 kernel")
     if not prefill_attention_supported(nh, nkv, d):
         raise ValueError(f"prefill_attention: {nh} heads over {nkv} groups of size {d} is not taken")
-    lib = load_library("attention_prefill.cu", defines=(f"HEAD_DIM={d}",))
+    lib = _load("attention_prefill.cu", defines=(f"HEAD_DIM={d}",))
     _check(lib.tokb200_prefill_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
         _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _f(scale), _stream()),
         "prefill_attention")
-
-
-_argmax_scratch = {}
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -428,12 +533,12 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     n_rows, vocab = logits.shape
     lib = _lib("sampling")
     key = (logits.device.index, n_rows)
-    if key not in _argmax_scratch:
+    if key not in _space.argmax:
         lib.tokb200_argmax_scratch_bytes.restype = ctypes.c_longlong
         size = lib.tokb200_argmax_scratch_bytes(_i(n_rows))
-        _argmax_scratch[key] = (torch.empty(size, dtype=torch.uint8, device=logits.device),
-                                torch.zeros(n_rows, dtype=torch.int32, device=logits.device))
-    scratch, counters = _argmax_scratch[key]
+        _space.argmax[key] = (torch.empty(size, dtype=torch.uint8, device=logits.device),
+                              torch.zeros(n_rows, dtype=torch.int32, device=logits.device))
+    scratch, counters = _space.argmax[key]
     _check(lib.tokb200_argmax(_ptr(logits), _i(n_rows), _i(vocab), _ptr(out), _ptr(scratch),
                               _ptr(counters), _stream()), "argmax")
 
@@ -647,7 +752,7 @@ def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
         raise ValueError("attention_tcgen05 is the bfloat16 kernel")
     if not attention_tcgen05_supported(nh, nkv, d):
         raise ValueError(f"attention_tcgen05: head size {d} is not taken (64 or 128)")
-    lib = load_library("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",))
+    lib = _load("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",))
     _check(lib.tokb200_attention_tcgen05(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
@@ -656,6 +761,6 @@ def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
 
 
 def attention_tcgen05_check(d: int) -> None:
-    flag = load_library("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",)).tokb200_attention_tcgen05_error()
+    flag = _load("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",)).tokb200_attention_tcgen05_error()
     if flag:
         raise KernelError("attention_tcgen05: a wait on the device ran out (status %d)" % flag)

@@ -13,17 +13,34 @@ from ..kernels import ops
 # TOKB200_STREAM=0 keeps the vocabulary projection of few rows on the kernel for single products
 _STREAM = os.environ.get("TOKB200_STREAM", "1") != "0"
 
-# blocks wanted in flight before a product with few weight rows is also cut along k
-_TARGET_BLOCKS = 296
+_sm_count = None
+
+
+def sm_count() -> int:
+    """SMs of the current device (148 on a B200; that figure where no device is visible, so
+    that the rules below can be read on a machine without one)."""
+    global _sm_count
+    if _sm_count is None:
+        try:
+            _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+                if torch.cuda.is_available() else 148
+        except Exception:
+            _sm_count = 148
+    return _sm_count
+
+
+def _target_blocks() -> int:
+    """Blocks wanted in flight before a product with few weight rows is also cut along k."""
+    return 2 * sm_count()
 
 
 def choose_k_splits(M: int, N: int, K: int) -> int:
     """How many pieces along k a small-M product is cut into (1: none)."""
     tiles = (N + 15) // 16
     blocks = (tiles + 1) // 2 if tiles >= 1024 else tiles
-    if blocks >= _TARGET_BLOCKS // 2:
+    if blocks >= _target_blocks() // 2:
         return 1
-    return max(1, min(-(-_TARGET_BLOCKS // blocks), K // 256, 16))
+    return max(1, min(-(-_target_blocks() // blocks), K // 256, 16))
 
 
 def choose_tile_k_splits(M: int, N: int, K: int) -> int:
@@ -31,9 +48,10 @@ def choose_tile_k_splits(M: int, N: int, K: int) -> int:
     device: about one unit of work per SM, at least two 64-element blocks of k a piece."""
     tiles = -(-M // 128) * -(-N // 128)
     k_blocks = -(-K // 64)
-    if tiles * 2 > 148 or N % 4 or k_blocks < 4:
+    sms = sm_count()
+    if tiles * 2 > sms or N % 4 or k_blocks < 4:
         return 1
-    want = min(148 // tiles, k_blocks // 2, 8)      # more pieces cost the consumer more than they save here
+    want = min(sms // tiles, k_blocks // 2, 8)      # more pieces cost the consumer more than they save here
     # the consumer reads every plane: beyond 8 MB of partial sums adding them costs more than the
     # idle SMs did (a step of 512 rows: 1.98 -> 1.81 ms with at most 4 planes of 1.8 MB)
     plane = M * N * 4
@@ -47,14 +65,15 @@ def use_pair(M: int, N: int, K: int) -> bool:
     (the down projection from 2,816 rows on, where tiles of 128 x 128 need a second round of
     CTAs and take 48 us at 3,072 rows): the product goes to pairs of CTAs, each loading half of
     the weight tile."""
-    return ops._PAIR and K >= 2048 and N % 8 == 0 and -(-M // 256) * -(-N // 256) >= 44
+    return ops._PAIR and K >= 2048 and N % 8 == 0 and -(-M // 256) * -(-N // 256) >= (sm_count() // 2) * 3 // 5
 
 
 def use_pair_halves(M: int, N: int, K: int) -> bool:
     """Between 1,536 rows and half the pairs' worth of tiles (the down projection of a portion of
     2,048 tokens: 32 tiles): the pair form with k cut in two, float32 partial sums for a consumer
     that adds them (product 25.2 -> 22.1 us, the norm behind it 3.6 -> 3.9 us)."""
-    return ops._PAIR and M >= 1536 and K >= 2048 and N % 4 == 0 and -(-M // 256) * -(-N // 256) <= 37
+    return ops._PAIR and M >= 1536 and K >= 2048 and N % 4 == 0 and \
+        -(-M // 256) * -(-N // 256) <= sm_count() // 4
 
 
 def use_tcgen05(M: int, N: int, K: int) -> bool:
@@ -75,7 +94,7 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     # whose few tiles would leave most SMs of the tile kernel idle
     # few rows and a weight of many rows (the vocabulary projection): one block an SM streams
     # its run of the weight through a shared-memory ring
-    if _STREAM and M <= ops.SMALL_M_ROWS and N >= 16 * 148 * 4 and ops.linear_stream_supported(M, N, K):
+    if _STREAM and M <= ops.SMALL_M_ROWS and N >= 16 * sm_count() * 4 and ops.linear_stream_supported(M, N, K):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         ops.linear_stream(a, weight, bias, out)
         return out

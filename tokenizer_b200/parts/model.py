@@ -74,6 +74,7 @@ class DecoderModel:
         self.head = head_cls(spec.head, store, runtime, tied_table=tied)
         self.order = spec.order
         self._side = None
+        self.scratch = ops.ScratchSpace()      # what this model's kernels use beyond inputs and outputs
 
     def _prefetcher(self, ctx):
         """Steps of few rows stream every weight once and wait on memory in each
@@ -98,7 +99,7 @@ class DecoderModel:
                 want_rows: torch.Tensor) -> torch.Tensor:
         """Run the rows of `ctx` through every call of the order and return the
         float32 logits of `want_rows` (int32 row indices), [len(want_rows), vocab]."""
-        with ops.bound_stream():
+        with ops.bound_stream(), ops.scratch_scope(self.scratch):
             return self._forward(ctx, bindings, want_rows)
 
     def _forward(self, ctx, bindings, want_rows):

@@ -37,6 +37,9 @@ class PendingIds:
         if self._host is None:
             return []
         self._done.synchronize()
+        # the step that made these logits has finished: had one of its bounded waits run out,
+        # the ids would come from wrong logits
+        ops.raise_if_error("found when a draw's ids were read")
         return self._host.tolist()
 
 
@@ -44,6 +47,7 @@ class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self._pinned = None
+        self.scratch = ops.ScratchSpace()       # the greedy choice's partial results and counters
 
     def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_p: Sequence[float],
                uniform: Sequence[float]) -> List[int]:
@@ -60,12 +64,13 @@ class Sampler:
         if logits.shape[1] == 0:
             raise ValueError("no logits to sample")
         out = torch.empty(n, dtype=torch.int32, device=self.device)
-        if all(t == 0 for t in temperature):
-            ops.sample(logits, None, None, None, out)
-        else:
-            params = torch.tensor([list(temperature), list(top_p), list(uniform)],
-                                  dtype=torch.float32).to(self.device, non_blocking=True)
-            ops.sample(logits, params[0], params[1], params[2], out)
+        with ops.scratch_scope(self.scratch):
+            if all(t == 0 for t in temperature):
+                ops.sample(logits, None, None, None, out)
+            else:
+                params = torch.tensor([list(temperature), list(top_p), list(uniform)],
+                                      dtype=torch.float32).to(self.device, non_blocking=True)
+                ops.sample(logits, params[0], params[1], params[2], out)
         if self._pinned is None or self._pinned.numel() < n:
             self._pinned = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
         host = self._pinned[:n]
@@ -76,5 +81,6 @@ class Sampler:
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
-        ops.sample(logits, None, None, None, out)
+        with ops.scratch_scope(self.scratch):
+            ops.sample(logits, None, None, None, out)
         return out

@@ -68,31 +68,31 @@ class ByteLevelBPE:
     def from_dict(cls, raw: dict) -> "ByteLevelBPE":
         normalizer = raw.get("normalizer")
         if not normalizer:
-            raise TokenizerError("tokenizer.json has no normalizer")
+            raise TokenizerError("the file names no normalizer (this tokenizer normalizes to NFC)")
         if normalizer.get("type") != "NFC":
-            raise TokenizerError(f"expected an NFC normalizer, found {normalizer.get('type')}")
+            raise TokenizerError(f"the normalizer is {normalizer.get('type')}; only NFC is handled")
         pre = raw.get("pre_tokenizer") or {}
         if pre.get("type") != "Sequence":
-            raise TokenizerError(f"expected a Sequence pre-tokenizer, found {pre.get('type')}")
+            raise TokenizerError(f"the pre-tokenizer is {pre.get('type')}; a Sequence of Split and ByteLevel is handled")
         steps = pre.get("pretokenizers", [])
         split = next((s for s in steps if s.get("type") == "Split"), None)
         if split is None:
-            raise TokenizerError("pre-tokenizer has no Split step")
+            raise TokenizerError("the pre-tokenizer Sequence lacks its Split step")
         if split.get("behavior") != "Isolated":
-            raise TokenizerError(f"expected Split behavior Isolated, found {split.get('behavior')}")
+            raise TokenizerError(f"the Split step behaves as {split.get('behavior')}; only Isolated is handled")
         if split.get("invert", False):
-            raise TokenizerError("Split invert=true is not supported")
+            raise TokenizerError("the Split step is inverted (invert: true), which is not handled")
         pattern = (split.get("pattern") or {}).get("Regex")
         if not pattern:
-            raise TokenizerError("Split step has no Regex pattern")
+            raise TokenizerError("the Split step gives no Regex pattern")
         byte_level = next((s for s in steps if s.get("type") == "ByteLevel"), None)
         if byte_level is None:
-            raise TokenizerError("pre-tokenizer has no ByteLevel step")
+            raise TokenizerError("the pre-tokenizer Sequence lacks its ByteLevel step")
         if byte_level.get("use_regex", False):
-            raise TokenizerError("ByteLevel use_regex must be false; the Split step owns the regex")
+            raise TokenizerError("the ByteLevel step has use_regex on; splitting belongs to the Split step alone")
         model = raw.get("model") or {}
         if model.get("type") != "BPE":
-            raise TokenizerError(f"expected a BPE model, found {model.get('type')}")
+            raise TokenizerError(f"the model is {model.get('type')}; only BPE is handled")
 
         alphabet = _byte_alphabet()
 
@@ -101,45 +101,45 @@ class ByteLevelBPE:
                 return bytes(alphabet[ch] for ch in token)
             except KeyError as err:
                 raise TokenizerError(
-                    f"vocab char U+{ord(err.args[0]):04X} is not a bytes_to_unicode scalar") from None
+                    f"a vocab entry holds U+{ord(err.args[0]):04X}, which stands for no byte in the byte-level alphabet") from None
 
         vocab: Dict[bytes, int] = {}
         ids = set()
         for token, token_id in model.get("vocab", {}).items():
             data = to_bytes(token)
             if data in vocab:
-                raise TokenizerError(f"duplicate vocab bytes for id {token_id}")
+                raise TokenizerError(f"id {token_id} spells bytes that another id already spells")
             if token_id in ids:
-                raise TokenizerError(f"duplicate token id {token_id}")
+                raise TokenizerError(f"id {token_id} is given to two vocab entries")
             vocab[data] = token_id
             ids.add(token_id)
         for byte in range(256):
             if bytes([byte]) not in vocab:
-                raise TokenizerError(f"missing single-byte token {byte}")
+                raise TokenizerError(f"the vocab has no token for the single byte {byte}")
         ranks: Dict[bytes, int] = {}
         for index, merge in enumerate(model.get("merges", [])):
             parts = merge.split(" ") if isinstance(merge, str) else list(merge)
             if len(parts) != 2 or not parts[0] or not parts[1]:
-                raise TokenizerError(f"merge {index} is not two bytes_to_unicode tokens")
+                raise TokenizerError(f"merge {index} is not a pair of tokens in the byte-level alphabet")
             left, right = to_bytes(parts[0]), to_bytes(parts[1])
             if left not in vocab or right not in vocab:
-                raise TokenizerError(f"merge {index} names a token that is not in the vocab")
+                raise TokenizerError(f"merge {index} joins a token the vocab does not hold")
             if left + right not in vocab:
-                raise TokenizerError(f"merge {index} concatenation is not in the vocab")
+                raise TokenizerError(f"merge {index} produces bytes the vocab does not hold")
             if left + right in ranks:
-                raise TokenizerError(f"merge {index} repeats a byte string")
+                raise TokenizerError(f"merge {index} produces bytes an earlier merge already produces")
             ranks[left + right] = index
         added: Dict[str, int] = {}
         for entry in raw.get("added_tokens", []):
             if entry.get("normalized", True):
                 raise TokenizerError(
-                    f"added token {entry.get('content')!r} is normalized; only normalized=false is supported")
+                    f"added token {entry.get('content')!r} asks for normalization; added tokens are matched as written")
             if not entry.get("content"):
-                raise TokenizerError("added token content is empty")
+                raise TokenizerError("an added token has no content")
             if entry["id"] in ids:
-                raise TokenizerError(f"added token id {entry['id']} already belongs to a vocab token")
+                raise TokenizerError(f"added token id {entry['id']} is taken by a vocab token")
             if entry["content"] in added:
-                raise TokenizerError(f"duplicate added token {entry['content']!r}")
+                raise TokenizerError(f"added token {entry['content']!r} appears twice")
             added[entry["content"]] = entry["id"]
         return cls(vocab, ranks, added, pattern)
 
