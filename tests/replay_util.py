@@ -192,10 +192,10 @@ def steps_mixed(requests, max_live=4, prompt_fraction=0.6, portion=(11, 2, 24, 5
             item[4] += 1
             if item[2] == len(ids):
                 ended.append(name)
-            for adopter, (donor, shared) in share.items():
-                if donor == name and donor not in published and item[2] >= shared:
-                    published.add(donor)
-                    publish.append(donor)
+            most = max([n_shared for donor, n_shared in share.values() if donor == name], default=None)
+            if most is not None and name not in published and item[2] >= most:
+                published.add(name)             # once all that its adopters will look for is in place
+                publish.append(name)
         peak = max(peak, sum(rounded64(item[2]) for item in live))
         if entries:
             steps.append({"step": at, "entries": entries, "end": ended})

@@ -10,7 +10,24 @@ import torch
 from tokenizer_b200.cache import CachePlan
 from tokenizer_b200.engine import batch as batch_module
 from tokenizer_b200.engine.batch import BatchBuilder, StepEntry
-from tokenizer_b200.parts.base import CacheNeed, KVNeed
+from tokenizer_b200.parts.attention import RowTiles
+from tokenizer_b200.parts.base import BatchAnnotation, CacheNeed, KVNeed
+
+
+class LongestFirst(BatchAnnotation):
+    """An annotation defined here: the requests in the order of their stored lengths."""
+    key = "longest_first"
+
+    def capacity(self, n_tokens, n_requests):
+        return n_requests
+
+    def fill(self, out, first_rows, counts, starts, padded):
+        order = np.argsort(-(starts + counts), kind="stable")
+        out[:len(order)] = order
+        return len(order)
+
+
+NOTES = [RowTiles(64), RowTiles(128), LongestFirst()]
 
 
 def make_plan(rng, windowed):
@@ -44,16 +61,25 @@ def test_single_token_steps_pack_alike_both_ways(seed, monkeypatch):
     outcomes = []
     for fast in (True, False):
         monkeypatch.setattr(batch_module, "_SINGLE_TOKEN_PATH", fast)
-        builder = BatchBuilder(plan, 1000, 4096, torch.device("cpu"))
+        builder = BatchBuilder(plan, 1000, 4096, torch.device("cpu"), NOTES)
         builder.validate(entries)
         packed = builder.pack(entries, **pads)
         outcomes.append((packed, packed_words(builder, packed)))
     (a, words_a), (b, words_b) = outcomes
     assert np.array_equal(words_a, words_b)
     for field in ("widths", "tokens", "requests", "wanted", "n_want", "q_lens", "kv_lens", "state_slots",
-                  "n_tiles", "n_wide_tiles"):
+                  "note_counts"):
         assert getattr(a, field) == getattr(b, field), field
     assert a.layout == b.layout
+    # what the annotations wrote: one tile of one row a request, most keys first; the order of
+    # the third annotation, which the builder has never heard of
+    lay, R = a.layout, len(entries)
+    lengths = np.array([c.length + 1 for c in caches])
+    tiles = words_a[lay.notes[0]:lay.notes[0] + 2 * R].reshape(R, 2)
+    assert tiles[:, 1].tolist() == [1] * R and sorted(tiles[:, 0].tolist()) == list(range(R))
+    assert (np.diff(lengths[tiles[:, 0]]) <= 0).all()
+    assert words_a[lay.notes[2]:lay.notes[2] + R].tolist() == np.argsort(-lengths, kind="stable").tolist()
+    assert a.note_counts[2] == R and a.note_counts[0] == (lay.note_words[0] // 2 if pads else R)
 
 
 def test_what_a_step_may_not_bring():

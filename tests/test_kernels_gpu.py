@@ -573,6 +573,66 @@ def test_gated_linear(M, inner, K):
         o.gated_linear(x, w[:-8], torch.empty(M, inner - 4, dtype=torch.bfloat16, device=DEV))
 
 
+def activation_reference(name, g):
+    if name == "silu":
+        return g * torch.sigmoid(g)
+    if name == "relu":
+        return torch.clamp(g, min=0.0)
+    return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+
+
+@pytest.mark.parametrize("activation", ["gelu_pytorch_tanh", "relu"])
+def test_the_activation_is_a_parameter_of_every_gated_kernel(activation):
+    """Another activation than the served model's through every kernel that applies one: the
+    separate gate kernel (both precisions), the gated product of few rows, of a few dozen
+    (plain product, then the gate kernel for the interleaved layout), of hundreds (tcgen05
+    epilogue, lone CTAs and pairs), and the fused feed-forward of a decoding step."""
+    o = ops()
+    inner, K = 384, 200
+    gate = rnd(inner, K, seed=72, dtype=torch.bfloat16, scale=0.2)
+    up = rnd(inner, K, seed=73, dtype=torch.bfloat16, scale=0.2)
+    w = o.interleave_gate_up(gate, up)
+    for M in (5, 40, 130, 300):
+        x = rnd(M, K, seed=70 + M, dtype=torch.bfloat16)
+        out = torch.full((M, inner), 7.0, dtype=torch.bfloat16, device=DEV)
+        o.gated_linear(x, w, out, activation)
+        torch.cuda.synchronize()
+        g = x.double().cpu() @ gate.double().cpu().t()
+        u = x.double().cpu() @ up.double().cpu().t()
+        want = (activation_reference(activation, g) * u).float()
+        got = out.float().cpu()
+        assert torch.allclose(got, want, atol=4e-3, rtol=2 ** -6), (M, float((got - want).abs().max()))
+    o.gemm_tcgen05_check()
+    for dtype in (torch.float32, torch.bfloat16):
+        gu = rnd(7, 2 * 100, seed=5, dtype=dtype)
+        out = torch.empty(7, 100, dtype=dtype, device=DEV)
+        o.silu_gate(gu, out, activation)
+        g, u = gu.double().cpu()[:, :100], gu.double().cpu()[:, 100:]
+        close(out, (activation_reference(activation, g) * u).float(), dtype)
+    with pytest.raises(ValueError, match="activations"):
+        o.silu_gate(gu, out, "swish-ish")
+    # the fused feed-forward
+    M, hidden, inner = 6, 160, 384
+    splits = o.ffn_small_m_splits(M, hidden, inner)
+    x = rnd(M, hidden, seed=81)
+    gain = 1.0 + rnd(hidden, seed=83, scale=0.1)
+    gate = rnd(inner, hidden, seed=84, dtype=torch.bfloat16, scale=0.06)
+    up = rnd(inner, hidden, seed=85, dtype=torch.bfloat16, scale=0.06)
+    down = rnd(hidden, inner, seed=86, dtype=torch.bfloat16, scale=0.04)
+    xs = x.double().cpu()
+    h = (xs / torch.sqrt((xs * xs).mean(-1, keepdim=True) + 1e-5) * gain.double().cpu()).float().to(torch.bfloat16).double()
+    g, u = h @ gate.double().cpu().t(), h @ up.double().cpu().t()
+    act = (activation_reference(activation, g) * u).float().to(torch.bfloat16).double()
+    want = (act @ down.double().cpu().t()).float()
+    x_out = torch.empty_like(x)
+    out = torch.zeros((splits, M, hidden), dtype=torch.float32, device=DEV)
+    o.ffn_small_m(x, x_out, None, gain, 1e-5, o.interleave_gate_up(gate, up), down, out, activation)
+    torch.cuda.synchronize()
+    o.ffn_small_m_check()
+    got = out.sum(0).cpu()
+    assert float((got - want).abs().max()) <= 2e-3 * float(want.abs().max()) + 1e-5
+
+
 @pytest.mark.parametrize("M,nh,nkv,d,K", [(1, 4, 2, 16, 64), (8, 14, 2, 64, 896), (5, 3, 1, 32, 96),
                                            (16, 5, 5, 48, 80), (3, 2, 1, 128, 200), (32, 14, 2, 64, 896),
                                            (23, 3, 3, 16, 72)])

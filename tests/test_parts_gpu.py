@@ -65,6 +65,31 @@ def test_feed_forward_part(dtype):
     assert torch.allclose(got, want, **tol(dtype)), float((got - want).abs().max())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [6, 150])
+def test_feed_forward_part_with_another_activation(dtype, rows):
+    """The activation is the part's parameter: the same part with a tanh-gelu gate (sizes the
+    gated kernels take, so that in bfloat16 the activation runs in their epilogues)."""
+    from tokenizer_b200.config import PartSpec
+    from tokenizer_b200.config.spec import ConfigError
+    from tokenizer_b200.parts import build_part, part_class
+    params = {"hidden_size": 64, "intermediate_size": 256, "activation": "gelu_pytorch_tanh"}
+    spec = PartSpec("gated_mlp", params, "mlp")
+    store = store_for(part_class("feed_forward", "gated_mlp").tensors(spec), scale={"": 5.0})
+    part = build_part("feed_forward", spec, store, runtime(dtype))
+    h = torch.randn(rows, 64, generator=torch.Generator().manual_seed(3)).to(dtype)
+    w = {k: store.get(k).float() for k in store.names()}
+    g, u = h.float() @ w["mlp.gate_proj.weight"].t(), h.float() @ w["mlp.up_proj.weight"].t()
+    act = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    want = (act * u) @ w["mlp.down_proj.weight"].t()
+    got = part.forward(h.to(DEV)).float()
+    got = (got.sum(0) if got.dim() == 3 else got).cpu()
+    assert torch.allclose(got, want, **tol(dtype)), float((got - want).abs().max())
+    with pytest.raises(ConfigError, match="activations"):
+        build_part("feed_forward", PartSpec("gated_mlp", dict(params, activation="swish-ish"), "mlp"), store,
+                   runtime(dtype))
+
+
 def small_model_pieces(dtype, window=None, nh=6, nkv=3, d=16, hidden=40):
     from tokenizer_b200.config import PartSpec
     position = PartSpec("rope_half_split", {"theta": 1e4, "rotary_dim": d, "max_positions": 256})
@@ -91,7 +116,7 @@ def test_attention_part_over_portions(dtype, window):
     mixer = build_part("mixer", spec, store, rt)
     cache = DeviceCache([mixer.cache_need()], num_pages=16, page_size=4, max_requests=2, runtime=rt)
     binding = cache.bindings([LayerCall(0)])[0]
-    builder = BatchBuilder(cache, 10, 256, DEV)
+    builder = BatchBuilder(cache, 10, 256, DEV, mixer.batch_annotations())
     g = torch.Generator().manual_seed(4)
     hs = {"a": torch.randn(23, 40, generator=g).to(dtype), "b": torch.randn(14, 40, generator=g).to(dtype)}
     weights = {k: store.get(k).float() for k in store.names()}

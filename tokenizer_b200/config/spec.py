@@ -31,16 +31,37 @@ class PartSpec:
         return PartSpec(self.kind, dict(self.params), prefix)
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: how its parts are arranged (`block`, e.g. pre-norm
-    residual), the token mixer, the feed-forward and the two norms."""
+    """One decoder layer: `block` names a registered arrangement (e.g. pre-norm residual) and
+    `parts` are the parts it arranges, by name.  The arrangement's class says which names it
+    wants and of which category each is (its `PARTS`), so another arrangement (a third norm,
+    two mixers side by side, no feed-forward) is a new registered block and nothing else.
+    The four names of the pre-norm residual block can be given positionally; every name is
+    also an attribute (`layer.mixer`)."""
 
-    block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    def __init__(self, block: str, mixer: Optional[PartSpec] = None,
+                 feed_forward: Optional[PartSpec] = None, mixer_norm: Optional[PartSpec] = None,
+                 feed_forward_norm: Optional[PartSpec] = None, **more: PartSpec):
+        parts: Dict[str, PartSpec] = {}
+        for name, spec in (("mixer", mixer), ("feed_forward", feed_forward),
+                           ("mixer_norm", mixer_norm), ("feed_forward_norm", feed_forward_norm)):
+            if spec is not None:
+                parts[name] = spec
+        parts.update(more)
+        for name, spec in parts.items():
+            if not isinstance(spec, PartSpec):
+                raise ConfigError(f"layer part {name!r} must be a PartSpec, found {type(spec).__name__}")
+        self.block = block
+        self.parts = parts
+
+    def __getattr__(self, name: str) -> PartSpec:
+        parts = self.__dict__.get("parts", {})
+        if name in parts:
+            return parts[name]
+        raise AttributeError(f"this layer has no part named {name!r} (it has {', '.join(parts) or 'none'})")
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.block!r}, {self.parts!r})"
 
 
 @dataclass(frozen=True)

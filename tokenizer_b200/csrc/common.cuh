@@ -112,6 +112,21 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
   return __float2bfloat16_rn(v);
 }
 
+// ---- the activation of a gated feed-forward -------------------------------------------
+// out = act(gate) * up.  Which activation is a PARAMETER of every kernel that applies one
+// (the separate gate kernels, the epilogues of the gated products, the fused feed-forward),
+// computed in 32-bit; the tags are shared with Python.
+enum : int { TOKB200_ACT_SILU = 0, TOKB200_ACT_GELU_TANH = 1, TOKB200_ACT_RELU = 2, TOKB200_ACT_COUNT = 3 };
+
+__device__ __forceinline__ float gate_activation(int kind, float g) {
+  if (kind == TOKB200_ACT_SILU) return g / (1.0f + expf(-g));            // z * sigmoid(z)
+  if (kind == TOKB200_ACT_GELU_TANH) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(inner));
+  }
+  return fmaxf(g, 0.f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -547,11 +547,11 @@ TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int
 }
 
 // ----------------------------------------------------------------------------
-// gated activation: out[t, i] = silu(gu[t, i]) * gu[t, inner + i]
-// silu(z) = z * sigmoid(z) = z / (1 + exp(-z)), in 32-bit
+// gated activation: out[t, i] = act(gu[t, i]) * gu[t, inner + i], `act` by its tag
+// (silu(z) = z * sigmoid(z) = z / (1 + exp(-z)) for the architecture served), in 32-bit
 // ----------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner) {
+__global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, int act) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.y;
@@ -559,13 +559,13 @@ __global__ void silu_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, 
   T* orow = out + (size_t)t * inner;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inner; i += gridDim.x * blockDim.x) {
     const float g = to_float(row[i]), u = to_float(row[inner + i]);
-    orow[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    orow[i] = from_float<T>(gate_activation(act, g) * u);
   }
 }
 
 // bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) a thread
 __global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
-                                        __nv_bfloat16* __restrict__ out, int inner, int n_rows) {
+                                        __nv_bfloat16* __restrict__ out, int inner, int n_rows, int act) {
   pdl_wait();
   pdl_launch();
   const int per_row = inner / 8;
@@ -583,7 +583,7 @@ __global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-      o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+      o2[e] = __floats2bfloat162_rn(gate_activation(act, g.x) * u.x, gate_activation(act, g.y) * u.y);
     }
     *reinterpret_cast<uint4*>(out + t * inner + c) = o4;
   }
@@ -592,7 +592,7 @@ __global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
 // the same for the interleaved layout of the gated kernels: for every 128 outputs,
 // 128 gate values followed by their 128 up values
 __global__ void silu_gate_interleaved_kernel(const __nv_bfloat16* __restrict__ gu,
-                                             __nv_bfloat16* __restrict__ out, int inner, int n_rows) {
+                                             __nv_bfloat16* __restrict__ out, int inner, int n_rows, int act) {
   pdl_wait();
   pdl_launch();
   const int per_row = inner / 8;
@@ -611,32 +611,32 @@ __global__ void silu_gate_interleaved_kernel(const __nv_bfloat16* __restrict__ g
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-      o2[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+      o2[e] = __floats2bfloat162_rn(gate_activation(act, g.x) * u.x, gate_activation(act, g.y) * u.y);
     }
     *reinterpret_cast<uint4*>(out + t * inner + c) = o4;
   }
 }
 
 TOKB200_API int tokb200_silu_gate_interleaved(const void* gu, void* out, int n_tokens, int inner,
-                                              cudaStream_t stream) {
+                                              int act, cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;
-  if (inner <= 0 || inner % 128) return TOKB200_BAD_SIZE;
+  if (inner <= 0 || inner % 128 || act < 0 || act >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (((uintptr_t)gu | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   const size_t total = (size_t)n_tokens * (inner / 8);
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   return launch_dependent(silu_gate_interleaved_kernel, dim3(blocks), dim3(256), 0, stream,
-                          (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens);
+                          (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens, act);
 }
 
 TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_tokens, int inner,
-                                  cudaStream_t stream) {
+                                  int act, cudaStream_t stream) {
   if (n_tokens <= 0) return TOKB200_OK;
-  if (inner <= 0 || n_tokens > 65535 * 1024) return TOKB200_BAD_SIZE;
+  if (inner <= 0 || n_tokens > 65535 * 1024 || act < 0 || act >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (dtype == TOKB200_BF16 && inner % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     const size_t total = (size_t)n_tokens * (inner / 8);
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     return launch_dependent(silu_gate_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream,
-                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens);
+                            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, n_tokens, act);
   }
   // grid.y is limited to 65535 rows; tile rows over several launches beyond it
   for (int row0 = 0; row0 < n_tokens; row0 += 65535) {
@@ -646,11 +646,11 @@ TOKB200_API int tokb200_silu_gate(const void* gu, void* out, int dtype, int n_to
     if (dtype == TOKB200_F32)
       status = launch_dependent(silu_gate_kernel<float>, grid, dim3(256), 0, stream,
                                 (const float*)gu + (size_t)row0 * 2 * inner,
-                                (float*)out + (size_t)row0 * inner, inner);
+                                (float*)out + (size_t)row0 * inner, inner, act);
     else if (dtype == TOKB200_BF16)
       status = launch_dependent(silu_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream,
                                 (const __nv_bfloat16*)gu + (size_t)row0 * 2 * inner,
-                                (__nv_bfloat16*)out + (size_t)row0 * inner, inner);
+                                (__nv_bfloat16*)out + (size_t)row0 * inner, inner, act);
     else
       return TOKB200_BAD_DTYPE;
     if (status != TOKB200_OK) return status;

@@ -3,7 +3,7 @@
 //
 //   x' = x + pending                      (the residual sum, 32-bit)
 //   h  = rms_norm(x') * gain              (bfloat16)
-//   a  = silu(h Wg^T) * (h Wu^T)          (bfloat16, [M, I])
+//   a  = act(h Wg^T) * (h Wu^T)           (bfloat16, [M, I]; act by its tag, silu for the model served)
 //   y  = a Wd^T as S partial sums over k  (32-bit, [S, M, H]; the next norm adds them)
 //
 // As separate kernels these are three launches whose time is mostly waiting: each
@@ -109,6 +109,7 @@ struct FfnParams {
   int s_down, k_per_split;      // the down product's cut along k (k_per_split a multiple of 32)
   int n_stages;
   int act_pitch;                // bytes between rows of the activation tile in shared memory
+  int activation;               // the gate's activation, by its tag
   int* sync;                    // [2] zero before the first launch; every launch leaves them zero
 };
 
@@ -351,7 +352,7 @@ ffn_small_m_kernel(const FfnParams p) {
     for (int i = threadIdx.x; i < 8 * p.M; i += FFN_CONSUMERS) {
       const int m = i / 8, rr = i % 8;
       const float gate = summed(rr, m), up = summed(rr + 8, m);
-      p.act[(size_t)m * p.I + tile * 8 + rr] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+      p.act[(size_t)m * p.I + tile * 8 + rr] = __float2bfloat16_rn(gate_activation(p.activation, gate) * up);
     }
     turn ^= 1;
   }
@@ -465,9 +466,9 @@ TOKB200_API int tokb200_ffn_small_m_splits(int M, int H, int I) { return ffn_pla
 TOKB200_API int tokb200_ffn_small_m(const float* x_in, float* x_out, const void* delta, int delta_is_f32,
                                     int n_partials, long long partial_stride, const float* gain,
                                     float eps, const void* w_gu, const void* w_d, void* act, float* out,
-                                    int M, int H, int I, int* sync, cudaStream_t stream) {
+                                    int M, int H, int I, int activation, int* sync, cudaStream_t stream) {
   const FfnPlan plan = ffn_plan(M, H, I);
-  if (plan.blocks == 0) return TOKB200_BAD_SIZE;
+  if (plan.blocks == 0 || activation < 0 || activation >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (((uintptr_t)w_gu | (uintptr_t)w_d | (uintptr_t)act) & 15) return TOKB200_BAD_ALIGNMENT;
   FfnParams p;
   p.x_in = x_in; p.x_out = x_out; p.delta = delta; p.delta_is_f32 = delta_is_f32;
@@ -475,7 +476,7 @@ TOKB200_API int tokb200_ffn_small_m(const float* x_in, float* x_out, const void*
   p.w_gu = (const __nv_bfloat16*)w_gu; p.w_d = (const __nv_bfloat16*)w_d;
   p.act = (__nv_bfloat16*)act; p.out = out; p.M = M; p.H = H; p.I = I;
   p.s_down = plan.s_down; p.k_per_split = plan.k_per_split; p.n_stages = plan.n_stages;
-  p.act_pitch = plan.act_pitch; p.sync = sync;
+  p.act_pitch = plan.act_pitch; p.sync = sync; p.activation = activation;
   void (*kernel)(const FfnParams) = M <= 8 ? ffn_small_m_kernel<1> : ffn_small_m_kernel<2>;
   static bool configured[64][2] = {};
   int device = 0;

@@ -354,9 +354,10 @@ struct TcPersistentSmem {
   static constexpr int kTotal = STAGES * kStage + kOutBytes + 1024 + 256;
 };
 
-// What the QKV epilogue needs besides the product: each row's position and cache slot, the
-// rotary tables, the key/value pools and the head geometry.  `heads` null: not a QKV product.
+// What the epilogues need besides the product.  QKV: each row's position and cache slot, the
+// rotary tables, the key/value pools and the head geometry.  GATED: the activation's tag.
 struct QkvEpilogue {
+  int activation;               // the gated epilogue's activation (TOKB200_ACT_*)
   const int* pos;
   const int* slot;              // may be null: no cache write
   const float* cos_t;
@@ -608,9 +609,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
               const float g0 = __uint_as_float(gate[8 * j + 2 * e]), g1 = __uint_as_float(gate[8 * j + 2 * e + 1]);
               const float u0 = __uint_as_float(up[8 * j + 2 * e]), u1 = __uint_as_float(up[8 * j + 2 * e + 1]);
               // silu in 32-bit with the fast exponential and reciprocal (a few ulp,
-              // far below the bfloat16 rounding of the result)
-              __nv_bfloat162 pair = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0,
-                                                          __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+              // far below the bfloat16 rounding of the result); another activation by its tag
+              const bool silu = qkv.activation == TOKB200_ACT_SILU;     // uniform over the grid
+              const float a0 = silu ? __fdividef(g0, 1.0f + __expf(-g0)) : gate_activation(qkv.activation, g0);
+              const float a1 = silu ? __fdividef(g1, 1.0f + __expf(-g1)) : gate_activation(qkv.activation, g1);
+              __nv_bfloat162 pair = __floats2bfloat162_rn(a0 * u0, a1 * u1);
               ow[e] = *reinterpret_cast<unsigned*>(&pair);
             }
             *reinterpret_cast<uint4*>(slab + (((piece0 + j) ^ (r & 7)) << 4)) = o;
@@ -761,7 +764,7 @@ static int make_out_map(CUtensorMap* map, void* base, long long M, long long N, 
 template <int BLOCK_N, int STAGES, bool OUT_F32, bool GATED = false, bool QKV = false, bool PAIR = false>
 static int launch_tc_persistent(const void* x, const void* w, const float* bias, void* out, int M, int N,
                                 int K, cudaStream_t stream, int k_splits = 1,
-                                const QkvEpilogue* qkv_in = nullptr) {
+                                const QkvEpilogue* qkv_in = nullptr, int activation = TOKB200_ACT_SILU) {
   using S = TcPersistentSmem<BLOCK_N, STAGES, OUT_F32, GATED, PAIR>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
   CUtensorMap map_x, map_w, map_out;
@@ -772,6 +775,7 @@ static int launch_tc_persistent(const void* x, const void* w, const float* bias,
   if (k_splits < 1 || (k_splits > 1 && (!OUT_F32 || bias))) return TOKB200_BAD_SIZE;
   QkvEpilogue qkv = {};
   if (QKV) qkv = *qkv_in;
+  qkv.activation = activation;
   status = make_out_map(&map_out, out, M, GATED ? N / 2 : (QKV ? (long long)qkv.nh * qkv.d : N), OUT_F32, k_splits);
   if (status != TOKB200_OK) return status;
   static bool configured[64] = {};
@@ -896,12 +900,12 @@ TOKB200_API int tokb200_gemm_tcgen05_partials(const void* x, const void* w, void
 // The pair form (two CTAs a tile of 256 rows x 256 columns; see the kernel).  kind 0: out [M,N]
 // bfloat16 (+ bias); kind 1: the gated product, out [M, N/2] bfloat16 (N a multiple of 256, no
 // bias); kind 2: float32 partial sums out [k_splits, M, N] (no bias); kind 3: as kind 0 with
-// 128-column tiles.
+// 128-column tiles.  `activation`: the gated product's activation tag (kind 1 only).
 TOKB200_API int tokb200_gemm_tcgen05_pair(const void* x, const void* w, const float* bias, void* out,
-                                          int kind, int M, int N, int K, int k_splits,
+                                          int kind, int M, int N, int K, int k_splits, int activation,
                                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return TOKB200_OK;
-  if (K <= 0 || K % 8 || k_splits < 1) return TOKB200_BAD_SIZE;
+  if (K <= 0 || K % 8 || k_splits < 1 || activation < 0 || activation >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   if (M > 128 * 65535) return TOKB200_BAD_SIZE;
   const int k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
@@ -913,7 +917,8 @@ TOKB200_API int tokb200_gemm_tcgen05_pair(const void* x, const void* w, const fl
       return launch_tc_persistent<256, 5, false, false, false, true>(x, w, bias, out, M, N, K, stream);
     case 1:
       if (N % 256 || k_splits != 1 || bias) return TOKB200_BAD_SIZE;
-      return launch_tc_persistent<256, 6, false, true, false, true>(x, w, nullptr, out, M, N, K, stream);
+      return launch_tc_persistent<256, 6, false, true, false, true>(x, w, nullptr, out, M, N, K, stream, 1,
+                                                                    nullptr, activation);
     case 2:
       if (N % 4 || bias) return TOKB200_BAD_SIZE;
       return launch_tc_persistent<256, 5, true, false, false, true>(x, w, nullptr, out, M, N, K, stream, k_splits);
@@ -924,15 +929,15 @@ TOKB200_API int tokb200_gemm_tcgen05_pair(const void* x, const void* w, const fl
   }
 }
 
-// out[M, N/2] = silu(x Wg^T) * (x Wu^T) where w [N, K] holds, for every 128 outputs,
-// their 128 gate rows followed by their 128 up rows (N a multiple of 256).
+// out[M, N/2] = act(x Wg^T) * (x Wu^T) where w [N, K] holds, for every 128 outputs,
+// their 128 gate rows followed by their 128 up rows (N a multiple of 256); act by its tag.
 TOKB200_API int tokb200_gemm_tcgen05_gated(const void* x, const void* w, void* out, int M, int N, int K,
-                                           cudaStream_t stream) {
+                                           int activation, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return TOKB200_OK;
-  if (K <= 0 || K % 8 || N % 256) return TOKB200_BAD_SIZE;
+  if (K <= 0 || K % 8 || N % 256 || activation < 0 || activation >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return TOKB200_BAD_ALIGNMENT;
   if (M > 128 * 65535) return TOKB200_BAD_SIZE;
-  return launch_tc_persistent<256, 3, false, true>(x, w, nullptr, out, M, N, K, stream);
+  return launch_tc_persistent<256, 3, false, true>(x, w, nullptr, out, M, N, K, stream, 1, nullptr, activation);
 }
 
 // The stacked q/k/v projection of many rows with bias, rotary encoding (the whole head, half-split

@@ -39,12 +39,12 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool ok) {
 // block's warps split into TPB teams of LSM_WARPS / TPB warps, a team per row tile.
 // GATED: w [N, K] holds, for every 128 outputs, their 128 "gate" rows followed by
 // their 128 "up" rows; a row tile is then 8 gate rows and the 8 up rows of the same
-// outputs, and the result is silu(gate) * up, [M, N / 2].
+// outputs, and the result is act(gate) * up, [M, N / 2] (`act`: the activation's tag).
 template <int MT, int TPB, bool GATED>
 __global__ void __launch_bounds__(LSM_THREADS)
 linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                       const float* __restrict__ bias, void* __restrict__ out, int out_is_f32,
-                      int M, int N, int K, int k_per_split) {
+                      int M, int N, int K, int k_per_split, int act) {
   constexpr int TEAM = LSM_WARPS / TPB;
   __shared__ float part[LSM_WARPS][16][8 * MT + 1];
 
@@ -135,7 +135,7 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
         up += part[tm * TEAM + s][rr + 8][m];
       }
       reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * half + n] =
-          __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+          __float2bfloat16_rn(gate_activation(act, gate) * up);
     }
     return;
   }
@@ -161,7 +161,7 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 
 template <int MT>
 static int launch_small_m_gated(const void* x, const void* w, void* out, int M, int N, int K,
-                                cudaStream_t stream) {
+                                int act, cudaStream_t stream) {
   const int tiles = (N / 2 + 7) / 8;
   const int k_per_split = (K + 31) / 32 * 32;
   // two row tiles a block from 300 tiles on: with one, a feed-forward of a few thousand
@@ -169,11 +169,11 @@ static int launch_small_m_gated(const void* x, const void* w, void* out, int M, 
   if (tiles >= 300) {
     return launch_dependent(linear_small_m_kernel<MT, 2, true>, dim3((tiles + 1) / 2), dim3(LSM_THREADS),
                             0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                            (const float*)nullptr, out, 0, M, N, K, k_per_split);
+                            (const float*)nullptr, out, 0, M, N, K, k_per_split, act);
   }
   return launch_dependent(linear_small_m_kernel<MT, 1, true>, dim3(tiles), dim3(LSM_THREADS), 0, stream,
                           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)nullptr, out,
-                          0, M, N, K, k_per_split);
+                          0, M, N, K, k_per_split, act);
 }
 
 template <int MT>
@@ -188,12 +188,12 @@ static int launch_small_m(const void* x, const void* w, const float* bias, void*
     dim3 grid((tiles + 1) / 2, k_splits);
     return launch_dependent(linear_small_m_kernel<MT, 2, false>, grid, dim3(LSM_THREADS), 0, stream,
                             (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
-                            M, N, K, k_per_split);
+                            M, N, K, k_per_split, 0);
   }
   dim3 grid(tiles, k_splits);
   return launch_dependent(linear_small_m_kernel<MT, 1, false>, grid, dim3(LSM_THREADS), 0, stream,
                           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
-                          M, N, K, k_per_split);
+                          M, N, K, k_per_split, 0);
 }
 
 // out: [M, N] bfloat16 or float32 when k_splits == 1 (bias added); float32
@@ -211,17 +211,17 @@ TOKB200_API int tokb200_linear_small_m(const void* x, const void* w, const float
   return launch_small_m<8>(x, w, bias, out, out_is_f32, M, N, K, k_splits, stream);
 }
 
-// out[M, N/2] (bfloat16) = silu(x Wg^T) * (x Wu^T), w in the 128-gate / 128-up row
-// blocks described at the kernel (N a multiple of 256).
+// out[M, N/2] (bfloat16) = act(x Wg^T) * (x Wu^T), w in the 128-gate / 128-up row
+// blocks described at the kernel (N a multiple of 256); `act` is the activation's tag.
 TOKB200_API int tokb200_linear_small_m_gated(const void* x, const void* w, void* out, int M, int N,
-                                             int K, cudaStream_t stream) {
+                                             int K, int act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return TOKB200_OK;
-  if (M > 64 || K <= 0 || K % 8 || N % 256) return TOKB200_BAD_SIZE;
+  if (M > 64 || K <= 0 || K % 8 || N % 256 || act < 0 || act >= TOKB200_ACT_COUNT) return TOKB200_BAD_SIZE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TOKB200_BAD_ALIGNMENT;
-  if (M <= 8) return launch_small_m_gated<1>(x, w, out, M, N, K, stream);
-  if (M <= 16) return launch_small_m_gated<2>(x, w, out, M, N, K, stream);
-  if (M <= 32) return launch_small_m_gated<4>(x, w, out, M, N, K, stream);
-  return launch_small_m_gated<8>(x, w, out, M, N, K, stream);
+  if (M <= 8) return launch_small_m_gated<1>(x, w, out, M, N, K, act, stream);
+  if (M <= 16) return launch_small_m_gated<2>(x, w, out, M, N, K, act, stream);
+  if (M <= 32) return launch_small_m_gated<4>(x, w, out, M, N, K, act, stream);
+  return launch_small_m_gated<8>(x, w, out, M, N, K, act, stream);
 }
 
 // ----------------------------------------------------------------------------

@@ -28,10 +28,6 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
-Q_TILE_ROWS = 64         # rows of one request that the mma.sync prompt-attention kernel takes per block
-Q_WIDE_TILE_ROWS = 128   # ... and the tcgen05 one
-
-
 def _round4(n: int) -> int:
     return (n + 3) // 4 * 4
 
@@ -51,16 +47,14 @@ class BatchLayout:
     kv_len: int = 0
     state_slot: int = 0
     want: int = 0
-    tiles: int = 0
-    max_tiles: int = 0
-    wide_tiles: int = 0
-    max_wide_tiles: int = 0
+    notes: Optional[List[int]] = None         # offsets of the parts' annotations ...
+    note_words: Optional[List[int]] = None    # ... and their sizes
     slots: Optional[List[int]] = None
     tables: Optional[List[int]] = None
     total: int = 0
 
     @classmethod
-    def compute(cls, T: int, R: int, W: int, table_widths: List[int]) -> "BatchLayout":
+    def compute(cls, T: int, R: int, W: int, table_widths: List[int], annotations=()) -> "BatchLayout":
         lay = cls(T, R, W, list(table_widths))
         at = 0
 
@@ -73,10 +67,8 @@ class BatchLayout:
         lay.ids, lay.pos, lay.row_req = take(T), take(T), take(T)
         lay.q_start, lay.kv_len, lay.state_slot = take(R + 1), take(R), take(R)
         lay.want = take(W)
-        lay.max_tiles = T // Q_TILE_ROWS + R
-        lay.tiles = take(2 * lay.max_tiles)
-        lay.max_wide_tiles = T // Q_WIDE_TILE_ROWS + R
-        lay.wide_tiles = take(2 * lay.max_wide_tiles)
+        lay.note_words = [int(a.capacity(T, R)) for a in annotations]
+        lay.notes = [take(n) for n in lay.note_words]
         lay.slots = [take(T) for _ in table_widths]
         lay.tables = [take(R * w) for w in table_widths]
         lay.total = at
@@ -97,8 +89,7 @@ class PackedStep:
     q_lens: List[int]
     kv_lens: List[int]
     state_slots: List[int]
-    n_tiles: int
-    n_wide_tiles: int
+    note_counts: List[int]            # what each annotation's `fill` returned
 
 
 # False sends steps of single tokens through the general packing loop too (tests compare the two)
@@ -106,7 +97,9 @@ _SINGLE_TOKEN_PATH = True
 
 
 class BatchBuilder:
-    def __init__(self, plan, vocab_size: int, max_positions: int, device):
+    def __init__(self, plan, vocab_size: int, max_positions: int, device, annotations=()):
+        """`annotations`: the `BatchAnnotation`s of the model's parts, one per key."""
+        self.annotations = list(annotations)
         self.plan = plan
         self.vocab_size = vocab_size
         self.max_positions = max_positions
@@ -190,7 +183,7 @@ class BatchBuilder:
             if widths[-1] < need:
                 raise ValueError("the captured block-table width is too small for this step")
         Tc, Rc, Wc = max(T, pad_tokens), max(R, pad_requests), max(W, pad_want)
-        lay = BatchLayout.compute(Tc, Rc, Wc, widths)
+        lay = BatchLayout.compute(Tc, Rc, Wc, widths, self.annotations)
         self._buffers(lay.total)
         turn = self._turn
         self._turn ^= 1
@@ -224,21 +217,12 @@ class BatchBuilder:
                     position = e.cache.length
                     buf[slots + r] = table[position // page] * page + position % page
             buf[lay.q_start + R:lay.q_start + Rc + 1] = R
-            # one tile of one row a request, most keys first (a stable order, as a sort of tuples gives)
-            order = np.argsort(-starts, kind="stable").astype(np.int32)
-            pairs = np.empty(2 * R, dtype=np.int32)
-            pairs[0::2] = order
-            pairs[1::2] = 1
-            buf[lay.tiles:lay.tiles + 2 * R] = pairs
-            buf[lay.wide_tiles:lay.wide_tiles + 2 * R] = pairs
+            counts = self._annotate(buf, lay, rows, np.ones(R, dtype=np.int32), starts, padded)
             return PackedStep(lay, turn, widths, Tc, Rc, Wc, W, [1] * R, (starts + 1).tolist(), state_slots,
-                              lay.max_tiles if padded else R, lay.max_wide_tiles if padded else R)
+                              counts)
         q_lens, kv_lens, state_slots = [], [], []
         row = 0
         want_at = 0
-        n_tiles = 0
-        tiles = []   # (last position + 1: the keys the tile walks, first row, rows)
-        wide_tiles = []
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = e.cache.length
@@ -252,13 +236,6 @@ class BatchBuilder:
             for w in e.want:
                 buf[lay.want + want_at] = row + int(w)
                 want_at += 1
-            for first in range(0, n, Q_TILE_ROWS):
-                rows_here = min(Q_TILE_ROWS, n - first)
-                tiles.append((start + first + rows_here, row + first, rows_here))
-                n_tiles += 1
-            for first in range(0, n, Q_WIDE_TILE_ROWS):
-                rows_here = min(Q_WIDE_TILE_ROWS, n - first)
-                wide_tiles.append((start + first + rows_here, row + first, rows_here))
             for g in range(len(widths)):
                 table = np.asarray(e.cache.tables[g], dtype=np.int32)
                 buf[lay.tables[g] + r * widths[g]:lay.tables[g] + r * widths[g] + len(table)] = table
@@ -269,18 +246,16 @@ class BatchBuilder:
             state_slots.append(e.cache.state_slot)
             row += n
         buf[lay.q_start + R:lay.q_start + Rc + 1] = row
-        # most keys first: the attention kernel pairs tile x with tile n - 1 - x
-        tiles.sort(key=lambda item: -item[0])
-        for at, (_, first_row, rows_here) in enumerate(tiles):
-            buf[lay.tiles + 2 * at] = first_row
-            buf[lay.tiles + 2 * at + 1] = rows_here
-        wide_tiles.sort(key=lambda item: -item[0])
-        for at, (_, first_row, rows_here) in enumerate(wide_tiles):
-            buf[lay.wide_tiles + 2 * at] = first_row
-            buf[lay.wide_tiles + 2 * at + 1] = rows_here
-        return PackedStep(lay, turn, widths, Tc, Rc, Wc, W, q_lens, kv_lens, state_slots,
-                          lay.max_tiles if padded else n_tiles,
-                          lay.max_wide_tiles if padded else len(wide_tiles))
+        q_counts = np.asarray(q_lens, dtype=np.int32)
+        first_rows = np.concatenate(([0], np.cumsum(q_counts)[:-1])).astype(np.int32)
+        starts = np.asarray(kv_lens, dtype=np.int32) - q_counts
+        counts = self._annotate(buf, lay, first_rows, q_counts, starts, padded)
+        return PackedStep(lay, turn, widths, Tc, Rc, Wc, W, q_lens, kv_lens, state_slots, counts)
+
+    def _annotate(self, buf, lay: BatchLayout, first_rows, counts, starts, padded: bool) -> List[int]:
+        """Let every annotation of the model's parts write its words (the buffer is zeroed)."""
+        return [int(note.fill(buf[at:at + words], first_rows, counts, starts, padded))
+                for note, at, words in zip(self.annotations, lay.notes, lay.note_words)]
 
     def set_ids(self, packed: "PackedStep", ids: Sequence[int]) -> None:
         """Put the token ids of a packed step of single tokens in place (row = entry)."""
@@ -324,7 +299,7 @@ class BatchBuilder:
             row_req=view(lay.row_req, Tc), q_start=view(lay.q_start, Rc + 1),
             kv_len=view(lay.kv_len, Rc), state_slot=view(lay.state_slot, Rc), groups=groups,
             q_lens=packed.q_lens, kv_lens=packed.kv_lens, state_slots=packed.state_slots,
-            q_tiles=view(lay.tiles, 2 * lay.max_tiles).view(lay.max_tiles, 2), n_q_tiles=packed.n_tiles,
-            q_wide_tiles=view(lay.wide_tiles, 2 * lay.max_wide_tiles).view(lay.max_wide_tiles, 2),
-            n_q_wide_tiles=packed.n_wide_tiles)
+            views={note.key: (note.view(view(at, words)), count)
+                   for note, at, words, count in zip(self.annotations, lay.notes, lay.note_words,
+                                                     packed.note_counts)})
         return ctx, view(lay.want, Wc), packed.n_want

@@ -68,16 +68,14 @@ class Engine:
                                  model.runtime, share_prefixes)
         self.bindings = self.cache.bindings(model.order)
         self.builder = BatchBuilder(self.cache, model.vocab_size, model.max_positions,
-                                    model.runtime.device)
+                                    model.runtime.device, model.batch_annotations())
         self.sampler = Sampler(model.runtime.device)
         self.max_positions = model.max_positions
         self.steps_run = 0
         self.steps_fed_on_device = 0      # of them: launched with a draw's ids before the host read them
         # a captured step bakes its launches: only mixers that say so may be replayed, and a
         # feed-forward may say that it cannot (a choice made on the host, say)
-        self.use_graphs = bool(use_graphs) and all(
-            getattr(block.mixer, "graph_safe", False) and getattr(block.feed_forward, "graph_safe", True)
-            for block in model.blocks)
+        self.use_graphs = bool(use_graphs) and model.graph_safe()
         self._graphs = {}
         self._graph_buffer = 0
         tables = sum(max_requests * (model.max_positions // page_size + 8) for _ in self.cache.groups)
@@ -143,8 +141,8 @@ class Engine:
         with prompt portions are when they bring a whole number of 128-token tiles, at
         least two: under a token budget most steps of a busy engine bring exactly the
         budget, and a replay spares the host the launches (a quarter of such a step's
-        time otherwise).  The kernel choice that depends on the longest portion is
-        part of the key."""
+        time otherwise).  What the model's parts say decides their kernels beyond the
+        sizes (`shape_key`) is part of the key."""
         widths = tuple(self._width(max(len(e.cache.tables[g]) for e in entries))
                        for g in range(len(self.cache.groups)))
         longest = max(len(e.tokens) for e in entries)
@@ -157,7 +155,8 @@ class Engine:
         padded = -(-total // 128) * 128
         if total < 256 or padded - total > total // 16 or sum(len(e.want) for e in entries) > requests:
             return None
-        return ("portions", padded, requests, widths, longest >= 96), padded, requests
+        kinds = self.model.shape_key([len(e.tokens) for e in entries])
+        return ("portions", padded, requests, widths, kinds), padded, requests
 
     def _step_captured(self, entries: List[StepEntry], key, tokens: int, requests: int) -> torch.Tensor:
         """A step whose launches are captured once per shape (padded batch size,

@@ -284,12 +284,26 @@ def rope_store(qkv, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d
         _stream()), "rope_store")
 
 
-def silu_gate(gu: torch.Tensor, out: torch.Tensor) -> None:
+# The activation of a gated feed-forward is a parameter of every kernel that applies one.
+ACTIVATIONS = {"silu": 0, "gelu_pytorch_tanh": 1, "relu": 2}
+
+
+def activation_tag(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise ValueError(f"the gated kernels know the activations {', '.join(ACTIVATIONS)}; found {name!r}") from None
+
+
+def silu_gate(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[t, i] = act(gu[t, i]) * gu[t, I + i] (the name is from the activation of the
+    architecture served; any of `ACTIVATIONS` is taken)."""
     n, inner = out.shape
     if gu.shape[1] != 2 * inner or gu.dtype != out.dtype:
         raise ValueError("silu_gate: input is [T, 2 I], output [T, I], same dtype")
     _check(_lib("elementwise").tokb200_silu_gate(
-        _ptr(gu), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _stream()), "silu_gate")
+        _ptr(gu), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _i(activation_tag(activation)), _stream()),
+        "silu_gate")
 
 
 def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page,
@@ -445,10 +459,10 @@ def ffn_small_m_splits(M: int, hidden: int, inner: int) -> int:
     return _ffn_plans[key]
 
 
-def ffn_small_m(x_in, x_out, delta, gain, eps, w_gate_up, w_down, out) -> None:
+def ffn_small_m(x_in, x_out, delta, gain, eps, w_gate_up, w_down, out, activation: str = "silu") -> None:
     """The gated feed-forward of few rows in one kernel: x_out = x_in + delta (delta as
     for rms_norm: [M, H] or float32 partial sums [S, M, H], or None), out [S', M, H] =
-    float32 partial sums over k of down(silu(gate(h)) * up(h)), h = rms_norm(x_out) * gain.
+    float32 partial sums over k of down(act(gate(h)) * up(h)), h = rms_norm(x_out) * gain.
     `w_gate_up` is in the interleaved row order of `interleave_gate_up`."""
     M, hidden = x_in.shape
     inner = w_down.shape[1]
@@ -471,7 +485,8 @@ def ffn_small_m(x_in, x_out, delta, gain, eps, w_gate_up, w_down, out) -> None:
     _check(_ffn_lib().tokb200_ffn_small_m(
         _ptr(x_in), _ptr(x_out), _ptr(delta), _i(1 if delta is not None and delta.dtype == torch.float32 else 0),
         _i(n_partials), _ll(stride), _ptr(gain), _f(eps), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
-        _ptr(out), _i(M), _i(hidden), _i(inner), _ptr(sync), _stream()), "ffn_small_m")
+        _ptr(out), _i(M), _i(hidden), _i(inner), _i(activation_tag(activation)), _ptr(sync), _stream()),
+        "ffn_small_m")
 
 
 def ffn_small_m_check() -> None:
@@ -592,7 +607,7 @@ PAIR_PLAIN, PAIR_GATED, PAIR_PARTIALS, PAIR_PLAIN_128 = 0, 1, 2, 3
 _PAIR = os.environ.get("TOKB200_GEMM_PAIR", "1") != "0"
 
 
-def gemm_tcgen05_pair(a, w, bias, out, kind: int) -> None:
+def gemm_tcgen05_pair(a, w, bias, out, kind: int, activation: str = "silu") -> None:
     """The product on pairs of CTAs (two SMs a tile of 256 rows x 256 columns, each loading half
     of the tile's rows of w).  PAIR_PLAIN: out [M,N] bfloat16 (+ bias); PAIR_GATED: out [M,N/2]
     bfloat16 = silu(gate) * up for w from `interleave_gate_up`; PAIR_PARTIALS: out [S,M,N]
@@ -617,8 +632,8 @@ def gemm_tcgen05_pair(a, w, bias, out, kind: int) -> None:
     if K % 8 or N % (4 if kind == PAIR_PARTIALS else 8):
         raise ValueError("gemm_tcgen05_pair: K a multiple of 8, N of 8 (4 for partial sums)")
     _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_pair(
-        _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(kind), _i(M), _i(N), _i(K), _i(splits), _stream()),
-        "gemm_tcgen05_pair")
+        _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(kind), _i(M), _i(N), _i(K), _i(splits),
+        _i(activation_tag(activation)), _stream()), "gemm_tcgen05_pair")
 
 
 def gemm_tcgen05_check() -> None:
@@ -642,8 +657,10 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         .reshape(2 * inner, k).contiguous()
 
 
-def gated_linear(x, w, out) -> None:
-    """out[M, N/2] = silu(x Wg^T) * (x Wu^T) for w from `interleave_gate_up`."""
+def gated_linear(x, w, out, activation: str = "silu") -> None:
+    """out[M, N/2] = act(x Wg^T) * (x Wu^T) for w from `interleave_gate_up`; the activation
+    is an epilogue parameter of whichever kernel the row count selects."""
+    act = _i(activation_tag(activation))
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -652,23 +669,23 @@ def gated_linear(x, w, out) -> None:
         raise ValueError("gated_linear: K a multiple of 8, N of 256, out [M, N/2]")
     if M <= SMALL_M_ROWS:
         _check(_lib("linear_small_m").tokb200_linear_small_m_gated(
-            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")
+            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), act, _stream()), "gated_linear")
     elif M <= 64:
         # too few rows to fill the 256-wide gated tiles over the SMs: the plain tensor-core
         # product over the same (interleaved) weight, then the activation on its output
         gu = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         gemm_tcgen05(x, w, None, gu)
         _check(_lib("elementwise").tokb200_silu_gate_interleaved(
-            _ptr(gu), _ptr(out), _i(M), _i(N // 2), _stream()), "silu_gate_interleaved")
+            _ptr(gu), _ptr(out), _i(M), _i(N // 2), act, _stream()), "silu_gate_interleaved")
     elif M >= 256 and _PAIR:
         # two tiles of rows and more: pairs of CTAs on tiles of 256 rows, each loading half of the
         # weight tile (a sixth fewer cycles than lone CTAs at 2,048 rows)
         _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_pair(
-            _ptr(x), _ptr(w), None, _ptr(out), _i(PAIR_GATED), _i(M), _i(N), _i(K), _i(1), _stream()),
+            _ptr(x), _ptr(w), None, _ptr(out), _i(PAIR_GATED), _i(M), _i(N), _i(K), _i(1), act, _stream()),
             "gated_linear")
     else:
         _check(_lib("gemm_tcgen05").tokb200_gemm_tcgen05_gated(
-            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _stream()), "gated_linear")
+            _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), act, _stream()), "gated_linear")
 
 
 def qkv_rope_small_m_supported(M: int, K: int, d: int, rotary: int) -> bool:

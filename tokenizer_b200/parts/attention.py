@@ -14,12 +14,13 @@ from __future__ import annotations
 import math
 import os
 
+import numpy as np
 import torch
 
 from ..config.spec import ConfigError
 from ..kernels import ops
 from ..weights.store import TensorSpec
-from .base import CacheNeed, KVNeed, build_part, register_part
+from .base import BatchAnnotation, CacheNeed, KVNeed, build_part, register_part
 from . import gemm_bf16
 from .linear import Linear
 
@@ -39,8 +40,63 @@ _FUSED_QKV = os.environ.get("TOKB200_QKV_ROPE", "separate") == "fused"
 _FUSED_NORM = os.environ.get("TOKB200_QKV_NORM", "fused") != "separate"
 
 
+class RowTiles(BatchAnnotation):
+    """The step's rows cut into tiles of up to `rows` consecutive rows of one request, as the
+    prompt-attention kernels take them: int32 [tiles, 2] = (first row, rows), the tile that
+    walks the most keys first (the kernels place blocks in that order, so the longest work
+    starts first).  Unused tiles of a padded step have no rows."""
+
+    def __init__(self, rows: int):
+        self.rows = rows
+        self.key = f"row_tiles_{rows}"
+
+    def capacity(self, n_tokens, n_requests):
+        return 2 * (n_tokens // self.rows + n_requests)
+
+    def fill(self, out, first_rows, counts, starts, padded):
+        n = len(counts)
+        if n and int(counts.max()) == 1:
+            # one tile of one row a request: a stable order, as a sort of tuples gives
+            order = np.argsort(-starts, kind="stable")
+            out[0:2 * n:2] = first_rows[order]
+            out[1:2 * n:2] = 1
+            made = n
+        else:
+            tiles = []    # (last position + 1: the keys the tile walks, first row, rows)
+            for first_row, count, start in zip(first_rows.tolist(), counts.tolist(), starts.tolist()):
+                for first in range(0, count, self.rows):
+                    here = min(self.rows, count - first)
+                    tiles.append((start + first + here, first_row + first, here))
+            tiles.sort(key=lambda item: -item[0])
+            for at, (_, first_row, here) in enumerate(tiles):
+                out[2 * at] = first_row
+                out[2 * at + 1] = here
+            made = len(tiles)
+        return len(out) // 2 if padded else made
+
+    def view(self, words):
+        return words.view(-1, 2)
+
+
+# the tiles of the two prompt kernels: 64 rows (mma.sync) and 128 rows (tcgen05)
+_TILES = RowTiles(ops.PREFILL_TILE_ROWS)
+_WIDE_TILES = RowTiles(ops.WIDE_TILE_ROWS)
+# portions from this length on go to the tcgen05 kernel (shorter ones would leave most of a
+# 128-row tile empty)
+_WIDE_FROM = 96
+
+
 class GQAttention:
     graph_safe = True   # launches depend on device-side metadata only
+
+    def batch_annotations(self):
+        return [_TILES, _WIDE_TILES]
+
+    def shape_key(self, q_lens):
+        """Which attention kernel a step of these portion lengths gets (part of the key under
+        which the engine keeps a captured step)."""
+        longest = max(q_lens) if q_lens else 0
+        return "single" if longest == 1 else ("wide" if longest >= _WIDE_FROM else "tiles")
 
     @staticmethod
     def tensors(spec):
@@ -170,20 +226,21 @@ class GQAttention:
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
             return
+        wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
         if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
-                ctx.q_wide_tiles is not None and ctx.max_q_len >= 96 and \
+                wide is not None and ctx.max_q_len >= _WIDE_FROM and \
                 ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
             # long portions on the tcgen05 kernel (128-row tiles, scores in tensor memory)
             ops.attention_tcgen05(
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                ctx.q_wide_tiles, ctx.n_q_wide_tiles, self.nh, self.nkv, self.d, group.page_size,
+                wide[0], wide[1], self.nh, self.nkv, self.d, group.page_size,
                 self.window, self.scale)
             return
-        if q.dtype == torch.bfloat16 and ctx.q_tiles is not None and \
+        if q.dtype == torch.bfloat16 and tiles is not None and \
                 ops.prefill_attention_supported(self.nh, self.nkv, self.d):
             ops.prefill_attention(
                 q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                ctx.q_tiles, ctx.n_q_tiles, self.nh, self.nkv, self.d, group.page_size,
+                tiles[0], tiles[1], self.nh, self.nkv, self.d, group.page_size,
                 self.window, self.scale)
             return
         ops.paged_attention_generic(

@@ -10,13 +10,21 @@ Interfaces (duck-typed; the classes below marked "interface" document them):
 
   mixer         tensors(spec); __init__(spec, store, runtime); cache_need();
                 forward(h [T,H], ctx: StepContext, cache: CacheBinding) -> delta
+                optional: batch_annotations() -> [BatchAnnotation] (integer data about the
+                batch that its kernels want packed with the step), shape_key(q_lens) -> hashable
+                (what, beyond the step's sizes, decides which kernels it launches: part of a
+                captured graph's key), advance_decode(ctx, cache) (move per-request state on
+                after a device-side decoding step), graph_safe = True (launches depend on
+                device-side metadata only)
   feed_forward  tensors(spec); __init__(spec, store, runtime); forward(h [T,H]) -> delta
                 (delta is [T,H] in the compute dtype, or float32 partial sums [S,T,H]
                 that the residual stream adds up in index order)
   norm          tensors(spec); __init__(spec, store, runtime);
                 forward(x f32 [T,H], delta=None, rows=None) -> h (compute dtype)
   position      tensors(spec); __init__(spec, store, runtime); tables used by the mixer
-  block         __init__(layer_spec, parts, runtime); forward(stream, ctx, cache)
+  block         PARTS = {name: category}; __init__(**parts by those names), kept as attributes
+                of those names (`mixer` is the part whose cache need the cache manager
+                serves); forward(stream, ctx, cache)
   embedding     forward(ids) -> x f32 [T,H];   head  forward(stream, rows) -> logits f32
 """
 from __future__ import annotations
@@ -129,13 +137,9 @@ class StepContext:
     kv_len: torch.Tensor         # [R] int32, tokens held after this step
     state_slot: torch.Tensor     # [R] int32
     groups: List[GroupView]
-    # the rows cut into tiles of up to 64 consecutive rows of one request:
-    # int32 [n_q_tiles, 2] = (first row, rows); None when the builder made none
-    q_tiles: Optional[torch.Tensor] = None
-    n_q_tiles: int = 0
-    # the same cut into tiles of up to 128 rows (the tcgen05 attention kernel's tile)
-    q_wide_tiles: Optional[torch.Tensor] = None
-    n_q_wide_tiles: int = 0
+    # what the model's parts asked to have packed with the batch (`BatchAnnotation`), by key:
+    # (the annotation's device view, the count its `fill` returned)
+    views: Dict[str, Tuple[Any, int]] = field(default_factory=dict)
     # host copies, for choosing kernels and for mixers that loop over requests
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)
@@ -148,6 +152,39 @@ class StepContext:
     @property
     def max_kv_len(self) -> int:
         return max(self.kv_lens) if self.kv_lens else 0
+
+
+class BatchAnnotation:
+    """Interface.  Integer data about a step's batch that a part's kernels want beside the
+    rows, positions and tables every part gets: a cut of the rows into tiles, a schedule, a
+    sorted order.  A part lists its annotations in `batch_annotations()`; the engine packs each
+    (once per `key`, however many layers ask) into the step's one metadata buffer, at an
+    offset that depends on the step's capacities only, so a captured graph finds it again; the
+    part reads `ctx.views[key]`.  The batch builder knows none of them.
+
+      key                         a string; equal keys are one annotation
+      capacity(T, R) -> int       int32 words for a step of up to T rows of R requests
+      fill(out, first_rows, counts, starts, padded) -> int
+                                  write the step's data into `out` (a zeroed numpy int32 array of
+                                  `capacity` words) from the requests' spans: request r brings
+                                  rows first_rows[r] .. + counts[r], the first at position
+                                  starts[r] (numpy arrays).  `padded`: the step will be replayed
+                                  from a graph, so the count returned must be the most the
+                                  capacities allow.  The count travels with the view.
+      view(words) -> Any          the device-side int32 words (a tensor of `capacity`) as the
+                                  part wants to see them
+    """
+
+    key = ""
+
+    def capacity(self, n_tokens: int, n_requests: int) -> int:
+        raise NotImplementedError
+
+    def fill(self, out, first_rows, counts, starts, padded: bool) -> int:
+        raise NotImplementedError
+
+    def view(self, words):
+        return words
 
 
 @dataclass

@@ -7,6 +7,11 @@ from .base import register_part
 
 
 class PreNormResidual:
+    # the parts this arrangement wants, by name, and the category each is built from; the
+    # model builds them from the layer's spec and hands them over as keyword arguments
+    PARTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm",
+             "feed_forward_norm": "norm"}
+
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm

@@ -1,6 +1,7 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), no biases; the gate and up
 products are one stacked product (reference: qwen-infer/src/model.rs:226-250,
-silu(z) = z * sigmoid(z))."""
+silu(z) = z * sigmoid(z)).  The activation is a parameter of the part and of the kernels
+behind it (`ops.ACTIVATIONS`); the architecture served asks for silu."""
 from __future__ import annotations
 
 import os
@@ -30,8 +31,10 @@ class GatedMLP:
 
     def __init__(self, spec, store, runtime):
         p, x = spec.params, spec.prefix
-        if p["activation"] != "silu":
-            raise ConfigError(f"gated feed-forward knows the silu activation, found {p['activation']}")
+        if p["activation"] not in ops.ACTIVATIONS:
+            raise ConfigError(f"gated feed-forward knows the activations {', '.join(ops.ACTIVATIONS)}; "
+                              f"found {p['activation']}")
+        self.activation = p["activation"]
         self.runtime = runtime
         self.inner = int(p["intermediate_size"])
         gate, up = store.get(x + ".gate_proj.weight"), store.get(x + ".up_proj.weight")
@@ -63,7 +66,8 @@ class GatedMLP:
         delta, stream.pending = stream.pending, None
         x_out = torch.empty_like(x)
         out = torch.empty((splits, rows, hidden), dtype=torch.float32, device=x.device)
-        ops.ffn_small_m(x, x_out, delta, gain, eps, self.gate_up_weight, self.down.weight, out)
+        ops.ffn_small_m(x, x_out, delta, gain, eps, self.gate_up_weight, self.down.weight, out,
+                        self.activation)
         stream.x, stream.pending = x_out, out
         return True
 
@@ -77,9 +81,9 @@ class GatedMLP:
     def forward(self, h):
         act = self.runtime.empty(h.shape[0], self.inner)
         if self.fused:
-            ops.gated_linear(h, self.gate_up_weight, act)
+            ops.gated_linear(h, self.gate_up_weight, act, self.activation)
         else:
-            ops.silu_gate(self.gate_up.forward(h), act)
+            ops.silu_gate(self.gate_up.forward(h), act, self.activation)
         return self.down.forward(act, partials_ok=True)
 
 

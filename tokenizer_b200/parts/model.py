@@ -7,20 +7,33 @@ from typing import List
 
 import torch
 
-from ..config.spec import ModelSpec
+from ..config.spec import ConfigError, ModelSpec
 from ..kernels import ops
 from ..weights.store import TensorSpec, WeightStore
 from .base import CacheBinding, ResidualStream, Runtime, StepContext, build_part, part_class
+
+
+def layer_parts(layer):
+    """[(category, PartSpec)] of a layer, in the order its arrangement names them.  The
+    arrangement (a registered block class) lists the names it wants and their categories in
+    `PARTS`; a layer that lacks one, or brings one more, is a configuration error."""
+    wanted = getattr(part_class("block", layer.block), "PARTS", None)
+    if wanted is None:
+        raise ConfigError(f"block {layer.block!r} does not say which parts it arranges (PARTS)")
+    missing = [n for n in wanted if n not in layer.parts]
+    unknown = [n for n in layer.parts if n not in wanted]
+    if missing or unknown:
+        raise ConfigError(f"block {layer.block!r} arranges {', '.join(wanted)}; the layer lacks "
+                          f"{', '.join(missing) or 'nothing'} and brings unknown {', '.join(unknown) or 'nothing'}")
+    return [(wanted[name], layer.parts[name]) for name in wanted]
 
 
 def declared_tensors(spec: ModelSpec) -> List[TensorSpec]:
     """Every tensor the model's parts declare, from the spec alone."""
     out = list(part_class("embedding", spec.embedding.kind).tensors(spec.embedding))
     for layer in spec.layers:
-        out += part_class("mixer", layer.mixer.kind).tensors(layer.mixer)
-        out += part_class("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
-        out += part_class("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
-        out += part_class("norm", layer.feed_forward_norm.kind).tensors(layer.feed_forward_norm)
+        for category, part in layer_parts(layer):
+            out += part_class(category, part.kind).tensors(part)
     out += part_class("norm", spec.final_norm.kind).tensors(spec.final_norm)
     out += part_class("head", spec.head.kind).tensors(spec.head)
     return out
@@ -63,11 +76,10 @@ class DecoderModel:
         self.embedding = build_part("embedding", spec.embedding, store, runtime)
         self.blocks = []
         for layer in spec.layers:
-            self.blocks.append(part_class("block", layer.block)(
-                build_part("mixer", layer.mixer, store, runtime),
-                build_part("feed_forward", layer.feed_forward, store, runtime),
-                build_part("norm", layer.mixer_norm, store, runtime),
-                build_part("norm", layer.feed_forward_norm, store, runtime)))
+            block_cls = part_class("block", layer.block)
+            built = {name: build_part(category, layer.parts[name], store, runtime)
+                     for name, (category, _) in zip(block_cls.PARTS, layer_parts(layer))}
+            self.blocks.append(block_cls(**built))
         self.final_norm = build_part("norm", spec.final_norm, store, runtime)
         head_cls = part_class("head", spec.head.kind)
         tied = self.embedding.table if spec.head.params.get("tied_to") else None
@@ -85,6 +97,38 @@ class DecoderModel:
         if self._side is None:
             self._side = torch.cuda.Stream(device=self.runtime.device)
         return _Prefetcher(self._side)
+
+    def parts(self):
+        """Every built part of every block (the mixer first), block by block."""
+        for block in self.blocks:
+            for name in type(block).PARTS:
+                yield name, getattr(block, name)
+
+    def batch_annotations(self):
+        """The annotations the parts want packed with every step, one per key."""
+        found = {}
+        for _, part in self.parts():
+            for note in getattr(part, "batch_annotations", lambda: [])():
+                found.setdefault(note.key, note)
+        return list(found.values())
+
+    def shape_key(self, q_lens):
+        """What, beyond its sizes, decides a step's kernels: the distinct answers of the parts
+        that have a say (a captured step is kept under it)."""
+        kinds = []
+        for _, part in self.parts():
+            say = getattr(part, "shape_key", None)
+            if say is not None:
+                kind = say(q_lens)
+                if kind not in kinds:
+                    kinds.append(kind)
+        return tuple(kinds)
+
+    def graph_safe(self) -> bool:
+        """Whether a step's launches depend on device-side metadata alone, so that a captured
+        step can be replayed: every mixer must say so (`graph_safe = True`); any other part may
+        say that it is not."""
+        return all(getattr(part, "graph_safe", name != "mixer") for name, part in self.parts())
 
     def cache_needs(self):
         """One entry per call of the order: the need of the mixer that runs
