@@ -3,6 +3,7 @@
 weights on one B200.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+                    [--config 0.5b|1.5b-mixed|7b]
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
@@ -11,6 +12,13 @@ entry point (`generate_batch`) runs: prompts come from the host, every step's
 positions, slots and block tables are copied from pinned host memory and its
 sampled ids are read back by the host, which judges the ends one step behind.  The line also carries the prefill of 2,048 tokens, the decode
 roofline and decode at batch 1 and 64.
+
+`--config 7b` prints the same line at Qwen2.5-7B sizes (prefill of 2,048 tokens, decoding at batch
+1/8/64 with 8,192-token contexts); `--config 1.5b-mixed` runs 32 requests of random prompt lengths
+in [64, 2048] with 128 new tokens each through the scheduler under a budget of 512 tokens a step,
+half of them beginning with one of four shared 256-token beginnings, at Qwen2.5-1.5B sizes.  Both
+first compare a few logits rows of a 2-layer model of the same layer sizes with the plain
+implementation under tests/, and refuse to time an engine that fails that.
 """
 import argparse
 import json
@@ -29,6 +37,15 @@ SIZES = dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14, num_
              head_dim=64, intermediate_size=4864, vocab_size=151936, rope_theta=1000000.0,
              rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768,
              use_sliding_window=False, sliding_window=32768, max_window_layers=24)
+# BASELINE.json configs[3] and configs[4]: Qwen2.5-1.5B and Qwen2.5-7B sizes
+SIZES_1_5B = dict(num_hidden_layers=28, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                  head_dim=128, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0,
+                  rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768,
+                  use_sliding_window=False, sliding_window=32768, max_window_layers=28)
+SIZES_7B = dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                head_dim=128, intermediate_size=18944, vocab_size=152064, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768,
+                use_sliding_window=False, sliding_window=32768, max_window_layers=28)
 PROMPT_LEN, NEW_TOKENS, PREFILL_TOKENS, PAGE = 512, 256, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -106,6 +123,64 @@ def prefill_flops(cfg, layers, tokens):
     return layers * (linear + attention) + 2 * h * cfg["vocab_size"]
 
 
+def full_config(sizes, layers=None):
+    layers = layers or sizes["num_hidden_layers"]
+    return dict(sizes, num_hidden_layers=layers, max_window_layers=layers,
+                architectures=["Qwen2ForCausalLM"], hidden_act="silu")
+
+
+def gate_on_logits(sizes, what):
+    """Before a configuration is timed: a 2-layer model of its layer sizes (random weights
+    through a model folder) must give, in bfloat16, the plain implementation's logits for a
+    prompt step, a portion that continues it and decoding steps of three requests together.
+    Returns the largest error as a fraction of the largest logit; raises if it passes 2 %."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_qwen2 as plain
+    config = tb.Qwen2Config.from_dict(dict(full_config(sizes, 2), max_position_embeddings=1024))
+    gen = torch.Generator().manual_seed(99)
+    ids = torch.randint(0, config.vocab_size, (150,), generator=gen).tolist()
+    rows = [16, 63, 99, 139, 140, 141, 142]
+    with tempfile.TemporaryDirectory() as folder:
+        tb.write_random_model(folder, config, seed=3)
+        cfg, w = plain.load_folder(folder)
+        want = plain.all_logits(cfg, w, ids[:143], rows=rows)
+        del w
+        model = tb.load_model(folder, dtype="bfloat16", device="cuda:0")
+    at = {r: i for i, r in enumerate(rows)}
+    engine = tb.engine_for(model, 3 * 160, PAGE, max_requests=3, share_prefixes=False)
+    caches = [engine.cache.open(("gate", i)) for i in range(3)]
+    lengths = [140, 100, 17]                         # each a beginning of the same sequence
+    worst = 0.0
+    scale = float(want.abs().max())
+
+    def check(logits, positions):
+        nonlocal worst
+        got = logits.float().cpu()
+        for row, position in zip(got, positions):
+            worst = max(worst, float((row - want[at[position]]).abs().max()) / scale)
+
+    engine.cache.reserve(caches[0], 100)
+    check(engine.step([StepEntry(caches[0], ids[:100], [63, 99])]), [63, 99])
+    engine.cache.reserve(caches[0], 40)
+    for c, n in zip(caches[1:], lengths[1:]):
+        engine.cache.reserve(c, n)
+    check(engine.step([StepEntry(caches[0], ids[100:140], [39]), StepEntry(caches[1], ids[:100], [99]),
+                       StepEntry(caches[2], ids[:17], [16])]), [139, 99, 16])
+    for step in range(3):
+        engine.cache.reserve(caches[0], 1)
+        check(engine.step([StepEntry(caches[0], [ids[140 + step]], [0])]), [140 + step])
+    engine.check()
+    del engine, model
+    torch.cuda.empty_cache()
+    if not worst <= 0.02:
+        raise SystemExit(f"bench.py: {what}: the engine's logits are off by {worst:.3%} of the largest logit "
+                         f"against the plain implementation; nothing is timed")
+    return worst
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -114,6 +189,12 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b"],
+                        help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
+                             "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes")
+    parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
+    parser.add_argument("--skip-gate", action="store_true",
+                        help="do not compare with the plain implementation first (profiling runs)")
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     parser.add_argument("--only-decode", action="store_true",
                         help="time the decode steps only and print a short line (for profiling)")
@@ -130,6 +211,10 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus)
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.config == "7b":
+        return run_7b(args)
+    if args.config == "1.5b-mixed":
+        return run_mixed(args)
     args.steps = max(1, min(args.steps, NEW_TOKENS - args.warmup - 1))
 
     import torch
@@ -290,6 +375,211 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
+    }
+    engine.check()                 # a bounded wait that ran out inside a kernel invalidates the numbers
+    print(json.dumps(line))
+    return 0
+
+
+def run_7b(args):
+    """Qwen2.5-7B sizes: a prefill of 2,048 tokens, decoding at batch 1/8/64 with `--context`
+    (8,192) tokens held by every request.  Weights are drawn on the device (15.2 GB in
+    bfloat16 would be a long file); the cache holds the live requests of the largest batch."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    from tokenizer_b200.kernels.ops import counter
+
+    torch.cuda.set_device(0)
+    layers = args.layers if args.layers != SIZES["num_hidden_layers"] else SIZES_7B["num_hidden_layers"]
+    gate = None if args.skip_gate else gate_on_logits(SIZES_7B, "7B layer sizes")
+    cfg = full_config(SIZES_7B, layers)
+    config = tb.Qwen2Config.from_dict(cfg)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(1234)
+    model = tb.random_model(config, seed=2, dtype="bfloat16", device="cuda:0")
+    context, steps = args.context, max(4, min(args.steps, 64))
+    batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    per_request = context + steps + args.warmup + 2 * PAGE
+    engine = tb.engine_for(model, max(batches) * per_request, PAGE, max_requests=max(batches),
+                           share_prefixes=False)
+
+    def random_ids(n):
+        return torch.randint(0, config.vocab_size, (n,), generator=gen).tolist()
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop), out
+
+    prefill_ms = []
+    for rep in range(3 + 3):
+        cache = engine.cache.open(("prefill", rep))
+        engine.cache.reserve(cache, PREFILL_TOKENS)
+        entry = StepEntry(cache, random_ids(PREFILL_TOKENS), [PREFILL_TOKENS - 1])
+        ms, _ = timed(lambda: engine.step([entry]))
+        if rep >= 3:
+            prefill_ms.append(ms)
+        engine.cache.close(cache)
+    prefill_best = sorted(prefill_ms)[len(prefill_ms) // 2]
+
+    results = {}
+    clocks_main = None
+    for batch in batches:
+        caches = [engine.cache.open(("decode", batch, i)) for i in range(batch)]
+        nexts = []
+        # contexts in steps of 2,048 tokens a request, four requests a step
+        for lo in range(0, batch, 4):
+            group = caches[lo:lo + 4]
+            prompts = [random_ids(context) for _ in group]
+            for done in range(0, context, 2048):
+                take = min(2048, context - done)
+                for c in group:
+                    engine.cache.reserve(c, take)
+                last = done + take == context
+                logits = engine.step([StepEntry(c, p[done:done + take], [take - 1] if last else [])
+                                      for c, p in zip(group, prompts)])
+            nexts += engine.sampler.greedy(logits).tolist()
+        ids = engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, nexts)], args.warmup)
+        clocks = ClockSampler() if batch == args.batch else None
+        if clocks:
+            clocks.start()
+            time.sleep(0.25)
+        launches = counter.launches
+        ms, ids = timed(lambda: engine.decode_steps([StepEntry(c, [t]) for c, t in zip(caches, ids[-1])], steps))
+        launches = counter.launches - launches
+        if clocks:
+            clocks_main = clocks.stop()
+        mean_context = caches[0].length - steps / 2
+        step_bytes = weight_bytes(cfg, layers) + batch * mean_context * kv_bytes_per_token(cfg, layers)
+        results[batch] = {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+                          "frac": step_bytes / (ms / steps / 1e3) / 1e9 / pk["hbm_gbs"],
+                          "gbs": step_bytes / (ms / steps / 1e3) / 1e9, "context": int(mean_context)}
+        for c in caches:
+            engine.cache.close(c)
+    engine.check()
+    main_run = results[args.batch]
+    line = {
+        "metric": "decode tok/s (Qwen2.5-7B sizes, batch %d, %d-token context)" % (args.batch, context),
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device (seed 2), uniform random token ids",
+        "config": {"model": "Qwen2.5-7B sizes", "layers": layers, "layers_of_config": SIZES_7B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "seq_len": context, "context_at_timing": main_run["context"],
+                   "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "each step reads > 126 MB of weights (inputs larger than L2)", "peaks": pk["source"],
+                   "logits_gate": gate},
+        "clocks": clocks_main, "gpu_launches": main_run["launches"],
+        "prefill": {"value": PREFILL_TOKENS / (prefill_best / 1e3), "tokens": PREFILL_TOKENS, "ms": prefill_best,
+                    "frac": prefill_flops(cfg, layers, PREFILL_TOKENS) / (prefill_best / 1e3)
+                    / (pk["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": main_run["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": main_run["frac"]},
+        "points": {f"decode_b{b}": r["tok_s"] for b, r in results.items()},
+        "points_frac": {f"decode_b{b}": r["frac"] for b, r in results.items()},
+        "points_ms": {f"decode_b{b}": r["ms_per_step"] for b, r in results.items()},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_mixed(args):
+    """BASELINE.json configs[3]: 32 requests at Qwen2.5-1.5B sizes, prompt lengths uniform in
+    [64, 2048] from a fixed seed, 128 new tokens each, continuous batching under a budget of 512
+    tokens a step, half of the prompts beginning with one of four shared beginnings of 256 tokens
+    (whole pages, taken over from the first request that computed them).  Host tokens in, host
+    ids out; the run is timed by the wall clock between two device synchronisations."""
+    import torch
+    import tokenizer_b200 as tb
+
+    torch.cuda.set_device(0)
+    layers = args.layers if args.layers != SIZES["num_hidden_layers"] else SIZES_1_5B["num_hidden_layers"]
+    gate = None if args.skip_gate else gate_on_logits(SIZES_1_5B, "1.5B layer sizes")
+    cfg = full_config(SIZES_1_5B, layers)
+    config = tb.Qwen2Config.from_dict(cfg)
+    pk = peaks()
+    model = tb.random_model(config, seed=2, dtype="bfloat16", device="cuda:0")
+    n_requests, new_tokens, budget, shared_len = 32, 128, 512, 256
+
+    def workload(seed):
+        gen = torch.Generator().manual_seed(seed)
+        lengths = torch.randint(64, 2049, (n_requests,), generator=gen).tolist()
+        beginnings = [torch.randint(0, config.vocab_size, (shared_len,), generator=gen).tolist() for _ in range(4)]
+        prompts = []
+        for i, n in enumerate(lengths):
+            ids = torch.randint(0, config.vocab_size, (n,), generator=gen).tolist()
+            if i % 2 == 0:                         # every other request starts with a shared beginning
+                ids = (beginnings[(i // 2) % 4] + ids)[:max(n, shared_len + 1)]
+            prompts.append(ids)
+        return prompts
+
+    def run(prompts, share):
+        pool = sum(len(p) + new_tokens + PAGE for p in prompts)
+        engine = tb.engine_for(model, pool, PAGE, max_requests=n_requests, share_prefixes=share)
+        scheduler = tb.Scheduler(engine, max_batch_size=n_requests, token_budget=budget)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ids = [scheduler.add_request(p, tb.GenerateParams.greedy(new_tokens)) for p in prompts]
+        finished = scheduler.run()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        engine.check()
+        assert all(len(finished[i].tokens) == new_tokens for i in ids)
+        return seconds, scheduler.stats, engine
+
+    run(workload(7), True)                          # warm-up on other tokens: compiles, captures shapes
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.25)
+    prompts = workload(1234)
+    seconds, stats, engine = run(prompts, True)
+    clock_record = clocks.stop()
+    seconds_private, stats_private, _ = run(workload(1234), False)
+    prompt_tokens = sum(len(p) for p in prompts)
+    # the least a device of the measured peaks would take: every step reads the weights once,
+    # every decoded token its request's keys and values; every token run costs its products
+    # and its attention over the keys before it
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    q, kv, inner = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d, cfg["intermediate_size"]
+    per_token_linear = 2 * layers * ((q + 2 * kv) * h + h * q + 3 * inner * h)
+    flops = stats.tokens_run * per_token_linear + n_requests * new_tokens * 2 * h * cfg["vocab_size"]
+    kv_read = 0
+    for p in prompts:
+        flops += layers * 4 * q * (len(p) + new_tokens) ** 2 / 2
+        kv_read += sum(len(p) + i for i in range(new_tokens)) * kv_bytes_per_token(cfg, layers)
+    bytes_read = stats.steps * weight_bytes(cfg, layers) + kv_read
+    bound_s = max(bytes_read / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops_sustained"] * 1e12))
+    line = {
+        "metric": "generated tok/s (Qwen2.5-1.5B sizes, 32 requests, prompts U[64,2048], 128 new tokens, "
+                  "512-token budget, shared beginnings)",
+        "value": n_requests * new_tokens / seconds, "unit": "tokens/s", "n_gpus": 1, "steps": stats.steps,
+        "warmup": 1, "ms_per_step": 1e3 * seconds / stats.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device (seed 2), uniform random token ids (seed 1234)",
+        "config": {"model": "Qwen2.5-1.5B sizes", "layers": layers,
+                   "layers_of_config": SIZES_1_5B["num_hidden_layers"], "hidden": h,
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": d,
+                   "intermediate": inner, "vocab": cfg["vocab_size"], "requests": n_requests,
+                   "prompt_tokens": prompt_tokens, "new_tokens": new_tokens, "token_budget": budget,
+                   "page_size": PAGE, "parallelism": "single GPU", "peaks": pk["source"], "logits_gate": gate},
+        "clocks": clock_record,
+        "mixed": {"seconds": seconds, "total_tok_s": (prompt_tokens + n_requests * new_tokens) / seconds,
+                  "tokens_run": stats.tokens_run, "shared_prefix_tokens": stats.shared_prefix_tokens,
+                  "preemptions": stats.preemptions, "max_running": stats.max_running,
+                  "peak_pages": stats.peak_pages, "steps_fed_on_device": engine.steps_fed_on_device,
+                  "seconds_without_sharing": seconds_private, "tokens_run_without_sharing": stats_private.tokens_run,
+                  "bound_seconds": bound_s, "frac": bound_s / seconds},
+        "e2e": {"value": n_requests * new_tokens / seconds, "unit": "tokens/s",
+                "h2d_bytes_per_step": engine.builder.last_bytes, "d2h_bytes_per_step": 4 * n_requests,
+                "note": "the run IS end to end: host prompts in, host ids out, through Scheduler"},
     }
     print(json.dumps(line))
     return 0

@@ -302,3 +302,22 @@ def test_the_head_waits_while_every_request_slot_is_held_elsewhere():
     assert out[rid].tokens == solo(prompt, params).tokens
     engine.cache.close(held[1])
     engine.cache.check()
+
+
+def test_requests_that_arrive_together_still_share_a_beginning():
+    """Four requests with the same 20-token beginning arrive in one iteration, under a budget
+    that lets only the first run at once.  The pages of the beginning are published as soon as
+    the first request's portion has computed them, and the others, which found nothing when
+    they were admitted, take them over when their own first portion comes up.  Ids equal solo."""
+    engine = FakeEngine(num_pages=128, page_size=4, share_prefixes=True)
+    s = Scheduler(engine, max_batch_size=4, token_budget=16)
+    begin = random_ids(20, 50, 21)
+    prompts = [begin + random_ids(6 + 3 * i, 50, 30 + i) for i in range(3)] + [begin + [7]]
+    ids = [s.add_request(p, GenerateParams(max_tokens=5)) for p in prompts]
+    out = run_checked(s)
+    for rid, p in zip(ids, prompts):
+        assert out[rid].tokens == solo(p, GenerateParams(max_tokens=5), page_size=4).tokens
+    # the first computed the beginning itself, 16 tokens of it in its first step; the second came up
+    # in the next step, when only those 16 were published; the others took over all 20
+    assert s.stats.shared_prefix_tokens == 16 + 20 + 20
+    assert s.stats.tokens_run == sum(len(p) + 4 for p in prompts) - 56

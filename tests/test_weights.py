@@ -131,3 +131,31 @@ def test_a_folder_of_several_files_with_an_index(tmp_path):
     (parts / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}}))
     with pytest.raises(WeightError, match="weight_map"):
         WeightStore.from_folder(str(parts))
+
+
+def test_seeded_tensors_stand_in_for_a_file():
+    """Random weights without a folder: each tensor is a function of (seed, name), drawn when
+    asked for; the store checks shapes without drawing anything."""
+    import torch
+    from tokenizer_b200.weights import SeededTensors, TensorSpec, WeightError, WeightStore
+    specs = [TensorSpec("a.weight", (40, 30)), TensorSpec("n.weight", (30,), "one_plus_normal"),
+             TensorSpec("z.bias", (5,), "zeros")]
+    source = SeededTensors(specs, seed=5)
+    drawn = []
+    original = SeededTensors.__getitem__
+    SeededTensors.__getitem__ = lambda self, name: drawn.append(name) or original(self, name)
+    try:
+        store = WeightStore(source)
+        store.check(specs)
+        assert drawn == []
+        with pytest.raises(WeightError, match="wrong shape: a.weight"):
+            store.check([TensorSpec("a.weight", (40, 31))] + specs[1:])
+        a = store.get("a.weight")
+    finally:
+        SeededTensors.__getitem__ = original
+    assert a.dtype == torch.bfloat16 and tuple(a.shape) == (40, 30)
+    assert torch.equal(a, store.get("a.weight"))
+    assert not torch.equal(a, WeightStore(SeededTensors(specs, seed=6)).get("a.weight"))
+    assert abs(float(a.float().std()) - 0.02) < 0.004
+    assert abs(float(store.get("n.weight").float().mean()) - 1.0) < 0.02
+    assert float(store.get("z.bias").abs().sum()) == 0.0

@@ -11,11 +11,11 @@ from typing import Callable, List, Optional, Sequence, Union
 
 from .engine.generate import Control, Generated, GenerateParams, StopReason
 from .engine.scheduler import Scheduler
-from .engine.step import Engine, load_model
+from .engine.step import Engine, load_model, random_model
 
 __all__ = ["Control", "Engine", "Generated", "GenerateParams", "StopReason", "generate",
            "generate_batch", "generate_with", "greedy_tokens", "load_eos_token_ids", "load_model",
-           "engine_for"]
+           "engine_for", "random_model"]
 
 
 def load_eos_token_ids(path: str) -> List[int]:

@@ -158,6 +158,12 @@ class Scheduler:
                            for r, n in plan]
                 logits = self.engine.step(entries)
         if plan:
+            for r, n in plan:
+                # whole pages of a prompt are offered to later requests as soon as they are
+                # computed, not only when the prompt is complete (a long prompt runs over
+                # several steps, and requests behind it may begin with the same tokens)
+                if not r.published and n > 1 and r.cache.length < len(r.prompt):
+                    self.cache.publish_prompt(r.cache, r.prompt[:r.cache.length])
             self.stats.steps += 1
             self.stats.tokens_run += sum(n for _, n in plan)
             self.stats.max_running = max(self.stats.max_running, len(self.running))
@@ -275,6 +281,14 @@ class Scheduler:
             head.cache = cache
             self.running.append(self.waiting.popleft())
 
+    def _adopt_late(self, r: _Request) -> None:
+        """A running request that holds nothing yet looks once more for pages that hold the
+        beginning of its context: requests admitted in the same iteration as the one that
+        computes a shared beginning find nothing at admission, but by the time their first
+        portion gets a share of a step, those pages have been published."""
+        if r.cache.length == 0 and not any(r.cache.tables):
+            self.stats.shared_prefix_tokens += self.cache.adopt_prefix(r.cache, r.context[:-1])
+
     def _shares(self) -> List:
         """(request, tokens this step): decoding requests first, then portions
         of contexts, oldest first, under the token budget."""
@@ -286,10 +300,15 @@ class Scheduler:
                 shares.append((r, 1))
                 left -= 1
         for r in by_age:
+            if left > 0 and len(r.context) - r.cache.length > 1:
+                self._adopt_late(r)
             remaining = len(r.context) - r.cache.length
             if remaining > 1 and left > 0:
                 shares.append((r, min(remaining, left)))
                 left -= shares[-1][1]
+            elif remaining == 1 and left > 0 and all(r is not s[0] for s in shares):
+                shares.append((r, 1))          # all but its last token were taken over just now
+                left -= 1
         return shares
 
     def _plan_and_reserve(self) -> List:

@@ -52,6 +52,24 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
     return model
 
 
+def random_model(config, seed: int, dtype="bfloat16", device="cuda:0") -> DecoderModel:
+    """The model of a typed configuration with seeded random weights drawn on the device, no
+    folder in between (for sizes whose file would be many gigabytes).  Same parts, same checks
+    as `load_model`; the values are not those of `write_random_model` for the same seed."""
+    from ..parts.model import declared_tensors
+    from ..weights import SeededTensors
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise KernelError(
+            "tokenizer_b200 runs on a CUDA GPU (sm_100a) only; no GPU is visible to this process")
+    spec = config.model_spec()
+    store = WeightStore(SeededTensors(declared_tensors(spec), seed, device), "<seeded random weights>")
+    with torch.cuda.device(device):
+        model = DecoderModel(spec, store, Runtime(device, parse_dtype(dtype)))
+    model.config = config
+    return model
+
+
 class PreparedDecode:
     """A decoding step whose metadata is packed and whose tokens are still to come."""
 
@@ -133,7 +151,10 @@ class Engine:
             b *= 2
         return b
 
-    PORTION_GRAPHS = 6       # captured shapes of prompt steps kept (each holds its activations)
+    # captured shapes of prompt steps are kept while their tokens add up to at most this (each
+    # holds its own activations, which grow with its tokens: a 2,048-token shape of a small
+    # model some hundred megabytes, a 512-token shape a quarter of that)
+    PORTION_GRAPH_TOKENS = 24576
 
     def _captured_shape(self, entries: List[StepEntry]):
         """(key, padded tokens, padded requests) when steps of this shape are replayed
@@ -143,12 +164,14 @@ class Engine:
         budget, and a replay spares the host the launches (a quarter of such a step's
         time otherwise).  What the model's parts say decides their kernels beyond the
         sizes (`shape_key`) is part of the key."""
-        widths = tuple(self._width(max(len(e.cache.tables[g]) for e in entries))
-                       for g in range(len(self.cache.groups)))
+        pages = [max(len(e.cache.tables[g]) for e in entries) for g in range(len(self.cache.groups))]
         longest = max(len(e.tokens) for e in entries)
         if longest == 1:
             rows = self._bucket(len(entries))
-            return (rows, widths), rows, rows
+            return (rows, tuple(self._width(n) for n in pages)), rows, rows
+        # the kernels for portions size their grids from the rows, not from the tables' reach:
+        # powers of two keep the shapes of a busy scheduler few
+        widths = tuple(self._bucket(n, 8) for n in pages)
         total = sum(len(e.tokens) for e in entries)
         requests = self._bucket(len(entries))
         # up to the next whole tile with idle rows, where that wastes little (a sixteenth)
@@ -175,8 +198,8 @@ class Engine:
             # first use: run it once plainly (this also compiles what is missing)
             if key[0] == "portions":
                 kept = [k for k in self._graphs if k[0] == "portions"]
-                if len(kept) >= self.PORTION_GRAPHS:
-                    del self._graphs[kept[0]]          # the oldest shape makes room
+                while kept and sum(k[1] for k in kept) + key[1] > self.PORTION_GRAPH_TOKENS:
+                    del self._graphs[kept.pop(0)]      # the oldest shapes make room
             self._graphs[key] = {}
             return self.model.forward(ctx, self.bindings, want_rows)[:n_want]
         if "graph" not in slot:

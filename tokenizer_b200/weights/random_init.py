@@ -38,6 +38,45 @@ def random_tensors(specs, seed: int, scale: Optional[Dict[str, float]] = None,
     return tensors
 
 
+class SeededTensors:
+    """A model's random weights without a file: a mapping from tensor name to a tensor drawn
+    when it is asked for, on `device`, from a generator seeded by (seed, name), so that a
+    tensor is a function of the configuration, the seed and its own name alone.  For models
+    whose weights would be many gigabytes on disk (a benchmark at 7B sizes); `WeightStore`
+    takes it in place of a dict.  The values differ from `write_random_model`'s (one
+    generator on the CPU, in sorted-name order): the two modes do not mix."""
+
+    def __init__(self, specs, seed: int, device="cpu", dtype: torch.dtype = torch.bfloat16):
+        self.specs = {spec.name: spec for spec in specs}
+        self.seed, self.device, self.dtype = int(seed), torch.device(device), dtype
+
+    def __contains__(self, name) -> bool:
+        return name in self.specs
+
+    def __iter__(self):
+        return iter(self.specs)
+
+    def __len__(self) -> int:
+        return len(self.specs)
+
+    def shape_of(self, name: str):
+        return tuple(self.specs[name].shape)
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        import zlib
+        spec = self.specs[name]
+        if spec.init == "zeros":
+            return torch.zeros(spec.shape, dtype=self.dtype, device=self.device)
+        generator = torch.Generator(device=self.device)
+        generator.manual_seed((self.seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
+        value = torch.randn(spec.shape, generator=generator, dtype=torch.float32, device=self.device) * spec.std
+        if spec.init == "one_plus_normal":
+            value = value + 1.0
+        elif spec.init != "normal":
+            raise ValueError(f"tensor {spec.name}: unknown init {spec.init!r}")
+        return value.to(self.dtype)
+
+
 def write_random_model(folder: str, config, seed: int,
                        scale: Optional[Dict[str, float]] = None,
                        dtype: torch.dtype = torch.bfloat16) -> str:

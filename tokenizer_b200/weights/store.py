@@ -85,9 +85,9 @@ class WeightStore:
         unexpected = sorted(
             name for name in self.tensors if name not in wanted and name not in ignorable)
         wrong = sorted(
-            (name, tuple(self.tensors[name].shape), shape)
+            (name, self._shape(name), shape)
             for name, shape in wanted.items()
-            if name in self.tensors and tuple(self.tensors[name].shape) != shape)
+            if name in self.tensors and self._shape(name) != shape)
         if not (missing or unexpected or wrong):
             return
         lines = [f"{self.source} does not fit the model:"]
@@ -98,6 +98,11 @@ class WeightStore:
         for name, found, shape in wrong:
             lines.append(f"  wrong shape: {name} is {list(found)}, the model needs {list(shape)}")
         raise WeightError("\n".join(lines))
+
+    def _shape(self, name: str) -> Tuple[int, ...]:
+        """A tensor's shape; a source that makes tensors on demand tells it without making one."""
+        shape_of = getattr(self.tensors, "shape_of", None)
+        return tuple(shape_of(name)) if shape_of is not None else tuple(self.tensors[name].shape)
 
     def get(self, name: str) -> torch.Tensor:
         """The tensor as stored (see `_keep_precision`), on the CPU."""
