@@ -1155,3 +1155,111 @@ def test_a_wait_that_runs_out_returns_and_is_reported(monkeypatch, tmp_path):
     engine.check()                           # reported once; the engine goes on
     after = engine.step([StepEntry(cache, [7], [0])])
     assert engine.sample(after, [0.0], [1.0], [0.0]) and bool(torch.isfinite(after).all())
+
+
+def layer_reference(x, delta, gain1, eps1, w_qkv, b_qkv, pos, dense, row_req, w_o, gain2, eps2, gate, up, down,
+                    nh, nkv, d, window, theta=10000.0):
+    """A pre-norm decoder layer for rows of one token each, in float64 with roundings to bfloat16
+    where the kernels round (normed rows, q/k/v, attention output, activation).  `dense[r]` holds
+    request r's keys and values up to the row's position (the entry AT the position is replaced by
+    the new key and value).  Returns x_mid, x_out, the feed-forward's output, new keys, new values."""
+    def bf(t):
+        return t.float().to(torch.bfloat16).double()
+    x1 = x.double() + (delta.double().sum(0) if delta is not None and delta.dim() == 3 else
+                       (delta.double() if delta is not None else 0.0))
+    h = bf(x1 / torch.sqrt((x1 * x1).mean(-1, keepdim=True) + eps1) * gain1.double())
+    qkv = h @ w_qkv.double().t() + (b_qkv.double() if b_qkv is not None else 0.0)
+    M = x.shape[0]
+    half = d // 2
+    inv_freq = torch.tensor([1.0 / (theta ** (i / d)) for i in range(0, d, 2)], dtype=torch.float64).float()
+    x2 = torch.zeros_like(x1)
+    k_new, v_new, mixed = [], [], torch.zeros(M, nh * d, dtype=torch.float64)
+    for m in range(M):
+        ang = torch.tensor(float(pos[m]), dtype=torch.float32) * inv_freq
+        cos, sin = torch.cos(ang).double(), torch.sin(ang).double()
+
+        def rot(v):
+            a, b = v[..., :half], v[..., half:]
+            return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+        q = bf(rot(qkv[m, :nh * d].view(nh, d)))
+        k = bf(rot(qkv[m, nh * d:(nh + nkv) * d].view(nkv, d)))
+        v = bf(qkv[m, (nh + nkv) * d:].view(nkv, d))
+        k_new.append(k)
+        v_new.append(v)
+        if row_req[m] < 0:
+            continue
+        keys, values = dense[row_req[m]][0].double().clone(), dense[row_req[m]][1].double().clone()
+        keys[pos[m]], values[pos[m]] = k, v
+        lo = 0 if window is None else max(0, pos[m] - window)
+        for hh in range(nh):
+            gk = hh // (nh // nkv)
+            s = (keys[lo:pos[m] + 1, gk] @ q[hh]) / math.sqrt(d)
+            mixed[m, hh * d:(hh + 1) * d] = torch.softmax(s, 0) @ values[lo:pos[m] + 1, gk]
+    x2 = x1 + bf(mixed) @ w_o.double().t()
+    h2 = bf(x2 / torch.sqrt((x2 * x2).mean(-1, keepdim=True) + eps2) * gain2.double())
+    g, u = h2 @ gate.double().t(), h2 @ up.double().t()
+    act = bf(g * torch.sigmoid(g) * u)
+    return x1.float(), x2.float(), (act @ down.double().t()).float(), k_new, v_new
+
+
+@pytest.mark.parametrize("M,hidden,inner,nh,nkv,d,page,window,lengths", [
+    (1, 128, 256, 2, 1, 64, 16, None, [300]),
+    (3, 160, 384, 4, 2, 64, 8, None, [1, 77, 600]),
+    (8, 896, 4864, 14, 2, 64, 16, None, [527, 3, 64, 65, 1000, 257, 256, 31]),
+    (5, 256, 512, 2, 2, 128, 16, 100, [40, 101, 102, 500, 2]),
+    (13, 384, 640, 6, 3, 64, 32, None, [5 + 97 * i for i in range(13)]),
+    (16, 1536, 1280, 12, 2, 128, 16, None, [9 + 61 * i for i in range(16)]),
+    (7, 192, 256, 16, 1, 64, 16, None, [2500, 1, 300, 17, 900, 64, 2049])])
+def test_layer_small_m(M, hidden, inner, nh, nkv, d, page, window, lengths):
+    """A whole decoder layer of few rows in one kernel (norm, q/k/v with bias and rotation, cache
+    write, attention over the paged keys with pieces merged across blocks, output projection,
+    second norm, gated feed-forward), twice in a row so that every counter is seen to come back
+    to zero, with an idle row in the padded batch."""
+    o = ops()
+    down_splits, o_splits = o.layer_small_m_splits(M, hidden, inner, nh, nkv, d)
+    assert down_splits > 0 and o_splits > 0
+    dtype = torch.bfloat16
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=41)
+    row_req = list(range(M))
+    pos = [n - 1 for n in lengths]
+    if M >= 5:
+        row_req[2] = -1                           # an idle row of a padded batch
+    slot = [int(tables[r, p // page]) * page + p % page if r >= 0 else -1 for r, p in zip(row_req, pos)]
+    x = rnd(M, hidden, seed=42)
+    delta = rnd(3, M, hidden, seed=43, scale=0.3)
+    gain1, gain2 = 1.0 + rnd(hidden, seed=44, scale=0.1), 1.0 + rnd(hidden, seed=45, scale=0.1)
+    w_qkv = rnd((nh + 2 * nkv) * d, hidden, seed=46, dtype=dtype, scale=0.08)
+    b_qkv = rnd((nh + 2 * nkv) * d, seed=47, scale=0.2)
+    w_o = rnd(hidden, nh * d, seed=48, dtype=dtype, scale=0.05)
+    gate = rnd(inner, hidden, seed=49, dtype=dtype, scale=0.06)
+    up = rnd(inner, hidden, seed=50, dtype=dtype, scale=0.06)
+    down = rnd(hidden, inner, seed=51, dtype=dtype, scale=0.04)
+    inv_freq = torch.tensor([1.0 / (10000.0 ** (i / d)) for i in range(0, d, 2)], dtype=torch.float64).float().to(DEV)
+    cos, sin = o.rope_table(inv_freq, max(lengths) + 1)
+    want_mid, want_out, want_ff, k_new, v_new = layer_reference(
+        x.cpu(), delta.cpu(), gain1.cpu(), 1e-5, w_qkv.cpu(), b_qkv.cpu(), pos, dense, row_req, w_o.cpu(),
+        gain2.cpu(), 2e-6, gate.cpu(), up.cpu(), down.cpu(), nh, nkv, d, window)
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    live = [m for m in range(M) if row_req[m] >= 0]
+    for _ in range(2):
+        x_mid, x_out = torch.full_like(x, 3.0), torch.full_like(x, 4.0)
+        out = torch.full((down_splits, M, hidden), 5.0, dtype=torch.float32, device=DEV)
+        o.layer_small_m(x, delta, x_mid, x_out, out, gain1, 1e-5, w_qkv, b_qkv, dev(pos), dev(slot), dev(row_req),
+                        tables, cos, sin, k_pool, v_pool, True, w_o, gain2, 2e-6, o.interleave_gate_up(gate, up),
+                        down, nh, nkv, d, page, window, 1.0 / math.sqrt(d))
+        torch.cuda.synchronize()
+        o.layer_small_m_check(d)
+        o.raise_if_error()
+        assert torch.allclose(x_mid.cpu(), want_mid, atol=1e-5, rtol=1e-6)
+        for m in live:                             # the new key and value in the row's slot
+            close(k_pool[slot[m]], k_new[m].float(), dtype)
+            close(v_pool[slot[m]], v_new[m].float(), dtype)
+        scale = float((want_out - want_mid).abs().max())
+        err = float((x_out.cpu() - want_out)[live].abs().max())
+        assert err <= 1.5e-2 * scale + 1e-4, f"attention half off by {err} of {scale}"
+        got = out.sum(0).cpu()
+        scale = float(want_ff.abs().max())
+        err = float((got - want_ff)[live].abs().max())
+        assert err <= 2e-2 * scale + 1e-4, f"feed-forward off by {err} of {scale}"
+    assert o.layer_small_m_splits(17, hidden, inner, nh, nkv, d) == (0, 0)
+    assert o.layer_small_m_splits(4, 100, inner, nh, nkv, d) == (0, 0)

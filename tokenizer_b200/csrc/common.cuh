@@ -39,7 +39,7 @@ enum : int {
   TOKB200_LIB_ATTENTION_TCGEN05 = 2,
   TOKB200_LIB_FFN_SMALL_M = 3,
   TOKB200_LIB_LINEAR_STREAM = 4,
-  TOKB200_LIB_ATTENTION_LAYER = 5,
+  TOKB200_LIB_LAYER_SMALL_M = 5,
 };
 __device__ int* tokb200_error_word = nullptr;
 

@@ -44,19 +44,30 @@ def _nvcc() -> str:
     return found
 
 
+_build_dir_found = None
+_build_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
-    preferred = os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(preferred, exist_ok=True)
-        probe = os.path.join(preferred, f".probe-{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return preferred
-    except OSError:
-        fallback = os.path.join(tempfile.gettempdir(), f"tokenizer_b200_build_{os.getuid()}")
-        os.makedirs(fallback, exist_ok=True)
-        return fallback
+    """`csrc/_build` inside the package where it can be written, else a folder of this user's
+    under the temporary directory.  Decided once per process (threads that compile side by
+    side must agree on it)."""
+    global _build_dir_found
+    with _build_dir_lock:
+        if _build_dir_found is None:
+            preferred = os.path.join(CSRC, "_build")
+            try:
+                os.makedirs(preferred, exist_ok=True)
+                probe = os.path.join(preferred, f".probe-{os.getpid()}-{threading.get_ident()}")
+                with open(probe, "w"):
+                    pass
+                os.remove(probe)
+                _build_dir_found = preferred
+            except OSError:
+                fallback = os.path.join(tempfile.gettempdir(), f"tokenizer_b200_build_{os.getuid()}")
+                os.makedirs(fallback, exist_ok=True)
+                _build_dir_found = fallback
+        return _build_dir_found
 
 
 def _digest(source: str, defines: Tuple[str, ...], extra: Tuple[str, ...]) -> str:

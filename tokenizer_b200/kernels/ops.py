@@ -103,7 +103,7 @@ class ScratchSpace:
     which is never inside a captured graph: a shape's first step runs plainly."""
 
     def __init__(self):
-        self.decode, self.ffn, self.argmax = {}, {}, {}
+        self.decode, self.ffn, self.argmax, self.layer = {}, {}, {}, {}
 
 
 _default_space = ScratchSpace()
@@ -135,7 +135,7 @@ class scratch_scope:
 # loaded; the host reads the word (plain memory, no CUDA call) wherever it has just
 # synchronised with the device, and raises.
 _LIBRARY_NAMES = {1: "gemm_tcgen05", 2: "attention_tcgen05", 3: "ffn_small_m", 4: "linear_stream",
-                  5: "attention_layer"}
+                  5: "layer_small_m"}
 _REASONS = {1: "a wait on a shared-memory barrier ran out", 2: "a wait between blocks ran out"}
 _error_word = None          # (ctypes int at the host address, device address)
 _registered = {}            # id(library handle) -> handle: libraries that know the word
@@ -191,7 +191,7 @@ def raise_if_error(where: str = "") -> None:
     for lib in _registered.values():          # clear the per-library flags too
         for name in ("tokb200_gemm_tcgen05_error", "tokb200_attention_tcgen05_error",
                      "tokb200_ffn_small_m_error", "tokb200_linear_stream_error",
-                     "tokb200_attention_layer_error"):
+                     "tokb200_layer_small_m_error"):
             try:
                 getattr(lib, name)()
             except AttributeError:
@@ -781,3 +781,115 @@ def attention_tcgen05_check(d: int) -> None:
     flag = _load("attention_tcgen05.cu", defines=(f"HEAD_DIM={d}",)).tokb200_attention_tcgen05_error()
     if flag:
         raise KernelError("attention_tcgen05: a wait on the device ran out (status %d)" % flag)
+
+
+# --------------------------------------------------------------------------- #
+# a whole decoder layer of few rows in one kernel
+class _LayerArgs(ctypes.Structure):
+    _fields_ = (
+        [(n, ctypes.c_void_p) for n in ("w_qkv", "b_qkv", "w_o", "gain1", "gain2", "w_gu", "w_d", "k_pool",
+                                        "v_pool", "k_read", "v_read", "cos_t", "sin_t")] +
+        [("eps1", ctypes.c_float), ("eps2", ctypes.c_float), ("scale", ctypes.c_float),
+         ("window", ctypes.c_int), ("activation", ctypes.c_int),
+         ("x_in", ctypes.c_void_p), ("delta", ctypes.c_void_p), ("delta_is_f32", ctypes.c_int),
+         ("n_partials", ctypes.c_int), ("partial_stride", ctypes.c_longlong)] +
+        [(n, ctypes.c_void_p) for n in ("x_mid", "x_out", "out", "pos", "slot", "row_req", "block_table")] +
+        [("table_stride", ctypes.c_int), ("page", ctypes.c_int)] +
+        [(n, ctypes.c_void_p) for n in ("q_buf", "att_part", "att_count", "att_out", "o_part", "act", "sync")] +
+        [(n, ctypes.c_int) for n in ("M", "H", "I", "nh", "nkv", "d")] + [("stamps", ctypes.c_void_p)])
+
+
+LAYER_HEAD_DIMS = (64, 128)
+LAYER_MAX_SPLITS = 32
+_layer_plans = {}
+# compile-time switches of the layer kernel's library (a test builds it with short wait limits)
+_LAYER_DEFINES = ()
+
+
+def _layer_lib(d: int):
+    return _load("layer_small_m.cu", defines=(f"HEAD_DIM={d}",) + tuple(_LAYER_DEFINES))
+
+
+def layer_small_m_splits(M: int, hidden: int, inner: int, nh: int, nkv: int, d: int):
+    """(partial sums of the feed-forward, partial sums of the output projection) that the
+    whole-layer kernel of few rows writes for these sizes on this device; (0, 0) when it does
+    not take them (more than 16 rows, a head size it is not built for, hidden not a multiple
+    of 32 or beyond 4096, inner not a multiple of 128, groups of more than 16 heads, too
+    little shared memory for its ring)."""
+    if M < 1 or M > 16 or d not in LAYER_HEAD_DIMS:
+        return 0, 0
+    key = (torch.cuda.current_device(), M <= 8, hidden, inner, nh, nkv, d)
+    if key not in _layer_plans:
+        o_splits = ctypes.c_int(0)
+        down = int(_layer_lib(d).tokb200_layer_small_m_splits(_i(M), _i(hidden), _i(inner), _i(nh), _i(nkv),
+                                                              ctypes.byref(o_splits)))
+        _layer_plans[key] = (down, int(o_splits.value))
+    return _layer_plans[key]
+
+
+def layer_small_m(x_in, delta, x_mid, x_out, out, gain1, eps1, w_qkv, b_qkv, pos, slot, row_req, block_table,
+                  cos, sin, k_pool, v_pool, writes: bool, w_o, gain2, eps2, w_gate_up, w_down, nh: int,
+                  nkv: int, d: int, page: int, window, scale: float, activation: str = "silu",
+                  stamps: Optional[torch.Tensor] = None) -> None:
+    """One pre-norm decoder layer for up to 16 rows of one token each (bfloat16): x_mid = x_in +
+    delta; attention (q/k/v with bias, rotary encoding, cache write when `writes`, softmax over
+    the paged keys) of rms_norm(x_mid) * gain1; x_out = x_mid + its output projection; out
+    [S, M, H] = float32 partial sums over k of the gated feed-forward of rms_norm(x_out) * gain2.
+    `delta` as for rms_norm ([M, H], float32 partial sums [S, M, H], or None); `w_gate_up` in the
+    row order of `interleave_gate_up`; `out` has `layer_small_m_splits(...)[0]` planes.  `stamps`
+    (int64 [blocks, 16], for profiling) receives the time in ns at which each block passes each phase."""
+    M, hidden = x_in.shape
+    inner = w_down.shape[1]
+    down_splits, o_splits = layer_small_m_splits(M, hidden, inner, nh, nkv, d)
+    if down_splits == 0:
+        raise ValueError(f"layer_small_m does not take {M} rows of {hidden}, inner {inner}, {nh}/{nkv} heads of {d}")
+    for t in (x_in, x_mid, x_out):
+        if t.dtype != torch.float32 or tuple(t.shape) != (M, hidden):
+            raise ValueError("layer_small_m: the residual stream is float32 [M, H], in, middle and out")
+    if tuple(out.shape) != (down_splits, M, hidden) or out.dtype != torch.float32:
+        raise ValueError(f"layer_small_m: out must be float32 {(down_splits, M, hidden)}")
+    q_width = nh * d
+    if w_qkv.dtype != torch.bfloat16 or tuple(w_qkv.shape) != ((nh + 2 * nkv) * d, hidden) or \
+            tuple(w_o.shape) != (hidden, q_width) or tuple(w_gate_up.shape) != (2 * inner, hidden) or \
+            tuple(w_down.shape) != (hidden, inner) or w_o.dtype != torch.bfloat16 or \
+            w_gate_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16:
+        raise ValueError("layer_small_m: bfloat16 weights [(nh + 2 nkv) d, H], [H, nh d], [2 I, H], [H, I]")
+    if cos.shape[1] != d // 2 or k_pool.dtype != torch.bfloat16:
+        raise ValueError("layer_small_m: the whole head is rotated, and the cache is bfloat16")
+    n_partials, stride = _partials(delta, x_in)
+    key = (x_in.device.index, M, hidden, inner, nh, nkv, d)
+    if key not in _space.layer:
+        dev = x_in.device
+        _space.layer[key] = dict(
+            q_buf=torch.empty((M, q_width), dtype=torch.bfloat16, device=dev),
+            att_part=torch.empty((M, nh, LAYER_MAX_SPLITS, d + 2), dtype=torch.float32, device=dev),
+            att_count=torch.zeros(M * nkv, dtype=torch.int32, device=dev),
+            att_out=torch.zeros((M, q_width), dtype=torch.bfloat16, device=dev),
+            o_part=torch.empty((o_splits, M, hidden), dtype=torch.float32, device=dev),
+            act=torch.empty((16, inner), dtype=torch.bfloat16, device=dev),
+            sync=torch.zeros(2, dtype=torch.int32, device=dev))
+    sc = _space.layer[key]
+
+    def ptr(t):
+        return _ptr(t).value
+
+    args = _LayerArgs(
+        w_qkv=ptr(w_qkv), b_qkv=ptr(b_qkv), w_o=ptr(w_o), gain1=ptr(gain1), gain2=ptr(gain2),
+        w_gu=ptr(w_gate_up), w_d=ptr(w_down), k_pool=ptr(k_pool) if writes else None,
+        v_pool=ptr(v_pool) if writes else None, k_read=ptr(k_pool), v_read=ptr(v_pool), cos_t=ptr(cos),
+        sin_t=ptr(sin), eps1=eps1, eps2=eps2, scale=scale, window=-1 if window is None else int(window),
+        activation=activation_tag(activation), x_in=ptr(x_in), delta=ptr(delta),
+        delta_is_f32=1 if delta is not None and delta.dtype == torch.float32 else 0, n_partials=n_partials,
+        partial_stride=stride, x_mid=ptr(x_mid), x_out=ptr(x_out), out=ptr(out), pos=ptr(pos),
+        slot=ptr(slot) if writes else None, row_req=ptr(row_req), block_table=ptr(block_table),
+        table_stride=block_table.shape[1], page=page, q_buf=ptr(sc["q_buf"]), att_part=ptr(sc["att_part"]),
+        att_count=ptr(sc["att_count"]), att_out=ptr(sc["att_out"]), o_part=ptr(sc["o_part"]),
+        act=ptr(sc["act"]), sync=ptr(sc["sync"]), M=M, H=hidden, I=inner, nh=nh, nkv=nkv, d=d,
+        stamps=ptr(stamps))
+    _check(_layer_lib(d).tokb200_layer_small_m(ctypes.byref(args), _stream()), "layer_small_m")
+
+
+def layer_small_m_check(d: int) -> None:
+    flag = _layer_lib(d).tokb200_layer_small_m_error()
+    if flag:
+        raise KernelError("layer_small_m: a wait on the device ran out (status %d)" % flag)

@@ -22,4 +22,6 @@ def all_variants():
         jobs.append(("attention_prefill.cu", (f"HEAD_DIM={head_dim}",), ()))
     for head_dim in (64, 128):
         jobs.append(("attention_tcgen05.cu", (f"HEAD_DIM={head_dim}",), ()))
+    for head_dim in (64, 128):
+        jobs.append(("layer_small_m.cu", (f"HEAD_DIM={head_dim}",), ()))
     return jobs

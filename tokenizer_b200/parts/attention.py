@@ -38,6 +38,10 @@ _PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "tcgen05")
 # unless asked for.
 _FUSED_QKV = os.environ.get("TOKB200_QKV_ROPE", "separate") == "fused"
 _FUSED_NORM = os.environ.get("TOKB200_QKV_NORM", "fused") != "separate"
+# TOKB200_LAYER=separate keeps a decoding step's layer as several kernels (projection, attention,
+# output projection, feed-forward) instead of one; so do the switches that take the norm or the
+# feed-forward out of their fusions
+_FUSED_LAYER = os.environ.get("TOKB200_LAYER", "fused") != "separate" and _FUSED_NORM
 
 
 class RowTiles(BatchAnnotation):
@@ -151,6 +155,39 @@ class GQAttention:
 
     def streamed_weights(self):
         return [self.qkv.weight, self.out.weight]
+
+    def fused_layer(self, stream, norm, ctx, cache, feed_forward, feed_forward_norm) -> bool:
+        """For a step of few rows of one token each in bfloat16: the WHOLE pre-norm layer in one
+        kernel (both norms, this attention, a gated feed-forward), straight from the stream.
+        The norms must offer `folded() -> (gain, eps)` of an RMS norm and the feed-forward
+        `gated_operands() -> (interleaved gate/up weight, down weight, activation)`.  True when it
+        was done: the stream then holds the sum after the attention, and the feed-forward's output
+        as pending partial sums.  False: the block runs the parts one by one."""
+        fold, fold2 = getattr(norm, "folded", None), getattr(feed_forward_norm, "folded", None)
+        operands = getattr(feed_forward, "gated_operands", None)
+        x = stream.x
+        if not (_FUSED_LAYER and fold is not None and fold2 is not None and operands is not None and
+                self.runtime.dtype == torch.bfloat16 and ctx.max_q_len == 1 and self.out.bias is None and
+                self.position.rotary_dim == self.d and cache.k_pool is not None):
+            return False
+        gated = operands()
+        if gated is None:
+            return False
+        w_gate_up, w_down, activation = gated
+        down_splits, _ = ops.layer_small_m_splits(x.shape[0], self.hidden, w_down.shape[1], self.nh, self.nkv, self.d)
+        if down_splits == 0:
+            return False
+        (gain1, eps1), (gain2, eps2) = fold(), fold2()
+        group = ctx.groups[cache.group]
+        delta, stream.pending = stream.pending, None
+        x_mid, x_out = torch.empty_like(x), torch.empty_like(x)
+        out = torch.empty((down_splits,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+        ops.layer_small_m(x, delta, x_mid, x_out, out, gain1, eps1, self.qkv.weight, self.qkv_bias, ctx.pos,
+                          group.slots, ctx.row_req, group.block_table, self.position.cos, self.position.sin,
+                          cache.k_pool, cache.v_pool, cache.writes, self.out.weight, gain2, eps2, w_gate_up,
+                          w_down, self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, activation)
+        stream.x, stream.pending = x_out, out
+        return True
 
     def fused_step(self, stream, norm, ctx, cache):
         """For few rows in bfloat16: the residual add and the norm in front are computed by

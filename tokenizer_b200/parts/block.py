@@ -24,6 +24,11 @@ class PreNormResidual:
         return out
 
     def forward(self, stream, ctx, cache):
+        # a mixer may take the whole layer (both norms, itself, the feed-forward) into one kernel
+        whole = getattr(self.mixer, "fused_layer", None)
+        if whole is not None and whole(stream, self.mixer_norm, ctx, cache, self.feed_forward,
+                                       self.feed_forward_norm):
+            return
         # a mixer may take the stream as it is and fold the norm into its own kernel
         fused = getattr(self.mixer, "fused_step", None)
         delta = fused(stream, self.mixer_norm, ctx, cache) if fused is not None else None

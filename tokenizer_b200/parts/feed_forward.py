@@ -71,6 +71,14 @@ class GatedMLP:
         stream.x, stream.pending = x_out, out
         return True
 
+    def gated_operands(self):
+        """(gate/up weight in the gated kernels' interleaved row order, down weight, activation)
+        for a kernel that computes this feed-forward inside a larger fusion; None when the sizes
+        or the precision have no such layout."""
+        if not (_FUSED_STEP and self.fused):
+            return None
+        return self.gate_up_weight, self.down.weight, self.activation
+
     def streamed_weights(self):
         """What a second stream may bring into L2 ahead of a step of few rows: nothing when
         the fused kernel runs, which streams its weights itself from its first cycle."""
