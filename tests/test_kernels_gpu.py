@@ -1209,7 +1209,9 @@ def layer_reference(x, delta, gain1, eps1, w_qkv, b_qkv, pos, dense, row_req, w_
     (5, 256, 512, 2, 2, 128, 16, 100, [40, 101, 102, 500, 2]),
     (13, 384, 640, 6, 3, 64, 32, None, [5 + 97 * i for i in range(13)]),
     (16, 1536, 1280, 12, 2, 128, 16, None, [9 + 61 * i for i in range(16)]),
-    (7, 192, 256, 16, 1, 64, 16, None, [2500, 1, 300, 17, 900, 64, 2049])])
+    (7, 192, 256, 16, 1, 64, 16, None, [2500, 1, 300, 17, 900, 64, 2049]),
+    (24, 896, 4864, 14, 2, 64, 16, None, [3 + 53 * i for i in range(24)]),
+    (32, 256, 640, 4, 2, 128, 16, None, [700 - 21 * i for i in range(32)])])
 def test_layer_small_m(M, hidden, inner, nh, nkv, d, page, window, lengths):
     """A whole decoder layer of few rows in one kernel (norm, q/k/v with bias and rotation, cache
     write, attention over the paged keys with pieces merged across blocks, output projection,
@@ -1261,5 +1263,5 @@ def test_layer_small_m(M, hidden, inner, nh, nkv, d, page, window, lengths):
         scale = float(want_ff.abs().max())
         err = float((got - want_ff)[live].abs().max())
         assert err <= 2e-2 * scale + 1e-4, f"feed-forward off by {err} of {scale}"
-    assert o.layer_small_m_splits(17, hidden, inner, nh, nkv, d) == (0, 0)
+    assert o.layer_small_m_splits(33, hidden, inner, nh, nkv, d) == (0, 0)
     assert o.layer_small_m_splits(4, 100, inner, nh, nkv, d) == (0, 0)

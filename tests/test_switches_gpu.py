@@ -16,15 +16,11 @@ from tiny import random_ids
 
 pytestmark = pytest.mark.gpu
 
-# a decoding step's layer is one kernel by default; TOKB200_LAYER=separate (and the two switches
-# that take one of its parts out: TOKB200_FFN, TOKB200_QKV_NORM) brings back the kernels per part,
-# which the switches about those kernels then choose between
 SWITCHES = [
-    {}, {"TOKB200_LAYER": "separate"}, {"TOKB200_ATTENTION": "mma"}, {"TOKB200_FFN": "separate"},
-    {"TOKB200_QKV_NORM": "separate"}, {"TOKB200_LAYER": "separate", "TOKB200_DECODE_MERGE": "scratch"},
-    {"TOKB200_STREAM": "0"}, {"TOKB200_PDL": "0"}, {"TOKB200_LAYER": "separate", "TOKB200_PDL": "0"},
+    {}, {"TOKB200_ATTENTION": "mma"}, {"TOKB200_FFN": "separate"}, {"TOKB200_QKV_NORM": "separate"},
+    {"TOKB200_DECODE_MERGE": "scratch"}, {"TOKB200_STREAM": "0"}, {"TOKB200_PDL": "0"},
     {"TOKB200_GEMM": "library"}, {"TOKB200_QKV_ROPE": "fused"}, {"TOKB200_L2_PREFETCH": "1"},
-    {"TOKB200_LAYER": "separate", "TOKB200_L2_PREFETCH": "1"}, {"TOKB200_GEMM_PAIR": "0"},
+    {"TOKB200_GEMM_PAIR": "0"}, {"TOKB200_LAYER": "fused"}, {"TOKB200_LAYER": "fused", "TOKB200_PDL": "0"},
 ]
 
 

@@ -358,6 +358,9 @@ ffn_small_m_kernel(const FfnParams p) {
   }
 
   // ---- all blocks have written their part of the activation ----
+  // (every consumer's writes of the activation are ordered before the arrival: a block barrier
+  // first, then one thread's fence and atomic, whose release is cumulative over what it has seen)
+  ffn_consumer_sync();
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(&p.sync[0], 1);

@@ -1,4 +1,4 @@
-// A whole decoder layer of a decoding step in ONE kernel, for few rows (M <= 16, bfloat16
+// A whole decoder layer of a decoding step in ONE kernel, for few rows (M <= 32, bfloat16
 // weights and cache, 32-bit sums): pre-norm residual arrangement, grouped-query attention with
 // biases on q/k/v and a half-split rotary encoding over the paged cache, gated feed-forward.
 //
@@ -54,6 +54,7 @@ static_assert(HEAD_DIM % 32 == 0 && HEAD_DIM >= 32 && HEAD_DIM <= 128, "head siz
 #define LAY_MAX_SPLITS 32                    // pieces of a row's keys (a lane each in the merge)
 #define LAY_TILE 32                          // keys a warp takes per pass
 #define LAY_MAX_GROUP 16                     // query heads per kv head: the rows of one mma
+#define LAY_TABLE_ENTRIES 256                // pages of a block's first attention unit kept in shared memory
 
 constexpr int kVStride = HEAD_DIM + 8;       // elements between staged value rows
 constexpr int kPieceRow = HEAD_DIM + 2;      // a piece: weighted values, max (log2 units), sum
@@ -154,16 +155,19 @@ struct LayerParams {
   float* att_part;              // [M, nh, LAY_MAX_SPLITS, d + 2]
   int* att_count;               // [M, nkv] zero between launches
   __nv_bfloat16* att_out;       // [M, nh d]
-  float* o_part;                // [s_o, M, H]
+  float* o_part;                // [M, H]: the output projection
   __nv_bfloat16* act;           // [M, I]
   int* sync;                    // [2] zero between launches
   // ---- sizes and the plan ----
   int M, H, I, nh, nkv;
   int n_stages, h_pitch;        // h_pitch: bytes between rows of the activation tile in shared memory
-  int s_o, k_per_split_o;       // the output projection's cut along k
-  int s_down, k_per_split_d;    // the down projection's cut along k
+  int s_down, k_per_split_d;    // the down projection's cut along k (k_per_split_d a multiple of 32)
   int att_splits;               // pieces a row's keys are cut into at most
-  long long* stamps;            // null, or [blocks, 16]: the time (ns) at which a block's consumers pass each phase
+  long long* stamps;            // null, or [blocks, 32]: the time (ns) at which a block's consumers pass each phase
+  const __nv_bfloat16* next_w;  // null, or the q/k/v weight (same shape) of the layer that runs next: brought into L2
+  const float* next_gain;       // ... its first norm's gain [H] and its q/k/v bias, likewise
+  const float* next_bias;
+  int repeat;                   // 1; more (profiling only): the same layer that many times in one launch
 };
 
 // One warp, one row of up to 128 KVEC elements kept in registers: x' = x + pending (the pending
@@ -179,7 +183,8 @@ __device__ __forceinline__ void lay_norm_row(const float* __restrict__ xr, const
   const float* df = reinterpret_cast<const float*>(delta);
   const __nv_bfloat16* dh = reinterpret_cast<const __nv_bfloat16*>(delta);
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 v[KVEC];
+  constexpr bool kGainEarly = KVEC <= 8;         // rows of up to 1024: the gain in the same trip as x
+  float4 v[KVEC], gn[kGainEarly ? KVEC : 1];
 #pragma unroll
   for (int grp = 0; grp < KVEC / 4; ++grp) {
     float4 a[3][4];
@@ -189,6 +194,7 @@ __device__ __forceinline__ void lay_norm_row(const float* __restrict__ xr, const
       const int i = (lane + 32 * (grp * 4 + e)) * 4;
       const bool in = i < H;
       v[grp * 4 + e] = in ? __ldcg(reinterpret_cast<const float4*>(xr + i)) : zero4;
+      if (kGainEarly) gn[grp * 4 + e] = in ? *reinterpret_cast<const float4*>(gain + i) : zero4;
       raw[e] = make_uint2(0u, 0u);
       if (delta && !delta_is_f32 && in) raw[e] = __ldcg(reinterpret_cast<const uint2*>(dh + i));
 #pragma unroll
@@ -242,9 +248,9 @@ __device__ __forceinline__ void lay_norm_row(const float* __restrict__ xr, const
   for (int e = 0; e < KVEC; ++e) {
     const int i = (lane + 32 * e) * 4;
     if (i < H) {
-      const float4 gn = *reinterpret_cast<const float4*>(gain + i);
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(v[e].x * inv * gn.x, v[e].y * inv * gn.y);
-      const __nv_bfloat162 hi = __floats2bfloat162_rn(v[e].z * inv * gn.z, v[e].w * inv * gn.w);
+      const float4 g4 = kGainEarly ? gn[kGainEarly ? e : 0] : *reinterpret_cast<const float4*>(gain + i);
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v[e].x * inv * g4.x, v[e].y * inv * g4.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(v[e].z * inv * g4.z, v[e].w * inv * g4.w);
       uint2 packed;
       packed.x = *reinterpret_cast<const unsigned*>(&lo);
       packed.y = *reinterpret_cast<const unsigned*>(&hi);
@@ -276,6 +282,20 @@ __device__ __forceinline__ void lay_norm(const float* x, const void* delta, int 
   }
 }
 
+// How the tiles of a product are dealt to the blocks: tile i of the product goes to block
+// (first + i) mod G, so that the products with fewer tiles than blocks (q/k/v, output, down)
+// start at different blocks and no block carries a share of all of them.
+struct Deal {
+  int n_tiles, first;
+  __device__ __forceinline__ int mine(int cta, int G) const {        // tiles of this block
+    const int offset = (cta - first % G + G) % G;
+    return offset < n_tiles ? (n_tiles - offset + G - 1) / G : 0;
+  }
+  __device__ __forceinline__ int tile(int cta, int G, int i) const { // its i-th tile
+    return (cta - first % G + G) % G + i * G;
+  }
+};
+
 template <int MT>
 __global__ void __launch_bounds__(LAY_THREADS, 1)
 layer_small_m_kernel(const LayerParams p) {
@@ -283,12 +303,12 @@ layer_small_m_kernel(const LayerParams p) {
   const int group = p.nh / p.nkv;
   unsigned char* ring = lay_raw;
   unsigned char* work = ring + (size_t)p.n_stages * LAY_STAGE_BYTES;
-  // the work area: h (later the attention's output, later pieces of the activation) and the
+  // the work area: h (later the attention's output, later a piece of the activation) and the
   // warps' partial sums; during the attention phase the same bytes stage values and hold the merge
   unsigned char* h_s = work;
-  float* part = reinterpret_cast<float*>(h_s + (size_t)8 * MT * p.h_pitch);     // [2][warps][16][8 MT + 1]
+  float* part = reinterpret_cast<float*>(h_s + (size_t)8 * MT * p.h_pitch);     // [warps][16][8 MT + 1]
   constexpr int kPart = LAY_WARPS * 16 * (8 * MT + 1);
-  size_t work_bytes = (size_t)8 * MT * p.h_pitch + (size_t)2 * kPart * 4;
+  size_t work_bytes = (size_t)8 * MT * p.h_pitch + (size_t)kPart * 4;
   {
     const size_t stage = (size_t)LAY_WARPS * LAY_TILE * kVStride * 2;
     const size_t merge = (size_t)LAY_WARPS * group * kPieceRow * 4;
@@ -298,27 +318,31 @@ layer_small_m_kernel(const LayerParams p) {
   }
   unsigned long long* full = reinterpret_cast<unsigned long long*>(work + work_bytes);
   unsigned long long* empty = full + p.n_stages;
+  int* table_s = reinterpret_cast<int*>(empty + p.n_stages);      // [LAY_TABLE_ENTRIES]: the first unit's pages
   __shared__ int grid_ok;
   __shared__ int is_last;
+  __shared__ int req_s[32], pos_s[32], slot_s[32];                // the rows' requests, positions, cache slots
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = gridDim.x, cta = blockIdx.x;
   const int d = HEAD_DIM, half = HEAD_DIM / 2;
   const int q_width = p.nh * d;
-  const int n_tiles_qkv = (p.nh + 2 * p.nkv) * (d / 16);
-  const int n_tiles_gu = p.I / 8;
+  // stages a tile takes: its 16 rows in pieces of LAY_KC along k
+  const int spt_h = (p.H + LAY_KC - 1) / LAY_KC, spt_o = (q_width + LAY_KC - 1) / LAY_KC;
+  const int spt_d = (p.k_per_split_d + LAY_KC - 1) / LAY_KC;
   const int n_row_tiles = p.H / 16;
-  // products cut along k: a block owns ONE k range (split = block mod S) and walks the row tiles
-  // of that range with the other blocks of the same split, so it stages its columns once
-  const int o_split = cta % p.s_o, o_first = cta / p.s_o, o_step = (G - o_split + p.s_o - 1) / p.s_o;
-  const int o_k0 = o_split * p.k_per_split_o, o_k1 = min(q_width, o_k0 + p.k_per_split_o);
-  const int d_split = cta % p.s_down, d_first = cta / p.s_down, d_step = (G - d_split + p.s_down - 1) / p.s_down;
-  const int d_k0 = d_split * p.k_per_split_d, d_k1 = min(p.I, d_k0 + p.k_per_split_d);
+  const Deal qkv = {(p.nh + 2 * p.nkv) * (d / 16), 0};
+  const Deal opr = {n_row_tiles, qkv.n_tiles};
+  const Deal gup = {p.I / 8, 0};
+  const Deal dwn = {n_row_tiles * p.s_down, qkv.n_tiles + opr.n_tiles};
+  const int n_qkv = qkv.mine(cta, G), n_opr = opr.mine(cta, G), n_gup = gup.mine(cta, G), n_dwn = dwn.mine(cta, G);
+  // the sequence numbers of the stages each product starts at, in this block
+  const int c_opr = n_qkv * spt_h, c_gup = c_opr + n_opr * spt_o, c_dwn = c_gup + n_gup * spt_h;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.n_stages; ++i) {
       lay_mbar_init(&full[i], 1);
-      lay_mbar_init(&empty[i], LAY_WARPS);
+      lay_mbar_init(&empty[i], 1);               // one warp consumes a stage
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     grid_ok = 1;
@@ -327,6 +351,56 @@ layer_small_m_kernel(const LayerParams p) {
 
   if (warp == LAY_WARPS) {
     // ------------------------------ producer ------------------------------
+    // First of all, ask for this block's share of the layer's weights to be brought into L2
+    // (cp.async.bulk.prefetch: no registers, no shared memory, returns at once): DRAM then
+    // streams at full rate from the kernel's first microsecond, and the ring below, which is
+    // only a few stages deep, has to hide the latency of L2, not that of DRAM.
+    auto ahead = [&](const __nv_bfloat16* rows_lo, const __nv_bfloat16* rows_hi, int K, int k0, int kn) {
+      if (lane < 16) {
+        const __nv_bfloat16* src = (lane < 8 ? rows_lo + (size_t)lane * K : rows_hi + (size_t)(lane - 8) * K) + k0;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((unsigned)kn * 2u) : "memory");
+      }
+    };
+    for (int i = 0; i < n_qkv; ++i) {
+      const int tile = qkv.tile(cta, G, i);
+      const int head = tile / (d / 16), j0 = (tile % (d / 16)) * 8;
+      const __nv_bfloat16* lo = p.w_qkv + (size_t)(head * d + j0) * p.H;
+      ahead(lo, lo + (size_t)half * p.H, p.H, 0, p.H);
+    }
+    for (int i = 0; i < n_opr; ++i) {
+      const __nv_bfloat16* rows = p.w_o + (size_t)opr.tile(cta, G, i) * 16 * q_width;
+      ahead(rows, rows + (size_t)8 * q_width, q_width, 0, q_width);
+    }
+    for (int i = 0; i < n_gup; ++i) {
+      const int out0 = gup.tile(cta, G, i) * 8;
+      const __nv_bfloat16* gate = p.w_gu + (size_t)((out0 / 128) * 256 + out0 % 128) * p.H;
+      ahead(gate, gate + (size_t)128 * p.H, p.H, 0, p.H);
+    }
+    for (int i = 0; i < n_dwn; ++i) {
+      const int unit = dwn.tile(cta, G, i), split = unit / n_row_tiles, rt = unit % n_row_tiles;
+      const int k_begin = split * p.k_per_split_d, k_end = min(p.I, k_begin + p.k_per_split_d);
+      const __nv_bfloat16* rows = p.w_d + (size_t)rt * 16 * p.I;
+      ahead(rows, rows + (size_t)8 * p.I, p.I, k_begin, k_end - k_begin);
+    }
+    // the small vectors: this layer's (a first layer has nobody to ask for them ahead) and those
+    // the layer that runs next starts with
+    if (cta < 5 && lane == 0) {
+      const unsigned h_bytes = (unsigned)p.H * 4u, b_bytes = (unsigned)(p.nh + 2 * p.nkv) * d * 4u;
+      const void* what = cta == 0 ? (const void*)p.gain1 : cta == 1 ? (const void*)p.gain2 :
+                         cta == 2 ? (const void*)p.b_qkv : cta == 3 ? (const void*)p.next_gain : (const void*)p.next_bias;
+      const unsigned bytes = (cta == 2 || cta == 4) ? b_bytes : h_bytes;
+      if (what && (bytes & ~15u))
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(what), "r"(bytes & ~15u) : "memory");
+    }
+    // and the q/k/v share of the layer that runs next (its kernel starts with those)
+    if (p.next_w) {
+      for (int i = 0; i < n_qkv; ++i) {
+        const int tile = qkv.tile(cta, G, i);
+        const int head = tile / (d / 16), j0 = (tile % (d / 16)) * 8;
+        const __nv_bfloat16* lo = p.next_w + (size_t)(head * d + j0) * p.H;
+        ahead(lo, lo + (size_t)half * p.H, p.H, 0, p.H);
+      }
+    }
     int c = 0;                                   // stages filled so far
     bool ok = true;
     auto fill = [&](const __nv_bfloat16* rows_lo, const __nv_bfloat16* rows_hi, int K, int k0, int kn) {
@@ -344,29 +418,38 @@ layer_small_m_kernel(const LayerParams p) {
       }
       ++c;
     };
+    for (int rep = 0; rep < p.repeat; ++rep) {
     // q/k/v: a tile is 8 lanes of a head and their rotation partners
-    for (int tile = cta; tile < n_tiles_qkv && ok; tile += G) {
+    for (int i = 0; i < n_qkv && ok; ++i) {
+      const int tile = qkv.tile(cta, G, i);
       const int head = tile / (d / 16), j0 = (tile % (d / 16)) * 8;
       const __nv_bfloat16* lo = p.w_qkv + (size_t)(head * d + j0) * p.H;
       for (int k0 = 0; k0 < p.H && ok; k0 += LAY_KC) fill(lo, lo + (size_t)half * p.H, p.H, k0, min(LAY_KC, p.H - k0));
     }
     // the output projection
-    for (int rt = o_first; rt < n_row_tiles && ok; rt += o_step) {
-      const __nv_bfloat16* rows = p.w_o + (size_t)rt * 16 * q_width;
-      for (int k0 = o_k0; k0 < o_k1 && ok; k0 += LAY_KC)
-        fill(rows, rows + (size_t)8 * q_width, q_width, k0, min(LAY_KC, o_k1 - k0));
+    for (int i = 0; i < n_opr && ok; ++i) {
+      const __nv_bfloat16* rows = p.w_o + (size_t)opr.tile(cta, G, i) * 16 * q_width;
+      for (int k0 = 0; k0 < q_width && ok; k0 += LAY_KC)
+        fill(rows, rows + (size_t)8 * q_width, q_width, k0, min(LAY_KC, q_width - k0));
     }
-    // gate and up
-    for (int tile = cta; tile < n_tiles_gu && ok; tile += G) {
-      const int out0 = tile * 8;
+    // gate and up: 8 gate rows and the 8 up rows of the same outputs
+    for (int i = 0; i < n_gup && ok; ++i) {
+      const int out0 = gup.tile(cta, G, i) * 8;
       const __nv_bfloat16* gate = p.w_gu + (size_t)((out0 / 128) * 256 + out0 % 128) * p.H;
       for (int k0 = 0; k0 < p.H && ok; k0 += LAY_KC) fill(gate, gate + (size_t)128 * p.H, p.H, k0, min(LAY_KC, p.H - k0));
     }
-    // down
-    for (int rt = d_first; rt < n_row_tiles && ok; rt += d_step) {
+    // down: a unit is (piece of k, row tile), pieces slowest
+    for (int i = 0; i < n_dwn && ok; ++i) {
+      const int unit = dwn.tile(cta, G, i), split = unit / n_row_tiles, rt = unit % n_row_tiles;
+      const int k_begin = split * p.k_per_split_d, k_end = min(p.I, k_begin + p.k_per_split_d);
       const __nv_bfloat16* rows = p.w_d + (size_t)rt * 16 * p.I;
-      for (int k0 = d_k0; k0 < d_k1 && ok; k0 += LAY_KC)
-        fill(rows, rows + (size_t)8 * p.I, p.I, k0, min(LAY_KC, d_k1 - k0));
+      for (int s = 0; s < spt_d && ok; ++s) {
+        const int k0 = k_begin + s * LAY_KC;
+        const int kn = k0 < k_end ? min(LAY_KC, k_end - k0) : 0;
+        // a piece that ends early still takes its stages (32 elements of padding: nothing adds up)
+        fill(rows, rows + (size_t)8 * p.I, p.I, kn ? k0 : k_begin, kn ? kn : 32);
+      }
+    }
     }
     return;
   }
@@ -374,23 +457,26 @@ layer_small_m_kernel(const LayerParams p) {
   // ------------------------------ consumers ------------------------------
   const int tid = threadIdx.x;                   // 0 .. 255
   const int g = lane >> 2, t = lane & 3;
-  int c = 0;                                     // stages consumed so far
   bool ok = true;
   int barriers = 0;
   float acc[MT][4];
-  // one stage: the warp takes the steps of 32 k that are its own (warp, warp + 8, ...)
-  auto multiply = [&](int k_local0, int kn) {
+  // One stage, consumed by this warp alone: 16 weight rows x kn elements of k against the rows of
+  // the activation tile in shared memory, from its column k_local0 on.
+  int c_rep = 0;                                 // stages of the repetitions before this one
+  auto multiply = [&](int c_in, int k_local0, int kn) {
+    const int c = c_rep + c_in;
     const int stage = c % p.n_stages, use = c / p.n_stages;
     ok = ok && __all_sync(0xffffffffu, lay_mbar_wait(&full[stage], use & 1));
     if (ok) {
       const unsigned char* st = ring + (size_t)stage * LAY_STAGE_BYTES;
-      for (int s = warp; s * 32 < kn; s += LAY_WARPS) {
-        const uint4 a = *reinterpret_cast<const uint4*>(st + g * LAY_ROW_PITCH + (s * 32 + 8 * t) * 2);
-        const uint4 b = *reinterpret_cast<const uint4*>(st + (g + 8) * LAY_ROW_PITCH + (s * 32 + 8 * t) * 2);
+#pragma unroll 2
+      for (int k = 0; k < kn; k += 32) {
+        const uint4 a = *reinterpret_cast<const uint4*>(st + g * LAY_ROW_PITCH + (k + 8 * t) * 2);
+        const uint4 b = *reinterpret_cast<const uint4*>(st + (g + 8) * LAY_ROW_PITCH + (k + 8 * t) * 2);
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           const uint4 xv = *reinterpret_cast<const uint4*>(
-              h_s + (size_t)(8 * j + g) * p.h_pitch + (k_local0 + s * 32 + 8 * t) * 2);
+              h_s + (size_t)(8 * j + g) * p.h_pitch + (k_local0 + k + 8 * t) * 2);
           lay_mma(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
           lay_mma(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
         }
@@ -398,31 +484,10 @@ layer_small_m_kernel(const LayerParams p) {
       __syncwarp();
       if (lane == 0) lay_mbar_arrive(&empty[stage]);
     }
-    ++c;
   };
   auto clear = [&]() {
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  };
-  // The warps' sums of a tile meet in one of two buffers, in turn: a thread that reads buffer
-  // b for tile i has, by the barrier of tile i + 1, finished reading it, so tile i + 2 may
-  // write it again, and one barrier a tile is enough.
-  int turn = 0;
-  auto spill = [&]() {
-    float* mine = part + (size_t)turn * kPart + (size_t)warp * 16 * (8 * MT + 1);
-#pragma unroll
-    for (int j = 0; j < MT; ++j) {
-      mine[g * (8 * MT + 1) + 8 * j + 2 * t] = acc[j][0];
-      mine[g * (8 * MT + 1) + 8 * j + 2 * t + 1] = acc[j][1];
-      mine[(g + 8) * (8 * MT + 1) + 8 * j + 2 * t] = acc[j][2];
-      mine[(g + 8) * (8 * MT + 1) + 8 * j + 2 * t + 1] = acc[j][3];
-    }
-  };
-  auto summed = [&](int row, int m) {
-    float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < LAY_WARPS; ++w) v += part[(size_t)turn * kPart + ((size_t)w * 16 + row) * (8 * MT + 1) + m];
-    return v;
   };
   // All blocks meet: every consumer's writes are ordered before its block's arrival (block
   // barrier, then one thread's fence and atomic), and the waiters' reads after it.  A wait that
@@ -440,7 +505,6 @@ layer_small_m_kernel(const LayerParams p) {
           int seen;
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.sync) : "memory");
           if (seen >= target) { met = true; break; }
-          __nanosleep(32);
         }
         if (!met) {
           atomicExch(&lay_error_flag, 2);
@@ -453,21 +517,80 @@ layer_small_m_kernel(const LayerParams p) {
     lay_consumer_sync();
     ok = ok && grid_ok;
   };
-
   int stamp_at = 0;
   auto stamp = [&]() {
     if (p.stamps && tid == 0) {
       long long now;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      p.stamps[(size_t)cta * 16 + stamp_at] = now;
+      p.stamps[(size_t)cta * 32 + stamp_at] = now;
     }
     ++stamp_at;
   };
+  auto stamp_to = [&](int slot) {          // finer marks inside a phase (slots 16..31)
+    if (p.stamps && tid == 0) {
+      long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      p.stamps[(size_t)cta * 32 + slot] = now;
+    }
+  };
   stamp();             // 0: consumers start
+
+  // ---- what the later phases need of the step's description, asked for now: the rows'
+  // requests, positions, slots and block tables were written before the predecessor started ----
+  if (tid < 32) {
+    req_s[tid] = tid < p.M ? p.row_req[tid] : -1;
+    pos_s[tid] = tid < p.M ? p.pos[tid] : 0;
+    slot_s[tid] = (tid < p.M && p.slot) ? p.slot[tid] : -1;
+  }
+  const int n_units = p.M * p.nkv * p.att_splits;
+  int u_first = 0, u_last = -1, u_splits = 0, u_req = -1, u_cached = 0;
+  const int unit0 = cta;
+  if (unit0 < n_units) {
+    const int split = unit0 % p.att_splits, row = unit0 / (p.att_splits * p.nkv);
+    u_req = p.row_req[row];
+    if (u_req >= 0) {
+      const int at = p.pos[row];      // (its own loads: the shared copies are not written yet)
+      const int lo = (p.window >= 0 && at - p.window > 0) ? at - p.window : 0;
+      const int n_keys = at - lo + 1;
+      const int chunk = ((n_keys + p.att_splits - 1) / p.att_splits + LAY_TILE - 1) / LAY_TILE * LAY_TILE;
+      u_splits = (n_keys + chunk - 1) / chunk;
+      u_first = lo + split * chunk;
+      u_last = min(at, u_first + chunk - 1);
+      if (split < u_splits) {
+        const int page0 = u_first / p.page, pages = u_last / p.page - page0 + 1;
+        if (pages <= LAY_TABLE_ENTRIES) {
+          u_cached = 1;
+          for (int e = tid; e < pages; e += LAY_CONSUMERS)
+            table_s[e] = p.block_table[(size_t)u_req * p.table_stride + page0 + e];
+        }
+      }
+    }
+  }
+  lay_consumer_sync();
+  if (u_cached) {
+    // the unit's keys and values into L2 (all but the newest were written by earlier steps)
+    const int kvh = (unit0 / p.att_splits) % p.nkv, page0 = u_first / p.page;
+    for (int key = u_first + tid; key <= u_last; key += LAY_CONSUMERS) {
+      const size_t at = ((size_t)(table_s[key / p.page - page0] * p.page + key % p.page) * p.nkv + kvh) * d;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.k_read + at));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.v_read + at));
+      if (HEAD_DIM > 64) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.k_read + at + 64));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.v_read + at + 64));
+      }
+    }
+  }
+  // the gains are constants: in registers before the wait (a warp per row reads the same pieces)
   pdl_wait();          // x and the pending sums come from the predecessor; the weights do not
   pdl_launch();
   stamp();             // 1: the predecessor is done
 
+  for (int rep = 0; rep < p.repeat; ++rep) {
+  if (rep > 0) {
+    grid_barrier();
+    stamp_at = 2;
+    c_rep += c_dwn + n_dwn * spt_d;
+  }
   // ======================= phase 0: the first norm =======================
   lay_norm<MT>(p.x_in, p.delta, p.delta_is_f32, p.n_partials, p.partial_stride, p.gain1, p.eps1,
                cta == 0 ? p.x_mid : nullptr, h_s, p.h_pitch, p.M, p.H, warp, lane);
@@ -475,50 +598,63 @@ layer_small_m_kernel(const LayerParams p) {
   stamp();             // 2: first norm done
 
   // ======================= phase 1: q, k, v with bias, rotation, cache write =======================
-  for (int tile = cta; tile < n_tiles_qkv; tile += G) {
-    const int head = tile / (d / 16), j0 = (tile % (d / 16)) * 8;
-    // what the epilogue needs from memory is asked for before the product
-    const int em = tid / 8, ej = j0 + tid % 8;
-    float e_bias_a = 0.f, e_bias_b = 0.f, e_cos = 1.f, e_sin = 0.f;
-    int e_slot = -1;
-    if (tid < 8 * p.M) {
-      if (p.b_qkv) {
-        e_bias_a = p.b_qkv[head * d + ej];
-        e_bias_b = p.b_qkv[head * d + ej + half];
-      }
-      if (head >= p.nh && p.slot) e_slot = p.slot[em];
-      if (head < p.nh + p.nkv) {
-        const int at = p.pos[em];
-        e_cos = p.cos_t[(size_t)at * half + ej];
-        e_sin = p.sin_t[(size_t)at * half + ej];
+  // a warp per tile; a thread's accumulators hold both halves of a rotation pair: c0,c1 are lane
+  // j0 + g of the head for rows 2t, 2t+1 (of each 8), c2,c3 its partner j0 + g + d/2
+  for (int i = warp; i < n_qkv; i += LAY_WARPS) {
+    const int tile = qkv.tile(cta, G, i);
+    const int head = tile / (d / 16), ej = (tile % (d / 16)) * 8 + g;
+    float bias_a = 0.f, bias_b = 0.f;
+    if (p.b_qkv) {
+      bias_a = p.b_qkv[head * d + ej];
+      bias_b = p.b_qkv[head * d + ej + half];
+    }
+    float e_cos[MT][2], e_sin[MT][2];
+    int e_slot[MT][2];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 8 * j + 2 * t + e;
+        e_cos[j][e] = 1.f; e_sin[j][e] = 0.f; e_slot[j][e] = -1;
+        if (m < p.M) {
+          if (head >= p.nh) e_slot[j][e] = slot_s[m];
+          if (head < p.nh + p.nkv) {
+            const int at = pos_s[m];
+            e_cos[j][e] = p.cos_t[(size_t)at * half + ej];
+            e_sin[j][e] = p.sin_t[(size_t)at * half + ej];
+          }
+        }
       }
     }
     clear();
-    for (int k0 = 0; k0 < p.H; k0 += LAY_KC) multiply(k0, min(LAY_KC, p.H - k0));
-    spill();
-    lay_consumer_sync();
-    if (tid < 8 * p.M && ok) {
-      const int rr = tid % 8;
-      float a = summed(rr, em) + e_bias_a, b = summed(rr + 8, em) + e_bias_b;
-      __nv_bfloat16* dst = nullptr;
-      if (head < p.nh) {
-        dst = p.q_buf + ((size_t)em * p.nh + head) * d;
-      } else if (e_slot >= 0) {
-        const bool is_key = head < p.nh + p.nkv;
-        __nv_bfloat16* pool = is_key ? p.k_pool : p.v_pool;
-        if (pool) dst = pool + ((size_t)e_slot * p.nkv + (head - p.nh - (is_key ? 0 : p.nkv))) * d;
-      }
-      if (head < p.nh + p.nkv) {                              // values are not rotated
-        const float ra = a * e_cos - b * e_sin, rb = b * e_cos + a * e_sin;
-        a = ra;
-        b = rb;
-      }
-      if (dst) {
-        dst[ej] = __float2bfloat16_rn(a);
-        dst[ej + half] = __float2bfloat16_rn(b);
+    for (int s = 0; s < spt_h; ++s) multiply(i * spt_h + s, s * LAY_KC, min(LAY_KC, p.H - s * LAY_KC));
+    if (!ok) break;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 8 * j + 2 * t + e;
+        if (m >= p.M) continue;
+        float a = acc[j][e] + bias_a, b = acc[j][2 + e] + bias_b;
+        __nv_bfloat16* dst = nullptr;
+        if (head < p.nh) {
+          dst = p.q_buf + ((size_t)m * p.nh + head) * d;
+        } else if (e_slot[j][e] >= 0) {
+          const bool is_key = head < p.nh + p.nkv;
+          __nv_bfloat16* pool = is_key ? p.k_pool : p.v_pool;
+          if (pool) dst = pool + ((size_t)e_slot[j][e] * p.nkv + (head - p.nh - (is_key ? 0 : p.nkv))) * d;
+        }
+        if (head < p.nh + p.nkv) {                            // values are not rotated
+          const float ra = a * e_cos[j][e] - b * e_sin[j][e], rb = b * e_cos[j][e] + a * e_sin[j][e];
+          a = ra;
+          b = rb;
+        }
+        if (dst) {
+          dst[ej] = __float2bfloat16_rn(a);
+          dst[ej + half] = __float2bfloat16_rn(b);
+        }
       }
     }
-    turn ^= 1;
   }
   stamp();             // 3: q/k/v done
   grid_barrier();
@@ -529,22 +665,31 @@ layer_small_m_kernel(const LayerParams p) {
   // the mma, so keys and values are read once per group
   {
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const int n_units = p.M * p.nkv * p.att_splits;
     __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(work) + (size_t)warp * LAY_TILE * kVStride;
     float* acc_s = reinterpret_cast<float*>(work);            // [warp][head][kPieceRow], after the passes
     for (int unit = cta; unit < n_units && ok; unit += G) {
       const int split = unit % p.att_splits, kvh = (unit / p.att_splits) % p.nkv, row = unit / (p.att_splits * p.nkv);
-      const int r = p.row_req[row];
-      if (r < 0) continue;                                    // uniform over the block
-      const int at = p.pos[row];
-      const int lo = (p.window >= 0 && at - p.window > 0) ? at - p.window : 0;
-      const int n_keys = at - lo + 1;
-      const int chunk = ((n_keys + p.att_splits - 1) / p.att_splits + LAY_TILE - 1) / LAY_TILE * LAY_TILE;
-      const int n_splits = (n_keys + chunk - 1) / chunk;
-      if (split >= n_splits) continue;
-      const int first = lo + split * chunk;
-      const int last = min(at, first + chunk - 1);
+      int r, first, last, n_splits;
+      const bool cached = unit == unit0 && u_cached;
+      if (unit == unit0) {
+        r = u_req; first = u_first; last = u_last; n_splits = u_splits;
+      } else {
+        r = req_s[row];
+        const int at = r < 0 ? 0 : pos_s[row];
+        const int lo = (p.window >= 0 && at - p.window > 0) ? at - p.window : 0;
+        const int n_keys = at - lo + 1;
+        const int chunk = ((n_keys + p.att_splits - 1) / p.att_splits + LAY_TILE - 1) / LAY_TILE * LAY_TILE;
+        n_splits = (n_keys + chunk - 1) / chunk;
+        first = lo + split * chunk;
+        last = min(at, first + chunk - 1);
+      }
+      if (r < 0 || split >= n_splits) continue;               // uniform over the block
       const int* table = p.block_table + (size_t)r * p.table_stride;
+      const int page0 = first / p.page;
+      auto slot_of = [&](int key) {
+        const int pg = cached ? table_s[key / p.page - page0] : table[key / p.page];
+        return pg * p.page + key % p.page;
+      };
 
       // ---- q fragments: heads g and g + 8 of the group, lanes in the permuted order ----
       unsigned qa[HEAD_DIM / 32][2][4];
@@ -560,6 +705,7 @@ layer_small_m_kernel(const LayerParams p) {
           qa[st][1][0] = a.z; qa[st][1][1] = b.z; qa[st][1][2] = a.w; qa[st][1][3] = b.w;
         }
       }
+      stamp_to(20);            // q is here
       float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
       float o[HEAD_DIM / 8][4];
 #pragma unroll
@@ -570,9 +716,7 @@ layer_small_m_kernel(const LayerParams p) {
           // the tile's values go straight to their staging rows (a lane per key)
           const int key = k0 + lane;
           const bool in = key <= last;
-          const int key_ok = in ? key : k0;
-          const int s = table[key_ok / p.page] * p.page + key_ok % p.page;
-          const __nv_bfloat16* vrow = p.v_read + ((size_t)s * p.nkv + kvh) * d;
+          const __nv_bfloat16* vrow = p.v_read + ((size_t)slot_of(in ? key : k0) * p.nkv + kvh) * d;
           const unsigned dst = lay_smem(v_s + lane * kVStride);
           const int bytes = in ? 16 : 0;
 #pragma unroll
@@ -581,19 +725,22 @@ layer_small_m_kernel(const LayerParams p) {
           asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
         float s[LAY_TILE / 8][4];
+        uint4 kf[LAY_TILE / 8][HEAD_DIM / 32];
+#pragma unroll
+        for (int nt = 0; nt < LAY_TILE / 8; ++nt) {            // all of the tile's keys asked for at once
+          const int key = k0 + nt * 8 + g;
+          const bool in = key <= last;
+          const __nv_bfloat16* krow = p.k_read + ((size_t)slot_of(in ? key : k0) * p.nkv + kvh) * d;
+#pragma unroll
+          for (int st = 0; st < HEAD_DIM / 32; ++st) kf[nt][st] = lay_load16_cg(krow + st * 32 + 8 * t, in);
+        }
 #pragma unroll
         for (int nt = 0; nt < LAY_TILE / 8; ++nt) {
           s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-          const int key = k0 + nt * 8 + g;
-          const bool in = key <= last;
-          const int key_ok = in ? key : k0;
-          const int sl = table[key_ok / p.page] * p.page + key_ok % p.page;
-          const __nv_bfloat16* krow = p.k_read + ((size_t)sl * p.nkv + kvh) * d;
 #pragma unroll
           for (int st = 0; st < HEAD_DIM / 32; ++st) {
-            const uint4 kv = lay_load16_cg(krow + st * 32 + 8 * t, in);
-            lay_mma(s[nt], qa[st][0][0], qa[st][0][1], qa[st][0][2], qa[st][0][3], kv.x, kv.y);
-            lay_mma(s[nt], qa[st][1][0], qa[st][1][1], qa[st][1][2], qa[st][1][3], kv.z, kv.w);
+            lay_mma(s[nt], qa[st][0][0], qa[st][0][1], qa[st][0][2], qa[st][0][3], kf[nt][st].x, kf[nt][st].y);
+            lay_mma(s[nt], qa[st][1][0], qa[st][1][1], qa[st][1][2], qa[st][1][3], kf[nt][st].z, kf[nt][st].w);
           }
         }
         // ---- scale, mask, running softmax: rows g (heads 0..7) and g + 8 (heads 8..15) ----
@@ -655,6 +802,7 @@ layer_small_m_kernel(const LayerParams p) {
 
       // ---- merge the warps of the block (the merge buffer takes the place of the staging area) ----
       lay_consumer_sync();
+      stamp_to(16);            // the passes over the keys are done
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int head = g + 8 * i;
@@ -694,14 +842,17 @@ layer_small_m_kernel(const LayerParams p) {
       }
       if (n_splits > 1) {
         // ---- the last block to finish a (row, kv head) merges its pieces, in index order ----
+        stamp_to(17);          // the piece is written
         __threadfence();
         lay_consumer_sync();
+        stamp_to(18);          // fenced
         if (tid == 0) {
           const int done = atomicAdd(&p.att_count[row * p.nkv + kvh], 1);
           is_last = done == n_splits - 1;
           if (is_last) p.att_count[row * p.nkv + kvh] = 0;   // ready for the next launch
         }
         lay_consumer_sync();
+        stamp_to(19);          // counted
         if (is_last) {
           __threadfence();
           for (int head = warp; head < group; head += LAY_WARPS) {
@@ -712,13 +863,28 @@ layer_small_m_kernel(const LayerParams p) {
             const float m_all = warp_max(m_s);
             const float f = exp2f(m_s - m_all);                 // 0 for lanes without a piece
             const float den = warp_sum(f * l_s);
-            for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-              const int cc = c0 + lane;
-              float num = 0.f;
-              for (int sp = 0; sp < n_splits; ++sp)
-                num += __shfl_sync(0xffffffffu, f, sp) * __ldcg(&pieces[(size_t)sp * kPieceRow + cc]);
-              p.att_out[((size_t)row * p.nh + kvh * group + head) * d + cc] = __float2bfloat16_rn(num / den);
+            float num[HEAD_DIM / 32];
+#pragma unroll
+            for (int c0 = 0; c0 < HEAD_DIM / 32; ++c0) num[c0] = 0.f;
+            for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {     // eight pieces' values asked for at once
+              float v[8][HEAD_DIM / 32];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+#pragma unroll
+                for (int c0 = 0; c0 < HEAD_DIM / 32; ++c0)
+                  v[k][c0] = sp0 + k < n_splits ? __ldcg(&pieces[(size_t)(sp0 + k) * kPieceRow + c0 * 32 + lane]) : 0.f;
+              }
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {                   // in index order
+                const float fk = __shfl_sync(0xffffffffu, f, (sp0 + k) & 31);
+#pragma unroll
+                for (int c0 = 0; c0 < HEAD_DIM / 32; ++c0) num[c0] += fk * v[k][c0];
+              }
             }
+#pragma unroll
+            for (int c0 = 0; c0 < HEAD_DIM / 32; ++c0)
+              p.att_out[((size_t)row * p.nh + kvh * group + head) * d + c0 * 32 + lane] =
+                  __float2bfloat16_rn(num[c0] / den);
           }
         }
       }
@@ -729,79 +895,129 @@ layer_small_m_kernel(const LayerParams p) {
   grid_barrier();
   stamp();             // 6: barrier 2 passed
 
-  // ======================= phase 3: the output projection, cut along k =======================
-  if (o_first < n_row_tiles) {
-    // this block's k range of the attention's output, all rows, into shared memory (idle rows and
-    // rows past M: zeros, so that they add nothing)
-    const int pieces = p.k_per_split_o / 8;
-    for (int i = tid; i < 8 * MT * pieces; i += LAY_CONSUMERS) {
-      const int m = i / pieces, piece = i % pieces;
-      const bool live = m < p.M && o_k0 + piece * 8 < o_k1 && p.row_req[m] >= 0;
-      const uint4 v = lay_load16_cg(p.att_out + (size_t)m * q_width + o_k0 + piece * 8, live);
-      *reinterpret_cast<uint4*>(h_s + (size_t)m * p.h_pitch + piece * 16) = v;
+  // ======================= phase 3: the output projection =======================
+  if (n_opr > 0) {
+    // the attention's output, all rows, into shared memory (idle rows and rows past M: zeros)
+    const int pieces = q_width / 8;
+    for (int i0 = tid; i0 < 8 * MT * pieces; i0 += 4 * LAY_CONSUMERS) {      // four loads in flight a thread
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * LAY_CONSUMERS, m = i / pieces, piece = i % pieces;
+        v[u] = lay_load16_cg(p.att_out + (size_t)m * q_width + piece * 8,
+                             i < 8 * MT * pieces && m < p.M && req_s[m < 32 ? m : 0] >= 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * LAY_CONSUMERS, m = i / pieces, piece = i % pieces;
+        if (i < 8 * MT * pieces) *reinterpret_cast<uint4*>(h_s + (size_t)m * p.h_pitch + piece * 16) = v[u];
+      }
     }
   }
   lay_consumer_sync();
-  for (int rt = o_first; rt < n_row_tiles; rt += o_step) {
+  for (int i = warp; i < n_opr; i += LAY_WARPS) {
+    const int rt = opr.tile(cta, G, i);
     clear();
-    for (int k0 = o_k0; k0 < o_k1; k0 += LAY_KC) multiply(k0 - o_k0, min(LAY_KC, o_k1 - k0));
-    spill();
-    lay_consumer_sync();
-    for (int i = tid; i < 16 * p.M; i += LAY_CONSUMERS) {
-      const int m = i / 16, rr = i % 16;
-      p.o_part[((size_t)o_split * p.M + m) * p.H + rt * 16 + rr] = summed(rr, m);
+    for (int s = 0; s < spt_o; ++s) multiply(c_opr + i * spt_o + s, s * LAY_KC, min(LAY_KC, q_width - s * LAY_KC));
+    if (!ok) break;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 8 * j + 2 * t + e;
+        if (m < p.M) {
+          p.o_part[(size_t)m * p.H + rt * 16 + g] = acc[j][e];
+          p.o_part[(size_t)m * p.H + rt * 16 + g + 8] = acc[j][2 + e];
+        }
+      }
     }
-    turn ^= 1;
   }
   stamp();             // 7: output projection done
   grid_barrier();
   stamp();             // 8: barrier 3 passed
 
   // ======================= phase 4: the second norm =======================
-  lay_norm<MT>(p.x_mid, p.o_part, 1, p.s_o, (long long)p.M * p.H, p.gain2, p.eps2,
+  lay_norm<MT>(p.x_mid, p.o_part, 1, 1, (long long)p.M * p.H, p.gain2, p.eps2,
                cta == 0 ? p.x_out : nullptr, h_s, p.h_pitch, p.M, p.H, warp, lane);
   lay_consumer_sync();
   stamp();             // 9: second norm done
 
   // ======================= phase 5: gate and up, activation =======================
-  for (int tile = cta; tile < n_tiles_gu; tile += G) {
+  for (int i = warp; i < n_gup; i += LAY_WARPS) {
+    const int tile = gup.tile(cta, G, i);
     clear();
-    for (int k0 = 0; k0 < p.H; k0 += LAY_KC) multiply(k0, min(LAY_KC, p.H - k0));
-    spill();
-    lay_consumer_sync();
-    for (int i = tid; i < 8 * p.M; i += LAY_CONSUMERS) {
-      const int m = i / 8, rr = i % 8;
-      const float gate = summed(rr, m), up = summed(rr + 8, m);
-      p.act[(size_t)m * p.I + tile * 8 + rr] = __float2bfloat16_rn(gate_activation(p.activation, gate) * up);
+    for (int s = 0; s < spt_h; ++s) multiply(c_gup + i * spt_h + s, s * LAY_KC, min(LAY_KC, p.H - s * LAY_KC));
+    if (!ok) break;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 8 * j + 2 * t + e;                      // c0,c1: gate of output g; c2,c3: its up
+        if (m < p.M)
+          p.act[(size_t)m * p.I + tile * 8 + g] =
+              __float2bfloat16_rn(gate_activation(p.activation, acc[j][e]) * acc[j][2 + e]);
+      }
     }
-    turn ^= 1;
   }
   stamp();             // 10: gate/up done
   grid_barrier();
   stamp();             // 11: barrier 4 passed
 
   // ======================= phase 6: down, cut along k =======================
-  if (d_first < n_row_tiles) {
-    const int pieces = p.k_per_split_d / 8;
-    for (int i = tid; i < 8 * MT * pieces; i += LAY_CONSUMERS) {
-      const int m = i / pieces, piece = i % pieces;
-      const uint4 v = lay_load16_cg(p.act + (size_t)m * p.I + d_k0 + piece * 8, m < p.M && d_k0 + piece * 8 < d_k1);
-      *reinterpret_cast<uint4*>(h_s + (size_t)m * p.h_pitch + piece * 16) = v;
+  // a unit is (piece of k, row tile); its stages go to the warps in turn, which meet once
+  for (int i = 0; i < n_dwn; ++i) {
+    const int unit = dwn.tile(cta, G, i), split = unit / n_row_tiles, rt = unit % n_row_tiles;
+    const int k_begin = split * p.k_per_split_d, k_end = min(p.I, k_begin + p.k_per_split_d);
+    if (i == 0 || split != dwn.tile(cta, G, i - 1) / n_row_tiles) {
+      // this piece's columns of the activation, all rows, into shared memory (rows past M: zeros)
+      lay_consumer_sync();
+      const int pieces = p.k_per_split_d / 8;
+      for (int e0 = tid; e0 < 8 * MT * pieces; e0 += 8 * LAY_CONSUMERS) {    // eight loads in flight a thread
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int e = e0 + u * LAY_CONSUMERS, m = e / pieces, piece = e % pieces;
+          v[u] = lay_load16_cg(p.act + (size_t)m * p.I + k_begin + piece * 8,
+                               e < 8 * MT * pieces && m < p.M && k_begin + piece * 8 < k_end);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int e = e0 + u * LAY_CONSUMERS, m = e / pieces, piece = e % pieces;
+          if (e < 8 * MT * pieces) *reinterpret_cast<uint4*>(h_s + (size_t)m * p.h_pitch + piece * 16) = v[u];
+        }
+      }
+      lay_consumer_sync();
+      stamp_to(21);            // the activation's piece is in shared memory
     }
-  }
-  lay_consumer_sync();
-  for (int rt = d_first; rt < n_row_tiles; rt += d_step) {
     clear();
-    for (int k0 = d_k0; k0 < d_k1; k0 += LAY_KC) multiply(k0 - d_k0, min(LAY_KC, d_k1 - k0));
-    spill();
-    lay_consumer_sync();
-    for (int i = tid; i < 16 * p.M; i += LAY_CONSUMERS) {
-      const int m = i / 16, rr = i % 16;
-      p.out[((size_t)d_split * p.M + m) * p.H + rt * 16 + rr] = summed(rr, m);
+    for (int s = warp; s < spt_d; s += LAY_WARPS) {
+      const int k0 = k_begin + s * LAY_KC;
+      const int kn = k0 < k_end ? min(LAY_KC, k_end - k0) : 0;
+      multiply(c_dwn + i * spt_d + s, kn ? s * LAY_KC : 0, kn);   // kn 0: the stage is only given back
     }
-    turn ^= 1;
+    {
+      float* mine = part + (size_t)warp * 16 * (8 * MT + 1);
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        mine[g * (8 * MT + 1) + 8 * j + 2 * t] = acc[j][0];
+        mine[g * (8 * MT + 1) + 8 * j + 2 * t + 1] = acc[j][1];
+        mine[(g + 8) * (8 * MT + 1) + 8 * j + 2 * t] = acc[j][2];
+        mine[(g + 8) * (8 * MT + 1) + 8 * j + 2 * t + 1] = acc[j][3];
+      }
+    }
+    lay_consumer_sync();
+    stamp_to(22);              // the warps' products are done
+    for (int e = tid; e < 16 * p.M && ok; e += LAY_CONSUMERS) {
+      const int m = e / 16, rr = e % 16;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < LAY_WARPS; ++w) v += part[((size_t)w * 16 + rr) * (8 * MT + 1) + m];
+      p.out[((size_t)split * p.M + m) * p.H + rt * 16 + rr] = v;
+    }
+    if (i + 1 < n_dwn) lay_consumer_sync();      // the partial sums are read before the next unit's
   }
   stamp();             // 12: down done
+  }
 
   // ---- the last block to leave makes the barrier ready for the next launch ----
   if (tid == 0) {
@@ -825,61 +1041,59 @@ TOKB200_API int tokb200_layer_small_m_head_dim(void) { return HEAD_DIM; }
 
 // The plan for sizes on this device; blocks == 0: the kernel does not take them.
 struct LayerPlan {
-  int blocks, n_stages, h_pitch, s_o, k_per_split_o, s_down, k_per_split_d, smem_max;
+  int blocks, n_stages, h_pitch, s_down, k_per_split_d, smem_max;
   size_t smem;
 };
 
-static int lay_cut(int sms, int row_tiles, int K, int* k_per_split) {
-  // about two units (row tile, piece of k) a block; pieces of whole 32s
-  int s = (2 * sms + row_tiles / 2) / row_tiles;
-  if (s < 1) s = 1;
-  if (s > 16) s = 16;
-  int kps = ((K + s - 1) / s + 31) / 32 * 32;
-  s = (K + kps - 1) / kps;
-  *k_per_split = kps;
-  return s;
-}
-
 static LayerPlan lay_plan(int M, int H, int I, int nh, int nkv) {
   LayerPlan plan = {};
-  if (M <= 0 || M > 16 || H <= 0 || H > 4096 || I <= 0 || H % 32 || I % 128 || nh <= 0 || nkv <= 0 || nh % nkv ||
+  if (M <= 0 || M > 32 || H <= 0 || H > 4096 || I <= 0 || H % 32 || I % 128 || nh <= 0 || nkv <= 0 || nh % nkv ||
       nh / nkv > LAY_MAX_GROUP || (nh * HEAD_DIM) % 32)
     return plan;
   int device = 0, sms = 0, smem_max = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return plan;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return plan;
   if (cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return plan;
-  const int MT = M <= 8 ? 1 : 2;
+  const int MT = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
   const int row_tiles = H / 16;
-  plan.s_o = lay_cut(sms, row_tiles, nh * HEAD_DIM, &plan.k_per_split_o);
-  plan.s_down = lay_cut(sms, row_tiles, I, &plan.k_per_split_d);
+  // down is cut along k so that a piece of the activation (all rows) fits the work area, and
+  // further while its units (piece, row tile) still number no more than the blocks
+  const int longest = MT == 4 ? 2048 : 4096;
+  int s = (I + longest - 1) / longest;
+  if (sms / row_tiles > s) s = sms / row_tiles;
+  if (s > 16) s = 16;
+  int kps = ((I + s - 1) / s + 31) / 32 * 32;
+  s = (I + kps - 1) / kps;
+  plan.s_down = s;
+  plan.k_per_split_d = kps;
   int widest = H;
-  if (plan.k_per_split_o > widest) widest = plan.k_per_split_o;
-  if (plan.k_per_split_d > widest) widest = plan.k_per_split_d;
+  if (nh * HEAD_DIM > widest) widest = nh * HEAD_DIM;
+  if (kps > widest) widest = kps;
   plan.h_pitch = (2 * widest + 127) / 128 * 128 + 64;
   const int group = nh / nkv;
-  size_t work = (size_t)8 * MT * plan.h_pitch + (size_t)2 * LAY_WARPS * 16 * (8 * MT + 1) * 4;
+  size_t work = (size_t)8 * MT * plan.h_pitch + (size_t)LAY_WARPS * 16 * (8 * MT + 1) * 4;
   const size_t stage = (size_t)LAY_WARPS * LAY_TILE * kVStride * 2;
   const size_t merge = (size_t)LAY_WARPS * group * kPieceRow * 4;
   const size_t att = stage > merge ? stage : merge;
   if (att > work) work = att;
   work = (work + 127) / 128 * 128;
-  const long long room = (long long)smem_max - 2048 - (long long)work - 1024;
+  const size_t tail = 2048;                         // the ring's barriers and the cached table entries
+  const long long room = (long long)smem_max - 2048 - (long long)work - (long long)tail;
   int stages = (int)(room / LAY_STAGE_BYTES);
   if (stages > 8) stages = 8;
   if (stages < 3) return plan;
   plan.blocks = sms;
   plan.n_stages = stages;
   plan.smem_max = smem_max;
-  plan.smem = work + (size_t)stages * LAY_STAGE_BYTES + 1024;
+  plan.smem = work + (size_t)stages * LAY_STAGE_BYTES + tail;
   return plan;
 }
 
-// Partial sums of the feed-forward that `out` holds for these sizes (0: sizes not taken), and
-// those of the output projection that `o_part` must hold.
+// Partial sums of the feed-forward that `out` holds for these sizes (0: sizes not taken); the
+// output projection's result is one plane (`o_splits` = 1).
 TOKB200_API int tokb200_layer_small_m_splits(int M, int H, int I, int nh, int nkv, int* o_splits) {
   const LayerPlan plan = lay_plan(M, H, I, nh, nkv);
-  if (o_splits) *o_splits = plan.blocks ? plan.s_o : 0;
+  if (o_splits) *o_splits = plan.blocks ? 1 : 0;
   return plan.blocks ? plan.s_down : 0;
 }
 
@@ -893,7 +1107,11 @@ struct LayerArgs {            // what the launcher takes, as plain C
   const int* pos; const int* slot; const int* row_req; const int* block_table; int table_stride, page;
   void* q_buf; float* att_part; int* att_count; void* att_out; float* o_part; void* act; int* sync;
   int M, H, I, nh, nkv, d;
-  long long* stamps;          // null, or [blocks, 16] for the phases' times (profiling)
+  long long* stamps;          // null, or [blocks, 32] for the phases' times (profiling)
+  const void* next_w_qkv;     // null, or the next layer's q/k/v weight, to be brought into L2
+  const float* next_gain1;    // ... and its first gain and q/k/v bias
+  const float* next_b_qkv;
+  int repeat;                 // 0 or 1: once; more (profiling only): the same layer again and again in one launch
 };
 
 TOKB200_API int tokb200_layer_small_m(const LayerArgs* a, cudaStream_t stream) {
@@ -920,7 +1138,9 @@ TOKB200_API int tokb200_layer_small_m(const LayerArgs* a, cudaStream_t stream) {
   p.q_buf = (__nv_bfloat16*)a->q_buf; p.att_part = a->att_part; p.att_count = a->att_count;
   p.att_out = (__nv_bfloat16*)a->att_out; p.o_part = a->o_part; p.act = (__nv_bfloat16*)a->act; p.sync = a->sync;
   p.M = a->M; p.H = a->H; p.I = a->I; p.nh = a->nh; p.nkv = a->nkv; p.stamps = a->stamps;
-  p.n_stages = plan.n_stages; p.h_pitch = plan.h_pitch; p.s_o = plan.s_o; p.k_per_split_o = plan.k_per_split_o;
+  p.next_w = (const __nv_bfloat16*)a->next_w_qkv; p.next_gain = a->next_gain1; p.next_bias = a->next_b_qkv;
+  p.repeat = a->repeat > 1 ? a->repeat : 1;
+  p.n_stages = plan.n_stages; p.h_pitch = plan.h_pitch;
   p.s_down = plan.s_down; p.k_per_split_d = plan.k_per_split_d;
   // pieces of a row's keys: enough units for the device, none shorter than one pass of a block's
   // warps (256 keys) as far as the table reaches
@@ -932,14 +1152,16 @@ TOKB200_API int tokb200_layer_small_m(const LayerArgs* a, cudaStream_t stream) {
   if (splits > LAY_MAX_SPLITS) splits = LAY_MAX_SPLITS;
   if (splits < 1) splits = 1;
   p.att_splits = splits;
-  void (*kernel)(const LayerParams) = a->M <= 8 ? layer_small_m_kernel<1> : layer_small_m_kernel<2>;
-  static bool configured[64][2] = {};
+  const int form = a->M <= 8 ? 0 : (a->M <= 16 ? 1 : 2);
+  void (*kernel)(const LayerParams) = form == 0 ? layer_small_m_kernel<1> :
+                                      form == 1 ? layer_small_m_kernel<2> : layer_small_m_kernel<4>;
+  static bool configured[64][3] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
-  if (!configured[device][a->M <= 8 ? 0 : 1]) {
+  if (!configured[device][form]) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem_max - 1024);
     if (err != cudaSuccess) return (int)err;
-    configured[device][a->M <= 8 ? 0 : 1] = true;
+    configured[device][form] = true;
   }
   // One block per SM, each with most of an SM's shared memory: all blocks become resident as the
   // predecessor's blocks leave (they wait for nothing of ours), so the barriers are met; their

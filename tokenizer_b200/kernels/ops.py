@@ -796,10 +796,13 @@ class _LayerArgs(ctypes.Structure):
         [(n, ctypes.c_void_p) for n in ("x_mid", "x_out", "out", "pos", "slot", "row_req", "block_table")] +
         [("table_stride", ctypes.c_int), ("page", ctypes.c_int)] +
         [(n, ctypes.c_void_p) for n in ("q_buf", "att_part", "att_count", "att_out", "o_part", "act", "sync")] +
-        [(n, ctypes.c_int) for n in ("M", "H", "I", "nh", "nkv", "d")] + [("stamps", ctypes.c_void_p)])
+        [(n, ctypes.c_int) for n in ("M", "H", "I", "nh", "nkv", "d")] +
+        [("stamps", ctypes.c_void_p), ("next_w_qkv", ctypes.c_void_p), ("next_gain1", ctypes.c_void_p),
+         ("next_b_qkv", ctypes.c_void_p), ("repeat", ctypes.c_int)])
 
 
 LAYER_HEAD_DIMS = (64, 128)
+LAYER_MAX_ROWS = 32
 LAYER_MAX_SPLITS = 32
 _layer_plans = {}
 # compile-time switches of the layer kernel's library (a test builds it with short wait limits)
@@ -813,12 +816,12 @@ def _layer_lib(d: int):
 def layer_small_m_splits(M: int, hidden: int, inner: int, nh: int, nkv: int, d: int):
     """(partial sums of the feed-forward, partial sums of the output projection) that the
     whole-layer kernel of few rows writes for these sizes on this device; (0, 0) when it does
-    not take them (more than 16 rows, a head size it is not built for, hidden not a multiple
+    not take them (more than 32 rows, a head size it is not built for, hidden not a multiple
     of 32 or beyond 4096, inner not a multiple of 128, groups of more than 16 heads, too
     little shared memory for its ring)."""
-    if M < 1 or M > 16 or d not in LAYER_HEAD_DIMS:
+    if M < 1 or M > LAYER_MAX_ROWS or d not in LAYER_HEAD_DIMS:
         return 0, 0
-    key = (torch.cuda.current_device(), M <= 8, hidden, inner, nh, nkv, d)
+    key = (torch.cuda.current_device(), (M > 8) + (M > 16), hidden, inner, nh, nkv, d)
     if key not in _layer_plans:
         o_splits = ctypes.c_int(0)
         down = int(_layer_lib(d).tokb200_layer_small_m_splits(_i(M), _i(hidden), _i(inner), _i(nh), _i(nkv),
@@ -830,14 +833,16 @@ def layer_small_m_splits(M: int, hidden: int, inner: int, nh: int, nkv: int, d: 
 def layer_small_m(x_in, delta, x_mid, x_out, out, gain1, eps1, w_qkv, b_qkv, pos, slot, row_req, block_table,
                   cos, sin, k_pool, v_pool, writes: bool, w_o, gain2, eps2, w_gate_up, w_down, nh: int,
                   nkv: int, d: int, page: int, window, scale: float, activation: str = "silu",
-                  stamps: Optional[torch.Tensor] = None) -> None:
-    """One pre-norm decoder layer for up to 16 rows of one token each (bfloat16): x_mid = x_in +
+                  stamps: Optional[torch.Tensor] = None, next_layer=None, repeat: int = 1) -> None:
+    """One pre-norm decoder layer for up to 32 rows of one token each (bfloat16): x_mid = x_in +
     delta; attention (q/k/v with bias, rotary encoding, cache write when `writes`, softmax over
     the paged keys) of rms_norm(x_mid) * gain1; x_out = x_mid + its output projection; out
     [S, M, H] = float32 partial sums over k of the gated feed-forward of rms_norm(x_out) * gain2.
     `delta` as for rms_norm ([M, H], float32 partial sums [S, M, H], or None); `w_gate_up` in the
     row order of `interleave_gate_up`; `out` has `layer_small_m_splits(...)[0]` planes.  `stamps`
-    (int64 [blocks, 16], for profiling) receives the time in ns at which each block passes each phase."""
+    (int64 [blocks, 16], for profiling) receives the time in ns at which each block passes each phase;
+    `next_layer` = (q/k/v weight of the same shape, first gain, q/k/v bias or None) of the layer that
+    runs next: what that layer's kernel starts with is brought into L2 ahead."""
     M, hidden = x_in.shape
     inner = w_down.shape[1]
     down_splits, o_splits = layer_small_m_splits(M, hidden, inner, nh, nkv, d)
@@ -866,7 +871,7 @@ def layer_small_m(x_in, delta, x_mid, x_out, out, gain1, eps1, w_qkv, b_qkv, pos
             att_count=torch.zeros(M * nkv, dtype=torch.int32, device=dev),
             att_out=torch.zeros((M, q_width), dtype=torch.bfloat16, device=dev),
             o_part=torch.empty((o_splits, M, hidden), dtype=torch.float32, device=dev),
-            act=torch.empty((16, inner), dtype=torch.bfloat16, device=dev),
+            act=torch.empty((LAYER_MAX_ROWS, inner), dtype=torch.bfloat16, device=dev),
             sync=torch.zeros(2, dtype=torch.int32, device=dev))
     sc = _space.layer[key]
 
@@ -885,7 +890,10 @@ def layer_small_m(x_in, delta, x_mid, x_out, out, gain1, eps1, w_qkv, b_qkv, pos
         table_stride=block_table.shape[1], page=page, q_buf=ptr(sc["q_buf"]), att_part=ptr(sc["att_part"]),
         att_count=ptr(sc["att_count"]), att_out=ptr(sc["att_out"]), o_part=ptr(sc["o_part"]),
         act=ptr(sc["act"]), sync=ptr(sc["sync"]), M=M, H=hidden, I=inner, nh=nh, nkv=nkv, d=d,
-        stamps=ptr(stamps))
+        stamps=ptr(stamps), repeat=repeat)
+    if next_layer is not None and next_layer[0].shape == w_qkv.shape:
+        args.next_w_qkv, args.next_gain1 = ptr(next_layer[0]), ptr(next_layer[1])
+        args.next_b_qkv = ptr(next_layer[2])
     _check(_layer_lib(d).tokb200_layer_small_m(ctypes.byref(args), _stream()), "layer_small_m")
 
 

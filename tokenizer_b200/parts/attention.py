@@ -38,10 +38,13 @@ _PROMPT_KERNEL = os.environ.get("TOKB200_ATTENTION", "tcgen05")
 # unless asked for.
 _FUSED_QKV = os.environ.get("TOKB200_QKV_ROPE", "separate") == "fused"
 _FUSED_NORM = os.environ.get("TOKB200_QKV_NORM", "fused") != "separate"
-# TOKB200_LAYER=separate keeps a decoding step's layer as several kernels (projection, attention,
-# output projection, feed-forward) instead of one; so do the switches that take the norm or the
-# feed-forward out of their fusions
-_FUSED_LAYER = os.environ.get("TOKB200_LAYER", "fused") != "separate" and _FUSED_NORM
+# TOKB200_LAYER=fused runs a decoding step's layer (up to 32 rows) as ONE kernel instead of four
+# (projection, attention, output projection, feed-forward).  It is correct and off by default:
+# measured at 36 us a layer against 27 us for the four kernels (8 rows, Qwen2.5-0.5B sizes),
+# because its phases run one after the other behind barriers over all blocks, each a chain of
+# two or three trips to L2, while the four kernels overlap their heads and tails.  The
+# switches that take the norm or the feed-forward out of their fusions turn it off as well.
+_FUSED_LAYER = os.environ.get("TOKB200_LAYER", "separate") == "fused" and _FUSED_NORM
 
 
 class RowTiles(BatchAnnotation):
@@ -156,6 +159,10 @@ class GQAttention:
     def streamed_weights(self):
         return [self.qkv.weight, self.out.weight]
 
+    def start_operands(self):
+        """(first weight, its bias): what this mixer's first kernel reads."""
+        return self.qkv.weight, self.qkv_bias
+
     def fused_layer(self, stream, norm, ctx, cache, feed_forward, feed_forward_norm) -> bool:
         """For a step of few rows of one token each in bfloat16: the WHOLE pre-norm layer in one
         kernel (both norms, this attention, a gated feed-forward), straight from the stream.
@@ -182,10 +189,12 @@ class GQAttention:
         delta, stream.pending = stream.pending, None
         x_mid, x_out = torch.empty_like(x), torch.empty_like(x)
         out = torch.empty((down_splits,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+        ahead = getattr(ctx.next_block, "layer_start_operands", None)
         ops.layer_small_m(x, delta, x_mid, x_out, out, gain1, eps1, self.qkv.weight, self.qkv_bias, ctx.pos,
                           group.slots, ctx.row_req, group.block_table, self.position.cos, self.position.sin,
                           cache.k_pool, cache.v_pool, cache.writes, self.out.weight, gain2, eps2, w_gate_up,
-                          w_down, self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, activation)
+                          w_down, self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, activation,
+                          next_layer=ahead() if ahead is not None else None)
         stream.x, stream.pending = x_out, out
         return True
 

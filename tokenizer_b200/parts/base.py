@@ -140,6 +140,9 @@ class StepContext:
     # what the model's parts asked to have packed with the batch (`BatchAnnotation`), by key:
     # (the annotation's device view, the count its `fill` returned)
     views: Dict[str, Tuple[Any, int]] = field(default_factory=dict)
+    # the block that runs after the one running now (None after the last): a part that asks for
+    # memory ahead of its use may look at what that block starts with
+    next_block: Any = None
     # host copies, for choosing kernels and for mixers that loop over requests
     q_lens: List[int] = field(default_factory=list)
     kv_lens: List[int] = field(default_factory=list)

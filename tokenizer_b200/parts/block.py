@@ -23,6 +23,17 @@ class PreNormResidual:
             out += list(getattr(part, "streamed_weights", lambda: [])())
         return out
 
+    def layer_start_operands(self):
+        """What this layer's kernels read first (the mixer's first weight, the first norm's
+        gain, the mixer's bias), for the layer before to bring into L2; None when the parts
+        have no such operands."""
+        start = getattr(self.mixer, "start_operands", None)
+        fold = getattr(self.mixer_norm, "folded", None)
+        if start is None or fold is None:
+            return None
+        weight, bias = start()
+        return weight, fold()[0], bias
+
     def forward(self, stream, ctx, cache):
         # a mixer may take the whole layer (both norms, itself, the feed-forward) into one kernel
         whole = getattr(self.mixer, "fused_layer", None)

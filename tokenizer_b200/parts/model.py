@@ -152,6 +152,7 @@ class DecoderModel:
         for at, (call, binding) in enumerate(zip(self.order, bindings)):
             if ahead is not None and at + 1 < len(self.order):
                 ahead.fetch(self.blocks[self.order[at + 1].layer].streamed_weights())
+            ctx.next_block = self.blocks[self.order[at + 1].layer] if at + 1 < len(self.order) else None
             self.blocks[call.layer].forward(stream, ctx, binding)
         if ahead is not None:
             ahead.join()
