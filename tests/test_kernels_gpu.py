@@ -374,6 +374,33 @@ def test_decode_attention_with_64_rows_of_8192_keys(nh, nkv, d):
         out.fill_(9.0)
 
 
+def test_decode_attention_serves_only_the_rows_it_is_given():
+    """With a list of rows (the single-token rows of a step that also brings portions), the
+    kernel serves those rows and leaves every other row of the output alone."""
+    nh, nkv, d, page, dtype = 12, 2, 128, 16, torch.bfloat16
+    lengths = [700, 33, 1300, 5]
+    k_pool, v_pool, tables, dense = paged_setup(lengths, nh, nkv, d, page, dtype, seed=25)
+    # ten batch rows: rows 2, 7, 8 and 4 are the last positions of the four requests
+    row_req = [-1, -1, 0, -1, 3, -1, -1, 1, 2, -1]
+    pos = [0, 0, 699, 0, 4, 0, 0, 32, 1299, 0]
+    rows = torch.tensor([8, 2, -1, 7, 4, -1, -1, -1], dtype=torch.int32, device=DEV)
+    q = rnd(10, nh, d, seed=26, dtype=dtype)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(d)
+    for _ in range(2):
+        ops().decode_attention(q.view(10, nh * d), k_pool, v_pool, out.view(10, nh * d), tables,
+                               torch.tensor(row_req, dtype=torch.int32, device=DEV),
+                               torch.tensor(pos, dtype=torch.int32, device=DEV), nh, nkv, d, page, None, scale,
+                               rows=rows)
+        live = [2, 4, 7, 8]
+        want = attention_reference(q.float().cpu()[live], dense, [row_req[i] for i in live],
+                                   [pos[i] for i in live], nh, nkv, None, scale)
+        close_tensor_core_attention(out[live], want)
+        idle = [i for i in range(10) if i not in live]
+        assert bool((out[idle] == 9.0).all())
+        out.fill_(9.0)
+
+
 def test_decode_attention_far_key_across_splits():
     nh, nkv, d, page, n = 7, 1, 64, 16, 1500
     dtype = torch.bfloat16

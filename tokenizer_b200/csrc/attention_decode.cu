@@ -99,14 +99,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
                         int nkv, int page, int window, float scale,
-                        float* __restrict__ scratch, int* __restrict__ counters, int min_chunk) {
+                        float* __restrict__ scratch, int* __restrict__ counters, int min_chunk,
+                        const int* __restrict__ rows) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   __shared__ int is_last;
   // The rows' requests, positions and block tables were written before the predecessor (the
   // projection that writes q and the newest key) started, so they are read while it still
   // runs; q, keys and values only after the wait.
-  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
-  const int r = row_req[row];
+  // `rows` (optional): the batch rows this launch serves, one per z (-1: none); scratch and
+  // counters are indexed by z, q, out, positions and requests by the row
+  const int split = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
+  const int row = rows ? rows[z] : z;
+  const int r = row < 0 ? -1 : row_req[row];
   const int p = r < 0 ? 0 : pos[row];
   const int lo = (window >= 0 && p - window > 0) ? p - window : 0;
   const int n_keys = p - lo + 1;
@@ -283,7 +287,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 
   // scratch layout per (row, head): [split][HEAD_DIM + 2] = weighted values, max (log2 units), sum
   const size_t per_head = (size_t)DEC_MAX_SPLITS * kRow;
-  float* base = scratch + ((size_t)row * nh + kvh * group) * per_head;
+  float* base = scratch + ((size_t)z * nh + kvh * group) * per_head;
   float* piece_s = acc_s + (size_t)DEC_WARPS * group * kRow;     // CLUSTER: this block's piece, [head][kRow]
   for (int i = tid; i < group * HEAD_DIM; i += DEC_THREADS) {
     const int head = i / HEAD_DIM, c = i % HEAD_DIM;
@@ -344,9 +348,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int done = atomicAdd(&counters[row * nkv + kvh], 1);
+    const int done = atomicAdd(&counters[z * nkv + kvh], 1);
     is_last = done == n_splits - 1;
-    if (is_last) counters[row * nkv + kvh] = 0;   // ready for the next launch
+    if (is_last) counters[z * nkv + kvh] = 0;     // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
@@ -383,11 +387,13 @@ TOKB200_API long long tokb200_decode_attention_scratch_floats(int n_rows, int nh
 TOKB200_API int tokb200_decode_attention_head_dim() { return HEAD_DIM; }
 
 // `counters` holds n_rows * nkv ints, zero before the first launch; every launch
-// leaves them zero again.
+// leaves them zero again.  `rows` (optional, n_rows ints): the batch rows to serve, -1 for none;
+// without it the launch serves rows 0 .. n_rows - 1.
 TOKB200_API int tokb200_decode_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, int n_rows, int nh, int nkv, int d,
-    int page, int window, float scale, float* scratch, int* counters, cudaStream_t stream) {
+    int page, int window, float scale, float* scratch, int* counters, const int* rows,
+    cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > DEC_MAX_GROUP || page <= 0 ||
       nkv > 65535 || n_rows > 65535)
@@ -439,7 +445,7 @@ TOKB200_API int tokb200_decode_attention(
   }();
   const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
-                 int, const int*, const int*, int, int, int, int, float, float*, int*, int) =
+                 int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*) =
       cluster ? decode_attention_kernel<true> : decode_attention_kernel<false>;
   if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
     static bool configured[64][2] = {};
@@ -457,7 +463,7 @@ TOKB200_API int tokb200_decode_attention(
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                             table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                            counters, min_chunk);
+                            counters, min_chunk, rows);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = dim3(DEC_THREADS);
@@ -479,6 +485,6 @@ TOKB200_API int tokb200_decode_attention(
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                        (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                                        table_stride, row_req, pos, nh, nkv, page, window, scale, scratch,
-                                       counters, min_chunk);
+                                       counters, min_chunk, rows);
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }

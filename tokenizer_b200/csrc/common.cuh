@@ -5,8 +5,10 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <string.h>
 
 #define TOKB200_API extern "C" __attribute__((visibility("default")))
 
@@ -82,22 +84,54 @@ TOKB200_API int tokb200_error_word_alloc(int** host_pointer, int** device_pointe
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
 
+// `early`: whether this launch may start before its predecessor has completed (false: the
+// kernel still takes part in the chain, its own successor may start early, but it starts
+// strictly after its predecessor).
+template <typename... KArgs, typename... Args>
+static inline int launch_ordered(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args);
+
 template <typename... KArgs, typename... Args>
 static inline int launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                    cudaStream_t stream, Args... args) {
+  return launch_ordered(true, kernel, grid, block, smem, stream, args...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_ordered(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  // TOKB200_PDL=0 in the environment launches every kernel strictly after its predecessor
+  // TOKB200_PDL=0 in the environment launches every kernel strictly after its predecessor;
+  // TOKB200_PDL_OFF=name[,name...] does so for the kernels of the libraries whose file names
+  // contain one of the names (to find which early start a fault depends on)
   static const int overlap = [] {
     const char* v = getenv("TOKB200_PDL");
-    return (v && v[0] == '0') ? 0 : 1;
+    if (v && v[0] == '0') return 0;
+    const char* off = getenv("TOKB200_PDL_OFF");
+    Dl_info here;
+    if (off && off[0] && dladdr((const void*)&tokb200_set_error_word, &here) && here.dli_fname) {
+      const char* at = off;
+      while (*at) {
+        const char* end = strchr(at, ',');
+        const size_t n = end ? (size_t)(end - at) : strlen(at);
+        char name[128];
+        if (n > 0 && n < sizeof(name)) {
+          memcpy(name, at, n);
+          name[n] = 0;
+          if (strstr(here.dli_fname, name)) return 0;
+        }
+        at = end ? end + 1 : at + n;
+      }
+    }
+    return 1;
   }();
   cudaLaunchAttribute attribute[1];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = overlap;
+  attribute[0].val.programmaticStreamSerializationAllowed = early ? overlap : 0;
   config.attrs = attribute;
   config.numAttrs = 1;
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);

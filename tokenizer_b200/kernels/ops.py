@@ -378,16 +378,18 @@ def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page, window,
-                     scale) -> None:
+                     scale, rows: Optional[torch.Tensor] = None) -> None:
     """Attention for rows of one token each (bfloat16): keys are split over
     blocks and merged; the scratch for the pieces is kept per (device, rows,
-    heads, head size) and reused by every layer, which run one after another."""
+    heads, head size) and reused by every layer, which run one after another.  With `rows`
+    (int32, -1 for none) only those rows of the batch are served: the single-token rows of a
+    step that also brings portions of prompts, which go to the kernels for portions."""
     if q.dtype != torch.bfloat16:
         raise ValueError("decode_attention is the bfloat16 kernel")
     if not decode_attention_supported(nh, nkv, d):
         raise ValueError(f"decode_attention: {nh} heads over {nkv} groups of size {d} is not taken")
     lib = _load("attention_decode.cu", defines=(f"HEAD_DIM={d}",))
-    n_rows = q.shape[0]
+    n_rows = q.shape[0] if rows is None else rows.shape[0]
     key = (q.device.index, n_rows, nh, nkv, d)
     if key not in _space.decode:
         lib.tokb200_decode_attention_scratch_floats.restype = ctypes.c_longlong
@@ -399,7 +401,7 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
         _i(page), _i(-1 if window is None else int(window)), _f(scale), _ptr(scratch),
-        _ptr(counters), _stream()), "decode_attention")
+        _ptr(counters), _ptr(rows), _stream()), "decode_attention")
 
 
 _stream_plans = {}

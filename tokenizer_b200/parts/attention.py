@@ -51,17 +51,24 @@ class RowTiles(BatchAnnotation):
     """The step's rows cut into tiles of up to `rows` consecutive rows of one request, as the
     prompt-attention kernels take them: int32 [tiles, 2] = (first row, rows), the tile that
     walks the most keys first (the kernels place blocks in that order, so the longest work
-    starts first).  Unused tiles of a padded step have no rows."""
+    starts first).  Unused tiles of a padded step have no rows.  With `long_only`, requests
+    that bring a single token get no tile when others bring more (their rows are `SingleRows`',
+    served by the decoding kernel: a tile of one row would walk its keys at a tile's cost)."""
 
-    def __init__(self, rows: int):
+    def __init__(self, rows: int, long_only: bool = False):
         self.rows = rows
-        self.key = f"row_tiles_{rows}"
+        self.long_only = long_only
+        self.key = f"row_tiles_{rows}" + ("_long" if long_only else "")
 
     def capacity(self, n_tokens, n_requests):
         return 2 * (n_tokens // self.rows + n_requests)
 
     def fill(self, out, first_rows, counts, starts, padded):
         n = len(counts)
+        if self.long_only and n and int(counts.max()) > 1:
+            keep = counts > 1
+            first_rows, counts, starts = first_rows[keep], counts[keep], starts[keep]
+            n = len(counts)
         if n and int(counts.max()) == 1:
             # one tile of one row a request: a stable order, as a sort of tuples gives
             order = np.argsort(-starts, kind="stable")
@@ -85,9 +92,35 @@ class RowTiles(BatchAnnotation):
         return words.view(-1, 2)
 
 
-# the tiles of the two prompt kernels: 64 rows (mma.sync) and 128 rows (tcgen05)
+class SingleRows(BatchAnnotation):
+    """The rows of requests that bring exactly one token, when the step also brings portions
+    of others: int32 [requests], row indices, -1 where there is none.  A step of single tokens
+    alone has none (all of its rows go to the decoding kernel anyway)."""
+
+    key = "single_rows"
+
+    def capacity(self, n_tokens, n_requests):
+        return n_requests
+
+    def fill(self, out, first_rows, counts, starts, padded):
+        out[:] = -1
+        made = 0
+        if len(counts) and int(counts.max()) > 1:
+            rows = first_rows[counts == 1]
+            out[:len(rows)] = rows
+            made = len(rows)
+        return len(out) if padded else made
+
+
+# the tiles of the two prompt kernels: 64 rows (mma.sync) and 128 rows (tcgen05), for all
+# requests and for those alone that bring more than one token
 _TILES = RowTiles(ops.PREFILL_TILE_ROWS)
 _WIDE_TILES = RowTiles(ops.WIDE_TILE_ROWS)
+_LONG_TILES = RowTiles(ops.PREFILL_TILE_ROWS, long_only=True)
+_LONG_WIDE_TILES = RowTiles(ops.WIDE_TILE_ROWS, long_only=True)
+_SINGLES = SingleRows()
+# TOKB200_MIXED=tiles sends the single-token rows of a mixed step through the kernels for portions
+_SPLIT_MIXED = os.environ.get("TOKB200_MIXED", "split") != "tiles"
 # portions from this length on go to the tcgen05 kernel (shorter ones would leave most of a
 # 128-row tile empty)
 _WIDE_FROM = 96
@@ -97,7 +130,7 @@ class GQAttention:
     graph_safe = True   # launches depend on device-side metadata only
 
     def batch_annotations(self):
-        return [_TILES, _WIDE_TILES]
+        return [_TILES, _WIDE_TILES, _LONG_TILES, _LONG_WIDE_TILES, _SINGLES]
 
     def shape_key(self, q_lens):
         """Which attention kernel a step of these portion lengths gets (part of the key under
@@ -273,6 +306,16 @@ class GQAttention:
                 self.nh, self.nkv, self.d, group.page_size, self.window, self.scale)
             return
         wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
+        singles = ctx.views.get(_SINGLES.key)
+        if _SPLIT_MIXED and q.dtype == torch.bfloat16 and singles is not None and singles[1] > 0 and \
+                ops.decode_attention_supported(self.nh, self.nkv, self.d) and \
+                ctx.views.get(_LONG_WIDE_TILES.key) is not None and ctx.views.get(_LONG_TILES.key) is not None:
+            # a step of portions AND single tokens: the single-token rows go to the decoding kernel
+            # (keys split over blocks, the group's heads as one tile), the portions to theirs
+            ops.decode_attention(
+                q, cache.k_pool, cache.v_pool, out, group.block_table, ctx.row_req, ctx.pos,
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0])
+            wide, tiles = ctx.views[_LONG_WIDE_TILES.key], ctx.views[_LONG_TILES.key]
         if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
                 wide is not None and ctx.max_q_len >= _WIDE_FROM and \
                 ops.attention_tcgen05_supported(self.nh, self.nkv, self.d):
