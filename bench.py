@@ -193,6 +193,9 @@ def main():
                         help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
                              "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes")
     parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
+    parser.add_argument("--layer-phases", action="store_true",
+                        help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
+                             "phase, from the kernel's own time stamps, beside the time of the four kernels it replaces")
     parser.add_argument("--skip-gate", action="store_true",
                         help="do not compare with the plain implementation first (profiling runs)")
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
@@ -211,6 +214,8 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus)
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.layer_phases:
+        return run_layer_phases(args)
     if args.config == "7b":
         return run_7b(args)
     if args.config == "1.5b-mixed":
@@ -378,6 +383,86 @@ def main():
     }
     engine.check()                 # a bounded wait that ran out inside a kernel invalidates the numbers
     print(json.dumps(line))
+    return 0
+
+
+def run_layer_phases(args):
+    """The whole-layer kernel for few rows at Qwen2.5-0.5B layer sizes: 24 launches with 24 sets of
+    weights (a step's worth, so nothing stays in L2), the median over the later layers of the time at
+    which the last block passes each phase (from the kernel's own stamps of %globaltimer), and the
+    time per layer of the captured chain."""
+    import math
+    import torch
+    from tokenizer_b200.kernels import ops as o
+
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    M, ctx = args.batch, PROMPT_LEN + 88
+    H, I, nh, nkv, d = (SIZES[k] for k in ("hidden_size", "intermediate_size", "num_attention_heads",
+                                           "num_key_value_heads", "head_dim"))
+    L = SIZES["num_hidden_layers"]
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rnd(*shape, dtype=torch.bfloat16, scale=0.05):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    layers = [dict(w_qkv=rnd((nh + 2 * nkv) * d, H), b=rnd((nh + 2 * nkv) * d, dtype=torch.float32),
+                   w_o=rnd(H, nh * d), g1=1 + rnd(H, dtype=torch.float32), g2=1 + rnd(H, dtype=torch.float32),
+                   w_gu=rnd(2 * I, H), w_d=rnd(H, I), k=rnd(M * 1024, nkv, d, scale=1.0),
+                   v=rnd(M * 1024, nkv, d, scale=1.0)) for _ in range(L)]
+    tables = torch.arange(M * 1024 // PAGE, dtype=torch.int32, device=dev).view(M, 1024 // PAGE)
+    pos = torch.full((M,), ctx - 1, dtype=torch.int32, device=dev)
+    slot = (tables[:, (ctx - 1) // PAGE] * PAGE + (ctx - 1) % PAGE).to(torch.int32)
+    row_req = torch.arange(M, dtype=torch.int32, device=dev)
+    inv = torch.tensor([1.0 / (1e6 ** (i / d)) for i in range(0, d, 2)], dtype=torch.float64).float().to(dev)
+    cos, sin = o.rope_table(inv, 2048)
+    down_splits, _ = o.layer_small_m_splits(M, H, I, nh, nkv, d)
+    if down_splits == 0:
+        print(json.dumps({"layer_phases": None, "why": "the layer kernel does not take %d rows" % M}))
+        return 0
+    x = rnd(M, H, dtype=torch.float32, scale=1.0)
+    blocks = torch.cuda.get_device_properties(0).multi_processor_count
+    stamps = torch.zeros(L, blocks, 32, dtype=torch.int64, device=dev)
+
+    def chain(with_stamps):
+        xin, delta = x, None
+        for at, w in enumerate(layers):
+            x_mid, x_out = torch.empty_like(x), torch.empty_like(x)
+            out = torch.empty(down_splits, M, H, dtype=torch.float32, device=dev)
+            nxt = layers[at + 1] if at + 1 < L else None
+            o.layer_small_m(xin, delta, x_mid, x_out, out, w["g1"], 1e-6, w["w_qkv"], w["b"], pos, slot, row_req,
+                            tables, cos, sin, w["k"], w["v"], True, w["w_o"], w["g2"], 1e-6, w["w_gu"], w["w_d"],
+                            nh, nkv, d, PAGE, None, 1 / math.sqrt(d), "silu", stamps[at] if with_stamps else None,
+                            (nxt["w_qkv"], nxt["g1"], nxt["b"]) if nxt else None)
+            xin, delta = x_out, out
+
+    for _ in range(3):
+        chain(False)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain(False)
+    for _ in range(3):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(20):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    per_layer_us = start.elapsed_time(stop) / 20 / L * 1e3
+    chain(True)
+    torch.cuda.synchronize()
+    o.raise_if_error()
+    st = stamps[4:].double().cpu()
+    base = st[:, :, 0].min(dim=1, keepdim=True).values
+    names = ["start", "predecessor done", "first norm", "q/k/v", "barrier 1", "attention", "barrier 2",
+             "output projection", "barrier 3", "second norm", "gate/up", "barrier 4", "down"]
+    phases = {n: round(float(((st[:, :, i] - base) / 1e3).max(dim=1).values.median()), 2)
+              for i, n in enumerate(names)}
+    print(json.dumps({"layer_phases_us_since_start_last_block": phases, "rows": M, "context": ctx,
+                      "us_per_layer_in_a_captured_chain": round(per_layer_us, 2), "layers": L,
+                      "model": "Qwen2.5-0.5B layer sizes"}))
     return 0
 
 

@@ -168,21 +168,25 @@ class PageAllocator:
         self._index[value] = _Published(page, parent_hash, parent_page, tuple(tokens))
         self._hash_of[page] = value
 
-    def publish_prompt(self, tokens: Sequence[int], pages: Sequence[int]) -> None:
+    def publish_prompt(self, tokens: Sequence[int], pages: Sequence[int], resume=None):
         """Publish every full page of a prompt, chained from its start; stops at
-        the first page that cannot be found again under its own hash."""
+        the first page that cannot be found again under its own hash.  Returns where it
+        got to, (pages done, their chain's hash, the last page) or None when the chain broke;
+        handed back as `resume` with more tokens of the same prompt, the walk goes on from
+        there instead of hashing the beginning again."""
         size = self.page_size
-        parent_hash, parent_page = 0, None
-        for at in range(min(len(tokens) // size, len(pages))):
+        first, parent_hash, parent_page = resume if resume is not None else (0, 0, None)
+        for at in range(first, min(len(tokens) // size, len(pages))):
             chunk = tuple(int(t) for t in tokens[at * size:(at + 1) * size])
             page = pages[at]
             if page < 0 or self._holders[page] == 0:
-                break
+                return None
             value = prefix_hash(parent_hash, chunk)
             self._publish(value, parent_hash, parent_page, chunk, page)
             if self._lookup(value, parent_hash, parent_page, chunk) != page:
-                break
-            parent_hash, parent_page = value, page
+                return None
+            parent_hash, parent_page, first = value, page, at + 1
+        return first, parent_hash, parent_page
 
     def take_shared_prefix(self, tokens: Sequence[int]) -> List[int]:
         """Pages that already hold the beginning of `tokens`, full pages only,

@@ -42,6 +42,7 @@ class RequestCache:
     length: int = 0
     state_slot: int = -1
     closed: bool = False
+    published: object = None     # where publishing the prompt's pages got to (None: not begun; False: broken)
 
     def pages_held(self, group: int) -> List[int]:
         return [p for p in self.tables[group] if p >= 0]
@@ -175,8 +176,17 @@ class CachePlan:
         return cache.length
 
     def publish_prompt(self, cache: RequestCache, tokens: Sequence[int]) -> None:
-        if self.share_prefixes:
-            self.allocators[0].publish_prompt(tokens, cache.tables[0])
+        """Offer the full pages that hold `tokens` (the beginning of the request's prompt, as far
+        as it is computed) to later requests.  Called again with more of the same prompt, only
+        the pages that are new are hashed."""
+        if not self.share_prefixes:
+            return
+        resume = cache.published
+        if resume is False:
+            return                       # the chain broke earlier: nothing behind it can be found
+        cache.published = self.allocators[0].publish_prompt(tokens, cache.tables[0], resume)
+        if cache.published is None:
+            cache.published = False
 
     def release_pages(self, cache: RequestCache) -> None:
         """Give back every page (the request stays open with nothing stored):
@@ -187,6 +197,7 @@ class CachePlan:
                     allocator.give_back(page)
             cache.tables[g] = []
         cache.length = 0
+        cache.published = None
 
     def close(self, cache: RequestCache) -> None:
         if cache.closed:

@@ -450,6 +450,14 @@ static FfnPlan ffn_plan(int M, int H, int I) {
   const long long room = (long long)smem_max - 2048 - (long long)fixed;
   int stages = (int)(room / FFN_STAGE_BYTES);
   if (stages > 8) stages = 8;
+  // TOKB200_FFN_STAGES caps the ring (fewer stages leave shared memory for the blocks of the
+  // kernels before this one, so that this kernel's blocks become resident, and its weights start
+  // to stream, while those still run)
+  static const int cap = [] {
+    const char* v = getenv("TOKB200_FFN_STAGES");
+    return v ? atoi(v) : 0;
+  }();
+  if (cap >= 3 && stages > cap) stages = cap;
   if (stages < 3) return plan;
   plan.blocks = sms;
   plan.s_down = s;
