@@ -122,6 +122,20 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int first_page = (lo + split * chunk) / page, last_page = min(p, lo + split * chunk + chunk - 1) / page;
     for (int e = first_page + (int)threadIdx.x * 32; e <= last_page; e += DEC_THREADS * 32)
       asm volatile("prefetch.global.L1 [%0];" ::"l"(block_table + (size_t)r * table_stride + e));
+    // ... and this piece's keys and values towards L2: all but the row's newest key were written
+    // by earlier steps, so they can be asked for while the projection before this kernel runs
+    {
+      const int* tb = block_table + (size_t)r * table_stride;
+      const int k_first = lo + split * chunk, k_last = min(p, k_first + chunk - 1);
+      for (int key = k_first + (int)threadIdx.x; key <= k_last; key += DEC_THREADS) {
+        const size_t at = ((size_t)(tb[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
+#pragma unroll
+        for (int c = 0; c < HEAD_DIM; c += 64) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(k_pool + at + c));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(v_pool + at + c));
+        }
+      }
+    }
   }
   pdl_wait();
   pdl_launch();

@@ -179,6 +179,9 @@ ffn_small_m_kernel(const FfnParams p) {
   }
 
   // ------------------------------ consumers ------------------------------
+  // the gain is a constant of the layer, first touched here in this step: asked towards L2
+  // before the wait, so that the norm does not pay a trip to DRAM after it
+  if ((int)threadIdx.x * 32 < p.H) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.gain + threadIdx.x * 32));
   pdl_wait();          // x and the pending sums come from the predecessor; the weights above do not
   pdl_launch();
   const int g = lane >> 2, t = lane & 3;

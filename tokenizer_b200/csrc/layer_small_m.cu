@@ -351,22 +351,20 @@ layer_small_m_kernel(const LayerParams p) {
 
   if (warp == LAY_WARPS) {
     // ------------------------------ producer ------------------------------
-    // First of all, ask for this block's share of the layer's weights to be brought into L2
-    // (cp.async.bulk.prefetch: no registers, no shared memory, returns at once): DRAM then
-    // streams at full rate from the kernel's first microsecond, and the ring below, which is
-    // only a few stages deep, has to hide the latency of L2, not that of DRAM.
+    // Once the ring is full for the first time (the first stages are on their way: what the
+    // first phases need must not queue behind anything), the rest of this block's share of the
+    // layer's weights is asked into L2 (cp.async.bulk.prefetch: no registers, no shared memory,
+    // returns at once): DRAM then streams at full rate from the kernel's first microseconds, and
+    // the ring, which is only a few stages deep, has to hide the latency of L2, not that of DRAM.
     auto ahead = [&](const __nv_bfloat16* rows_lo, const __nv_bfloat16* rows_hi, int K, int k0, int kn) {
       if (lane < 16) {
         const __nv_bfloat16* src = (lane < 8 ? rows_lo + (size_t)lane * K : rows_hi + (size_t)(lane - 8) * K) + k0;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((unsigned)kn * 2u) : "memory");
       }
     };
-    for (int i = 0; i < n_qkv; ++i) {
-      const int tile = qkv.tile(cta, G, i);
-      const int head = tile / (d / 16), j0 = (tile % (d / 16)) * 8;
-      const __nv_bfloat16* lo = p.w_qkv + (size_t)(head * d + j0) * p.H;
-      ahead(lo, lo + (size_t)half * p.H, p.H, 0, p.H);
-    }
+    bool asked = false;
+    auto ask_rest = [&]() {
+    asked = true;
     for (int i = 0; i < n_opr; ++i) {
       const __nv_bfloat16* rows = p.w_o + (size_t)opr.tile(cta, G, i) * 16 * q_width;
       ahead(rows, rows + (size_t)8 * q_width, q_width, 0, q_width);
@@ -401,11 +399,13 @@ layer_small_m_kernel(const LayerParams p) {
         ahead(lo, lo + (size_t)half * p.H, p.H, 0, p.H);
       }
     }
+    };
     int c = 0;                                   // stages filled so far
     bool ok = true;
     auto fill = [&](const __nv_bfloat16* rows_lo, const __nv_bfloat16* rows_hi, int K, int k0, int kn) {
       // rows_lo: 8 consecutive rows of K elements (stage rows 0..7), rows_hi: stage rows 8..15
       const int stage = c % p.n_stages, use = c / p.n_stages;
+      if (use > 0 && !asked) ask_rest();           // the ring is full: before the first wait
       if (use > 0) ok = ok && __all_sync(0xffffffffu, lay_mbar_wait(&empty[stage], (use - 1) & 1));
       if (ok) {
         const unsigned bytes = (unsigned)kn * 2u;
@@ -450,6 +450,7 @@ layer_small_m_kernel(const LayerParams p) {
         fill(rows, rows + (size_t)8 * p.I, p.I, kn ? k0 : k_begin, kn ? kn : 32);
       }
     }
+    if (!asked) ask_rest();
     }
     return;
   }
@@ -463,31 +464,66 @@ layer_small_m_kernel(const LayerParams p) {
   // One stage, consumed by this warp alone: 16 weight rows x kn elements of k against the rows of
   // the activation tile in shared memory, from its column k_local0 on.
   int c_rep = 0;                                 // stages of the repetitions before this one
+  // Four independent chains of mma (k steps 0, 1, 2, 3 mod 4) so that a warp working through a
+  // tile alone is not one long chain of dependent instructions; they are added at the tile's end.
+  float acc4[4][MT][4];
   auto multiply = [&](int c_in, int k_local0, int kn) {
     const int c = c_rep + c_in;
     const int stage = c % p.n_stages, use = c / p.n_stages;
     ok = ok && __all_sync(0xffffffffu, lay_mbar_wait(&full[stage], use & 1));
     if (ok) {
       const unsigned char* st = ring + (size_t)stage * LAY_STAGE_BYTES;
-#pragma unroll 2
-      for (int k = 0; k < kn; k += 32) {
-        const uint4 a = *reinterpret_cast<const uint4*>(st + g * LAY_ROW_PITCH + (k + 8 * t) * 2);
-        const uint4 b = *reinterpret_cast<const uint4*>(st + (g + 8) * LAY_ROW_PITCH + (k + 8 * t) * 2);
+      const unsigned char* a_row = st + g * LAY_ROW_PITCH + 8 * t * 2;
+      const unsigned char* b_row = st + (g + 8) * LAY_ROW_PITCH + 8 * t * 2;
+      const unsigned char* x_row = h_s + (size_t)g * p.h_pitch + (k_local0 + 8 * t) * 2;
+      int k = 0;
+      for (; k + 128 <= kn; k += 128) {
+        uint4 a[4], b[4], xv[4][MT];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a[u] = *reinterpret_cast<const uint4*>(a_row + (k + 32 * u) * 2);
+          b[u] = *reinterpret_cast<const uint4*>(b_row + (k + 32 * u) * 2);
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            xv[u][j] = *reinterpret_cast<const uint4*>(x_row + (size_t)8 * j * p.h_pitch + (k + 32 * u) * 2);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            lay_mma(acc4[u][j], a[u].x, b[u].x, a[u].y, b[u].y, xv[u][j].x, xv[u][j].y);
+            lay_mma(acc4[u][j], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][j].z, xv[u][j].w);
+          }
+        }
+      }
+      for (; k < kn; k += 32) {
+        const uint4 a = *reinterpret_cast<const uint4*>(a_row + k * 2);
+        const uint4 b = *reinterpret_cast<const uint4*>(b_row + k * 2);
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(
-              h_s + (size_t)(8 * j + g) * p.h_pitch + (k_local0 + k + 8 * t) * 2);
-          lay_mma(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
-          lay_mma(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+          const uint4 xv = *reinterpret_cast<const uint4*>(x_row + (size_t)8 * j * p.h_pitch + k * 2);
+          lay_mma(acc4[(k >> 5) & 3][j], a.x, b.x, a.y, b.y, xv.x, xv.y);
+          lay_mma(acc4[(k >> 5) & 3][j], a.z, b.z, a.w, b.w, xv.z, xv.w);
         }
       }
       __syncwarp();
       if (lane == 0) lay_mbar_arrive(&empty[stage]);
     }
   };
+  // acc = the sum of the four chains (after a tile's last stage)
+  auto gather = [&]() {
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[j][e] = (acc4[0][j][e] + acc4[1][j][e]) + (acc4[2][j][e] + acc4[3][j][e]);
+    }
+  };
   auto clear = [&]() {
 #pragma unroll
-    for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int u = 0; u < 4; ++u) {
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc4[u][j][0] = acc4[u][j][1] = acc4[u][j][2] = acc4[u][j][3] = 0.f;
+    }
   };
   // All blocks meet: every consumer's writes are ordered before its block's arrival (block
   // barrier, then one thread's fence and atomic), and the waiters' reads after it.  A wait that
@@ -497,7 +533,7 @@ layer_small_m_kernel(const LayerParams p) {
     lay_consumer_sync();
     if (tid == 0) {
       __threadfence();
-      atomicAdd(&p.sync[0], 1);
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.sync) : "memory");
       if (grid_ok) {
         bool met = false;
         const int target = barriers * G;
@@ -627,8 +663,11 @@ layer_small_m_kernel(const LayerParams p) {
       }
     }
     clear();
+    stamp_to(23);              // (warp 0's tile) before the product
     for (int s = 0; s < spt_h; ++s) multiply(i * spt_h + s, s * LAY_KC, min(LAY_KC, p.H - s * LAY_KC));
     if (!ok) break;
+    gather();
+    stamp_to(24);              // the product is done
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
 #pragma unroll
@@ -656,6 +695,7 @@ layer_small_m_kernel(const LayerParams p) {
       }
     }
   }
+  stamp_to(25);          // warp 0 is through its tiles
   stamp();             // 3: q/k/v done
   grid_barrier();
   stamp();             // 4: barrier 1 passed
@@ -920,6 +960,7 @@ layer_small_m_kernel(const LayerParams p) {
     clear();
     for (int s = 0; s < spt_o; ++s) multiply(c_opr + i * spt_o + s, s * LAY_KC, min(LAY_KC, q_width - s * LAY_KC));
     if (!ok) break;
+    gather();
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
 #pragma unroll
@@ -948,6 +989,7 @@ layer_small_m_kernel(const LayerParams p) {
     clear();
     for (int s = 0; s < spt_h; ++s) multiply(c_gup + i * spt_h + s, s * LAY_KC, min(LAY_KC, p.H - s * LAY_KC));
     if (!ok) break;
+    gather();
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
 #pragma unroll
@@ -995,6 +1037,7 @@ layer_small_m_kernel(const LayerParams p) {
       const int kn = k0 < k_end ? min(LAY_KC, k_end - k0) : 0;
       multiply(c_dwn + i * spt_d + s, kn ? s * LAY_KC : 0, kn);   // kn 0: the stage is only given back
     }
+    gather();
     {
       float* mine = part + (size_t)warp * 16 * (8 * MT + 1);
 #pragma unroll

@@ -387,6 +387,8 @@ qkv_rope_small_m_kernel(const NormInput norm, const __nv_bfloat16* __restrict__ 
       }
     }
   }
+  if (NORM && (int)threadIdx.x * 32 < K)       // the gain, first touched here in this step: towards L2 before the wait
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(norm.gain + threadIdx.x * 32));
   pdl_wait();
   pdl_launch();
   if (NORM) {
