@@ -690,11 +690,14 @@ def gated_linear(x, w, out, activation: str = "silu") -> None:
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), act, _stream()), "gated_linear")
 
 
-def qkv_rope_small_m_supported(M: int, K: int, d: int, rotary: int) -> bool:
-    """Up to 32 rows: beyond 16 the streaming product is no longer the fastest on its own, but
+def qkv_rope_small_m_supported(M: int, K: int, d: int, rotary: int, n_out: int = 0) -> bool:
+    """Where the fused kernel is the one to use (it takes up to 64 rows).  Up to 32 rows: beyond 16 the streaming product is no longer the fastest on its own, but
     with rotation and cache write in its epilogue it still beats a tile product and a second
-    kernel (batch 32: 1.30 -> see the decoding map)."""
-    return 0 < M <= 32 and K % 8 == 0 and d % 16 == 0 and rotary == d
+    kernel.  Up to 64 rows where the stacked weight is small (`n_out` x K up to two million
+    elements: the 0.5B sizes), so that the product's own time hardly matters beside a launch
+    saved (batch 64: 1.37 -> 1.28 ms a step)."""
+    most = 64 if 0 < n_out * K <= 2_000_000 else 32
+    return 0 < M <= most and K % 8 == 0 and d % 16 == 0 and rotary == d
 
 
 def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh, nkv, d) -> None:
@@ -703,8 +706,8 @@ def qkv_rope_small_m(x, w, bias, pos, slot, cos, sin, q_out, k_pool, v_pool, nh,
     M, K = x.shape
     if w.shape != ((nh + 2 * nkv) * d, K) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ValueError("qkv_rope_small_m: w is the stacked [(heads + 2 kv heads) d, K] weight")
-    if not qkv_rope_small_m_supported(M, K, d, 2 * cos.shape[1]):
-        raise ValueError("qkv_rope_small_m: sizes it does not take")
+    if not (0 < M <= 64 and K % 8 == 0 and d % 16 == 0 and 2 * cos.shape[1] == d):
+        raise ValueError("qkv_rope_small_m: up to 64 rows, K a multiple of 8, the whole head (a multiple of 16) rotated")
     _check(_lib("linear_small_m").tokb200_qkv_rope_small_m(
         _ptr(x), _ptr(w), _ptr(bias), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin), _ptr(q_out),
         _ptr(k_pool), _ptr(v_pool), _i(M), _i(nh), _i(nkv), _i(d), _i(K), _stream()),

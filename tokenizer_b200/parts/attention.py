@@ -261,7 +261,7 @@ class GQAttention:
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.d)
         group = ctx.groups[cache.group]
         if h.dtype == torch.bfloat16 and ops.qkv_rope_small_m_supported(
-                h.shape[0], self.hidden, self.d, self.position.rotary_dim):
+                h.shape[0], self.hidden, self.d, self.position.rotary_dim, self.qkv.out_features):
             # few rows: projection, bias, rotation and cache write in one kernel
             ops.qkv_rope_small_m(
                 h, self.qkv.weight, self.qkv_bias, ctx.pos, group.slots if cache.writes else None,
