@@ -263,6 +263,21 @@ def main():
             prefill_ms.append(start.elapsed_time(stop))
         engine.cache.close(cache)
     prefill_best = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
+    # a portion of 512 tokens (the budget of the 1.5B configuration's scheduler), as a step of its own
+    portion_ms = []
+    for rep in range(0 if (args.only_decode or args.only_prefill) else 3 + 5):
+        cache = engine.cache.open(("portion", rep))
+        engine.cache.reserve(cache, 512)
+        entry = StepEntry(cache, random_prompt(512), [511])
+        torch.cuda.synchronize()
+        start, stop = events()
+        start.record()
+        engine.step([entry])
+        stop.record()
+        torch.cuda.synchronize()
+        if rep >= 3:
+            portion_ms.append(start.elapsed_time(stop))
+        engine.cache.close(cache)
     if args.only_prefill:
         print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": args.layers,
                           "ms": prefill_best, "tok_s": PREFILL_TOKENS / (prefill_best / 1e3)}))
@@ -311,6 +326,8 @@ def main():
                           "tok_s": main_run["tok_s"], "gpu_launches": main_run["launches"]}))
         return 0
     points = {}
+    if portion_ms:
+        points["prefill_512"] = 512 / (sorted(portion_ms)[len(portion_ms) // 2] / 1e3)
     if not args.no_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = decode_run(b, min(args.steps, 64), 4, False)["tok_s"]

@@ -413,3 +413,24 @@ def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_fac
             if e.cache is not old:
                 engine.cache.close(e.cache)
     assert any(k[0] == "portions" and "graph" in v for k, v in engine._graphs.items())
+
+
+def test_logits_of_a_replayed_step_live_until_the_next_step(tmp_path_factory):
+    """`Engine.step` says that its logits are valid until the engine's next step: a step replayed
+    from a captured graph returns a view of the graph's output buffer.  Held across the next replay
+    of the same shape they show that step's values; a clone keeps its own."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200.engine import StepEntry
+    path, config, page = make_folder(tmp_path_factory, "a", scale=SHARPEN)
+    engine = tb.engine_for(tb.load_model(path, dtype="bfloat16"), 128, page, max_requests=1)
+    cache = engine.cache.open("x")
+    ids = random_ids(8, config.vocab_size, 4)
+    kept = []
+    for t in ids:                                 # the shape's first step runs plainly, the second is captured
+        engine.cache.reserve(cache, 1)
+        logits = engine.step([StepEntry(cache, [t], [0])])
+        kept.append((logits, logits.clone()))
+    views = [view for view, _ in kept[3:]]        # replays: the same buffer every time
+    assert all(v.data_ptr() == views[0].data_ptr() for v in views)
+    assert torch.equal(views[0], kept[-1][1])     # an old view shows the last step's logits ...
+    assert not torch.equal(kept[3][1], kept[-1][1])            # ... which its clone does not

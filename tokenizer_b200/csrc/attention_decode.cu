@@ -41,6 +41,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head siz
 constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma
 constexpr bool kTail16 = HEAD_DIM % 32 != 0;         // one more step of 16 lanes: an 8-byte load
 constexpr int kVStride = HEAD_DIM + 8;               // elements between staged value rows
+constexpr int kVBuffers = HEAD_DIM <= 128 ? 2 : 1;   // staging buffers of values a warp (two fit up to 128)
 
 __device__ __forceinline__ int split_chunk(int n_keys, int min_chunk) {
   int chunk = min_chunk;
@@ -93,7 +94,7 @@ __device__ __forceinline__ float dec_peer_load(const float* local, unsigned rank
 // the first block through distributed shared memory instead of scratch memory, a fence and a
 // counter.
 template <bool CLUSTER>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, HEAD_DIM <= 64 ? 2 : 1)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ block_table, int table_stride,
@@ -122,11 +123,13 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int first_page = (lo + split * chunk) / page, last_page = min(p, lo + split * chunk + chunk - 1) / page;
     for (int e = first_page + (int)threadIdx.x * 32; e <= last_page; e += DEC_THREADS * 32)
       asm volatile("prefetch.global.L1 [%0];" ::"l"(block_table + (size_t)r * table_stride + e));
-    // ... and this piece's keys and values towards L2: all but the row's newest key were written
-    // by earlier steps, so they can be asked for while the projection before this kernel runs
+    // ... and the keys and values of the block's first pass towards L2: all but the row's newest
+    // key were written by earlier steps, so they can be asked for while the projection before
+    // this kernel runs.  Only the first pass: asking for a long piece at once made the kernel
+    // slower (268 MB at 64 rows of 8,192 keys: 76 us against 68 without).
     {
       const int* tb = block_table + (size_t)r * table_stride;
-      const int k_first = lo + split * chunk, k_last = min(p, k_first + chunk - 1);
+      const int k_first = lo + split * chunk, k_last = min(p, k_first + min(chunk, DEC_BLOCK_KEYS) - 1);
       for (int key = k_first + (int)threadIdx.x; key <= k_last; key += DEC_THREADS) {
         const size_t at = ((size_t)(tb[key / page] * page + key % page) * nkv + kvh) * HEAD_DIM;
 #pragma unroll
@@ -175,59 +178,103 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
   }
 
-  __nv_bfloat16* v_s = reinterpret_cast<__nv_bfloat16*>(dec_smem) + (size_t)warp * DEC_TILE * kVStride;
+  // two staging buffers of values a warp: the next tile's values are on their way while this
+  // tile is computed
+  __nv_bfloat16* v_buf = reinterpret_cast<__nv_bfloat16*>(dec_smem) + (size_t)warp * kVBuffers * DEC_TILE * kVStride;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[HEAD_DIM / 8][4];
 #pragma unroll
   for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const float scale_log2 = scale * 1.4426950408889634f;
 
-  for (int k0 = first + warp * DEC_TILE; k0 <= last; k0 += DEC_BLOCK_KEYS) {
-    // ---- request the values of this tile (a lane per key) and the keys (mma layout) ----
-    {
-      // the values go straight to their staging rows (asynchronous 16-byte copies, zeros for
-      // idle keys): no registers hold them while the scores are computed
-      const int key = k0 + lane;
-      const bool ok = key <= last;
-      const int key_ok = ok ? key : k0;
-      const int slot = table[key_ok / page] * page + key_ok % page;
-      const __nv_bfloat16* vrow = v_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM;
-      const unsigned dst = (unsigned)__cvta_generic_to_shared(v_s + lane * kVStride);
-      const int bytes = ok ? 16 : 0;
+  // A tile's values go straight to a staging buffer (asynchronous 16-byte copies, zeros for idle
+  // keys); its keys come as mma fragments in registers.  Both are asked for one tile AHEAD: the
+  // next tile's values when this tile starts, the next tile's keys as soon as this tile's scores
+  // are computed (the registers are free then), so that their trip to memory runs beside the
+  // softmax and the weighted sum of this tile.  Lane l looks up the place of a tile's key l in
+  // the block table, once for the keys and the values; the loads get a row's place from the
+  // lane that looked it up.
+  const int page_shift = (page & (page - 1)) == 0 ? __ffs(page) - 1 : -1;
+  auto tile_slots = [&](int k0) {
+    const int key = k0 + lane;
+    if (key > last) return -1;
+    const int pg = page_shift >= 0 ? key >> page_shift : key / page;
+    return table[pg] * page + (key - pg * page);
+  };
+  auto stage_values = [&](int my_slot, __nv_bfloat16* dst_rows) {
+    // the copies run over the tile's 16-byte pieces in order: neighbouring lanes take
+    // neighbouring pieces of one row, so that every 32-byte sector is asked for once
+    constexpr int kPieces = HEAD_DIM / 8;   // 16-byte pieces a row
 #pragma unroll
-      for (int c = 0; c < HEAD_DIM / 8; ++c)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + c * 16), "l"(vrow + c * 8), "r"(bytes));
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    for (int c = 0; c < kPieces; ++c) {
+      const int i = c * 32 + lane;
+      const int row = i / kPieces, piece = i % kPieces;
+      const int slot = __shfl_sync(0xffffffffu, my_slot, row);
+      const __nv_bfloat16* src = v_pool + ((size_t)max(slot, 0) * nkv + kvh) * HEAD_DIM + piece * 8;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_rows + row * kVStride + piece * 8);
+      const int bytes = slot < 0 ? 0 : 16;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
     }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  uint4 kf[DEC_TILE / 8][kSteps32 > 0 ? kSteps32 : 1];
+  uint2 kt[DEC_TILE / 8];
+  auto load_keys = [&](int my_slot) {
+#pragma unroll
+    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+      const int slot = __shfl_sync(0xffffffffu, my_slot, nt * 8 + g);
+      const bool ok = slot >= 0;
+      const __nv_bfloat16* krow = k_pool + ((size_t)max(slot, 0) * nkv + kvh) * HEAD_DIM;
+#pragma unroll
+      for (int st = 0; st < kSteps32; ++st) kf[nt][st] = dec_load16(krow + st * 32 + 8 * t, ok);
+      if (kTail16) kt[nt] = dec_load8(krow + kSteps32 * 32 + 4 * t, ok);
+    }
+  };
+  int turn = 0, slots_now = -1;
+  if (first + warp * DEC_TILE <= last) {
+    slots_now = tile_slots(first + warp * DEC_TILE);
+    if (kVBuffers == 2) stage_values(slots_now, v_buf);
+    load_keys(slots_now);
+  }
+  for (int k0 = first + warp * DEC_TILE; k0 <= last; k0 += DEC_BLOCK_KEYS, turn ^= 1) {
+    __nv_bfloat16* v_s = v_buf + (size_t)(kVBuffers == 2 ? turn : 0) * DEC_TILE * kVStride;
+    const bool more = k0 + DEC_BLOCK_KEYS <= last;
+    const int slots_next = more ? tile_slots(k0 + DEC_BLOCK_KEYS) : -1;
+    if (kVBuffers == 1) stage_values(slots_now, v_s);   // the last tile's sum is done (the __syncwarp below)
+    else if (more) stage_values(slots_next, v_buf + (size_t)(turn ^ 1) * DEC_TILE * kVStride);
+    slots_now = slots_next;
     float s[DEC_TILE / 8][4];
 #pragma unroll
     for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const int key = k0 + nt * 8 + g;
-      const bool ok = key <= last;
-      const int key_ok = ok ? key : k0;
-      const int slot = table[key_ok / page] * page + key_ok % page;
-      const __nv_bfloat16* krow = k_pool + ((size_t)slot * nkv + kvh) * HEAD_DIM;
 #pragma unroll
       for (int st = 0; st < kSteps32; ++st) {
-        const uint4 kv = dec_load16(krow + st * 32 + 8 * t, ok);
-        dec_mma(s[nt], qa[st][0], kv.x, kv.y);
-        dec_mma(s[nt], qa[st][1], kv.z, kv.w);
+        dec_mma(s[nt], qa[st][0], kf[nt][st].x, kf[nt][st].y);
+        dec_mma(s[nt], qa[st][1], kf[nt][st].z, kf[nt][st].w);
       }
-      if (kTail16) {
-        const uint2 kv = dec_load8(krow + kSteps32 * 32 + 4 * t, ok);
-        dec_mma(s[nt], qt, kv.x, kv.y);
-      }
+      if (kTail16) dec_mma(s[nt], qt, kt[nt].x, kt[nt].y);
     }
+    if (more) load_keys(slots_next);
     // ---- scale, mask, running softmax: rows g (heads 0..7) and g + 8 (heads 8..15) ----
     float m_new[2] = {m_run[0], m_run[1]};
+    if (k0 + DEC_TILE - 1 <= last) {          // a whole tile (every tile of a piece but its last): no key to mask
 #pragma unroll
-    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = k0 + nt * 8 + 2 * t + (e & 1);
-        s[nt][e] = key <= last ? s[nt][e] * scale_log2 : -INFINITY;
-        m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] *= scale_log2;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = k0 + nt * 8 + 2 * t + (e & 1);
+          s[nt][e] = key <= last ? s[nt][e] * scale_log2 : -INFINITY;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+        }
       }
     }
     float corr[2], sum[2] = {0.f, 0.f};
@@ -235,7 +282,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int i = 0; i < 2; ++i) {
       m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
       m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));   // finite: key k0 is live
-      corr[i] = exp2f(m_run[i] - m_new[i]);                                      // 0 on the first pass
+      corr[i] = exp2f(m_run[i] - m_new[i]);                                   // 0 on the first pass
       m_run[i] = m_new[i];
     }
 #pragma unroll
@@ -258,7 +305,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       o[i][0] *= corr[0]; o[i][1] *= corr[0];
       o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // the tile's values have landed
+    if (kVBuffers == 2 && more) asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this tile's values have landed (the next tile's may not)
+    else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncwarp();
     // ---- o += p v ----
 #pragma unroll
@@ -415,7 +463,7 @@ TOKB200_API int tokb200_decode_attention(
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15)
     return TOKB200_BAD_ALIGNMENT;
   const int group = nh / nkv;
-  const size_t stage = (size_t)DEC_WARPS * DEC_TILE * kVStride * sizeof(__nv_bfloat16);
+  const size_t stage = (size_t)kVBuffers * DEC_WARPS * DEC_TILE * kVStride * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(DEC_WARPS + 1) * group * (HEAD_DIM + 2) * sizeof(float);
   const size_t smem = stage > merge ? stage : merge;
   // no row sees more keys than its table reaches (or its window holds), so no row has
