@@ -5,8 +5,8 @@
 // batch plays its N side (8 rows of x per instruction), and every thread feeds
 // its fragments straight from 16-byte global loads, with no staging of W in
 // shared memory.  That works because a dot product does not care about the
-// order of k: within a step of 32 k, thread t of a quad loads k = 8t .. 8t+7 of
-// its weight row, and the same 8 of its x row, and both are handed to the two
+// order of k: within a step of 64 k, thread t of a quad loads k = 16t .. 16t+15 of
+// its weight row, and the same 16 of its x row, and both are handed to the four
 // instructions of the step under the same (permuted) k slots.
 //
 // Work is cut three ways: row tiles of 16 over the grid's x, the warps of a block
@@ -18,7 +18,8 @@
 
 #define LSM_WARPS 8
 #define LSM_THREADS (LSM_WARPS * 32)
-#define LSM_PRE 4            // steps of weights in flight per thread
+#define LSM_PRE 4            // steps of 32 k of weights in flight per thread (the q/k/v kernel)
+#define LSM_WIDE_PRE 2       // steps of 64 k of weights in flight per thread (the plain and the gated product)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
                                                unsigned a3, unsigned b0, unsigned b1) {
@@ -67,21 +68,27 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
     row_b = row_a + 128;
   }
   const bool row_a_ok = row_a < N, row_b_ok = row_b < N;
-  const __nv_bfloat16* wa = w + (size_t)row_a * K + 8 * t;
-  const __nv_bfloat16* wb = w + (size_t)row_b * K + 8 * t;
+  const __nv_bfloat16* wa = w + (size_t)row_a * K + 16 * t;
+  const __nv_bfloat16* wb = w + (size_t)row_b * K + 16 * t;
 
-  // A ring of LSM_PRE steps of weights is requested before the wait on the
-  // predecessor (weights are written by no kernel of the step); x, which the
-  // predecessor produced, is read after it.
-  constexpr int step = TEAM * 32;
-  const int k_first = k_begin + member * 32;
-  uint4 a_ring[LSM_PRE], b_ring[LSM_PRE];
+  // A step is 64 k: thread t of a quad takes k = 16t .. 16t+15 of its two weight rows as two
+  // 16-byte loads next to each other, so that a quad asks for a whole 128-byte line of a row
+  // (half a line per request, with the other half asked for by another warp, streams at little
+  // more than half the rate: 3.7 against 6.9 TB/s with the same bytes in flight).  A ring of
+  // LSM_WIDE_PRE steps of weights is requested before the wait on the predecessor (weights are
+  // written by no kernel of the step); x, which the predecessor produced, is read after it.
+  constexpr int step = TEAM * 64;
+  const int k_first = k_begin + member * 64;
+  uint4 a_ring[LSM_WIDE_PRE][2], b_ring[LSM_WIDE_PRE][2];
 #pragma unroll
-  for (int i = 0; i < LSM_PRE; ++i) {
-    const int kk = k_first + i * step;
-    const bool k_ok = kk + 8 * t + 8 <= k_end;
-    a_ring[i] = load16(wa + kk, row_a_ok && k_ok);
-    b_ring[i] = load16(wb + kk, row_b_ok && k_ok);
+  for (int i = 0; i < LSM_WIDE_PRE; ++i) {
+    const int kk = k_first + i * step + 16 * t;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const bool k_ok = kk + 8 * h + 8 <= k_end;
+      a_ring[i][h] = load16(wa + k_first + i * step + 8 * h, row_a_ok && k_ok);
+      b_ring[i][h] = load16(wb + k_first + i * step + 8 * h, row_b_ok && k_ok);
+    }
   }
   // The successor may start now, before this kernel has even waited for its own predecessor:
   // the kernels that follow a plain product (a norm, the fused feed-forward, the sampler) touch
@@ -89,23 +96,32 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   // feed-forward thus streams its weights while the attention before this product still runs.
   pdl_launch();
   pdl_wait();
-  for (int k = k_first; k < k_end; k += LSM_PRE * step) {
+  for (int k = k_first; k < k_end; k += LSM_WIDE_PRE * step) {
 #pragma unroll
-    for (int i = 0; i < LSM_PRE; ++i) {
+    for (int i = 0; i < LSM_WIDE_PRE; ++i) {
       const int kk = k + i * step;
-      const uint4 a = a_ring[i], b = b_ring[i];
-      const int kn = kk + LSM_PRE * step;
-      const bool next_ok = kn + 8 * t + 8 <= k_end;
-      a_ring[i] = load16(wa + kn, row_a_ok && next_ok);
-      b_ring[i] = load16(wb + kn, row_b_ok && next_ok);
-      const bool k_ok = kk + 8 * t + 8 <= k_end;
+      uint4 a[2], b[2];
+      const int kn = kk + LSM_WIDE_PRE * step;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[h] = a_ring[i][h];
+        b[h] = b_ring[i][h];
+        const bool next_ok = kn + 16 * t + 8 * h + 8 <= k_end;
+        a_ring[i][h] = load16(wa + kn + 8 * h, row_a_ok && next_ok);
+        b_ring[i][h] = load16(wb + kn + 8 * h, row_b_ok && next_ok);
+      }
       if (kk < k_end) {
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           const int m = 8 * j + g;
-          const uint4 xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
-          mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
-          mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const bool k_ok = kk + 16 * t + 8 * h + 8 <= k_end;
+            // (x a round ahead like the weights costs 16 registers and a resident block: slower)
+            const uint4 xv = load16(x + (size_t)m * K + kk + 16 * t + 8 * h, m < M && k_ok);
+            mma_bf16_16816(acc[j], a[h].x, b[h].x, a[h].y, b[h].y, xv.x, xv.y);
+            mma_bf16_16816(acc[j], a[h].z, b[h].z, a[h].w, b[h].w, xv.z, xv.w);
+          }
         }
       }
     }
@@ -346,18 +362,22 @@ qkv_rope_small_m_kernel(const NormInput norm, const __nv_bfloat16* __restrict__ 
   float acc[MT][4];
 #pragma unroll
   for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  const __nv_bfloat16* wa = w + (size_t)row_a * K + 8 * t;
-  const __nv_bfloat16* wb = w + (size_t)row_b * K + 8 * t;
+  const __nv_bfloat16* wa = w + (size_t)row_a * K + 16 * t;
+  const __nv_bfloat16* wb = w + (size_t)row_b * K + 16 * t;
 
-  constexpr int step = LSM_WARPS * 32;
-  const int k_first = warp * 32;
-  uint4 a_ring[LSM_PRE], b_ring[LSM_PRE];
+  // steps of 64 k, a whole 128-byte line of a row per quad (see linear_small_m_kernel)
+  constexpr int step = LSM_WARPS * 64;
+  const int k_first = warp * 64;
+  uint4 a_ring[LSM_WIDE_PRE][2], b_ring[LSM_WIDE_PRE][2];
 #pragma unroll
-  for (int i = 0; i < LSM_PRE; ++i) {
+  for (int i = 0; i < LSM_WIDE_PRE; ++i) {
     const int kk = k_first + i * step;
-    const bool k_ok = kk + 8 * t + 8 <= K;
-    a_ring[i] = load16(wa + kk, k_ok);
-    b_ring[i] = load16(wb + kk, k_ok);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const bool k_ok = kk + 16 * t + 8 * h + 8 <= K;
+      a_ring[i][h] = load16(wa + kk + 8 * h, k_ok);
+      b_ring[i][h] = load16(wb + kk + 8 * h, k_ok);
+    }
   }
   // What the epilogue needs from memory is asked for now, so that it has arrived by then
   // (thread i of the epilogue serves row m = i / 8 and lane pair j0 + i % 8), and before the
@@ -400,42 +420,53 @@ qkv_rope_small_m_kernel(const NormInput norm, const __nv_bfloat16* __restrict__ 
     __syncthreads();
   }
   constexpr bool kXRing = MT <= 2 && !NORM;
-  uint4 x_ring[kXRing ? LSM_PRE : 1][MT];
+  uint4 x_ring[kXRing ? LSM_WIDE_PRE : 1][MT][2];
   if (kXRing) {
 #pragma unroll
-    for (int i = 0; i < LSM_PRE; ++i) {
+    for (int i = 0; i < LSM_WIDE_PRE; ++i) {
       const int kk = k_first + i * step;
-      const bool k_ok = kk + 8 * t + 8 <= K;
 #pragma unroll
       for (int j = 0; j < MT; ++j)
-        x_ring[i][j] = load16(x + (size_t)(8 * j + g) * K + kk + 8 * t, 8 * j + g < M && k_ok);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          x_ring[i][j][h] = load16(x + (size_t)(8 * j + g) * K + kk + 16 * t + 8 * h,
+                                   8 * j + g < M && kk + 16 * t + 8 * h + 8 <= K);
     }
   }
-  for (int k = k_first; k < K; k += LSM_PRE * step) {
+  for (int k = k_first; k < K; k += LSM_WIDE_PRE * step) {
 #pragma unroll
-    for (int i = 0; i < LSM_PRE; ++i) {
+    for (int i = 0; i < LSM_WIDE_PRE; ++i) {
       const int kk = k + i * step;
-      const uint4 a = a_ring[i], b = b_ring[i];
-      const int kn = kk + LSM_PRE * step;
-      const bool next_ok = kn + 8 * t + 8 <= K;
-      a_ring[i] = load16(wa + kn, next_ok);
-      b_ring[i] = load16(wb + kn, next_ok);
-      const bool k_ok = kk + 8 * t + 8 <= K;
+      const int kn = kk + LSM_WIDE_PRE * step;
+      uint4 a[2], b[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[h] = a_ring[i][h];
+        b[h] = b_ring[i][h];
+        const bool next_ok = kn + 16 * t + 8 * h + 8 <= K;
+        a_ring[i][h] = load16(wa + kn + 8 * h, next_ok);
+        b_ring[i][h] = load16(wb + kn + 8 * h, next_ok);
+      }
       if (kk < K) {
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
           const int m = 8 * j + g;
-          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-          if (NORM) {
-            if (k_ok) xv = *reinterpret_cast<const uint4*>(qkv_h + (size_t)m * norm.h_pitch + (kk + 8 * t) * 2);
-          } else if (kXRing) {
-            xv = x_ring[i][j];
-            x_ring[i][j] = load16(x + (size_t)m * K + kn + 8 * t, m < M && next_ok);
-          } else {
-            xv = load16(x + (size_t)m * K + kk + 8 * t, m < M && k_ok);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const bool k_ok = kk + 16 * t + 8 * h + 8 <= K;
+            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+            if (NORM) {
+              if (k_ok) xv = *reinterpret_cast<const uint4*>(qkv_h + (size_t)m * norm.h_pitch + (kk + 16 * t + 8 * h) * 2);
+            } else if (kXRing) {
+              xv = x_ring[i][j][h];
+              x_ring[i][j][h] = load16(x + (size_t)m * K + kn + 16 * t + 8 * h,
+                                       m < M && kn + 16 * t + 8 * h + 8 <= K);
+            } else {
+              xv = load16(x + (size_t)m * K + kk + 16 * t + 8 * h, m < M && k_ok);
+            }
+            mma_bf16_16816(acc[j], a[h].x, b[h].x, a[h].y, b[h].y, xv.x, xv.y);
+            mma_bf16_16816(acc[j], a[h].z, b[h].z, a[h].w, b[h].w, xv.z, xv.w);
           }
-          mma_bf16_16816(acc[j], a.x, b.x, a.y, b.y, xv.x, xv.y);
-          mma_bf16_16816(acc[j], a.z, b.z, a.w, b.w, xv.z, xv.w);
         }
       }
     }

@@ -105,22 +105,29 @@ linear_stream_kernel(const LsParams p) {
     // Every consumer warp has stages of its own (p.per_warp of them), which only it waits on,
     // one use after the other: a barrier's parity tells two consecutive uses apart, no more,
     // so a stage must not be waited on by a warp that has not seen its uses before.
+    // The order of the copies: a round of tiles (one per consumer warp), and within the round
+    // slab by slab across the warps, so that every warp's stages are filled as it frees them
+    // and all warps multiply at the same time (tile after tile, a tile of several slabs would
+    // keep all warps but its owner waiting).
     bool ok = true;
-    for (int tile = tile_first; tile < tile_last && ok; ++tile) {
-      const int j = tile - tile_first, owner = j % p.warps;
-      const int rows = min(16, p.N - tile * 16);
+    const int n_mine = tile_last - tile_first;
+    for (int j0 = 0; j0 < n_mine && ok; j0 += p.warps) {
       for (int sl = 0; sl < slabs && ok; ++sl) {
-        const int c = (j / p.warps) * slabs + sl;                     // the owner's stages filled so far
-        const int stage = owner * p.per_warp + c % p.per_warp, use = c / p.per_warp;
-        if (use > 0) ok = __all_sync(0xffffffffu, ls_mbar_wait(&empty[stage], (use - 1) & 1));
-        if (!ok) break;
+        const int c = (j0 / p.warps) * slabs + sl;                    // an owner's stages filled so far
         const int k0 = sl * p.kc, kn = min(p.kc, p.K - k0);
         const unsigned bytes = (unsigned)kn * 2u;
-        if (lane == 0) ls_mbar_expect(&full[stage], (unsigned)rows * bytes);
-        __syncwarp();
-        if (lane < rows)
-          ls_bulk_copy(ring + (size_t)stage * p.stage_bytes + lane * p.row_pitch,
-                       p.w + (size_t)(tile * 16 + lane) * p.K + k0, bytes, &full[stage]);
+        for (int owner = 0; owner < p.warps && j0 + owner < n_mine; ++owner) {
+          const int tile = tile_first + j0 + owner;
+          const int rows = min(16, p.N - tile * 16);
+          const int stage = owner * p.per_warp + c % p.per_warp, use = c / p.per_warp;
+          if (use > 0) ok = __all_sync(0xffffffffu, ls_mbar_wait(&empty[stage], (use - 1) & 1));
+          if (!ok) break;
+          if (lane == 0) ls_mbar_expect(&full[stage], (unsigned)rows * bytes);
+          __syncwarp();
+          if (lane < rows)
+            ls_bulk_copy(ring + (size_t)stage * p.stage_bytes + lane * p.row_pitch,
+                         p.w + (size_t)(tile * 16 + lane) * p.K + k0, bytes, &full[stage]);
+        }
       }
     }
     return;
