@@ -40,6 +40,13 @@
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size");
 constexpr int kSteps32 = HEAD_DIM / 32;              // steps of 32 lanes: one 16-byte load, two mma
 constexpr bool kTail16 = HEAD_DIM % 32 != 0;         // one more step of 16 lanes: an 8-byte load
+// Where lane t of a quad reads its 8 elements of step `st` in a row of q or of keys.  Steps go in
+// pairs over 64 elements, in which a lane's two pieces lie next to each other (32 bytes), so
+// that a quad's two loads ask for one whole 128-byte line of the row; a last step without a
+// partner takes 8t.  q and the keys use the same places, which is all a dot product needs.
+__device__ __forceinline__ int dec_k_offset(int st, int t) {
+  return (st | 1) < kSteps32 ? (st >> 1) * 64 + 16 * t + 8 * (st & 1) : st * 32 + 8 * t;
+}
 constexpr int kVStride = HEAD_DIM + 8;               // elements between staged value rows
 constexpr int kVBuffers = HEAD_DIM <= 128 ? 2 : 1;   // staging buffers of values a warp (two fit up to 128)
 
@@ -166,8 +173,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const __nv_bfloat16* qb_row = qa_row + (size_t)8 * HEAD_DIM;
 #pragma unroll
     for (int st = 0; st < kSteps32; ++st) {
-      const uint4 a = dec_load16(qa_row + st * 32 + 8 * t, ok_a);
-      const uint4 b = dec_load16(qb_row + st * 32 + 8 * t, ok_b);
+      const uint4 a = dec_load16(qa_row + dec_k_offset(st, t), ok_a);
+      const uint4 b = dec_load16(qb_row + dec_k_offset(st, t), ok_b);
       qa[st][0][0] = a.x; qa[st][0][1] = b.x; qa[st][0][2] = a.y; qa[st][0][3] = b.y;
       qa[st][1][0] = a.z; qa[st][1][1] = b.z; qa[st][1][2] = a.w; qa[st][1][3] = b.w;
     }
@@ -226,7 +233,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       const bool ok = slot >= 0;
       const __nv_bfloat16* krow = k_pool + ((size_t)max(slot, 0) * nkv + kvh) * HEAD_DIM;
 #pragma unroll
-      for (int st = 0; st < kSteps32; ++st) kf[nt][st] = dec_load16(krow + st * 32 + 8 * t, ok);
+      for (int st = 0; st < kSteps32; ++st) kf[nt][st] = dec_load16(krow + dec_k_offset(st, t), ok);
       if (kTail16) kt[nt] = dec_load8(krow + kSteps32 * 32 + 4 * t, ok);
     }
   };
@@ -470,27 +477,39 @@ TOKB200_API int tokb200_decode_attention(
   // more pieces than this; blocks beyond would only find that out and leave
   long long reach = (long long)table_stride * page;
   if (window >= 0 && window + 1 < reach) reach = window + 1;
-  // The shortest piece for this launch: the candidate with the least estimated time, from a
-  // block's fixed cost (3), 2 per pass of 256 keys, 3 for a merge across blocks, and as many
-  // waves as the blocks need at two a multiprocessor (figures in microseconds, fitted to
-  // measurements at 8 and 64 rows, contexts of 600 to 16,000).
-  static int slots = 0;
-  if (!slots) {
-    int device = 0, sms = 148;
-    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    slots = 2 * sms;
-  }
+  // The shortest piece for this launch: the candidate (a whole number of passes of 256 keys)
+  // with the least estimated time, from a block's fixed cost (3), 2 per pass of 256 keys at head
+  // size 64 (in proportion for others), 3 for a merge across blocks, and as many waves as the
+  // blocks need at the number of blocks a multiprocessor holds (figures in microseconds, fitted
+  // to measurements at 8 and 64 rows, contexts of 600 to 16,000).  Pieces need not be powers of
+  // two: 64 rows of 8,192 keys with 4 kv heads of size 128 take 213 us in pieces of 2,816 keys
+  // (768 blocks, 5.2 waves of 148) against 266 us in pieces of 2,048 (1,024 blocks, 6.9 waves).
+  static int slots = 0;      // blocks the device holds at once
   const long long pairs = (long long)n_rows * nkv;
   int min_chunk = DEC_MIN_CHUNK;
-  double best = 1e30;
-  for (int c = DEC_MIN_CHUNK; c <= 2048; c <<= 1) {
-    int chunk = c;
-    while ((reach + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
-    const long long pieces = (reach + chunk - 1) / chunk;
-    const long long passes = ((reach < chunk ? reach : chunk) + DEC_BLOCK_KEYS - 1) / DEC_BLOCK_KEYS;
-    const long long waves = (pairs * pieces + slots - 1) / slots;
-    const double t = (double)waves * (3.0 + 2.0 * (double)passes + (pieces > 1 ? 3.0 : 0.0));
-    if (t < best - 1e-9) { best = t; min_chunk = c; }
+  {
+    int& have = slots;
+    if (!have) {
+      int device = 0, sms = 148, per_sm = 0;
+      if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(decode_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<false>, DEC_THREADS, smem) !=
+              cudaSuccess || per_sm < 1)
+        per_sm = 1;
+      have = per_sm * sms;
+    }
+    const double per_pass = 2.0 * HEAD_DIM / 64.0;
+    double best = 1e30;
+    for (int c = DEC_MIN_CHUNK; c <= 4096; c += DEC_BLOCK_KEYS) {
+      int chunk = c;
+      while ((reach + chunk - 1) / chunk > DEC_MAX_SPLITS) chunk <<= 1;
+      const long long pieces = (reach + chunk - 1) / chunk;
+      const long long passes = ((reach < chunk ? reach : chunk) + DEC_BLOCK_KEYS - 1) / DEC_BLOCK_KEYS;
+      const long long waves = (pairs * pieces + have - 1) / have;
+      const double t = (double)waves * (3.0 + per_pass * (double)passes + (pieces > 1 ? 3.0 : 0.0));
+      if (t < best - 1e-9) { best = t; min_chunk = c; }
+    }
   }
   // no row has more pieces than this (a row a little shorter than the reach may be cut finer
   // than the reach itself would be: its pieces are counted from min_chunk, not from the

@@ -84,6 +84,9 @@ def use_tcgen05(M: int, N: int, K: int) -> bool:
     return ops.gemm_tcgen05_supported(M, N, K) and choice != "library"
 
 
+STREAM_WHOLE_ROW = 1024     # the longest row (elements) that the ring-streaming kernel copies in one piece
+
+
 def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                 out_dtype: torch.dtype, partials_ok: bool = False) -> torch.Tensor:
     """a[M,K] weight[N,K]^T (+ bias float32) as bfloat16 or float32 [M,N]; with
@@ -93,8 +96,11 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     # few rows: the streaming kernel; up to 64 rows it also keeps the narrow matrices,
     # whose few tiles would leave most SMs of the tile kernel idle
     # few rows and a weight of many rows (the vocabulary projection): one block an SM streams
-    # its run of the weight through a shared-memory ring
-    if _STREAM and M <= ops.SMALL_M_ROWS and N >= 16 * sm_count() * 4 and ops.linear_stream_supported(M, N, K):
+    # its run of the weight through a shared-memory ring.  Only where a copy brings a whole row
+    # (K up to STREAM_WHOLE_ROW): the copy engine takes a fixed time per copy, so that pieces of
+    # 1 KB stream at 3.2 TB/s where whole rows of 1.8 KB reach 5.4 and the kernel below 5.7 to 6.7.
+    if _STREAM and M <= ops.SMALL_M_ROWS and K <= STREAM_WHOLE_ROW and N >= 16 * sm_count() * 4 and \
+            ops.linear_stream_supported(M, N, K):
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         ops.linear_stream(a, weight, bias, out)
         return out
