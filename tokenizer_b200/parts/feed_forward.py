@@ -17,6 +17,13 @@ from .linear import Linear
 
 # TOKB200_FFN=separate runs the feed-forward of few rows as norm, gate/up and down kernels
 _FUSED_STEP = os.environ.get("TOKB200_FFN", "fused") != "separate"
+# Where the one-kernel feed-forward leads the separate kernels (norm, gate/up with activation, down),
+# measured: up to 8 rows of a narrow stream (hidden 896: 0.69 against 0.74 ms a decoding step of 24
+# layers).  With 9 to 16 rows it trails (0.91 against 0.86 ms), and so it does on a wider stream,
+# where every block's own norm of all rows costs more than a launch (hidden 1,536, 32 requests with
+# portions of 512 tokens: 0.63 against 0.56 s).
+FUSED_ROWS = 8
+FUSED_HIDDEN = 1024
 
 
 class GatedMLP:
@@ -59,6 +66,8 @@ class GatedMLP:
             return False
         x = stream.x
         rows, hidden = x.shape
+        if rows > FUSED_ROWS or hidden > FUSED_HIDDEN:
+            return False
         splits = ops.ffn_small_m_splits(rows, hidden, self.inner)
         if splits == 0:
             return False
