@@ -524,7 +524,11 @@ TOKB200_API int tokb200_decode_attention(
     const char* v = getenv("TOKB200_DECODE_MERGE");
     return !(v && v[0] == 's');
   }();
-  const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX;
+  // ... and only while all blocks are resident at once: a block of a cluster whose row has fewer
+  // pieces than the grid stays until its siblings are done, which costs nothing in a single wave
+  // and a quarter of the device's block slots in a long run of uneven rows (64 rows of 4,900 to
+  // 8,192 keys, head size 128: 227 us with clusters, 172 us through scratch memory)
+  const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX && pairs * most <= slots;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
                  int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*) =
       cluster ? decode_attention_kernel<true> : decode_attention_kernel<false>;
