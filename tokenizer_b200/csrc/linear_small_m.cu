@@ -19,6 +19,7 @@
 #define LSM_WARPS 8
 #define LSM_THREADS (LSM_WARPS * 32)
 #define LSM_PRE 4            // steps of 32 k of weights in flight per thread (the q/k/v kernel)
+#define LSM_DENSE_ELEMENTS 9000000LL    // the largest weight (elements) that takes the DENSE form (3584 x 3584: 9.0 -> 11.2 us with it)
 #define LSM_WIDE_PRE 2       // steps of 64 k of weights in flight per thread (the plain and the gated product)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
@@ -41,8 +42,11 @@ __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p, bool ok) {
 // GATED: w [N, K] holds, for every 128 outputs, their 128 "gate" rows followed by
 // their 128 "up" rows; a row tile is then 8 gate rows and the 8 up rows of the same
 // outputs, and the result is act(gate) * up, [M, N / 2] (`act`: the activation's tag).
-template <int MT, int TPB, bool GATED>
-__global__ void __launch_bounds__(LSM_THREADS)
+// DENSE (9 to 16 rows, a weight of up to LSM_DENSE_ELEMENTS): the kernel is held to 80 registers so
+// that three blocks fit a multiprocessor.  A small matrix gains from the loads in flight (hidden
+// 896, 16 rows: 0.86 -> 0.80 ms a decoding step); a large one loses (3584 x 18944: 38 -> 55 us).
+template <int MT, int TPB, bool GATED, bool DENSE = false>
+__global__ void __launch_bounds__(LSM_THREADS, DENSE ? 3 : 1)
 linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                       const float* __restrict__ bias, void* __restrict__ out, int out_is_f32,
                       int M, int N, int K, int k_per_split, int act) {
@@ -182,6 +186,17 @@ static int launch_small_m_gated(const void* x, const void* w, void* out, int M, 
   const int k_per_split = (K + 31) / 32 * 32;
   // two row tiles a block from 300 tiles on: with one, a feed-forward of a few thousand
   // outputs needs more blocks than the device holds at once and runs a second, short wave
+  if constexpr (MT == 2) {
+    if ((long long)N * K <= LSM_DENSE_ELEMENTS) {
+      if (tiles >= 300)
+        return launch_dependent(linear_small_m_kernel<MT, 2, true, true>, dim3((tiles + 1) / 2), dim3(LSM_THREADS),
+                                0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                (const float*)nullptr, out, 0, M, N, K, k_per_split, act);
+      return launch_dependent(linear_small_m_kernel<MT, 1, true, true>, dim3(tiles), dim3(LSM_THREADS), 0, stream,
+                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)nullptr, out,
+                              0, M, N, K, k_per_split, act);
+    }
+  }
   if (tiles >= 300) {
     return launch_dependent(linear_small_m_kernel<MT, 2, true>, dim3((tiles + 1) / 2), dim3(LSM_THREADS),
                             0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
@@ -200,6 +215,17 @@ static int launch_small_m(const void* x, const void* w, const float* bias, void*
   int k_per_split = (K + k_splits - 1) / k_splits;
   k_per_split = (k_per_split + 31) / 32 * 32;
   // many row tiles: two per block (teams of 4 warps); few: one per block (8 warps on its k)
+  if constexpr (MT == 2) {
+    if ((long long)N * K <= LSM_DENSE_ELEMENTS) {
+      if (tiles >= 1024)
+        return launch_dependent(linear_small_m_kernel<MT, 2, false, true>, dim3((tiles + 1) / 2, k_splits),
+                                dim3(LSM_THREADS), 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                bias, out, out_is_f32, M, N, K, k_per_split, 0);
+      return launch_dependent(linear_small_m_kernel<MT, 1, false, true>, dim3(tiles, k_splits), dim3(LSM_THREADS),
+                              0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, out_is_f32,
+                              M, N, K, k_per_split, 0);
+    }
+  }
   if (tiles >= 1024) {
     dim3 grid((tiles + 1) / 2, k_splits);
     return launch_dependent(linear_small_m_kernel<MT, 2, false>, grid, dim3(LSM_THREADS), 0, stream,
