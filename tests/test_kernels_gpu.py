@@ -432,7 +432,9 @@ def test_decode_attention_refuses_groups_it_cannot_hold():
 
 @pytest.mark.parametrize("M,N,K", [(1, 16, 32), (3, 130, 72), (8, 1152, 896), (8, 896, 4864), (5, 301, 96),
                                    (16, 64, 64), (17, 200, 176), (33, 1000, 256), (64, 896, 896),
-                                   (8, 20000, 96), (2, 896, 1000)])
+                                   (8, 20000, 96), (2, 896, 1000),
+                                   # 9 to 16 rows: the form held to 80 registers (small weights) and the other
+                                   (12, 1152, 896), (12, 20000, 96), (16, 4000, 3584)])
 def test_linear_small_m(M, N, K):
     """The streaming product for few rows against float64, bfloat16 and float32
     results, with a bias, and cut along k into partial sums."""
