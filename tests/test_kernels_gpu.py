@@ -572,7 +572,8 @@ def test_gemm_tcgen05(M, N, K, block_n, out_dtype):
 
 
 @pytest.mark.parametrize("M,inner,K", [(1, 128, 64), (8, 256, 96), (5, 4864, 896), (33, 384, 200),
-                                       (64, 128, 72), (65, 128, 64), (300, 640, 896), (2048, 1280, 128)])
+                                       (64, 128, 72), (65, 128, 64), (300, 640, 896), (2048, 1280, 128),
+                                       (17, 4864, 896), (47, 640, 200), (64, 8960, 1536)])
 def test_gated_linear(M, inner, K):
     """Gate and up products with silu(gate) * up folded into the epilogue, for few
     rows (streaming kernel) and many (tcgen05), from the interleaved weight."""
