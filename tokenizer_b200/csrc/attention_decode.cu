@@ -100,7 +100,9 @@ __device__ __forceinline__ float dec_peer_load(const float* local, unsigned rank
 // CLUSTER: the grid's x (the pieces of a row) is one thread-block cluster; the pieces meet in
 // the first block through distributed shared memory instead of scratch memory, a fence and a
 // counter.
-template <bool CLUSTER>
+// EARLY: the warps' first tiles are asked for before the wait on the predecessor (short pieces,
+// where a trip to memory is a good part of the kernel's time; in a long piece it only costs registers).
+template <bool CLUSTER, bool EARLY>
 __global__ void __launch_bounds__(DEC_THREADS, HEAD_DIM <= 64 ? 2 : 1)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
@@ -147,52 +149,16 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       }
     }
   }
-  pdl_wait();
-  pdl_launch();
-  if (idle) {
-    // in a cluster whose row is live, a block without keys still keeps the two appointments
-    if (CLUSTER && r >= 0) {
-      dec_cluster_sync();
-      dec_cluster_sync();
-    }
-    return;
-  }
   const int group = nh / nkv;                       // <= DEC_MAX_GROUP, checked by the launcher
   const int first = lo + split * chunk;
   const int last = min(p, first + chunk - 1);
-  const int* table = block_table + (size_t)r * table_stride;
+  const int* table = block_table + (size_t)(r < 0 ? 0 : r) * table_stride;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-
-  // ---- q fragments: heads g and g + 8 of the group, lanes in the permuted order ----
-  unsigned qa[kSteps32 > 0 ? kSteps32 : 1][2][4];
-  unsigned qt[4];
-  {
-    const bool ok_a = g < group, ok_b = g + 8 < group;
-    const __nv_bfloat16* qa_row = q + ((size_t)row * nh + kvh * group + g) * HEAD_DIM;
-    const __nv_bfloat16* qb_row = qa_row + (size_t)8 * HEAD_DIM;
-#pragma unroll
-    for (int st = 0; st < kSteps32; ++st) {
-      const uint4 a = dec_load16(qa_row + dec_k_offset(st, t), ok_a);
-      const uint4 b = dec_load16(qb_row + dec_k_offset(st, t), ok_b);
-      qa[st][0][0] = a.x; qa[st][0][1] = b.x; qa[st][0][2] = a.y; qa[st][0][3] = b.y;
-      qa[st][1][0] = a.z; qa[st][1][1] = b.z; qa[st][1][2] = a.w; qa[st][1][3] = b.w;
-    }
-    if (kTail16) {
-      const uint2 a = dec_load8(qa_row + kSteps32 * 32 + 4 * t, ok_a);
-      const uint2 b = dec_load8(qb_row + kSteps32 * 32 + 4 * t, ok_b);
-      qt[0] = a.x; qt[1] = b.x; qt[2] = a.y; qt[3] = b.y;
-    }
-  }
 
   // two staging buffers of values a warp: the next tile's values are on their way while this
   // tile is computed
   __nv_bfloat16* v_buf = reinterpret_cast<__nv_bfloat16*>(dec_smem) + (size_t)warp * kVBuffers * DEC_TILE * kVStride;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[HEAD_DIM / 8][4];
-#pragma unroll
-  for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const float scale_log2 = scale * 1.4426950408889634f;
 
   // A tile's values go straight to a staging buffer (asynchronous 16-byte copies, zeros for idle
   // keys); its keys come as mma fragments in registers.  Both are asked for one tile AHEAD: the
@@ -237,9 +203,56 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       if (kTail16) kt[nt] = dec_load8(krow + kSteps32 * 32 + 4 * t, ok);
     }
   };
+  // The warp's first tile is asked for BEFORE the wait on the predecessor when none of its keys
+  // is the row's newest (the only one the predecessor writes; all others are from earlier steps):
+  // after the wait only q is still to come.
   int turn = 0, slots_now = -1;
-  if (first + warp * DEC_TILE <= last) {
-    slots_now = tile_slots(first + warp * DEC_TILE);
+  const int k_mine = first + warp * DEC_TILE;
+  const bool have_tile = !idle && k_mine <= last;
+  const bool early = EARLY && have_tile && k_mine + DEC_TILE - 1 < p;
+  if (early) {
+    slots_now = tile_slots(k_mine);
+    if (kVBuffers == 2) stage_values(slots_now, v_buf);
+    load_keys(slots_now);
+  }
+  pdl_wait();
+  pdl_launch();
+  if (idle) {
+    // in a cluster whose row is live, a block without keys still keeps the two appointments
+    if (CLUSTER && r >= 0) {
+      dec_cluster_sync();
+      dec_cluster_sync();
+    }
+    return;
+  }
+  // ---- q fragments: heads g and g + 8 of the group, lanes in the permuted order ----
+  unsigned qa[kSteps32 > 0 ? kSteps32 : 1][2][4];
+  unsigned qt[4];
+  {
+    const bool ok_a = g < group, ok_b = g + 8 < group;
+    const __nv_bfloat16* qa_row = q + ((size_t)row * nh + kvh * group + g) * HEAD_DIM;
+    const __nv_bfloat16* qb_row = qa_row + (size_t)8 * HEAD_DIM;
+#pragma unroll
+    for (int st = 0; st < kSteps32; ++st) {
+      const uint4 a = dec_load16(qa_row + dec_k_offset(st, t), ok_a);
+      const uint4 b = dec_load16(qb_row + dec_k_offset(st, t), ok_b);
+      qa[st][0][0] = a.x; qa[st][0][1] = b.x; qa[st][0][2] = a.y; qa[st][0][3] = b.y;
+      qa[st][1][0] = a.z; qa[st][1][1] = b.z; qa[st][1][2] = a.w; qa[st][1][3] = b.w;
+    }
+    if (kTail16) {
+      const uint2 a = dec_load8(qa_row + kSteps32 * 32 + 4 * t, ok_a);
+      const uint2 b = dec_load8(qb_row + kSteps32 * 32 + 4 * t, ok_b);
+      qt[0] = a.x; qt[1] = b.x; qt[2] = a.y; qt[3] = b.y;
+    }
+  }
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HEAD_DIM / 8][4];
+#pragma unroll
+  for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (have_tile && !early) {
+    slots_now = tile_slots(k_mine);
     if (kVBuffers == 2) stage_values(slots_now, v_buf);
     load_keys(slots_now);
   }
@@ -493,8 +506,8 @@ TOKB200_API int tokb200_decode_attention(
       int device = 0, sms = 148, per_sm = 0;
       if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
       if (smem > 48 * 1024)
-        cudaFuncSetAttribute(decode_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<false>, DEC_THREADS, smem) !=
+        cudaFuncSetAttribute(decode_attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_kernel<false, false>, DEC_THREADS, smem) !=
               cudaSuccess || per_sm < 1)
         per_sm = 1;
       have = per_sm * sms;
@@ -529,17 +542,20 @@ TOKB200_API int tokb200_decode_attention(
   // and a quarter of the device's block slots in a long run of uneven rows (64 rows of 4,900 to
   // 8,192 keys, head size 128: 227 us with clusters, 172 us through scratch memory)
   const bool cluster = clusters_allowed && most <= DEC_CLUSTER_MAX && pairs * most <= slots;
+  // pieces of up to two passes: the first tiles before the wait (see EARLY)
+  const bool early = min_chunk <= 2 * DEC_BLOCK_KEYS;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
                  int, const int*, const int*, int, int, int, int, float, float*, int*, int, const int*) =
-      cluster ? decode_attention_kernel<true> : decode_attention_kernel<false>;
+      early ? (cluster ? decode_attention_kernel<true, true> : decode_attention_kernel<false, true>)
+            : (cluster ? decode_attention_kernel<true, false> : decode_attention_kernel<false, false>);
   if (smem > 48 * 1024) {   // the larger shared memory is granted per device, once
-    static bool configured[64][2] = {};
+    static bool configured[64][4] = {};
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return TOKB200_BAD_SIZE;
-    if (!configured[device][cluster]) {
+    if (!configured[device][2 * early + cluster]) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (err != cudaSuccess) return (int)err;
-      configured[device][cluster] = true;
+      configured[device][2 * early + cluster] = true;
     }
   }
   dim3 grid((unsigned)most, nkv, n_rows);
