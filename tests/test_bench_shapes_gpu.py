@@ -110,11 +110,15 @@ def test_decoding_with_many_live_requests(tmp_path_factory, widths, dtype):
         torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_a_step_of_2048_prompt_tokens(tmp_path_factory, dtype):
+@pytest.mark.parametrize("dtype,products", [("bfloat16", ""), ("bfloat16", "own"), ("float32", "")])
+def test_a_step_of_2048_prompt_tokens(tmp_path_factory, monkeypatch, dtype, products):
     """The benchmark's prompt step: 2,048 tokens of one request, and of three requests
     (700 + 700 + 648), each shape three times over with other contents (run plainly, captured,
-    replayed), against the plain logits at rows around every tile edge."""
+    replayed), against the plain logits at rows around every tile edge.  In bfloat16 once as
+    served (plain products of many rows from the vendor library) and once with every product on
+    the framework's own tensor-core kernels (tiles on pairs of CTAs, products cut along k)."""
+    if products:
+        monkeypatch.setenv("TOKB200_GEMM", products)
     import tokenizer_b200 as tb
     from tokenizer_b200.engine import StepEntry
     path, config, cfg, w = make_model(tmp_path_factory, "0.5B", 4096)

@@ -76,12 +76,27 @@ def use_pair_halves(M: int, N: int, K: int) -> bool:
         -(-M // 256) * -(-N // 256) <= sm_count() // 4
 
 
+LIBRARY_ROWS = 256      # from here on a plain product goes to the vendor library unless TOKB200_GEMM=own
+
+
 def use_tcgen05(M: int, N: int, K: int) -> bool:
-    """Which many-row products go to the framework's tcgen05 kernel.  TOKB200_GEMM
-    = library sends them to the vendor library instead (for comparisons); sizes
-    the kernel does not take (K not a multiple of 8) go there as well."""
+    """Which plain products (no epilogue of the framework's own) go to the framework's tcgen05
+    kernel: those of fewer than LIBRARY_ROWS rows.  With more rows the vendor library's product
+    leads it at the layer sizes measured (a captured chain of products, us, library / own best
+    form): 512 rows, hidden 896: q/k/v 4.4 / 6.7, output 3.9 / 6.1, down 9.0 / 10.3; 2,048 rows:
+    6.3 / 8.3, 5.7 / 8.2, 14.5 / 22.0; hidden 1,536, 512 rows: 6.0 / 8.3, 5.1 / 7.3, 15.6 / 20.4;
+    hidden 3,584, 512 rows: 14.8 / 30.4, 12.1 / 30.3, 59.5 / 172.7; 2,048 rows: 52.7 / 50.9,
+    43.3 / 45.5, 192.6 / 211.7.  The own kernel's tiles of 128 x 128 keep five stages of 32 KB in
+    flight per multiprocessor, which at the latency of a load from L2 feeds the tensor core at
+    about 0.4 of its rate (tensor pipe 45 % on the down projection); only its 256 x 256 tiles on
+    pairs of CTAs (the gate/up product with its activation, which stays the framework's own at
+    every row count) move few enough bytes per instruction.  TOKB200_GEMM=own keeps every
+    product on the own kernels, TOKB200_GEMM=library sends all plain many-row products to the
+    library; sizes the kernel does not take (K not a multiple of 8) go there as well."""
     choice = os.environ.get("TOKB200_GEMM", "")
-    return ops.gemm_tcgen05_supported(M, N, K) and choice != "library"
+    if choice == "library" or not ops.gemm_tcgen05_supported(M, N, K):
+        return False
+    return choice == "own" or M < LIBRARY_ROWS
 
 
 STREAM_WHOLE_ROW = 1024     # the longest row (elements) that the ring-streaming kernel copies in one piece
