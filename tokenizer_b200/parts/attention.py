@@ -109,7 +109,10 @@ class SingleRows(BatchAnnotation):
             rows = first_rows[counts == 1]
             out[:len(rows)] = rows
             made = len(rows)
-        return len(out) if padded else made
+        # a captured step keeps the launch for as many rows as it has requests, but only a step
+        # that has such rows at all: steps of portions alone are captured without it (their key
+        # differs, see Attention.shape_key)
+        return (len(out) if made else 0) if padded else made
 
 
 # the tiles of the two prompt kernels: 64 rows (mma.sync) and 128 rows (tcgen05), for all
@@ -136,7 +139,11 @@ class GQAttention:
         """Which attention kernel a step of these portion lengths gets (part of the key under
         which the engine keeps a captured step)."""
         longest = max(q_lens) if q_lens else 0
-        return "single" if longest == 1 else ("wide" if longest >= _WIDE_FROM else "tiles")
+        if longest == 1:
+            return "single"
+        kind = "wide" if longest >= _WIDE_FROM else "tiles"
+        # portions with single tokens beside them launch the decoding kernel too
+        return kind + "+1" if min(q_lens) == 1 else kind
 
     @staticmethod
     def tensors(spec):
