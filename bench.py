@@ -196,6 +196,10 @@ def main():
     parser.add_argument("--layer-phases", action="store_true",
                         help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
                              "phase, from the kernel's own time stamps, beside the time of the four kernels it replaces")
+    parser.add_argument("--stream-probe", action="store_true",
+                        help="read a 1 GB matrix once in each of the access patterns the decoding kernels choose "
+                             "between (plain loads by whole and by half lines, bulk copies of several sizes) and "
+                             "print the bytes a second each reaches")
     parser.add_argument("--skip-gate", action="store_true",
                         help="do not compare with the plain implementation first (profiling runs)")
     parser.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
@@ -216,6 +220,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.layer_phases:
         return run_layer_phases(args)
+    if args.stream_probe:
+        return run_stream_probe(args)
     if args.config == "7b":
         return run_7b(args)
     if args.config == "1.5b-mixed":
@@ -400,6 +406,51 @@ def main():
     }
     engine.check()                 # a bounded wait that ran out inside a kernel invalidates the numbers
     print(json.dumps(line))
+    return 0
+
+
+def run_stream_probe(args):
+    """What a read-only stream reaches on this device in the access patterns of the decoding
+    kernels: a [151552, 3584] bfloat16 matrix (1.09 GB, larger than L2) read once per launch,
+    five launches after two of warm-up, CUDA events around them.  One JSON line."""
+    import torch
+    from tokenizer_b200.kernels import ops
+
+    torch.cuda.set_device(0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    N, K = 151552, 3584
+    w = torch.ones((N, K), dtype=torch.bfloat16, device="cuda:0")
+    sink = torch.zeros(16, dtype=torch.int32, device="cuda:0")
+    nbytes = N * K * 2
+
+    def rate(fn):
+        fn(); fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return round(nbytes / (start.elapsed_time(stop) / 5 / 1e3) / 1e12, 2)
+
+    out = {}
+    for pattern in ("coalesced", "fragment", "fragment_wide"):
+        for in_flight in (2, 4, 8):
+            for per_sm in (2, 4, 8):
+                if pattern == "coalesced" and in_flight == 2:
+                    continue
+                key = f"{pattern}, {in_flight} steps in flight, {per_sm} blocks an SM"
+                out[key] = rate(lambda: ops.stream_probe_loads(w, pattern, in_flight, per_sm * sms, sink))
+    for piece in (512, 1024, 1792, 3584, 7168):
+        for rows in (16, 32):
+            for kb in (64, 192):
+                stages = min(16, kb * 1024 // (rows * piece))
+                if stages < 2:
+                    continue
+                key = f"bulk copies of {piece} bytes, {rows} a stage, {stages} stages ({stages * rows * piece // 1024} KB)"
+                out[key] = rate(lambda: ops.stream_probe_bulk(w, piece, rows, stages, sms, sink))
+    print(json.dumps({"stream_probe_TB_per_s": out, "bytes": nbytes}))
     return 0
 
 

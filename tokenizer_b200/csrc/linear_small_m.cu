@@ -77,8 +77,9 @@ linear_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 
   // A step is 64 k: thread t of a quad takes k = 16t .. 16t+15 of its two weight rows as two
   // 16-byte loads next to each other, so that a quad asks for a whole 128-byte line of a row
-  // (half a line per request, with the other half asked for by another warp, streams at little
-  // more than half the rate: 3.7 against 6.9 TB/s with the same bytes in flight).  A ring of
+  // (with half a line per request, the other half asked for by another warp, the gate/up product
+  // of a wide model took 64 us instead of 44; the loads alone: 3.8 against 4.6 TB/s at two blocks a
+  // multiprocessor).  A ring of
   // LSM_WIDE_PRE steps of weights is requested before the wait on the predecessor (weights are
   // written by no kernel of the step); x, which the predecessor produced, is read after it.
   constexpr int step = TEAM * 64;

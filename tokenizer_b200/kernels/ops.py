@@ -906,3 +906,26 @@ def layer_small_m_check(d: int) -> None:
     flag = _layer_lib(d).tokb200_layer_small_m_error()
     if flag:
         raise KernelError("layer_small_m: a wait on the device ran out (status %d)" % flag)
+
+
+# ---- read-only streams in the decoding kernels' access patterns (bench.py --stream-probe) ----
+STREAM_PATTERNS = {"coalesced": 0, "fragment": 1, "fragment_wide": 2}
+
+
+def stream_probe_loads(w: torch.Tensor, pattern: str, in_flight: int, blocks: int, sink: torch.Tensor) -> None:
+    """Read the bfloat16 matrix `w` [N, K] once with plain loads in one of STREAM_PATTERNS,
+    `in_flight` (2, 4 or 8) steps of loads a thread, from `blocks` blocks of 256 threads."""
+    N, K = w.shape
+    _check(_lib("stream_probe").tokb200_stream_probe_loads(
+        _ptr(w), _i(N), _i(K), _i(STREAM_PATTERNS[pattern]), _i(in_flight), _i(blocks), _ptr(sink), _stream()),
+        "stream_probe_loads")
+
+
+def stream_probe_bulk(w: torch.Tensor, piece_bytes: int, rows_per_stage: int, stages: int, blocks: int,
+                      sink: torch.Tensor) -> None:
+    """Read `w` once through a ring of shared-memory stages filled by bulk copies of `piece_bytes`
+    of a row each (a stage: `rows_per_stage` pieces), one producer and one consumer warp a block."""
+    N, K = w.shape
+    _check(_lib("stream_probe").tokb200_stream_probe_bulk(
+        _ptr(w), _i(N), _i(K), _i(piece_bytes), _i(rows_per_stage), _i(stages), _i(blocks), _ptr(sink), _stream()),
+        "stream_probe_bulk")

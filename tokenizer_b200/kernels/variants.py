@@ -15,6 +15,7 @@ def all_variants():
         ("gemm_tcgen05.cu", (), ()),
         ("ffn_small_m.cu", (), ()),
         ("linear_stream.cu", (), ()),
+        ("stream_probe.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))
