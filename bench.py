@@ -442,6 +442,12 @@ def run_stream_probe(args):
                     continue
                 key = f"{pattern}, {in_flight} steps in flight, {per_sm} blocks an SM"
                 out[key] = rate(lambda: ops.stream_probe_loads(w, pattern, in_flight, per_sm * sms, sink))
+    for depth in (4, 6, 8):
+        for per_sm in (1, 2, 3):
+            if per_sm * 8 * depth * 16 * 144 > 220 * 1024:
+                continue
+            key = f"async ring of {depth} stages a warp, {per_sm} blocks an SM ({per_sm * 8 * (depth - 1) * 2} KB in flight)"
+            out[key] = rate(lambda: ops.stream_probe_async_ring(w, depth, per_sm * sms, sink))
     for piece in (512, 1024, 1792, 3584, 7168):
         for rows in (16, 32):
             for kb in (64, 192):

@@ -434,7 +434,9 @@ def test_decode_attention_refuses_groups_it_cannot_hold():
                                    (16, 64, 64), (17, 200, 176), (33, 1000, 256), (64, 896, 896),
                                    (8, 20000, 96), (2, 896, 1000),
                                    # 9 to 16 rows: the form held to 80 registers (small weights) and the other
-                                   (12, 1152, 896), (12, 20000, 96), (16, 4000, 3584)])
+                                   (12, 1152, 896), (12, 20000, 96), (16, 4000, 3584),
+                                   # large weights
+                                   (5, 3584, 18944), (13, 9001, 1032), (1, 152064, 1536)])
 def test_linear_small_m(M, N, K):
     """The streaming product for few rows against float64, bfloat16 and float32
     results, with a bias, and cut along k into partial sums."""
@@ -573,7 +575,7 @@ def test_gemm_tcgen05(M, N, K, block_n, out_dtype):
 
 @pytest.mark.parametrize("M,inner,K", [(1, 128, 64), (8, 256, 96), (5, 4864, 896), (33, 384, 200),
                                        (64, 128, 72), (65, 128, 64), (300, 640, 896), (2048, 1280, 128),
-                                       (17, 4864, 896), (47, 640, 200), (64, 8960, 1536)])
+                                       (17, 4864, 896), (47, 640, 200), (64, 8960, 1536), (8, 8960, 1536), (14, 5120, 1032)])
 def test_gated_linear(M, inner, K):
     """Gate and up products with silu(gate) * up folded into the epilogue, for few
     rows (streaming kernel) and many (tcgen05), from the interleaved weight."""

@@ -9,6 +9,8 @@
 //                   warp for the other half)
 //   fragment, wide  the same with 32 bytes a lane at k + 16t as two loads next to each other, steps
 //                   of 64 k (a quad asks for a whole line)
+//   async ring      the fragment pattern's rows through a ring of shared-memory stages a warp, filled by
+//                   16-byte cp.async copies: the bytes in flight cost no registers
 //   bulk            one block per multiprocessor, a producer warp copies row pieces into a ring of
 //                   shared-memory stages with cp.async.bulk, a consumer warp frees them
 #include "common.cuh"
@@ -57,6 +59,47 @@ __global__ void __launch_bounds__(256) probe_fragment_kernel(const char* w, int 
 #pragma unroll
         for (int h = 0; h <= WIDE; ++h) acc ^= probe_fold(a[i][h]) ^ probe_fold(b[i][h]);
     }
+  }
+  if (acc == 0x12345678u) sink[0] = acc;
+}
+
+// The fragment pattern's rows through shared memory instead of registers: every warp owns a ring of
+// DEPTH stages of 16 rows x 128 bytes (steps of 64 k) that it fills with 16-byte asynchronous copies
+// (cp.async), 8 lanes on a row's line, and reads a word of when a stage has landed.
+template <int DEPTH>
+__global__ void __launch_bounds__(256) probe_async_ring_kernel(const char* w, int N, int K, unsigned* sink) {
+  extern __shared__ __align__(128) unsigned char probe_ring[];
+  constexpr int kPitch = 144, kStage = 16 * kPitch;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* mine = probe_ring + (size_t)warp * DEPTH * kStage;
+  unsigned acc = 0;
+  const int steps = K / 64;                       // steps of 64 k in a tile; warps take them in turn
+  const int my_steps = (steps - warp + 7) / 8;
+  for (int tile = blockIdx.x; tile < N / 16; tile += gridDim.x) {
+    const char* rows = w + (size_t)tile * 16 * K * 2;
+    auto fill = [&](int i) {                      // the warp's i-th step of this tile into stage i % DEPTH
+      if (i < my_steps) {
+        const int k = (warp + 8 * i) * 64;
+        unsigned char* st = mine + (i % DEPTH) * kStage;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int piece = c * 32 + lane, row = piece >> 3, at = (piece & 7) * 16;
+          const unsigned dst = (unsigned)__cvta_generic_to_shared(st + row * kPitch + at);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(rows + ((size_t)row * K + k) * 2 + at));
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int i = 0; i < DEPTH - 1; ++i) fill(i);
+    for (int i = 0; i < my_steps; ++i) {
+      fill(i + DEPTH - 1);
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+      __syncwarp();
+      acc ^= *reinterpret_cast<const unsigned*>(mine + (i % DEPTH) * kStage + (lane >> 1) * kPitch + (lane & 1) * 64);
+      __syncwarp();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   if (acc == 0x12345678u) sink[0] = acc;
 }
@@ -144,6 +187,23 @@ TOKB200_API int tokb200_stream_probe_loads(const void* w, int N, int K, int patt
   else if (pattern == 2) { PROBE_PRE(PROBE_WIDE, p, N, K, sink) }
   else return TOKB200_BAD_SIZE;
   cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? TOKB200_OK : (int)err;
+}
+
+// the fragment pattern through a ring of `depth` (4, 6 or 8) stages a warp in shared memory
+TOKB200_API int tokb200_stream_probe_async_ring(const void* w, int N, int K, int depth, int blocks, unsigned* sink,
+                                                cudaStream_t stream) {
+  if (N <= 0 || K <= 0 || N % 16 || K % 64 || blocks <= 0 || ((uintptr_t)w & 15)) return TOKB200_BAD_SIZE;
+  const size_t smem = (size_t)8 * depth * 16 * 144;
+  cudaError_t err = cudaSuccess;
+#define PROBE_RING(n)                                                                                            \
+  err = cudaFuncSetAttribute(probe_async_ring_kernel<n>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+  if (err == cudaSuccess) probe_async_ring_kernel<n><<<blocks, 256, smem, stream>>>((const char*)w, N, K, sink);
+  if (depth == 4) { PROBE_RING(4) }
+  else if (depth == 6) { PROBE_RING(6) }
+  else if (depth == 8) { PROBE_RING(8) }
+  else return TOKB200_BAD_SIZE;
+  if (err == cudaSuccess) err = cudaGetLastError();
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }
 

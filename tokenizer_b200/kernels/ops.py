@@ -929,3 +929,11 @@ def stream_probe_bulk(w: torch.Tensor, piece_bytes: int, rows_per_stage: int, st
     _check(_lib("stream_probe").tokb200_stream_probe_bulk(
         _ptr(w), _i(N), _i(K), _i(piece_bytes), _i(rows_per_stage), _i(stages), _i(blocks), _ptr(sink), _stream()),
         "stream_probe_bulk")
+
+
+def stream_probe_async_ring(w: torch.Tensor, depth: int, blocks: int, sink: torch.Tensor) -> None:
+    """Read `w` once in the fragment pattern through rings of `depth` (4, 6 or 8) shared-memory
+    stages a warp, filled by 16-byte asynchronous copies."""
+    N, K = w.shape
+    _check(_lib("stream_probe").tokb200_stream_probe_async_ring(
+        _ptr(w), _i(N), _i(K), _i(depth), _i(blocks), _ptr(sink), _stream()), "stream_probe_async_ring")
