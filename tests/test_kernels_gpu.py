@@ -463,6 +463,54 @@ def test_linear_small_m(M, N, K):
         o.linear_small_m(rnd(65, K, dtype=torch.bfloat16), w, None, torch.empty(65, N, device=DEV))
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(1, 4000, 3584, (1, 2)), (8, 3584, 18944, (3, 4)), (13, 9001, 1032, (1,)),
+                                          (16, 20011, 1536, (1, 2)), (5, 50, 512, (1,)), (9, 3584, 3584, (3, 5))])
+def test_linear_ring(M, N, K, splits):
+    """The product of few rows for large weights (one block a multiprocessor, the weights through
+    rings in shared memory) against float64: k cut in pieces, a k that ends inside a step of 64,
+    row counts that end inside a tile, fewer tiles than blocks, twice for the same bits."""
+    o = ops()
+    x = rnd(M, K, seed=131, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=132, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=133)
+    want = x.double().cpu() @ w.double().cpu().t()
+    tol = 2e-5 * float(want.abs().max()) + 1e-6 * K
+    for s in splits:
+        assert o.linear_ring_supported(M, N, K, s), (M, N, K, s)
+        if s == 1:
+            out32 = torch.full((M, N), 7.0, device=DEV)
+            o.linear_ring(x, w, None, out32)
+            assert float((out32.double().cpu() - want).abs().max()) <= tol
+            again = torch.full((M, N), 3.0, device=DEV)
+            o.linear_ring(x, w, None, again)
+            assert torch.equal(again, out32)
+            out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            o.linear_ring(x, w, bias, out16)
+            close(out16, (want + bias.double().cpu()).float(), torch.bfloat16)
+        else:
+            parts = torch.full((s, M, N), 7.0, device=DEV)
+            o.linear_ring(x, w, None, parts, k_splits=s)
+            assert float((parts.sum(0).double().cpu() - want).abs().max()) <= tol, s
+    assert not o.linear_ring_supported(17, N, K) and not o.linear_ring_supported(M, N, 100)
+    assert not o.linear_ring_supported(M, N, K, 64)
+
+
+@pytest.mark.parametrize("M,inner,K", [(1, 8960, 1536), (8, 18944, 3584), (14, 5120, 1032), (16, 256, 512)])
+def test_linear_ring_gated(M, inner, K):
+    o = ops()
+    x = rnd(M, K, seed=141, dtype=torch.bfloat16)
+    gate = rnd(inner, K, seed=142, dtype=torch.bfloat16, scale=0.1)
+    up = rnd(inner, K, seed=143, dtype=torch.bfloat16, scale=0.1)
+    w = o.interleave_gate_up(gate, up)
+    assert o.linear_ring_supported(M, 2 * inner, K, 1, True)
+    out = torch.full((M, inner), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.linear_ring_gated(x, w, out)
+    torch.cuda.synchronize()
+    g = x.double().cpu() @ gate.double().cpu().t()
+    u = x.double().cpu() @ up.double().cpu().t()
+    close(out, (g * torch.sigmoid(g) * u).float(), torch.bfloat16)
+
+
 def test_norm_adds_partial_sums():
     x = rnd(5, 200, seed=41)
     parts = rnd(3, 5, 200, seed=42)

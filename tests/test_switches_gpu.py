@@ -21,7 +21,7 @@ SWITCHES = [
     {"TOKB200_DECODE_MERGE": "scratch"}, {"TOKB200_STREAM": "0"}, {"TOKB200_PDL": "0"},
     {"TOKB200_GEMM": "library"}, {"TOKB200_QKV_ROPE": "fused"}, {"TOKB200_L2_PREFETCH": "1"},
     {"TOKB200_GEMM_PAIR": "0"}, {"TOKB200_LAYER": "fused"}, {"TOKB200_LAYER": "fused", "TOKB200_PDL": "0"},
-    {"TOKB200_MIXED": "tiles"}, {"TOKB200_GEMM": "own"},
+    {"TOKB200_MIXED": "tiles"}, {"TOKB200_GEMM": "own"}, {"TOKB200_RING": "0"},
 ]
 
 

@@ -669,7 +669,9 @@ def gated_linear(x, w, out, activation: str = "silu") -> None:
         raise ValueError("gated_linear is the bfloat16 kernel")
     if not gated_linear_supported(K, N) or w.shape[1] != K or tuple(out.shape) != (M, N // 2):
         raise ValueError("gated_linear: K a multiple of 8, N of 256, out [M, N/2]")
-    if M <= SMALL_M_ROWS:
+    if M <= SMALL_M_ROWS and _RING and N * K >= RING_ELEMENTS and linear_ring_supported(M, N, K, 1, True):
+        linear_ring_gated(x, w, out, activation)
+    elif M <= SMALL_M_ROWS:
         _check(_lib("linear_small_m").tokb200_linear_small_m_gated(
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), act, _stream()), "gated_linear")
     elif M <= 64:
@@ -906,6 +908,74 @@ def layer_small_m_check(d: int) -> None:
     flag = _layer_lib(d).tokb200_layer_small_m_error()
     if flag:
         raise KernelError("layer_small_m: a wait on the device ran out (status %d)" % flag)
+
+
+# ---- few rows, a large weight: one block a multiprocessor streams it through rings in shared memory ----
+RING_ELEMENTS = 13_000_000     # from this many weight elements on (26 MB) the ring kernel leads the one with plain loads
+_RING = os.environ.get("TOKB200_RING", "1") != "0"     # TOKB200_RING=0: large weights on linear_small_m too
+_ring_plans = {}
+
+
+def linear_ring_supported(M: int, N: int, K: int, k_splits: int = 1, gated: bool = False) -> bool:
+    """Sizes `linear_ring` / its gated form take on this device (up to 16 rows, K a multiple of 8 with at
+    least 512 per piece of k, x's piece of k and the rings within a block's shared memory)."""
+    if not (0 < M <= 16 and N > 0 and K > 0 and K % 8 == 0):
+        return False
+    key = (torch.cuda.current_device(), M <= 8, N, K, k_splits, gated)
+    if key not in _ring_plans:
+        _ring_plans[key] = bool(_lib("linear_ring").tokb200_linear_ring_supported(
+            _i(M), _i(N), _i(K), _i(k_splits), _i(1 if gated else 0)))
+    return _ring_plans[key]
+
+
+def linear_ring_splits(M: int, N: int, K: int, sms: int) -> int:
+    """Pieces of k for a product whose consumer takes partial sums: the count (1 to 8) whose units of
+    work (row tiles x pieces) divide most evenly over one block a multiprocessor, among those the
+    kernel takes; 0 if it takes none."""
+    tiles = -(-N // 16)
+    best, best_waste = 0, None
+    for s in range(1, 9):
+        if not linear_ring_supported(M, N, K, s):
+            continue
+        units = tiles * s
+        rounds = -(-units // sms)
+        waste = rounds * sms / units
+        if best_waste is None or waste < best_waste - 0.02:
+            best, best_waste = s, waste
+    return best
+
+
+def linear_ring(x, w, bias, out, k_splits: int = 1) -> None:
+    """out = x @ w.T (+ bias) for up to 16 rows and a large weight (bfloat16 in; out [M,N]
+    bfloat16/float32, or float32 partial sums [k_splits, M, N] without bias)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise ValueError("linear_ring: bfloat16 x [M,K] and w [N,K]")
+    if not linear_ring_supported(M, N, K, k_splits):
+        raise ValueError(f"linear_ring does not take {M} rows, {N} x {K}, {k_splits} pieces of k")
+    if k_splits > 1:
+        if tuple(out.shape) != (k_splits, M, N) or out.dtype != torch.float32 or bias is not None:
+            raise ValueError("linear_ring: partial sums are float32 [S,M,N] without bias")
+    elif tuple(out.shape) != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("linear_ring: out is [M,N] bfloat16 or float32")
+    _check(_lib("linear_ring").tokb200_linear_ring(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K),
+        _i(k_splits), _stream()), "linear_ring")
+
+
+def linear_ring_gated(x, w, out, activation: str = "silu") -> None:
+    """out[M, N/2] = act(x Wg^T) * (x Wu^T) for w from `interleave_gate_up`, up to 16 rows, a large weight."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
+            w.shape[1] != K or tuple(out.shape) != (M, N // 2):
+        raise ValueError("linear_ring_gated: bfloat16 x [M,K], w [N,K], out [M,N/2]")
+    if not linear_ring_supported(M, N, K, 1, True):
+        raise ValueError(f"linear_ring_gated does not take {M} rows, {N} x {K}")
+    _check(_lib("linear_ring").tokb200_linear_ring_gated(
+        _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), _i(activation_tag(activation)), _stream()),
+        "linear_ring_gated")
 
 
 # ---- read-only streams in the decoding kernels' access patterns (bench.py --stream-probe) ----

@@ -16,6 +16,7 @@ def all_variants():
         ("ffn_small_m.cu", (), ()),
         ("linear_stream.cu", (), ()),
         ("stream_probe.cu", (), ()),
+        ("linear_ring.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -135,6 +135,16 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         out = torch.empty((tiles_cut, M, N), dtype=torch.float32, device=a.device)
         ops.gemm_tcgen05_partials(a, weight, out)
         return out
+    if ops._RING and M <= ops.SMALL_M_ROWS and N * K >= ops.RING_ELEMENTS:
+        # few rows and a large weight (a wide model's matrices, its vocabulary projection): one block a
+        # multiprocessor streams it through rings in shared memory (`linear_ring.cu`)
+        splits = ops.linear_ring_splits(M, N, K, sm_count()) if (partials_ok and bias is None) else \
+            (1 if ops.linear_ring_supported(M, N, K, 1) else 0)
+        if splits:
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else \
+                torch.empty((M, N), dtype=out_dtype, device=a.device)
+            ops.linear_ring(a, weight, bias, out, splits)
+            return out
     if ops.linear_small_m_supported(M, K) and (M <= ops.SMALL_M_ROWS or N < 4096):
         splits = choose_k_splits(M, N, K) if (partials_ok and bias is None) else 1
         if splits > 1:
