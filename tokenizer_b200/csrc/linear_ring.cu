@@ -130,15 +130,19 @@ linear_ring_kernel(const LrParams p) {
   pdl_wait();          // x comes from the predecessor
   pdl_launch();
 
-  // ---- the block's piece of x into shared memory, rows past M as zeros ----
+  // ---- the block's piece of x into shared memory (asynchronous copies, all in flight at once),
+  // rows past M and pieces past the end of k as zeros ----
   {
-    const int pieces = p.k_per_split / 8;                        // 16-byte pieces a row: the whole piece of k, zeros past its end
+    const int pieces = p.k_per_split / 8;                        // 16-byte pieces a row: the whole piece of k
     for (int i = threadIdx.x; i < 8 * MT * pieces; i += LR_THREADS) {
       const int m = i / pieces, at = (i % pieces) * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (m < p.M && k_begin + at + 8 <= k_end) v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + k_begin + at);
-      *reinterpret_cast<uint4*>(x_s + (size_t)m * p.x_pitch + at * 2) = v;
+      const bool ok = m < p.M && k_begin + at + 8 <= k_end;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(x_s + (size_t)m * p.x_pitch + at * 2);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                   ::"r"(dst), "l"(ok ? p.x + (size_t)m * p.K + k_begin + at : p.x), "r"(ok ? 16 : 0));
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");         // x (and the ring's first stages, asked for long before)
   }
   __syncthreads();
 
