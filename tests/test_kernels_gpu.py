@@ -464,7 +464,8 @@ def test_linear_small_m(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(1, 4000, 3584, (1, 2)), (8, 3584, 18944, (3, 4)), (13, 9001, 1032, (1,)),
-                                          (16, 20011, 1536, (1, 2)), (5, 50, 512, (1,)), (9, 3584, 3584, (3, 5))])
+                                          (16, 20011, 1536, (1, 2)), (5, 50, 512, (1,)), (9, 3584, 3584, (3, 5)),
+                                          (17, 896, 4864, (3, 5)), (32, 1536, 8960, (6,)), (29, 1000, 1032, (1,))])
 def test_linear_ring(M, N, K, splits):
     """The product of few rows for large weights (one block a multiprocessor, the weights through
     rings in shared memory) against float64: k cut in pieces, a k that ends inside a step of 64,
@@ -491,11 +492,12 @@ def test_linear_ring(M, N, K, splits):
             parts = torch.full((s, M, N), 7.0, device=DEV)
             o.linear_ring(x, w, None, parts, k_splits=s)
             assert float((parts.sum(0).double().cpu() - want).abs().max()) <= tol, s
-    assert not o.linear_ring_supported(17, N, K) and not o.linear_ring_supported(M, N, 100)
+    assert not o.linear_ring_supported(33, N, K) and not o.linear_ring_supported(M, N, 100)
     assert not o.linear_ring_supported(M, N, K, 64)
 
 
-@pytest.mark.parametrize("M,inner,K", [(1, 8960, 1536), (8, 18944, 3584), (14, 5120, 1032), (16, 256, 512)])
+@pytest.mark.parametrize("M,inner,K", [(1, 8960, 1536), (8, 18944, 3584), (14, 5120, 1032), (16, 256, 512),
+                                       (17, 4864, 896), (32, 8960, 1536), (25, 640, 520)])
 def test_linear_ring_gated(M, inner, K):
     o = ops()
     x = rnd(M, K, seed=141, dtype=torch.bfloat16)

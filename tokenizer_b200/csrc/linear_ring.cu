@@ -1,4 +1,4 @@
-// y[M,N] = x[M,K] W[N,K]^T for few rows (M <= 16) and a LARGE weight (the matrices of a wide
+// y[M,N] = x[M,K] W[N,K]^T for few rows (M <= 32) and a LARGE weight (the matrices of a wide
 // model's decoding step: tens to hundreds of MB each), bfloat16 operands, 32-bit accumulation.
 // The product is bound by reading W once, and this kernel is built to keep that stream at the
 // device's rate from the first cycle to the last:
@@ -240,13 +240,13 @@ struct LrPlan {
 
 static LrPlan lr_plan(int M, int N, int K, int k_splits, bool gated) {
   LrPlan plan = {};
-  if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 8 || k_splits < 1 || k_splits > 16) return plan;
+  if (M <= 0 || M > 32 || N <= 0 || K <= 0 || K % 8 || k_splits < 1 || k_splits > 16) return plan;
   if (gated && (N % 256 || k_splits != 1)) return plan;
   int device = 0, sms = 0, smem_max = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return plan;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return plan;
   if (cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return plan;
-  const int MT = M <= 8 ? 1 : 2;
+  const int MT = M <= 8 ? 1 : M <= 16 ? 2 : 4;
   int kps = ((K + k_splits - 1) / k_splits + 63) / 64 * 64;
   if ((long long)(k_splits - 1) * kps >= K) return plan;               // an empty piece
   if (kps < 64 * LR_WARPS) return plan;                                 // every warp has a step to take
@@ -302,7 +302,8 @@ TOKB200_API int tokb200_linear_ring(const void* x, const void* w, const float* b
   p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = out; p.out_is_f32 = out_is_f32;
   p.M = M; p.N = N; p.K = K; p.k_splits = k_splits; p.k_per_split = plan.k_per_split; p.depth = plan.depth;
   p.x_pitch = plan.x_pitch; p.act = 0;
-  return M <= 8 ? lr_launch<1, false>(p, plan, stream) : lr_launch<2, false>(p, plan, stream);
+  return M <= 8 ? lr_launch<1, false>(p, plan, stream)
+                : M <= 16 ? lr_launch<2, false>(p, plan, stream) : lr_launch<4, false>(p, plan, stream);
 }
 
 // out[M, N/2] (bfloat16) = act(x Wg^T) * (x Wu^T), w in the 128-gate / 128-up row blocks (N a multiple of 256)
@@ -315,5 +316,6 @@ TOKB200_API int tokb200_linear_ring_gated(const void* x, const void* w, void* ou
   p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = nullptr; p.out = out; p.out_is_f32 = 0;
   p.M = M; p.N = N; p.K = K; p.k_splits = 1; p.k_per_split = plan.k_per_split; p.depth = plan.depth;
   p.x_pitch = plan.x_pitch; p.act = act;
-  return M <= 8 ? lr_launch<1, true>(p, plan, stream) : lr_launch<2, true>(p, plan, stream);
+  return M <= 8 ? lr_launch<1, true>(p, plan, stream)
+                : M <= 16 ? lr_launch<2, true>(p, plan, stream) : lr_launch<4, true>(p, plan, stream);
 }

@@ -674,6 +674,11 @@ def gated_linear(x, w, out, activation: str = "silu") -> None:
     elif M <= SMALL_M_ROWS:
         _check(_lib("linear_small_m").tokb200_linear_small_m_gated(
             _ptr(x), _ptr(w), _ptr(out), _i(M), _i(N), _i(K), act, _stream()), "gated_linear")
+    elif M <= RING_MAX_ROWS and _RING and (M <= 24 or N * K <= 9_000_000) and linear_ring_supported(M, N, K, 1, True):
+        # 17 to 32 rows: the ring kernel where it leads a tensor-core tile that is mostly padding
+        # followed by the activation's own kernel (us in a captured chain, hidden 896: 11.3 -> 9.0
+        # at 17 rows, 13.3 -> 10.6 at 32; hidden 1,536: 24.3 -> 17.5 at 17 rows, but 18.8 -> 20.6 at 32)
+        linear_ring_gated(x, w, out, activation)
     elif M <= 64:
         # too few rows to fill the 256-wide gated tiles over the SMs: the plain tensor-core
         # product over the same (interleaved) weight, then the activation on its output
@@ -912,16 +917,17 @@ def layer_small_m_check(d: int) -> None:
 
 # ---- few rows, a large weight: one block a multiprocessor streams it through rings in shared memory ----
 RING_ELEMENTS = 13_000_000     # from this many weight elements on (26 MB) the ring kernel leads the one with plain loads
+RING_MAX_ROWS = 32
 _RING = os.environ.get("TOKB200_RING", "1") != "0"     # TOKB200_RING=0: large weights on linear_small_m too
 _ring_plans = {}
 
 
 def linear_ring_supported(M: int, N: int, K: int, k_splits: int = 1, gated: bool = False) -> bool:
-    """Sizes `linear_ring` / its gated form take on this device (up to 16 rows, K a multiple of 8 with at
+    """Sizes `linear_ring` / its gated form take on this device (up to 32 rows, K a multiple of 8 with at
     least 512 per piece of k, x's piece of k and the rings within a block's shared memory)."""
-    if not (0 < M <= 16 and N > 0 and K > 0 and K % 8 == 0):
+    if not (0 < M <= RING_MAX_ROWS and N > 0 and K > 0 and K % 8 == 0):
         return False
-    key = (torch.cuda.current_device(), M <= 8, N, K, k_splits, gated)
+    key = (torch.cuda.current_device(), (M > 8) + (M > 16), N, K, k_splits, gated)
     if key not in _ring_plans:
         _ring_plans[key] = bool(_lib("linear_ring").tokb200_linear_ring_supported(
             _i(M), _i(N), _i(K), _i(k_splits), _i(1 if gated else 0)))

@@ -128,6 +128,17 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         ops.gemm_tcgen05_pair(a, weight, None, out, ops.PAIR_PARTIALS)
         return out
     tiles_cut = 1
+    if ops._RING and partials_ok and bias is None and ops.SMALL_M_ROWS < M <= ops.RING_MAX_ROWS and N <= 2048:
+        # 17 to 32 rows and a narrow output whose consumer takes partial sums (the output and down
+        # projections of a model up to hidden 2,048): the ring kernel leads the tensor-core tiles cut
+        # along k (hidden 896: down 7.1 -> 5.2 to 5.8 us, output 4.9 -> 3.8 to 4.5; hidden 1,536: 11.5 ->
+        # 10.2 to 11.3, 5.5 -> 4.3; at hidden 3,584 it does not)
+        splits = ops.linear_ring_splits(M, N, K, sm_count())
+        if splits:
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else \
+                torch.empty((M, N), dtype=out_dtype, device=a.device)
+            ops.linear_ring(a, weight, None, out, splits)
+            return out
     if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):
         tiles_cut = choose_tile_k_splits(M, N, K)
     if tiles_cut > 1:
