@@ -399,9 +399,18 @@ __global__ void rope_store_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, 
     const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
     a[2 * e] = fa.x; a[2 * e + 1] = fa.y; b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
   }
+  // eight consecutive floats as two 16-byte loads (j, half and d are multiples of 8; the tables and the bias
+  // are 16-byte aligned, checked by the launcher)
+  auto load8 = [](const float* p, float (&v)[8]) {
+    const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+  };
   if (bias) {
+    float ba[8], bb[8];
+    load8(bias + head * d + j, ba);
+    load8(bias + head * d + j + half, bb);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { a[e] += bias[head * d + j + e]; b[e] += bias[head * d + j + half + e]; }
+    for (int e = 0; e < 8; ++e) { a[e] += ba[e]; b[e] += bb[e]; }
   }
   __nv_bfloat16* dst;
   if (head < nh) {
@@ -414,8 +423,9 @@ __global__ void rope_store_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, 
     dst = pool + ((size_t)s * nkv + (head - nh - (is_key ? 0 : nkv))) * d;
   }
   if (head < nh + nkv) {
-    const float* c = cos_t + (size_t)pos[t] * half + j;
-    const float* sn = sin_t + (size_t)pos[t] * half + j;
+    float c[8], sn[8];
+    load8(cos_t + (size_t)pos[t] * half + j, c);
+    load8(sin_t + (size_t)pos[t] * half + j, sn);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const float ra = a[e] * c[e] - b[e] * sn[e], rb = b[e] * c[e] + a[e] * sn[e];
@@ -525,7 +535,8 @@ TOKB200_API int tokb200_rope_store(const void* qkv, const float* bias, const int
   if (d <= 0 || (d & 1) || rotary < 0 || rotary > d || (rotary & 1) || ((d - rotary) & 1))
     return TOKB200_BAD_SIZE;
   if (dtype == TOKB200_BF16 && rotary == d && d % 16 == 0 && n_tokens >= 64 &&
-      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)bias |
+        (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0) {
     const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (d / 16);
     return launch_dependent(rope_store_bf16x8_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
                             stream, (const __nv_bfloat16*)qkv, bias, pos, slot, cos_t, sin_t,
