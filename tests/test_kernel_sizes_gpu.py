@@ -56,6 +56,43 @@ def test_few_row_products_at_random_sizes():
     o.gemm_tcgen05_check()
 
 
+def test_ring_products_at_random_sizes():
+    """The product that streams a large weight through rings in shared memory (up to 32 rows), its
+    pieces of k and its gated form, wherever it takes the sizes drawn."""
+    o = ops()
+    rng = random.Random(13)
+    taken = 0
+    for case in range(16):
+        M = rng.randint(1, 32)
+        K = 8 * rng.randint(64, 1200)
+        N = rng.choice([16, 50, 896, 1000, 3001, 9000])
+        x = rnd(M, K, seed=9000 + case, dtype=torch.bfloat16)
+        w = rnd(N, K, seed=9500 + case, scale=0.1, dtype=torch.bfloat16)
+        want = x.double().cpu() @ w.double().cpu().t()
+        tol = 2e-5 * float(want.abs().max()) + 1e-6 * K
+        for splits in (1, 2, 3, 5):
+            if not o.linear_ring_supported(M, N, K, splits):
+                continue
+            taken += 1
+            out = torch.full((splits, M, N), 3.0, device=DEV) if splits > 1 else torch.full((M, N), 3.0, device=DEV)
+            o.linear_ring(x, w, None, out, splits)
+            got = out.sum(0) if splits > 1 else out
+            assert float((got.double().cpu() - want).abs().max()) <= tol, (M, N, K, splits)
+        inner = 128 * rng.randint(1, 8)
+        if o.linear_ring_supported(M, 2 * inner, K, 1, True):
+            taken += 1
+            gate = rnd(inner, K, seed=9700 + case, scale=0.1, dtype=torch.bfloat16)
+            up = rnd(inner, K, seed=9800 + case, scale=0.1, dtype=torch.bfloat16)
+            got = torch.empty(M, inner, dtype=torch.bfloat16, device=DEV)
+            o.linear_ring_gated(x, o.interleave_gate_up(gate, up), got)
+            g = x.double().cpu() @ gate.double().cpu().t()
+            u = x.double().cpu() @ up.double().cpu().t()
+            want_act = (g * torch.sigmoid(g) * u).float()
+            assert torch.allclose(got.float().cpu(), want_act, atol=4e-3 * max(1.0, float(want_act.abs().max())),
+                                  rtol=2 ** -6), (M, inner, K)
+    assert taken >= 20
+
+
 def test_decode_attention_at_random_sizes():
     o = ops()
     rng = random.Random(12)
