@@ -395,7 +395,7 @@ def main():
                    "new_tokens": NEW_TOKENS, "context_at_timing": int(mean_context),
                    "page_size": PAGE, "parallelism": "single GPU",
                    "l2": "each step reads > 126 MB of weights (inputs larger than L2)",
-                   "peaks": pk["source"], "plain_products_of_256_rows_and_more": products_note()},
+                   "peaks": pk["source"], "plain_products_of_65_rows_and_more": products_note()},
         "clocks": main_run["clocks"],
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps,
@@ -642,7 +642,7 @@ def run_7b(args):
                    "global_batch": args.batch, "seq_len": context, "context_at_timing": main_run["context"],
                    "page_size": PAGE, "parallelism": "single GPU",
                    "l2": "each step reads > 126 MB of weights (inputs larger than L2)", "peaks": pk["source"],
-                   "logits_gate": gate, "plain_products_of_256_rows_and_more": products_note()},
+                   "logits_gate": gate, "plain_products_of_65_rows_and_more": products_note()},
         "clocks": clocks_main, "gpu_launches": main_run["launches"],
         "prefill": {"value": PREFILL_TOKENS / (prefill_best / 1e3), "tokens": PREFILL_TOKENS, "ms": prefill_best,
                     "frac": prefill_flops(cfg, layers, PREFILL_TOKENS) / (prefill_best / 1e3)
@@ -751,7 +751,7 @@ def run_mixed(args):
                    "intermediate": inner, "vocab": cfg["vocab_size"], "requests": n_requests,
                    "prompt_tokens": prompt_tokens, "new_tokens": new_tokens, "token_budget": budget,
                    "page_size": PAGE, "parallelism": "single GPU", "peaks": pk["source"], "logits_gate": gate,
-                   "plain_products_of_256_rows_and_more": products_note()},
+                   "plain_products_of_65_rows_and_more": products_note()},
         "clocks": clock_record,
         "mixed": {"seconds": seconds, "total_tok_s": (prompt_tokens + n_requests * new_tokens) / seconds,
                   "tokens_run": stats.tokens_run, "shared_prefix_tokens": stats.shared_prefix_tokens,

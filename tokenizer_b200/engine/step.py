@@ -159,10 +159,10 @@ class Engine:
     def _captured_shape(self, entries: List[StepEntry]):
         """(key, padded tokens, padded requests) when steps of this shape are replayed
         from a captured graph, else None.  Steps of single tokens always are.  Steps
-        with prompt portions are when they bring a whole number of 128-token tiles, at
-        least two: under a token budget most steps of a busy engine bring exactly the
-        budget, and a replay spares the host the launches (a quarter of such a step's
-        time otherwise).  What the model's parts say decides their kernels beyond the
+        with prompt portions are when they bring (nearly) a whole number of 128-token tiles
+        or fewer than 256 tokens: under a token budget most steps of a busy engine bring exactly
+        the budget, and a replay spares the host the launches (a quarter of such a step's
+        time otherwise, two thirds of a short step's).  What the model's parts say decides their kernels beyond the
         sizes (`shape_key`) is part of the key."""
         pages = [max(len(e.cache.tables[g]) for e in entries) for g in range(len(self.cache.groups))]
         longest = max(len(e.tokens) for e in entries)
@@ -174,9 +174,16 @@ class Engine:
         widths = tuple(self._bucket(n, 8) for n in pages)
         total = sum(len(e.tokens) for e in entries)
         requests = self._bucket(len(entries))
-        # up to the next whole tile with idle rows, where that wastes little (a sixteenth)
-        padded = -(-total // 128) * 128
-        if total < 256 or padded - total > total // 16 or sum(len(e.want) for e in entries) > requests:
+        # up to the next whole tile with idle rows, where that wastes little (a sixteenth); a short
+        # step (a short prompt, the last portion of a long one) is padded to whole half tiles whatever
+        # that wastes: launched from the host its 200 launches take 3 ms, replayed a third of that
+        if total >= 256:
+            padded = -(-total // 128) * 128
+            if padded - total > total // 16:
+                return None
+        else:
+            padded = -(-total // 64) * 64
+        if total < 16 or sum(len(e.want) for e in entries) > requests:
             return None
         kinds = self.model.shape_key([len(e.tokens) for e in entries])
         return ("portions", padded, requests, widths, kinds), padded, requests

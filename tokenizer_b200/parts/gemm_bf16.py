@@ -76,12 +76,12 @@ def use_pair_halves(M: int, N: int, K: int) -> bool:
         -(-M // 256) * -(-N // 256) <= sm_count() // 4
 
 
-LIBRARY_ROWS = 256      # from here on a plain product goes to the vendor library unless TOKB200_GEMM=own
+LIBRARY_ROWS = 256      # from here on every plain product goes to the vendor library unless TOKB200_GEMM=own
 
 
-def use_tcgen05(M: int, N: int, K: int) -> bool:
+def use_tcgen05(M: int, N: int, K: int, cut_along_k: bool = False) -> bool:
     """Which plain products (no epilogue of the framework's own) go to the framework's tcgen05
-    kernel: those of fewer than LIBRARY_ROWS rows.  With more rows the vendor library's product
+    kernel: those of up to 64 rows, and from 65 to LIBRARY_ROWS - 1 rows the long-k products cut along k.  With more rows the vendor library's product
     leads it at the layer sizes measured (a captured chain of products, us, library / own best
     form): 512 rows, hidden 896: q/k/v 4.4 / 6.7, output 3.9 / 6.1, down 9.0 / 10.3; 2,048 rows:
     6.3 / 8.3, 5.7 / 8.2, 14.5 / 22.0; hidden 1,536, 512 rows: 6.0 / 8.3, 5.1 / 7.3, 15.6 / 20.4;
@@ -96,7 +96,14 @@ def use_tcgen05(M: int, N: int, K: int) -> bool:
     choice = os.environ.get("TOKB200_GEMM", "")
     if choice == "library" or not ops.gemm_tcgen05_supported(M, N, K):
         return False
-    return choice == "own" or M < LIBRARY_ROWS
+    if choice == "own" or M <= 64:
+        return True
+    if M < LIBRARY_ROWS:
+        # 65 to 255 rows: the own kernel's floor is 5 to 8 us where the library's product takes 3.5
+        # (q/k/v 1152 x 896 at 128 rows: 8.5 against 3.6, output 5.4 against 3.6); only the long-k
+        # product cut along k into partial sums leads it (down 896 x 4864: 7.6 against 8.5)
+        return cut_along_k and K >= 4 * N
+    return False
 
 
 STREAM_WHOLE_ROW = 1024     # the longest row (elements) that the ring-streaming kernel copies in one piece
@@ -139,7 +146,7 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
                 torch.empty((M, N), dtype=out_dtype, device=a.device)
             ops.linear_ring(a, weight, None, out, splits)
             return out
-    if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K):
+    if partials_ok and bias is None and M > ops.SMALL_M_ROWS and use_tcgen05(M, N, K, cut_along_k=True):
         tiles_cut = choose_tile_k_splits(M, N, K)
     if tiles_cut > 1:
         # few output tiles (a narrow matrix, a few dozen rows): pieces of k over all SMs
