@@ -175,15 +175,17 @@ class Engine:
         total = sum(len(e.tokens) for e in entries)
         requests = self._bucket(len(entries))
         # up to the next whole tile with idle rows, where that wastes little (a sixteenth); a short
-        # step (a short prompt, the last portion of a long one) is padded to whole half tiles whatever
-        # that wastes: launched from the host its 200 launches take 3 ms, replayed a third of that
+        # step (a short prompt, the last portion of a long one) is padded to whole half tiles (to 16
+        # rows under 64) whatever that wastes: launched from the host its 200 launches take 3 ms, replayed a third of that
         if total >= 256:
             padded = -(-total // 128) * 128
             if padded - total > total // 16:
                 return None
-        else:
+        elif total >= 64:
             padded = -(-total // 64) * 64
-        if total < 16 or sum(len(e.want) for e in entries) > requests:
+        else:
+            padded = -(-total // 16) * 16
+        if sum(len(e.want) for e in entries) > requests:
             return None
         kinds = self.model.shape_key([len(e.tokens) for e in entries])
         return ("portions", padded, requests, widths, kinds), padded, requests
