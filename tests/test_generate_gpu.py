@@ -415,6 +415,56 @@ def test_steps_of_a_captured_shape_are_replayed_with_other_contents(tmp_path_fac
     assert any(k[0] == "portions" and "graph" in v for k, v in engine._graphs.items())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_steps_are_captured_and_replayed(tmp_path_factory, dtype):
+    """Steps of a few tokens to a few dozen (a short prompt, a long one's last portion, alone or
+    beside a decoding token) are captured per padded shape (whole 16 rows under 64, whole 64 under
+    256) and replayed: three uses of each shape with other contents and other cuts, each against
+    the plain logits."""
+    import tokenizer_b200 as tb
+    from tokenizer_b200 import Qwen2Config, write_random_model
+    from tokenizer_b200.engine import StepEntry
+    config = Qwen2Config.from_dict(dict(
+        architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=2, hidden_size=128,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=256, vocab_size=333,
+        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+        use_sliding_window=False, sliding_window=None, max_window_layers=2))
+    path = str(tmp_path_factory.mktemp("tiny_short_steps"))
+    write_random_model(path, config, 8, scale=SHARPEN)
+    cfg, w = plain.load_folder(path)
+    model = tb.load_model(path, dtype=dtype)
+    engine = tb.engine_for(model, 4096, 16, max_requests=4)
+    old = engine.cache.open("old")
+    old_ids = random_ids(80, config.vocab_size, 1)
+    old_want = plain.all_logits(cfg, w, old_ids)
+    engine.cache.reserve(old, 30)
+    engine.step([StepEntry(old, old_ids[:30], [])])
+    old_at = 30
+    use = 0
+    for total, with_decode in ((37, False), (90, False), (7, False), (150, True), (21, True), (200, False)):
+        for rep in range(3):
+            use += 1
+            n_a = total - (3 + rep if total > 40 else 0)            # another cut every time, the same padded shape
+            a_ids = random_ids(n_a, config.vocab_size, 100 + use)
+            a = engine.cache.open(("a", use))
+            engine.cache.reserve(a, n_a)
+            entries = [StepEntry(a, a_ids, [n_a - 1])]
+            wants = [plain.all_logits(cfg, w, a_ids)[[n_a - 1]]]
+            if with_decode:
+                engine.cache.reserve(old, 1)
+                entries.append(StepEntry(old, old_ids[old_at:old_at + 1], [0]))
+                wants.append(old_want[[old_at]])
+                old_at += 1
+            got = engine.step(entries).float().cpu()
+            want = torch.cat(wants)
+            bound = 1e-4 if dtype == "float32" else 2e-2 * float(want.abs().max())
+            assert float((got - want).abs().max()) <= bound, f"{total} tokens, use {rep}"
+            engine.cache.close(a)
+    engine.check()
+    padded = sorted({k[1] for k, v in engine._graphs.items() if k[0] == "portions" and "graph" in v})
+    assert padded == [16, 32, 48, 128, 192, 256], padded
+
+
 def test_logits_of_a_replayed_step_live_until_the_next_step(tmp_path_factory):
     """`Engine.step` says that its logits are valid until the engine's next step: a step replayed
     from a captured graph returns a view of the graph's output buffer.  Held across the next replay
